@@ -1,0 +1,147 @@
+/* libresinfer_b200 -- C ABI of the B200 (sm_100a) kernels behind the MEXT / KEXT / ResAttn paths.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (cudaStream_t passed as
+ * void*), launches asynchronously on that stream, performs no host synchronisation and returns
+ *     0   success,
+ *   < 0   arguments rejected (RI_ERR_*); nothing was launched,
+ *   > 0   a cudaError_t from the launch.
+ * ri_last_error() gives the message of the last failure on the calling thread.  Unless a function
+ * says otherwise it allocates nothing: every output and scratch buffer is owned by the caller,
+ * like the torch ops these functions replace (ShawRong/ResInfer csrc/bindings/pybind.cpp:28-54:
+ * outputs are Tensor(a!) arguments, the ops return ()).
+ *
+ * File:line citations name the interface of the reference project (ShawRong/ResInfer) that the
+ * function stands in for.
+ */
+#ifndef RESINFER_B200_H_
+#define RESINFER_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RI_ABI_VERSION 1
+
+/* error codes (negative returns) */
+#define RI_ERR_ARG (-1)
+#define RI_ERR_UNSUPPORTED (-2)
+#define RI_ERR_DEVICE (-3)
+#define RI_ERR_TIMEOUT (-4)
+
+/* input dtypes */
+#define RI_DTYPE_BF16 0
+#define RI_DTYPE_FP16 1
+
+/* FP4 formats */
+#define RI_FMT_NVFP4 0 /* 16-element blocks, E4M3 block scale, FP32 global scale */
+#define RI_FMT_MXFP4 1 /* 32-element blocks, E8M0 block scale */
+
+/* MEXT output layouts = MExtR1LayoutMode, csrc/nvfp4/cuda/nvfp4_quant_kernels.cu:344-353 */
+#define RI_MEXT_CONCAT 0
+#define RI_MEXT_ROW_PAIR 1
+#define RI_MEXT_TILE8 2
+#define RI_MEXT_CONCAT_K 3
+#define RI_MEXT_ATTN_TILE8 4
+
+/* activation layouts the GEMM accepts */
+#define RI_GEMM_PLAIN 0    /* act [M, K/2]: y = act . W^T (KEXT: K = K_base + S)            */
+#define RI_GEMM_ROW_PAIR 1 /* act [2M, K/2] rows 2i / 2i+1 = base / residue: y_i = sum of both */
+#define RI_GEMM_CONCAT_K 2 /* act [M, K] bytes = base | residue along K, W reused for both     */
+
+int ri_abi_version(void);
+const char* ri_last_error(void);
+
+/* Number of SMs / compute capability of the current device (cached per device).
+ * Returns 0 or an error code. */
+int ri_device_info(int* sm_count, int* cc_major, int* cc_minor);
+
+/* NVFP4 MEXT quantiser: x[M,K] (bf16/fp16, row stride in elements) -> base and residue codes plus
+ * 128x4-swizzled E4M3 scales in one of the five layouts.
+ * gs_inv: device float[n_gs], reciprocal global scale (n_gs == 2: separate residue scale).
+ * codes: 2*M'*K/2 bytes (M' = M rounded up to 8 for the tile8 layouts); sf: see the layout rules of
+ * csrc/nvfp4/mext.py:151-174 (attn_tile8 expects a zero-filled scale buffer).
+ * Replaces torch op nvfp4::scaled_fp4_quant_mext_r1 (csrc/bindings/pybind.cpp:33-37; entry
+ * csrc/nvfp4/cuda/nvfp4_quant_kernels.cu:532-612). */
+int ri_nvfp4_quant_mext(const void* x, int dtype, int m, int k, int64_t row_stride,
+                        const float* gs_inv, int n_gs, uint8_t* codes, int64_t codes_bytes,
+                        uint8_t* sf, int64_t sf_bytes, int layout, int enable_pdl, void* stream);
+
+/* NVFP4 KEXT quantiser: base codes of all K channels followed by the residues of the channels
+ * selected by mask[K/8] (exactly per8 in {1,2,4} bits set per byte); n_ext = K + K/8*per8.
+ * codes [M, n_ext/2]; sf swizzled over n_ext columns, rows up to the next multiple of 128 are
+ * written (scale 0).
+ * Replaces torch op nvfp4::scaled_fp4_quant (csrc/bindings/pybind.cpp:29-32; entry
+ * csrc/nvfp4/cuda/nvfp4_quant_entry.cu:145-186). */
+int ri_nvfp4_quant_kext(const void* x, int dtype, int m, int k, int64_t row_stride,
+                        const float* gs_inv, const uint8_t* mask, int per8, int n_ext,
+                        uint8_t* codes, int64_t codes_bytes, uint8_t* sf, int64_t sf_bytes,
+                        int use_swapped_residue, void* stream);
+
+/* ResAttn query quantiser: q[B,Hkv,G,D] bf16 contiguous -> q_pack[B,Hkv,P,D/2] (P = 8 if G == 4
+ * else 16; base rows g, residue rows P/2+g; the caller zero-fills q_pack once) and q_sf
+ * [B*Hkv*128*D/16] (one private swizzled 128-row tile per (b,hkv)); global scale 1.
+ * Replaces torch op nvfp4::scaled_fp4_quant_mext_r1_grouped_q (csrc/bindings/pybind.cpp:38-40;
+ * entry csrc/nvfp4/cuda/nvfp4_quant_kernels.cu:655-689). */
+int ri_nvfp4_quant_grouped_q(const void* q_bf16, int batch, int num_kv_heads, int group,
+                             int head_dim, uint8_t* q_pack, int64_t q_pack_bytes, uint8_t* q_sf,
+                             int64_t q_sf_bytes, void* stream);
+
+/* MXFP4 quantiser.  masks == NULL: MEXT, codes [out_rows, K/2] with out_rows = 2M (row_pair) or a
+ * multiple of 16 >= 2M (tile8).  masks != NULL: selective, codes [M, out_row_bytes] with
+ * out_row_bytes*2 >= K + K/8*per8 (zero padded).  sf: 128x4-swizzled (swizzle != 0) or linear
+ * [out_rows, Ktot/32]; its size must match exactly.  x may be strided (strides in elements).
+ * Replaces torch op nvfp4::mxfp4_residue_quant (csrc/bindings/pybind.cpp:41-45; entry
+ * csrc/mxfp4/cuda/mxfp4_residue_quant.cu:320-381). */
+int ri_mxfp4_quant(const void* x, int dtype, int m, int k, int64_t row_stride, int64_t col_stride,
+                   const uint8_t* masks, int per8, uint8_t* codes, int out_rows, int out_row_bytes,
+                   uint8_t* sf, int64_t sf_bytes, int swizzle, int tile8, int pdl_mode,
+                   void* stream);
+
+/* Block-scaled FP4 GEMM  out[M,N] = alpha * act . W^T  on tcgen05 tensor cores (FP32 accumulate
+ * in tensor memory), W [N, K/2] packed codes with row stride w_row_bytes (multiple of 16),
+ * scales 128x4-swizzled.  `layout` is one of RI_GEMM_*; K is the weight's K in elements
+ * (multiple of 128).  alpha: device float[n_alpha] (n_alpha == 2 with RI_GEMM_ROW_PAIR /
+ * RI_GEMM_CONCAT_K: separate factor for the residue term); NULL = 1.0 (MXFP4 has none).
+ * splits: K partitions per output tile (0 = choose); splits > 1 needs `workspace` of
+ * ri_fp4_gemm_workspace_bytes() bytes, whose first ri_fp4_gemm_counter_bytes() bytes must be zero
+ * before the first use (the kernel leaves them zero).  out: bf16 or fp16 [M, out_row_stride].
+ * Replaces mext_fold_gemm / kext_kloop_gemm_sm100 (csrc/common/fold/sm10x/host.py:190-334), the
+ * MXFP4 gemm / fold_gemm (csrc/mxfp4/dense.py:35-66) and the flashinfer.mm_fp4 call of the KEXT
+ * route (quant/vllm_integration/residue_linear_op.py:127-137). */
+int ri_fp4_gemm(const uint8_t* act, int64_t act_row_bytes, const uint8_t* act_sf,
+                int64_t act_sf_bytes, const uint8_t* w, int64_t w_row_bytes, const uint8_t* w_sf,
+                int64_t w_sf_bytes, const float* alpha, int n_alpha, void* out, int out_dtype,
+                int64_t out_row_stride, int m, int n, int k, int fmt, int layout, int splits,
+                void* workspace, int64_t workspace_bytes, int32_t* status, int enable_pdl,
+                void* stream);
+int64_t ri_fp4_gemm_workspace_bytes(int m, int n, int k, int fmt, int layout, int splits);
+int64_t ri_fp4_gemm_counter_bytes(int m, int n);
+/* The split count ri_fp4_gemm would choose for splits == 0 on the current device. */
+int ri_fp4_gemm_auto_splits(int m, int n, int k, int fmt, int layout);
+
+/* ResAttn: residue-compensated paged NVFP4-KV decode attention, one query token per sequence.
+ * q [B,Hq,D] bf16; k_data/v_data [pages,Hkv,page_size,D/2]; k_sf/v_sf [pages,Hkv,page_size,D/16]
+ * E4M3 bytes (linear); block_tables int32 [B, bt_stride]; seq_lens int32 [B]; out [B,Hq,D] bf16.
+ * score_scale = sm_scale * k_global_scale, out_scale = v_global_scale.  The query is quantised
+ * to NVFP4 + NVFP4 residue inside (q_pack / q_sf scratch as for ri_nvfp4_quant_grouped_q; q_pack
+ * zero-filled once by the caller).  splits > 1 uses `workspace` (ri_resattn_workspace_bytes) for the
+ * per-split partial (o, l, m) and a second merge kernel.
+ * Replaces run_paged_fp4_decode_qmul4_tmem (csrc/resattn/host.py:489-606). */
+int ri_resattn_decode(const void* q_bf16, const uint8_t* k_data, const uint8_t* k_sf,
+                      const uint8_t* v_data, const uint8_t* v_sf, int64_t num_pages,
+                      const int32_t* block_tables, int64_t bt_stride, const int32_t* seq_lens,
+                      int batch, int num_q_heads, int num_kv_heads, int head_dim, int page_size,
+                      float score_scale, float out_scale, void* out_bf16, uint8_t* q_pack,
+                      int64_t q_pack_bytes, uint8_t* q_sf, int64_t q_sf_bytes, int splits,
+                      void* workspace, int64_t workspace_bytes, int q_residue, void* stream);
+int64_t ri_resattn_workspace_bytes(int batch, int num_q_heads, int head_dim, int splits);
+
+/* Test helper: out[i] = rcp.approx.ftz.f32(in[i]) on the device (the quantisers' reciprocal). */
+int ri_rcp_approx(const float* in, float* out, int n, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RESINFER_B200_H_ */

@@ -1,0 +1,617 @@
+// Block-scaled FP4 GEMM on the Blackwell tensor cores (tcgen05), used by MEXT and KEXT.
+//
+//   out[M, N] = alpha * act . W^T      act: FP4 codes of the tokens (+ residue), W: FP4 weights
+//
+// The weight is the 128-row MMA-A operand, the tokens are the MMA-N operand (16..256 columns), so
+// decode-sized batches do not waste tensor-core rows and the kernel is a weight-streaming kernel:
+// every CTA pulls one 128 x K slice of W through a TMA pipeline exactly once.
+//   * operands: TMA (cp.async.bulk.tensor, 128B-swizzled K-major tiles of 256 FP4 = 128 bytes),
+//     no cluster multicast anywhere;
+//   * block scales: 1-D bulk copies of the 512-byte 128x4 chunks, tcgen05.cp into tensor memory;
+//   * MMA: tcgen05.mma kind::mxf4nvf4.block_scale (block16 / UE4M3 for NVFP4) or kind::mxf4
+//     (block32 / UE8M0 for MXFP4), issued by one thread, FP32 accumulators in tensor memory;
+//   * residue fold: row_pair activations put base / residue in adjacent accumulator columns that
+//     the epilogue adds; concat_k activations issue two MMA groups per W tile into one accumulator
+//     (W is read once, unlike a K loop over 2K);
+//   * split-K over CTAs for small grids: FP32 partials in a caller workspace, the CTA that arrives
+//     last (atomic ticket, nobody waits) reduces in split order, so the result is deterministic.
+// Warp roles: warp 0 = TMA producer, warp 1 = MMA issuer (owns tensor memory), warps 2-5 =
+// epilogue (one per 32-lane quarter of tensor memory).  Every mbarrier wait is bounded: on
+// expiry the kernel records a status word, stops issuing and tears down normally.
+//
+// Stands in for the reference's CuTeDSL Fold kernel (ShawRong/ResInfer
+// csrc/common/fold/sm10x/kernel_sm100_fold.py) and the library GEMM of its KEXT route.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "resinfer_b200.h"
+
+namespace ri {
+namespace {
+
+constexpr int kTileW = 128;       // weight rows per CTA (MMA M)
+constexpr int kTileKBytes = 128;  // 256 FP4 per K tile
+constexpr int kMmaPerTile = 4;    // 4 x K64 instructions per K tile
+constexpr int kThreads = 192;
+constexpr int kTmemCols = 512;
+constexpr int kSfaCol = 256;
+constexpr int kSfbCol = 272;
+constexpr int kMaxStages = 10;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // 2 s
+
+struct GemmParams {
+  int m, n, k;                  // tokens, weight rows, weight K (elements)
+  int fmt, layout;
+  int n_tile;                   // accumulator columns per CTA
+  int tok_per_tile;             // tokens per CTA tile
+  int act_rows;                 // rows of the activation operand (M or 2M)
+  int k_tiles, k_tiles_per_split, splits;
+  int stages;
+  int chunks;                   // 512-byte scale chunks per K tile (4 NVFP4, 2 MXFP4)
+  int act_row_tiles;            // 128-row scale tiles the activation buffer holds
+  int64_t w_sf_tile_stride;     // bytes between 128-row tiles of the weight scales
+  int64_t act_sf_tile_stride;
+  int act_res_chunk0;           // concat_k: first chunk of the residue half
+  int act_res_col0;             // concat_k: byte column of the residue half
+  const uint8_t* w_sf;
+  const uint8_t* act_sf;
+  const float* alpha;
+  int n_alpha;
+  void* out;
+  int out_fp16;
+  int64_t out_stride;
+  float* ws_partial;
+  int* ws_counter;
+  int32_t* status;
+  // shared memory carve-up
+  int smem_act_off, smem_sfa_off, smem_sfb_off, stage_bytes;
+};
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait.  Returns false when another role aborted or the time limit expired (then sets
+// the abort flag itself).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try(bar, parity)) return true;
+  const unsigned long long t0 = global_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (global_ns() - t0 > kWaitLimitNs) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+// shared-memory matrix descriptors (sm_100 format: version 1 in bits 46-47)
+__device__ __forceinline__ uint64_t desc_sw128(uint32_t saddr) {   // K-major, 128B swizzle
+  return uint64_t((saddr & 0x3FFFFu) >> 4) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32) |
+         (uint64_t(1) << 46) | (uint64_t(2) << 61);
+}
+__device__ __forceinline__ uint64_t desc_sf(uint32_t saddr) {      // 32 rows x 16 B, no swizzle
+  return uint64_t((saddr & 0x3FFFFu) >> 4) | (uint64_t(128 >> 4) << 32) | (uint64_t(1) << 46);
+}
+
+__device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint64_t desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+template <bool MX>
+__device__ __forceinline__ void mma_fp4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                        uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
+  if constexpr (MX) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.block32 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb) : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb) : "memory");
+  }
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void store_out(const GemmParams& p, int tok, int n, float v) {
+  if (p.out_fp16)
+    static_cast<__half*>(p.out)[int64_t(tok) * p.out_stride + n] = __float2half_rn(v);
+  else
+    static_cast<__nv_bfloat16*>(p.out)[int64_t(tok) * p.out_stride + n] = __float2bfloat16_rn(v);
+}
+
+// ---------------------------------------------------------------------------------------------
+// kernel
+// ---------------------------------------------------------------------------------------------
+template <bool MX>
+__global__ void __launch_bounds__(kThreads, 1)
+fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap act_map,
+                const GemmParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[kMaxStages];
+  __shared__ __align__(8) uint64_t bar_empty[kMaxStages];
+  __shared__ __align__(8) uint64_t bar_acc;
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ volatile int abort_flag;
+  __shared__ int is_last_cta;
+  __shared__ int acc_ok;
+
+  // dynamic shared memory is only guaranteed 16-byte aligned: round up to the 1024-byte swizzle atom
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int w_tile = blockIdx.x;
+  const int tok_tile = blockIdx.y;
+  const int split = blockIdx.z;
+  const int kt_begin = split * p.k_tiles_per_split;
+  const int kt_end = min(kt_begin + p.k_tiles_per_split, p.k_tiles);
+  const int num_kt = kt_end - kt_begin;
+  const bool kcat = p.layout == RI_GEMM_CONCAT_K;
+  const int halves = kcat ? 2 : 1;
+  const int row_tiles = (p.n_tile + 127) / 128;             // scale row tiles per activation tile
+  const int act_tile_bytes = p.n_tile * kTileKBytes;
+  const int first_row_tile = (tok_tile * p.n_tile) / 128;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    mbar_init(smem_u32(&bar_acc), 1);
+    abort_flag = 0;
+    is_last_cta = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      // bytes per stage: W tile + scale chunks that exist + activation tile(s)
+      int valid_row_tiles = 0;
+      for (int t = 0; t < row_tiles; ++t)
+        if (first_row_tile + t < p.act_row_tiles) ++valid_row_tiles;
+      const uint32_t sf_bytes = p.chunks * 512;
+      const uint32_t tx = kTileW * kTileKBytes + sf_bytes + halves * (act_tile_bytes + valid_row_tiles * sf_bytes);
+      const uint8_t* w_sf_row = p.w_sf + int64_t(w_tile) * p.w_sf_tile_stride;
+      bool dep_synced = false;
+      for (int i = 0; i < num_kt; ++i) {
+        const int s = i % p.stages;
+        const int kt = kt_begin + i;
+        if (i >= p.stages) {
+          if (!mbar_wait(smem_u32(&bar_empty[s]), ((i / p.stages) - 1) & 1, &abort_flag)) break;
+        }
+        uint8_t* st = smem + int64_t(s) * p.stage_bytes;
+        const uint32_t full = smem_u32(&bar_full[s]);
+        mbar_expect_tx(full, tx);
+        // weights first: they do not depend on the quantiser that may still be running
+        tma_load_2d(smem_u32(st), &w_map, kt * kTileKBytes, w_tile * kTileW, full);
+        bulk_load_1d(smem_u32(st + p.smem_sfa_off), w_sf_row + int64_t(kt) * sf_bytes, sf_bytes, full);
+        if (!dep_synced) {
+          // programmatic dependent launch: the activation comes from the preceding kernel
+          asm volatile("griddepcontrol.wait;" ::: "memory");
+          dep_synced = true;
+        }
+        for (int h = 0; h < halves; ++h) {
+          tma_load_2d(smem_u32(st + p.smem_act_off + h * act_tile_bytes), &act_map,
+                      kt * kTileKBytes + h * p.act_res_col0, tok_tile * p.n_tile, full);
+          for (int t = 0; t < row_tiles; ++t) {
+            if (first_row_tile + t >= p.act_row_tiles) continue;
+            const uint8_t* src = p.act_sf + int64_t(first_row_tile + t) * p.act_sf_tile_stride +
+                                 (int64_t(kt) * p.chunks + h * p.act_res_chunk0) * 512;
+            bulk_load_1d(smem_u32(st + p.smem_sfb_off + (h * row_tiles + t) * sf_bytes), src, sf_bytes, full);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      // instruction descriptor: E2M1 x E2M1, K-major A and B, M = 128, N = n_tile
+      const uint32_t idesc_base = (1u << 7) | (1u << 10) | (uint32_t(p.n_tile >> 3) << 17) |
+                                  (MX ? (1u << 23) : 0u) | (uint32_t(kTileW >> 4) << 24);
+      const uint32_t sf_bytes = p.chunks * 512;
+      uint32_t accumulate = 0;
+      bool ok = true;
+      for (int i = 0; i < num_kt && ok; ++i) {
+        const int s = i % p.stages;
+        if (!mbar_wait(smem_u32(&bar_full[s]), (i / p.stages) & 1, &abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        uint8_t* st = smem + int64_t(s) * p.stage_bytes;
+        // scales: shared memory -> tensor memory (4 columns per 512-byte chunk)
+        for (int c = 0; c < p.chunks; ++c) {
+          tmem_cp_sf(tmem_base + kSfaCol + 4 * c, desc_sf(smem_u32(st + p.smem_sfa_off + c * 512)));
+          for (int h = 0; h < halves; ++h)
+            for (int t = 0; t < row_tiles; ++t)
+              tmem_cp_sf(tmem_base + kSfbCol + ((h * p.chunks + c) * row_tiles + t) * 4,
+                         desc_sf(smem_u32(st + p.smem_sfb_off + (h * row_tiles + t) * sf_bytes + c * 512)));
+        }
+        const uint64_t a_desc = desc_sw128(smem_u32(st));
+        for (int h = 0; h < halves; ++h) {
+          const uint64_t b_desc = desc_sw128(smem_u32(st + p.smem_act_off + h * act_tile_bytes));
+#pragma unroll
+          for (int j = 0; j < kMmaPerTile; ++j) {
+            // NVFP4: one chunk per instruction; MXFP4: one chunk per two instructions, the second
+            // uses scale bytes 2-3 of each column (scale-factor id 2)
+            const int c = MX ? (j >> 1) : j;
+            const uint32_t sf_id = MX ? uint32_t((j & 1) * 2) : 0u;
+            const uint32_t idesc = idesc_base | (sf_id << 4) | (sf_id << 29);
+            mma_fp4<MX>(tmem_base, a_desc + uint64_t(j * 2), b_desc + uint64_t(j * 2), idesc,
+                        tmem_base + kSfaCol + 4 * c,
+                        tmem_base + kSfbCol + ((h * p.chunks + c) * row_tiles) * 4, accumulate);
+            accumulate = 1;
+          }
+        }
+        mma_commit(smem_u32(&bar_empty[s]));       // frees the stage when these MMAs have read it
+      }
+      if (ok) mma_commit(smem_u32(&bar_acc));      // accumulator complete
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;                  // tensor-memory lanes 32*quarter .. +31
+    const int n_row = w_tile * kTileW + quarter * 32 + lane;
+    // one thread waits for the accumulator so that all four warps take the same decision
+    if (warp == 2 && lane == 0) acc_ok = mbar_wait(smem_u32(&bar_acc), 0, &abort_flag) ? 1 : 0;
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    const bool ok = acc_ok != 0;
+    tc_fence_after();
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const float a0 = p.alpha ? __ldg(p.alpha) : 1.0f;
+    const float a1 = (p.alpha && p.n_alpha > 1) ? __ldg(p.alpha + 1) : a0;
+    const bool pair = p.layout == RI_GEMM_ROW_PAIR;
+    const uint32_t t_lane = tmem_base + (uint32_t(quarter * 32) << 16);
+    const int tok0 = tok_tile * p.tok_per_tile;
+    if (ok && p.splits == 1) {
+      for (int c0 = 0; c0 < p.n_tile; c0 += 16) {
+        float v[16];
+        tmem_ld16(t_lane + c0, v);
+        if (n_row < p.n) {
+          if (pair) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int tok = tok0 + (c0 >> 1) + j;
+              if (tok < p.m)
+                store_out(p, tok, n_row, p.n_alpha > 1 ? a0 * v[2 * j] + a1 * v[2 * j + 1]
+                                                        : a0 * (v[2 * j] + v[2 * j + 1]));
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int tok = tok0 + c0 + j;
+              if (tok < p.m) store_out(p, tok, n_row, a0 * v[j]);
+            }
+          }
+        }
+      }
+    } else if (ok) {
+      // split-K: park the FP32 partial tile, last CTA to arrive reduces all of them in order
+      const int tile_id = w_tile * gridDim.y + tok_tile;
+      const int64_t tile_elems = int64_t(kTileW) * p.n_tile;
+      float* mine = p.ws_partial + (int64_t(split) * gridDim.x * gridDim.y + tile_id) * tile_elems;
+      for (int c0 = 0; c0 < p.n_tile; c0 += 16) {
+        float v[16];
+        tmem_ld16(t_lane + c0, v);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) mine[int64_t(c0 + j) * kTileW + quarter * 32 + lane] = v[j];
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (warp == 2 && lane == 0) {
+        const int ticket = atomicAdd(p.ws_counter + tile_id, 1);
+        const int last = ticket == p.splits - 1;
+        if (last) p.ws_counter[tile_id] = 0;       // ready for the next call
+        is_last_cta = last;
+        __threadfence();
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (is_last_cta && n_row < p.n) {
+        const float* base = p.ws_partial + int64_t(tile_id) * tile_elems + quarter * 32 + lane;
+        const int64_t split_stride = int64_t(gridDim.x) * gridDim.y * tile_elems;
+        const int step = pair ? 2 : 1;
+        for (int c = 0; c < p.n_tile; c += step) {
+          float s0 = 0.f, s1 = 0.f;
+          for (int sp = 0; sp < p.splits; ++sp) {
+            const float* src = base + sp * split_stride + int64_t(c) * kTileW;
+            s0 += __ldcg(src);
+            if (pair) s1 += __ldcg(src + kTileW);
+          }
+          const int tok = tok0 + (pair ? (c >> 1) : c);
+          if (tok < p.m)
+            store_out(p, tok, n_row, pair ? (p.n_alpha > 1 ? a0 * s0 + a1 * s1 : a0 * (s0 + s1)) : a0 * s0);
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (abort_flag) {
+    if (threadIdx.x == 0 && p.status) atomicExch(p.status, 1 + (int)blockIdx.x);
+    __nanosleep(1000000);                          // let copies that are still in flight land
+  }
+  asm volatile("griddepcontrol.launch_dependents;");
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int get_encode_fn(EncodeTiledFn* out) {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    RI_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
+    if (q != cudaDriverEntryPointSuccess || !p) {
+      set_error("cuTensorMapEncodeTiled is not available from the installed driver");
+      return RI_ERR_DEVICE;
+    }
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  *out = fn;
+  return RI_OK;
+}
+
+// 2-D byte tensor [rows, row_bytes] (row stride `stride` bytes) with a [box_rows, 128 B] box,
+// 128-byte swizzle, zero fill outside.
+int make_map(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t rows, uint64_t stride,
+             uint32_t box_rows) {
+  EncodeTiledFn fn;
+  int s = get_encode_fn(&fn);
+  if (s) return s;
+  cuuint64_t dims[2] = {row_bytes, rows};
+  cuuint64_t strides[1] = {stride};
+  cuuint32_t box[2] = {kTileKBytes, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with CUresult %d (base %p, row_bytes %llu, rows %llu, stride %llu, box_rows %u)",
+              (int)r, base, (unsigned long long)row_bytes, (unsigned long long)rows, (unsigned long long)stride, box_rows);
+    return RI_ERR_ARG;
+  }
+  return RI_OK;
+}
+
+struct Plan {
+  int n_tile, tok_per_tile, tok_tiles, w_tiles, k_tiles, splits, k_tiles_per_split, stages;
+  int chunks, stage_bytes, smem_act_off, smem_sfa_off, smem_sfb_off, smem_total;
+};
+
+int auto_splits(int tiles, int k_tiles, int sm_count) {
+  if (tiles * 4 >= sm_count * 3) return 1;
+  int s = sm_count / tiles;
+  int cap = k_tiles / 2 > 0 ? k_tiles / 2 : 1;       // at least two K tiles per split
+  if (s > cap) s = cap;
+  if (s > 16) s = 16;
+  return s < 1 ? 1 : s;
+}
+
+int make_plan(int m, int n, int k, int fmt, int layout, int splits, int sm_count, Plan* pl) {
+  const int act_rows = layout == RI_GEMM_ROW_PAIR ? 2 * m : m;
+  pl->n_tile = act_rows <= 256 ? (act_rows + 15) / 16 * 16 : 256;
+  pl->tok_per_tile = layout == RI_GEMM_ROW_PAIR ? pl->n_tile / 2 : pl->n_tile;
+  pl->tok_tiles = (act_rows + pl->n_tile - 1) / pl->n_tile;
+  pl->w_tiles = (n + kTileW - 1) / kTileW;
+  pl->k_tiles = k / 256;
+  pl->chunks = fmt == RI_FMT_NVFP4 ? 4 : 2;
+  if (splits <= 0) splits = auto_splits(pl->w_tiles * pl->tok_tiles, pl->k_tiles, sm_count);
+  if (splits > pl->k_tiles) splits = pl->k_tiles;
+  pl->k_tiles_per_split = (pl->k_tiles + splits - 1) / splits;
+  pl->splits = (pl->k_tiles + pl->k_tiles_per_split - 1) / pl->k_tiles_per_split;
+  const int halves = layout == RI_GEMM_CONCAT_K ? 2 : 1;
+  const int row_tiles = (pl->n_tile + 127) / 128;
+  const int sf_bytes = pl->chunks * 512;
+  pl->smem_act_off = kTileW * kTileKBytes;
+  pl->smem_sfa_off = pl->smem_act_off + halves * pl->n_tile * kTileKBytes;
+  pl->smem_sfb_off = pl->smem_sfa_off + sf_bytes;
+  int stage = pl->smem_sfb_off + halves * row_tiles * sf_bytes;
+  pl->stage_bytes = (stage + 1023) / 1024 * 1024;
+  const int budget = 227 * 1024 - 2048;            // static barriers + alignment slack
+  int stages = budget / pl->stage_bytes;
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages < 2) return RI_ERR_UNSUPPORTED;
+  pl->stages = stages;
+  pl->smem_total = stages * pl->stage_bytes + 1024;
+  return RI_OK;
+}
+
+}  // namespace
+}  // namespace ri
+
+using namespace ri;
+
+extern "C" int64_t ri_fp4_gemm_counter_bytes(int m, int n) {
+  (void)m;
+  // one ticket per output tile; sized for the smallest tile the planner uses
+  const int64_t w_tiles = (int64_t(n) + kTileW - 1) / kTileW;
+  const int64_t tok_tiles = (2 * int64_t(m) + 255) / 256 + 1;
+  return (w_tiles * tok_tiles * 4 + 255) / 256 * 256;
+}
+
+extern "C" int ri_fp4_gemm_auto_splits(int m, int n, int k, int fmt, int layout) {
+  DeviceInfo di;
+  if (device_info(&di)) return -1;
+  Plan pl;
+  if (make_plan(m, n, k, fmt, layout, 0, di.sm_count, &pl)) return -1;
+  return pl.splits;
+}
+
+extern "C" int64_t ri_fp4_gemm_workspace_bytes(int m, int n, int k, int fmt, int layout, int splits) {
+  if (splits <= 1) return 0;
+  Plan pl;
+  if (make_plan(m, n, k, fmt, layout, splits, 148, &pl)) return -1;
+  const int64_t partial = int64_t(pl.splits) * pl.w_tiles * pl.tok_tiles * kTileW * pl.n_tile * 4;
+  return ri_fp4_gemm_counter_bytes(m, n) + partial;
+}
+
+extern "C" int ri_fp4_gemm(const uint8_t* act, int64_t act_row_bytes, const uint8_t* act_sf,
+                           int64_t act_sf_bytes, const uint8_t* w, int64_t w_row_bytes,
+                           const uint8_t* w_sf, int64_t w_sf_bytes, const float* alpha, int n_alpha,
+                           void* out, int out_dtype, int64_t out_row_stride, int m, int n, int k,
+                           int fmt, int layout, int splits, void* workspace, int64_t workspace_bytes,
+                           int32_t* status, int enable_pdl, void* stream) {
+  RI_CHECK_ARG(fmt == RI_FMT_NVFP4 || fmt == RI_FMT_MXFP4, "unknown FP4 format: %d", fmt);
+  RI_CHECK_ARG(layout >= RI_GEMM_PLAIN && layout <= RI_GEMM_CONCAT_K, "unknown activation layout %d", layout);
+  RI_CHECK_ARG(m >= 0 && n > 0 && k > 0, "positive dimensions required");
+  RI_CHECK_ARG(k % 256 == 0, "K must be a multiple of 256 (got %d)", k);
+  RI_CHECK_ARG(out_dtype == RI_DTYPE_BF16 || out_dtype == RI_DTYPE_FP16, "output must be bf16 or fp16");
+  RI_CHECK_ARG(out_row_stride >= n, "output row stride smaller than N");
+  RI_CHECK_ARG(w_row_bytes >= k / 2 && w_row_bytes % 16 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0,
+               "weight rows must be 16-byte aligned with stride >= K/2 (stride %lld)", (long long)w_row_bytes);
+  const int vec = fmt == RI_FMT_NVFP4 ? 16 : 32;
+  const int act_rows = layout == RI_GEMM_ROW_PAIR ? 2 * m : m;
+  const int64_t act_cols = layout == RI_GEMM_CONCAT_K ? int64_t(k) : k / 2;       // bytes
+  const int act_k_total = layout == RI_GEMM_CONCAT_K ? 2 * k : k;
+  RI_CHECK_ARG(act_row_bytes >= act_cols && act_row_bytes % 16 == 0 && (reinterpret_cast<uintptr_t>(act) & 15) == 0,
+               "activation must be compact 16-byte aligned rows of %lld bytes; got stride %lld",
+               (long long)act_cols, (long long)act_row_bytes);
+  RI_CHECK_ARG(n_alpha >= 0 && n_alpha <= 2 && (n_alpha < 2 || layout == RI_GEMM_ROW_PAIR),
+               "a separate residue alpha needs the row_pair layout");
+  RI_CHECK_ARG(fmt == RI_FMT_NVFP4 || alpha == nullptr, "MXFP4 has no global scale");
+  const int64_t w_chunks = (int64_t(k) + 4 * vec - 1) / (4 * vec);
+  const int64_t act_chunks = (int64_t(act_k_total) + 4 * vec - 1) / (4 * vec);
+  const int64_t need_wsf = ((int64_t(n) + 127) / 128) * w_chunks * 512;
+  const int64_t act_row_tiles = (int64_t(act_rows) + 127) / 128;
+  RI_CHECK_ARG(w_sf_bytes >= need_wsf, "expected a 128x4 weight scale buffer of %lld bytes, got %lld",
+               (long long)need_wsf, (long long)w_sf_bytes);
+  RI_CHECK_ARG(act_sf_bytes >= act_row_tiles * act_chunks * 512,
+               "expected a 128x4 activation scale buffer of %lld bytes, got %lld",
+               (long long)(act_row_tiles * act_chunks * 512), (long long)act_sf_bytes);
+  RI_CHECK_ARG((reinterpret_cast<uintptr_t>(w_sf) & 15) == 0 && (reinterpret_cast<uintptr_t>(act_sf) & 15) == 0,
+               "scale buffers must be 16-byte aligned");
+  if (m == 0) return RI_OK;
+
+  DeviceInfo di;
+  int s = device_info(&di);
+  if (s) return s;
+  Plan pl;
+  s = make_plan(m, n, k, fmt, layout, splits, di.sm_count, &pl);
+  if (s) {
+    set_error("no tile plan for M=%d N=%d K=%d", m, n, k);
+    return s;
+  }
+  float* ws_partial = nullptr;
+  int* ws_counter = nullptr;
+  if (pl.splits > 1) {
+    const int64_t counter_bytes = ri_fp4_gemm_counter_bytes(m, n);
+    const int64_t partial = int64_t(pl.splits) * pl.w_tiles * pl.tok_tiles * kTileW * pl.n_tile * 4;
+    RI_CHECK_ARG(workspace != nullptr && workspace_bytes >= counter_bytes + partial,
+                 "split-K with %d splits needs a workspace of %lld bytes, got %lld", pl.splits,
+                 (long long)(counter_bytes + partial), (long long)workspace_bytes);
+    RI_CHECK_ARG((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "workspace must be 256-byte aligned");
+    RI_CHECK_ARG(int64_t(pl.w_tiles) * pl.tok_tiles * 4 <= counter_bytes, "internal: counter area too small");
+    ws_counter = static_cast<int*>(workspace);
+    ws_partial = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + counter_bytes);
+  }
+
+  CUtensorMap w_map, act_map;
+  s = make_map(&w_map, w, uint64_t(k / 2), uint64_t(n), uint64_t(w_row_bytes), kTileW);
+  if (s) return s;
+  s = make_map(&act_map, act, uint64_t(act_cols), uint64_t(act_rows), uint64_t(act_row_bytes), uint32_t(pl.n_tile));
+  if (s) return s;
+
+  GemmParams p{};
+  p.m = m; p.n = n; p.k = k; p.fmt = fmt; p.layout = layout;
+  p.n_tile = pl.n_tile; p.tok_per_tile = pl.tok_per_tile; p.act_rows = act_rows;
+  p.k_tiles = pl.k_tiles; p.k_tiles_per_split = pl.k_tiles_per_split; p.splits = pl.splits;
+  p.stages = pl.stages; p.chunks = pl.chunks;
+  p.act_row_tiles = int(act_row_tiles);
+  p.w_sf_tile_stride = w_chunks * 512;
+  p.act_sf_tile_stride = act_chunks * 512;
+  p.act_res_chunk0 = int(k / (4 * vec));
+  p.act_res_col0 = k / 2;
+  p.w_sf = w_sf; p.act_sf = act_sf; p.alpha = alpha; p.n_alpha = alpha ? (n_alpha > 0 ? n_alpha : 1) : 0;
+  p.out = out; p.out_fp16 = out_dtype == RI_DTYPE_FP16; p.out_stride = out_row_stride;
+  p.ws_partial = ws_partial; p.ws_counter = ws_counter; p.status = status;
+  p.smem_act_off = pl.smem_act_off; p.smem_sfa_off = pl.smem_sfa_off; p.smem_sfb_off = pl.smem_sfb_off;
+  p.stage_bytes = pl.stage_bytes;
+
+  auto kernel = fmt == RI_FMT_MXFP4 ? fp4_gemm_kernel<true> : fp4_gemm_kernel<false>;
+  static bool attr_set[2] = {false, false};
+  if (!attr_set[fmt]) {
+    RI_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 2048));
+    attr_set[fmt] = true;
+  }
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(pl.w_tiles, pl.tok_tiles, pl.splits);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = pl.smem_total;
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr{};
+  if (enable_pdl) {
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+  }
+  return cuda_status(cudaLaunchKernelEx(&cfg, kernel, w_map, act_map, p), "fp4 gemm launch");
+}
