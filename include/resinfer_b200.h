@@ -33,6 +33,7 @@ extern "C" {
 /* input dtypes */
 #define RI_DTYPE_BF16 0
 #define RI_DTYPE_FP16 1
+#define RI_DTYPE_F32 2 /* outputs only: unrounded FP32 result, for accuracy checks */
 
 /* FP4 formats */
 #define RI_FMT_NVFP4 0 /* 16-element blocks, E4M3 block scale, FP32 global scale */
@@ -89,7 +90,8 @@ int ri_nvfp4_quant_grouped_q(const void* q_bf16, int batch, int num_kv_heads, in
                              int64_t q_sf_bytes, void* stream);
 
 /* MXFP4 quantiser.  masks == NULL: MEXT, codes [out_rows, K/2] with out_rows = 2M (row_pair) or a
- * multiple of 16 >= 2M (tile8).  masks != NULL: selective, codes [M, out_row_bytes] with
+ * multiple of 16 >= 2M (tile8); masks == NULL with per8 == 0 and out_rows == M: plain quantisation
+ * without residue (the reference takes that one from FlashInfer, csrc/mxfp4/quantization.py:22-49).  masks != NULL: selective, codes [M, out_row_bytes] with
  * out_row_bytes*2 >= K + K/8*per8 (zero padded).  sf: 128x4-swizzled (swizzle != 0) or linear
  * [out_rows, Ktot/32]; its size must match exactly.  x may be strided (strides in elements).
  * Replaces torch op nvfp4::mxfp4_residue_quant (csrc/bindings/pybind.cpp:41-45; entry
@@ -102,11 +104,12 @@ int ri_mxfp4_quant(const void* x, int dtype, int m, int k, int64_t row_stride, i
 /* Block-scaled FP4 GEMM  out[M,N] = alpha * act . W^T  on tcgen05 tensor cores (FP32 accumulate
  * in tensor memory), W [N, K/2] packed codes with row stride w_row_bytes (multiple of 16),
  * scales 128x4-swizzled.  `layout` is one of RI_GEMM_*; K is the weight's K in elements
- * (multiple of 128).  alpha: device float[n_alpha] (n_alpha == 2 with RI_GEMM_ROW_PAIR /
- * RI_GEMM_CONCAT_K: separate factor for the residue term); NULL = 1.0 (MXFP4 has none).
+ * (multiple of 64 for NVFP4, 128 for MXFP4, 256 for RI_GEMM_CONCAT_K).  alpha: device float[n_alpha] (n_alpha == 2, RI_GEMM_ROW_PAIR only:
+ * separate factor for the residue term); NULL = 1.0 (MXFP4 has none).
  * splits: K partitions per output tile (0 = choose); splits > 1 needs `workspace` of
  * ri_fp4_gemm_workspace_bytes() bytes, whose first ri_fp4_gemm_counter_bytes() bytes must be zero
- * before the first use (the kernel leaves them zero).  out: bf16 or fp16 [M, out_row_stride].
+ * before the first use (the kernel leaves them zero).  out: bf16 or fp16 (or RI_DTYPE_F32) [M, out_row_stride].
+ * status: optional device word, set non-zero if a bounded wait inside the kernel expired.
  * Replaces mext_fold_gemm / kext_kloop_gemm_sm100 (csrc/common/fold/sm10x/host.py:190-334), the
  * MXFP4 gemm / fold_gemm (csrc/mxfp4/dense.py:35-66) and the flashinfer.mm_fp4 call of the KEXT
  * route (quant/vllm_integration/residue_linear_op.py:127-137). */
@@ -123,19 +126,24 @@ int ri_fp4_gemm_auto_splits(int m, int n, int k, int fmt, int layout);
 
 /* ResAttn: residue-compensated paged NVFP4-KV decode attention, one query token per sequence.
  * q [B,Hq,D] bf16; k_data/v_data [pages,Hkv,page_size,D/2]; k_sf/v_sf [pages,Hkv,page_size,D/16]
- * E4M3 bytes (linear); block_tables int32 [B, bt_stride]; seq_lens int32 [B]; out [B,Hq,D] bf16.
+ * E4M3 bytes (linear); block_tables int32 [B, bt_stride]; seq_lens int32 [B]; out [B,Hq,D] bf16
+ * (out_dtype RI_DTYPE_BF16; RI_DTYPE_F32 writes the unrounded result).
  * score_scale = sm_scale * k_global_scale, out_scale = v_global_scale.  The query is quantised
- * to NVFP4 + NVFP4 residue inside (q_pack / q_sf scratch as for ri_nvfp4_quant_grouped_q; q_pack
- * zero-filled once by the caller).  splits > 1 uses `workspace` (ri_resattn_workspace_bytes) for the
- * per-split partial (o, l, m) and a second merge kernel.
+ * to NVFP4 + NVFP4 residue inside the kernel (q_residue == 0 drops the residue rows); q_pack / q_sf
+ * are optional (NULL) outputs that receive the quantised query in the layout of
+ * ri_nvfp4_quant_grouped_q.  page_size is a multiple of 16.  splits > 1 (KV split per sequence)
+ * uses `workspace` (ri_resattn_workspace_bytes) for the per-split partial (o, l, m) and a second,
+ * deterministic merge kernel.  status: optional device word, set non-zero if a bounded wait inside
+ * the kernel expired.
  * Replaces run_paged_fp4_decode_qmul4_tmem (csrc/resattn/host.py:489-606). */
 int ri_resattn_decode(const void* q_bf16, const uint8_t* k_data, const uint8_t* k_sf,
                       const uint8_t* v_data, const uint8_t* v_sf, int64_t num_pages,
                       const int32_t* block_tables, int64_t bt_stride, const int32_t* seq_lens,
                       int batch, int num_q_heads, int num_kv_heads, int head_dim, int page_size,
-                      float score_scale, float out_scale, void* out_bf16, uint8_t* q_pack,
+                      float score_scale, float out_scale, void* out, int out_dtype, uint8_t* q_pack,
                       int64_t q_pack_bytes, uint8_t* q_sf, int64_t q_sf_bytes, int splits,
-                      void* workspace, int64_t workspace_bytes, int q_residue, void* stream);
+                      void* workspace, int64_t workspace_bytes, int q_residue, int32_t* status,
+                      void* stream);
 int64_t ri_resattn_workspace_bytes(int batch, int num_q_heads, int head_dim, int splits);
 
 /* Test helper: out[i] = rcp.approx.ftz.f32(in[i]) on the device (the quantisers' reciprocal). */

@@ -184,4 +184,114 @@ __device__ __forceinline__ void load16(const T* p, float (&v)[16]) {
   }
 }
 
+
+// ------------------------------------------------------------------------------------------
+// NVFP4 block quantisation shared by the quantiser kernels and the ResAttn query prologue
+// ------------------------------------------------------------------------------------------
+struct BlockQ {
+  uint2 base;       // 16 base codes
+  uint2 res;        // 16 residue codes (MEXT)
+  uint8_t sf, sf_res;
+};
+
+// Base quantisation of one 16-block; leaves the FP32 residues x - deq(q(x)) in r[].
+__device__ __forceinline__ uint2 quant_base16(const float (&x)[16], float gs, uint8_t* sf, float (&r)[16]) {
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(x[i]));
+  float mult = nvfp4_scale(amax, gs, sf);
+  float s[8];
+  uint2 out;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) s[i] = mul_ftz(x[i], mult);
+  out.x = cvt_e2m1x8(s);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) s[i] = mul_ftz(x[8 + i], mult);
+  out.y = cvt_e2m1x8(s);
+  float inv = mult != 0.0f ? rcp_approx_ftz(mult) : 0.0f;
+  float hat[8];
+  e2m1x8_to_float(out.x, hat);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) r[i] = residue_fma(x[i], hat[i], inv);
+  e2m1x8_to_float(out.y, hat);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) r[8 + i] = residue_fma(x[8 + i], hat[i], inv);
+  return out;
+}
+
+__device__ __forceinline__ uint2 quant_plain16(const float (&r)[16], float mult) {
+  float s[8];
+  uint2 out;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) s[i] = mul_ftz(r[i], mult);
+  out.x = cvt_e2m1x8(s);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) s[i] = mul_ftz(r[8 + i], mult);
+  out.y = cvt_e2m1x8(s);
+  return out;
+}
+
+__device__ __forceinline__ BlockQ quant_mext16(const float (&x)[16], float gs, float gs_res) {
+  BlockQ q;
+  float r[16];
+  q.base = quant_base16(x, gs, &q.sf, r);
+  float ramax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) ramax = fmaxf(ramax, fabsf(r[i]));
+  float rmult = nvfp4_scale(ramax, gs_res, &q.sf_res);
+  q.res = quant_plain16(r, rmult);
+  return q;
+}
+
+
+// ------------------------------------------------------------------------------------------
+// mbarrier / bulk-copy helpers.  Every wait is bounded: it gives up after kWaitLimitNs (or as
+// soon as another role of the CTA has given up) and reports that to the caller.
+// ------------------------------------------------------------------------------------------
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // 2 s
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait.  Returns false when another role aborted or the time limit expired (then sets
+// the abort flag itself).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try(bar, parity)) return true;
+  const unsigned long long t0 = global_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (global_ns() - t0 > kWaitLimitNs) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+
 }  // namespace ri

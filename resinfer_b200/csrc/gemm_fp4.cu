@@ -37,7 +37,7 @@ constexpr int kTmemCols = 512;
 constexpr int kSfaCol = 256;
 constexpr int kSfbCol = 272;
 constexpr int kMaxStages = 10;
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // 2 s
+constexpr int kMaxDynSmem = 227 * 1024 - 2048;    // 227 KB per CTA minus the static barriers / flags
 
 struct GemmParams {
   int m, n, k;                  // tokens, weight rows, weight K (elements)
@@ -58,7 +58,7 @@ struct GemmParams {
   const float* alpha;
   int n_alpha;
   void* out;
-  int out_fp16;
+  int out_fp16;                 // 0 bf16, 1 fp16, 2 fp32
   int64_t out_stride;
   float* ws_partial;
   int* ws_counter;
@@ -70,55 +70,11 @@ struct GemmParams {
 // ---------------------------------------------------------------------------------------------
 // PTX wrappers
 // ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ unsigned long long global_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-// Bounded wait.  Returns false when another role aborted or the time limit expired (then sets
-// the abort flag itself).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try(bar, parity)) return true;
-  const unsigned long long t0 = global_ns();
-  for (;;) {
-#pragma unroll 1
-    for (int i = 0; i < 64; ++i)
-      if (mbar_try(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (global_ns() - t0 > kWaitLimitNs) {
-      *abort_flag = 1;
-      return false;
-    }
-  }
-}
-
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
 }
-__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
-
 // shared-memory matrix descriptors (sm_100 format: version 1 in bits 46-47)
 __device__ __forceinline__ uint64_t desc_sw128(uint32_t saddr) {   // K-major, 128B swizzle
   return uint64_t((saddr & 0x3FFFFu) >> 4) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32) |
@@ -164,7 +120,9 @@ __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence:
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
 __device__ __forceinline__ void store_out(const GemmParams& p, int tok, int n, float v) {
-  if (p.out_fp16)
+  if (p.out_fp16 == 2)
+    static_cast<float*>(p.out)[int64_t(tok) * p.out_stride + n] = v;
+  else if (p.out_fp16)
     static_cast<__half*>(p.out)[int64_t(tok) * p.out_stride + n] = __float2half_rn(v);
   else
     static_cast<__nv_bfloat16*>(p.out)[int64_t(tok) * p.out_stride + n] = __float2bfloat16_rn(v);
@@ -230,13 +188,17 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
       int valid_row_tiles = 0;
       for (int t = 0; t < row_tiles; ++t)
         if (first_row_tile + t < p.act_row_tiles) ++valid_row_tiles;
-      const uint32_t sf_bytes = p.chunks * 512;
-      const uint32_t tx = kTileW * kTileKBytes + sf_bytes + halves * (act_tile_bytes + valid_row_tiles * sf_bytes);
+      const uint32_t sf_stride = p.chunks * 512;           // bytes of a full tile's scale chunks
       const uint8_t* w_sf_row = p.w_sf + int64_t(w_tile) * p.w_sf_tile_stride;
       bool dep_synced = false;
       for (int i = 0; i < num_kt; ++i) {
         const int s = i % p.stages;
         const int kt = kt_begin + i;
+        // the last K tile may hold fewer than four K64 steps: copy only the scale chunks that exist
+        const int rem = p.k - kt * 256;
+        const int n_mma = rem >= 256 ? kMmaPerTile : rem / 64;
+        const uint32_t sf_bytes = uint32_t(MX ? (n_mma + 1) / 2 : n_mma) * 512;
+        const uint32_t tx = kTileW * kTileKBytes + sf_bytes + halves * (act_tile_bytes + valid_row_tiles * sf_bytes);
         if (i >= p.stages) {
           if (!mbar_wait(smem_u32(&bar_empty[s]), ((i / p.stages) - 1) & 1, &abort_flag)) break;
         }
@@ -245,7 +207,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
         mbar_expect_tx(full, tx);
         // weights first: they do not depend on the quantiser that may still be running
         tma_load_2d(smem_u32(st), &w_map, kt * kTileKBytes, w_tile * kTileW, full);
-        bulk_load_1d(smem_u32(st + p.smem_sfa_off), w_sf_row + int64_t(kt) * sf_bytes, sf_bytes, full);
+        bulk_load_1d(smem_u32(st + p.smem_sfa_off), w_sf_row + int64_t(kt) * sf_stride, sf_bytes, full);
         if (!dep_synced) {
           // programmatic dependent launch: the activation comes from the preceding kernel
           asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -258,7 +220,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
             if (first_row_tile + t >= p.act_row_tiles) continue;
             const uint8_t* src = p.act_sf + int64_t(first_row_tile + t) * p.act_sf_tile_stride +
                                  (int64_t(kt) * p.chunks + h * p.act_res_chunk0) * 512;
-            bulk_load_1d(smem_u32(st + p.smem_sfb_off + (h * row_tiles + t) * sf_bytes), src, sf_bytes, full);
+            bulk_load_1d(smem_u32(st + p.smem_sfb_off + (h * row_tiles + t) * sf_stride), src, sf_bytes, full);
           }
         }
       }
@@ -269,7 +231,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
       // instruction descriptor: E2M1 x E2M1, K-major A and B, M = 128, N = n_tile
       const uint32_t idesc_base = (1u << 7) | (1u << 10) | (uint32_t(p.n_tile >> 3) << 17) |
                                   (MX ? (1u << 23) : 0u) | (uint32_t(kTileW >> 4) << 24);
-      const uint32_t sf_bytes = p.chunks * 512;
+      const uint32_t sf_stride = p.chunks * 512;
       uint32_t accumulate = 0;
       bool ok = true;
       for (int i = 0; i < num_kt && ok; ++i) {
@@ -277,19 +239,23 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
         if (!mbar_wait(smem_u32(&bar_full[s]), (i / p.stages) & 1, &abort_flag)) { ok = false; break; }
         tc_fence_after();
         uint8_t* st = smem + int64_t(s) * p.stage_bytes;
+        const int rem = p.k - (kt_begin + i) * 256;
+        const int n_mma = rem >= 256 ? kMmaPerTile : rem / 64;
+        const int n_chunks = MX ? (n_mma + 1) / 2 : n_mma;
         // scales: shared memory -> tensor memory (4 columns per 512-byte chunk)
-        for (int c = 0; c < p.chunks; ++c) {
+        for (int c = 0; c < n_chunks; ++c) {
           tmem_cp_sf(tmem_base + kSfaCol + 4 * c, desc_sf(smem_u32(st + p.smem_sfa_off + c * 512)));
           for (int h = 0; h < halves; ++h)
             for (int t = 0; t < row_tiles; ++t)
               tmem_cp_sf(tmem_base + kSfbCol + ((h * p.chunks + c) * row_tiles + t) * 4,
-                         desc_sf(smem_u32(st + p.smem_sfb_off + (h * row_tiles + t) * sf_bytes + c * 512)));
+                         desc_sf(smem_u32(st + p.smem_sfb_off + (h * row_tiles + t) * sf_stride + c * 512)));
         }
         const uint64_t a_desc = desc_sw128(smem_u32(st));
         for (int h = 0; h < halves; ++h) {
           const uint64_t b_desc = desc_sw128(smem_u32(st + p.smem_act_off + h * act_tile_bytes));
 #pragma unroll
           for (int j = 0; j < kMmaPerTile; ++j) {
+            if (j >= n_mma) break;
             // NVFP4: one chunk per instruction; MXFP4: one chunk per two instructions, the second
             // uses scale bytes 2-3 of each column (scale-factor id 2)
             const int c = MX ? (j >> 1) : j;
@@ -461,7 +427,7 @@ int make_plan(int m, int n, int k, int fmt, int layout, int splits, int sm_count
   pl->tok_per_tile = layout == RI_GEMM_ROW_PAIR ? pl->n_tile / 2 : pl->n_tile;
   pl->tok_tiles = (act_rows + pl->n_tile - 1) / pl->n_tile;
   pl->w_tiles = (n + kTileW - 1) / kTileW;
-  pl->k_tiles = k / 256;
+  pl->k_tiles = (k + 255) / 256;
   pl->chunks = fmt == RI_FMT_NVFP4 ? 4 : 2;
   if (splits <= 0) splits = auto_splits(pl->w_tiles * pl->tok_tiles, pl->k_tiles, sm_count);
   if (splits > pl->k_tiles) splits = pl->k_tiles;
@@ -475,7 +441,7 @@ int make_plan(int m, int n, int k, int fmt, int layout, int splits, int sm_count
   pl->smem_sfb_off = pl->smem_sfa_off + sf_bytes;
   int stage = pl->smem_sfb_off + halves * row_tiles * sf_bytes;
   pl->stage_bytes = (stage + 1023) / 1024 * 1024;
-  const int budget = 227 * 1024 - 2048;            // static barriers + alignment slack
+  const int budget = kMaxDynSmem - 1024;           // 1 KB of slack to align the tiles to 1024 bytes
   int stages = budget / pl->stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) return RI_ERR_UNSUPPORTED;
@@ -522,8 +488,11 @@ extern "C" int ri_fp4_gemm(const uint8_t* act, int64_t act_row_bytes, const uint
   RI_CHECK_ARG(fmt == RI_FMT_NVFP4 || fmt == RI_FMT_MXFP4, "unknown FP4 format: %d", fmt);
   RI_CHECK_ARG(layout >= RI_GEMM_PLAIN && layout <= RI_GEMM_CONCAT_K, "unknown activation layout %d", layout);
   RI_CHECK_ARG(m >= 0 && n > 0 && k > 0, "positive dimensions required");
-  RI_CHECK_ARG(k % 256 == 0, "K must be a multiple of 256 (got %d)", k);
-  RI_CHECK_ARG(out_dtype == RI_DTYPE_BF16 || out_dtype == RI_DTYPE_FP16, "output must be bf16 or fp16");
+  RI_CHECK_ARG(k % (fmt == RI_FMT_NVFP4 ? 64 : 128) == 0, "K must be a multiple of %d (got %d)",
+               fmt == RI_FMT_NVFP4 ? 64 : 128, k);
+  RI_CHECK_ARG(layout != RI_GEMM_CONCAT_K || k % 256 == 0, "the concat_k layout needs K %% 256 == 0 (got %d)", k);
+  RI_CHECK_ARG(out_dtype == RI_DTYPE_BF16 || out_dtype == RI_DTYPE_FP16 || out_dtype == RI_DTYPE_F32,
+               "output must be bf16 or fp16");
   RI_CHECK_ARG(out_row_stride >= n, "output row stride smaller than N");
   RI_CHECK_ARG(w_row_bytes >= k / 2 && w_row_bytes % 16 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0,
                "weight rows must be 16-byte aligned with stride >= K/2 (stride %lld)", (long long)w_row_bytes);
@@ -590,7 +559,7 @@ extern "C" int ri_fp4_gemm(const uint8_t* act, int64_t act_row_bytes, const uint
   p.act_res_chunk0 = int(k / (4 * vec));
   p.act_res_col0 = k / 2;
   p.w_sf = w_sf; p.act_sf = act_sf; p.alpha = alpha; p.n_alpha = alpha ? (n_alpha > 0 ? n_alpha : 1) : 0;
-  p.out = out; p.out_fp16 = out_dtype == RI_DTYPE_FP16; p.out_stride = out_row_stride;
+  p.out = out; p.out_fp16 = out_dtype == RI_DTYPE_F32 ? 2 : (out_dtype == RI_DTYPE_FP16 ? 1 : 0); p.out_stride = out_row_stride;
   p.ws_partial = ws_partial; p.ws_counter = ws_counter; p.status = status;
   p.smem_act_off = pl.smem_act_off; p.smem_sfa_off = pl.smem_sfa_off; p.smem_sfb_off = pl.smem_sfb_off;
   p.stage_bytes = pl.stage_bytes;
@@ -598,7 +567,7 @@ extern "C" int ri_fp4_gemm(const uint8_t* act, int64_t act_row_bytes, const uint
   auto kernel = fmt == RI_FMT_MXFP4 ? fp4_gemm_kernel<true> : fp4_gemm_kernel<false>;
   static bool attr_set[2] = {false, false};
   if (!attr_set[fmt]) {
-    RI_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 2048));
+    RI_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem));
     attr_set[fmt] = true;
   }
   cudaLaunchConfig_t cfg{};

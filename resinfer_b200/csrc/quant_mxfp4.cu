@@ -46,6 +46,7 @@ __device__ __forceinline__ void load32(const T* p, int64_t col_stride, float (&v
 }
 
 // PER8 == 8: MEXT (full residue rows).  PER8 in {1,2,4}: selective residue appended along K.
+// PER8 == 0: plain quantisation, no residue.
 template <typename T, int PER8>
 __global__ void __launch_bounds__(128) mxfp4_quant_kernel(
     const T* __restrict__ x, int64_t row_stride, int64_t col_stride, const uint8_t* __restrict__ masks,
@@ -56,7 +57,7 @@ __global__ void __launch_bounds__(128) mxfp4_quant_kernel(
   const int groups_in = k / 32;                                   // base blocks per row
   const int sf_groups = k_total / 32;
   const int sf_groups_out = swizzle ? (sf_groups + 3) / 4 * 4 : sf_groups;
-  const int sel = MEXT ? 0 : k / 8 * PER8;
+  const int sel = (MEXT || PER8 == 0) ? 0 : k / 8 * PER8;
   const int sel_groups = (sel + 31) / 32;
   // logical rows this grid walks: tokens for MEXT (two physical rows each), rows otherwise
   const int sf_rows = swizzle ? padded_rows : out_rows;
@@ -148,6 +149,8 @@ __global__ void __launch_bounds__(128) mxfp4_quant_kernel(
         sf_at(base_row, g) = 0;
         sf_at(res_row, g) = 0;
       }
+    } else if constexpr (PER8 == 0) {
+      if (!has && g < sf_groups_out) sf_at(row, g) = 0;
     } else {
       constexpr int NRES = 4 * PER8;              // residues per thread (32 channels = 4 mask bytes)
       constexpr int SF_THREADS = 32 / NRES;       // threads sharing one residue scale
@@ -241,6 +244,8 @@ template <typename T>
 int dispatch_mx(int per8, bool has_masks, cudaStream_t st, int pdl, const T* x, int64_t rs, int64_t cs,
                 const uint8_t* masks, uint8_t* out, uint8_t* sf, int rows, int k, int k_total,
                 int out_rows, int padded_rows, int swizzle, int tile8) {
+  if (!has_masks && per8 == 0 && out_rows == rows && !tile8)
+    return launch_mx<T, 0>(st, pdl, x, rs, cs, masks, out, sf, rows, k, k_total, out_rows, padded_rows, swizzle, tile8);
   if (!has_masks) return launch_mx<T, 8>(st, pdl, x, rs, cs, masks, out, sf, rows, k, k_total, out_rows, padded_rows, swizzle, tile8);
   switch (per8) {
     case 1: return launch_mx<T, 1>(st, pdl, x, rs, cs, masks, out, sf, rows, k, k_total, out_rows, padded_rows, swizzle, tile8);
@@ -264,7 +269,8 @@ extern "C" int ri_mxfp4_quant(const void* x, int dtype, int m, int k, int64_t ro
   RI_CHECK_ARG(!masks || per8 == 1 || per8 == 2 || per8 == 4, "per8 must be 1/2/4");
   RI_CHECK_ARG(!tile8 || (!masks && swizzle), "tile8 requires full residue and 128x4 scales");
   const int sel = masks ? k / 8 * per8 : 0;
-  RI_CHECK_ARG(tile8 ? (out_rows >= 2 * m && out_rows % 16 == 0) : out_rows == m * (masks ? 1 : 2),
+  const bool plain = !masks && per8 == 0 && out_rows == m && !tile8 && m > 0;
+  RI_CHECK_ARG(plain || (tile8 ? (out_rows >= 2 * m && out_rows % 16 == 0) : out_rows == m * (masks ? 1 : 2)),
                "invalid output rows");
   const int k_total = out_row_bytes * 2;
   RI_CHECK_ARG(k_total % 32 == 0 && (masks ? k_total >= k + sel : k_total == k), "invalid output K");

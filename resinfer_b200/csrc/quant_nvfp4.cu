@@ -12,61 +12,6 @@
 namespace ri {
 namespace {
 
-struct BlockQ {
-  uint2 base;       // 16 base codes
-  uint2 res;        // 16 residue codes (MEXT)
-  uint8_t sf, sf_res;
-};
-
-// Base quantisation of one 16-block; leaves the FP32 residues x - deq(q(x)) in r[].
-__device__ __forceinline__ uint2 quant_base16(const float (&x)[16], float gs, uint8_t* sf, float (&r)[16]) {
-  float amax = 0.f;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(x[i]));
-  float mult = nvfp4_scale(amax, gs, sf);
-  float s[8];
-  uint2 out;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) s[i] = mul_ftz(x[i], mult);
-  out.x = cvt_e2m1x8(s);
-#pragma unroll
-  for (int i = 0; i < 8; ++i) s[i] = mul_ftz(x[8 + i], mult);
-  out.y = cvt_e2m1x8(s);
-  float inv = mult != 0.0f ? rcp_approx_ftz(mult) : 0.0f;
-  float hat[8];
-  e2m1x8_to_float(out.x, hat);
-#pragma unroll
-  for (int i = 0; i < 8; ++i) r[i] = residue_fma(x[i], hat[i], inv);
-  e2m1x8_to_float(out.y, hat);
-#pragma unroll
-  for (int i = 0; i < 8; ++i) r[8 + i] = residue_fma(x[8 + i], hat[i], inv);
-  return out;
-}
-
-__device__ __forceinline__ uint2 quant_plain16(const float (&r)[16], float mult) {
-  float s[8];
-  uint2 out;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) s[i] = mul_ftz(r[i], mult);
-  out.x = cvt_e2m1x8(s);
-#pragma unroll
-  for (int i = 0; i < 8; ++i) s[i] = mul_ftz(r[8 + i], mult);
-  out.y = cvt_e2m1x8(s);
-  return out;
-}
-
-__device__ __forceinline__ BlockQ quant_mext16(const float (&x)[16], float gs, float gs_res) {
-  BlockQ q;
-  float r[16];
-  q.base = quant_base16(x, gs, &q.sf, r);
-  float ramax = 0.f;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) ramax = fmaxf(ramax, fabsf(r[i]));
-  float rmult = nvfp4_scale(ramax, gs_res, &q.sf_res);
-  q.res = quant_plain16(r, rmult);
-  return q;
-}
-
 // token row -> physical rows of the layout (0 concat, 1 row_pair, 2 tile8, 4 attn_tile8);
 // reference: nvfp4_utils.cuh:1109-1160
 __device__ __forceinline__ void mext_rows(int i, int rows, int layout, int& base, int& res, int& sfb,

@@ -1,0 +1,128 @@
+"""Tensor-level entry points of the GEMM and attention kernels (thin wrappers over the C ABI).
+
+These are the functions the reference-named modules (``nvfp4.cute_fold.host``,
+``nvfp4.mxfp4.dense``, ``nvfp4.cute_attn.host``) call.  Workspaces are cached per
+(device, size) like the reference caches its reduction workspaces
+(ShawRong/ResInfer quant/vllm_integration/attn/decode.py:23-53); nothing is allocated once a
+shape has been seen, so the calls stay CUDA-graph capturable after a warm-up.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _cabi
+
+_WORKSPACES: dict[tuple, torch.Tensor] = {}
+_STATUS: dict[torch.device, torch.Tensor] = {}
+
+
+def _workspace(device, nbytes: int, tag: str, zero_prefix: int = 0) -> torch.Tensor:
+    key = (str(device), tag, nbytes)
+    ws = _WORKSPACES.get(key)
+    if ws is None:
+        ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
+        if zero_prefix:
+            ws[:zero_prefix].zero_()
+        _WORKSPACES[key] = ws
+    return ws
+
+
+def status_word(device) -> torch.Tensor:
+    """Device int32 that kernels set non-zero when one of their bounded waits expired."""
+    device = torch.device(device)
+    st = _STATUS.get(device)
+    if st is None:
+        st = torch.zeros(1, dtype=torch.int32, device=device)
+        _STATUS[device] = st
+    return st
+
+
+def check_status(device) -> None:
+    """Synchronising check of the status word (tests and debugging only)."""
+    st = status_word(device)
+    v = int(st.item())
+    if v:
+        st.zero_()
+        raise RuntimeError(f"a device-side wait expired (status {v})")
+
+
+def fp4_gemm(act: torch.Tensor, act_sf: torch.Tensor, weight: torch.Tensor, weight_sf: torch.Tensor,
+             alpha: torch.Tensor | None, *, m: int, fmt: str = "nvfp4", layout: str = "plain",
+             out_dtype: torch.dtype = torch.bfloat16, out: torch.Tensor | None = None,
+             splits: int = 0, enable_pdl: bool = True) -> torch.Tensor:
+    """out[m, N] = alpha * act . weight^T with block-scaled FP4 operands.
+
+    act: uint8 codes, [M, K/2] (plain), [2M, K/2] (row_pair) or [M, K] (concat_k); weight uint8
+    [N, K/2] (row stride may exceed K/2); scale buffers 128x4-swizzled uint8 (E4M3 for nvfp4, E8M0
+    for mxfp4); alpha float32 device tensor with 1 (or, row_pair, 2) elements or None."""
+    lib = _cabi.load()
+    fmt_c = {"nvfp4": _cabi.FMT_NVFP4, "mxfp4": _cabi.FMT_MXFP4}[fmt]
+    lay_c = {"plain": _cabi.GEMM_PLAIN, "row_pair": _cabi.GEMM_ROW_PAIR, "concat_k": _cabi.GEMM_CONCAT_K}[layout]
+    n, kp = weight.shape
+    k = kp * 2
+    dev = weight.device
+    if weight.stride(1) != 1:
+        raise ValueError(f"weight must stay K-contiguous within a row; got stride {weight.stride()}")
+    if act.dim() != 2 or act.stride(1) != 1:
+        raise ValueError(f"activation must be compact rows; got stride {act.stride()}")
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype, device=dev)
+    with torch.cuda.device(dev):
+        if splits == 0:
+            splits = lib.ri_fp4_gemm_auto_splits(m, n, k, fmt_c, lay_c)
+            if splits < 1:
+                _cabi.check(_cabi.RI_ERR_ARG, "fp4_gemm plan")
+        ws = None
+        ws_bytes = 0
+        if splits > 1:
+            ws_bytes = lib.ri_fp4_gemm_workspace_bytes(m, n, k, fmt_c, lay_c, splits)
+            ws = _workspace(dev, ws_bytes, "gemm", zero_prefix=lib.ri_fp4_gemm_counter_bytes(m, n))
+        st = lib.ri_fp4_gemm(
+            act.data_ptr(), act.stride(0), act_sf.data_ptr(), act_sf.numel(),
+            weight.data_ptr(), weight.stride(0), weight_sf.data_ptr(), weight_sf.numel(),
+            _cabi.ptr(alpha), 0 if alpha is None else alpha.numel(),
+            out.data_ptr(), _cabi.torch_dtype_code(out.dtype, allow_f32=True), out.stride(0), m, n, k, fmt_c, lay_c,
+            splits, _cabi.ptr(ws), ws_bytes, status_word(dev).data_ptr(), int(enable_pdl),
+            _cabi.current_stream(dev))
+    _cabi.check(st, "fp4_gemm")
+    return out
+
+
+def resattn_decode(q: torch.Tensor, k_data: torch.Tensor, k_sf: torch.Tensor, v_data: torch.Tensor,
+                   v_sf: torch.Tensor, block_tables: torch.Tensor, seq_lens: torch.Tensor,
+                   score_scale: float, out_scale: float, out: torch.Tensor, *, splits: int = 1,
+                   q_residue: bool = True, q_pack: torch.Tensor | None = None,
+                   q_sf: torch.Tensor | None = None) -> torch.Tensor:
+    """Paged NVFP4-KV decode attention.  q bf16 [B,Hq,D]; k_data/v_data uint8 [pages,Hkv,page,D/2];
+    k_sf/v_sf uint8 (or float8_e4m3fn) [pages,Hkv,page,D/16]; out bf16 [B,Hq,D] (written)."""
+    lib = _cabi.load()
+    b, hq, d = q.shape
+    pages, hkv, page, _ = k_data.shape
+    dev = q.device
+    with torch.cuda.device(dev):
+        ws = None
+        ws_bytes = 0
+        if splits > 1:
+            ws_bytes = lib.ri_resattn_workspace_bytes(b, hq, d, splits)
+            ws = _workspace(dev, ws_bytes, "attn")
+        st = lib.ri_resattn_decode(
+            q.data_ptr(), k_data.data_ptr(), k_sf.data_ptr(), v_data.data_ptr(), v_sf.data_ptr(), pages,
+            block_tables.data_ptr(), block_tables.stride(0), seq_lens.data_ptr(), b, hq, hkv, d, page,
+            float(score_scale), float(out_scale), out.data_ptr(),
+            _cabi.torch_dtype_code(out.dtype, allow_f32=True), _cabi.ptr(q_pack), 0 if q_pack is None else q_pack.numel(),
+            _cabi.ptr(q_sf), 0 if q_sf is None else q_sf.numel(),
+            splits, _cabi.ptr(ws), ws_bytes, int(q_residue), status_word(dev).data_ptr(),
+            _cabi.current_stream(dev))
+    _cabi.check(st, "resattn_decode")
+    return out
+
+
+def rcp_approx(x: torch.Tensor) -> torch.Tensor:
+    """rcp.approx.ftz.f32 of a float32 CUDA tensor (test helper)."""
+    lib = _cabi.load()
+    x = x.contiguous()
+    y = torch.empty_like(x)
+    with torch.cuda.device(x.device):
+        _cabi.check(lib.ri_rcp_approx(x.data_ptr(), y.data_ptr(), x.numel(), _cabi.current_stream(x.device)),
+                    "rcp_approx")
+    return y
