@@ -1,0 +1,444 @@
+#!/usr/bin/env python
+"""Benchmark of the MEXT hot path (online NVFP4 quantiser + folded FP4 GEMM) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (N = 1): the NVFP4 MEXT sweep over the four Qwen3-32B-shaped projections
+(K->N: qkv 5120->10240, o 8192->5120, gate_up 5120->51200, down 25600->5120) and tokens
+M in {1,2,4,8,16,32,64,128}.  One *step* is one pass over all 32 (shape, M) cases; each case is
+two kernels of this library (quantiser, GEMM).  The step is captured in a CUDA graph (the
+reference measures under CUDA graphs as well) and timed with CUDA events on the launching
+stream.  Successive cases stream different weights (274 MB per pass over the four shapes, more
+than the 126 MB L2), so every weight read comes from HBM.
+
+Printed JSON (one line, rank 0):
+  value / ms_per_step   mean microseconds per linear op over the sweep (lower is better)
+  roofline              the GEMM kernel: algorithmic bytes per launch / mean launch time, against the
+                        measured HBM copy bandwidth (MEASURED_PEAKS.json)
+  e2e                   the same sweep through the public op ``residue::nvfp4_linear`` with pinned host
+                        buffers: H2D of x and D2H of y inside the timed region
+  cpu_baseline          the reference's torch-eager quantise/dequantise/matmul path on the host cores
+                        for a bounded sample (N = 1 only)
+  detail                per-case microseconds, TFLOP/s, fraction of roofline; ResAttn decode numbers
+
+N > 1 (torchrun): tensor parallel on one node.  qkv / gate_up are column-parallel (N/tp per rank),
+o / down row-parallel (K/tp per rank) followed by an NCCL all-reduce of the BF16 output; time is the
+maximum over ranks.  ``--impl reference`` times the CPU restatement of the reference's eager path.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SHAPES = [("qkv", 5120, 10240, "col"), ("o", 8192, 5120, "row"), ("gate_up", 5120, 51200, "col"),
+          ("down", 25600, 5120, "row")]
+MS = [1, 2, 4, 8, 16, 32, 64, 128]
+L2_BYTES = 126 * 1024 * 1024
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.samples, self._stop, self._t = index, [], threading.Event(), None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                      "-i", str(self.index)], capture_output=True, text=True, timeout=5).stdout
+                parts = [p.strip() for p in out.strip().split(",")]
+                if len(parts) >= 6:
+                    self.samples.append(parts)
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._t = threading.Thread(target=self._run, daemon=True)
+        self._t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._t.join(timeout=6)
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        sm = [float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit()]
+        mx = [float(s[1]) for s in self.samples if s[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+# ------------------------------------------------------------------------------------------------
+# algorithmic work
+# ------------------------------------------------------------------------------------------------
+def mext_bytes(m, k, n):
+    """x (bf16) + W codes and block scales + y (bf16): the bytes a fused MEXT linear must move."""
+    return 2 * m * k + n * k * (0.5 + 1.0 / 16.0) + 2 * m * n
+
+
+def gemm_bytes(m, k, n):
+    """GEMM kernel alone: activation codes+scales (base and residue), W codes+scales, y."""
+    return 2 * m * k * (0.5 + 1.0 / 16.0) + n * k * (0.5 + 1.0 / 16.0) + 2 * m * n
+
+
+def mext_flops(m, k, n):
+    return 2.0 * m * n * (2 * k)
+
+
+# ------------------------------------------------------------------------------------------------
+# reference arm / CPU baseline: the torch-eager path on host cores
+# ------------------------------------------------------------------------------------------------
+def cpu_eager_sample(repeats: int = 3, shape=("qkv", 5120, 10240), m: int = 16):
+    """Times the eager quantise/dequantise/matmul path (oracle port of the reference's
+    ResidueQuantLinear._forward_residue_qdq) for one case on all host threads."""
+    import torch
+    import oracle
+    cores = len(os.sched_getaffinity(0))
+    torch.set_num_threads(cores)
+    name, k, n = shape
+    x = torch.from_numpy(oracle.make_activation(m, k, seed=0)).to(torch.bfloat16)
+    w = torch.from_numpy(oracle.make_weight(n, k, seed=1)).to(torch.bfloat16)
+    oracle.eager_residue_linear(x, w)                      # warm-up
+    ts = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        oracle.eager_residue_linear(x, w)
+        ts.append((time.perf_counter() - t0) * 1e6)
+    return {"value": statistics.median(ts), "unit": "us", "cores": cores, "kind": "port",
+            "sample": f"1 of 32 sweep cases: {name} {k}->{n}, M={m}, ratio 1.0, median of {repeats} runs"}
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    ts = []
+    for _ in range(max(1, args.warmup)):
+        cpu_eager_sample(repeats=1)
+    for _ in range(args.steps):
+        ts.append(cpu_eager_sample(repeats=1)["value"])
+    base = cpu_eager_sample(repeats=1)
+    v = statistics.mean(ts)
+    line = {
+        "impl": "reference", "metric": "mext_nvfp4_linear_latency", "value": v, "unit": "us", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": v / 1e3, "higher_is_better": False,
+        "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4 (E2M1 x E4M3 block scales), fp32 accumulate",
+        "data": "synthetic", "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": v, "unit": "us", "cores": base["cores"], "kind": "port", "sample": base["sample"]},
+        "e2e": {"value": v, "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus):
+    return {"workload": "MEXT NVFP4 sweep: qkv 5120->10240, o 8192->5120, gate_up 5120->51200, down 25600->5120; "
+                        "M in {1,2,4,8,16,32,64,128}; online quantiser + folded GEMM per case",
+            "l2": "inputs larger than L2: 274 MB of weights stream per pass over the four shapes, rotating copies",
+            "parallelism": "tp%d" % n_gpus if n_gpus > 1 else "single GPU", "cuda_graph": True}
+
+
+# ------------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------------
+class Layer:
+    """One projection on one rank: prequantised weight copies + activation buffers."""
+
+    def __init__(self, name, k, n, par, tp, rank, dev, copies_bytes=2 * L2_BYTES):
+        import torch
+        from resinfer_b200.quant import weight_prep
+        self.name, self.par = name, par
+        self.k_full, self.n_full = k, n
+        self.k = k // tp if par == "row" else k
+        self.n = n // tp if par == "col" else n
+        g = torch.Generator(device=dev).manual_seed(1 + rank)
+        w = (torch.randn(self.n, self.k, generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+        prep = weight_prep.quantize_weight_nvfp4(w)
+        del w
+        wbytes = prep["weight"].numel() + prep["weight_scale"].numel()
+        self.copies = max(1, min(8, -(-copies_bytes // wbytes)))
+        self.w = [prep["weight"].clone() for _ in range(self.copies)]
+        self.w_sf = [prep["weight_scale"].clone() for _ in range(self.copies)]
+        self.w_gs = prep["weight_global_scale"]
+        self.x, self.gs_inv, self.alpha = {}, {}, {}
+        for m in MS:
+            gx = torch.Generator(device=dev).manual_seed(0)
+            x = torch.randn(m, k, generator=gx, device=dev, dtype=torch.float32)
+            out_ch = torch.randperm(k, generator=gx, device=dev)[: max(1, k // 100)]
+            x[:, out_ch] *= 20.0
+            x = x.to(torch.bfloat16)
+            gs = float(x.float().abs().max()) / (6.0 * 448.0)
+            if par == "row":
+                x = x[:, rank * self.k:(rank + 1) * self.k].contiguous()
+            self.x[m] = x
+            self.gs_inv[m] = torch.tensor([1.0 / gs], dtype=torch.float32, device=dev)
+            self.alpha[m] = (self.w_gs * gs).float().reshape(1)
+        self.use = 0
+
+    def next_copy(self):
+        c = self.use % self.copies
+        self.use += 1
+        return c
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-detail", action="store_true", help="skip the per-case and ResAttn detail measurements")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        return run_reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (B200); there is no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    tp = world
+
+    from resinfer_b200 import nvfp4, ops
+    from resinfer_b200.quant.vllm_integration import residue_linear_op  # noqa: F401
+    nvfp4.ensure_loaded()
+
+    layers = [Layer(nm, k, n, par, tp, rank, dev) for nm, k, n, par in SHAPES]
+    outs = {(L.name, m): torch.empty(m, L.n, dtype=torch.bfloat16, device=dev) for L in layers for m in MS}
+    launches = {"n": 0}
+
+    def run_case(L, m, quant=True, pre=None):
+        c = L.next_copy()
+        if quant:
+            codes, sf = nvfp4.scaled_fp4_quant_mext_r1(L.x[m], L.gs_inv[m], layout_mode=1, enable_pdl=True)
+            launches["n"] += 1
+        else:
+            codes, sf = pre
+        y = ops.fp4_gemm(codes, sf, L.w[c], L.w_sf[c], L.alpha[m], m=m, fmt="nvfp4", layout="row_pair",
+                         out=outs[(L.name, m)])
+        launches["n"] += 1
+        if tp > 1 and L.par == "row":
+            dist.all_reduce(y)
+        return y
+
+    def sweep(quant=True, pre=None):
+        for m in MS:
+            for L in layers:
+                run_case(L, m, quant, None if pre is None else pre[(L.name, m)])
+
+    def capture(fn):
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            fn()                                           # warm-up: workspaces, attributes
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        try:
+            with torch.cuda.graph(g):
+                fn()
+            return g.replay
+        except Exception as e:                             # e.g. a collective that cannot be captured
+            if rank == 0:
+                print(f"[bench] CUDA graph capture failed ({type(e).__name__}: {e}); timing eagerly", file=sys.stderr)
+            torch.cuda.synchronize()
+            return fn
+
+    def timed(replay, steps, warmup):
+        for _ in range(warmup):
+            replay()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            replay()
+        e1.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        ms = e0.elapsed_time(e1) / steps
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    n_cases = len(MS) * len(layers)
+    # ---- headline: quantiser + GEMM over the sweep
+    launches["n"] = 0
+    replay = capture(lambda: sweep(True))
+    per_step_launches = launches["n"] // 2                  # warm-up + capture both counted
+    with ClockSampler(local) as clk:
+        ms_step = timed(replay, args.steps, args.warmup)
+    ops.check_status(dev)
+    us_per_op = ms_step * 1e3 / n_cases
+
+    # ---- GEMM kernel alone (pre-quantised activations) for the roofline of the dominant kernel
+    pre = {(L.name, m): nvfp4.scaled_fp4_quant_mext_r1(L.x[m], L.gs_inv[m], layout_mode=1) for L in layers for m in MS}
+    replay_g = capture(lambda: sweep(False, pre)) if tp == 1 else None
+    hbm_gbs, peak_kind = load_peaks()
+    roofline = None
+    if replay_g is not None:
+        ms_gemm = timed(replay_g, args.steps, args.warmup)
+        gbytes = sum(gemm_bytes(m, L.k, L.n) for L in layers for m in MS) / n_cases
+        achieved = gbytes / (ms_gemm * 1e-3 / n_cases) / 1e9
+        roofline = {"kernel": "fp4_gemm_kernel (tcgen05 block-scaled, 32 launches per step)", "bound": "hbm",
+                    "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs,
+                    "peak_source": peak_kind, "traffic": None,
+                    "us_per_launch": ms_gemm * 1e3 / n_cases, "algorithmic_bytes_per_launch": gbytes}
+
+    # ---- e2e through the public op with pinned host buffers
+    e2e = None
+    if tp == 1:
+        hx = {(L.name, m): L.x[m].cpu().pin_memory() for L in layers for m in MS}
+        hy = {(L.name, m): torch.empty(m, L.n, dtype=torch.bfloat16).pin_memory() for L in layers for m in MS}
+        zero_mask = torch.zeros(1, dtype=torch.uint8, device=dev)
+
+        def e2e_sweep():
+            for m in MS:
+                for L in layers:
+                    c = L.next_copy()
+                    xd = hx[(L.name, m)].to(dev, non_blocking=True)
+                    y = torch.ops.residue.nvfp4_linear(xd, L.w[c], L.gs_inv[m], L.w_sf[c], L.w_sf[c], zero_mask,
+                                                       L.alpha[m], L.k, 0, 0, L.n, True, False, True)
+                    hy[(L.name, m)].copy_(y, non_blocking=True)
+            torch.cuda.synchronize()
+
+        for _ in range(2):
+            e2e_sweep()
+        t0 = time.perf_counter()
+        reps = max(3, min(args.steps, 10))
+        for _ in range(reps):
+            e2e_sweep()
+        e2e_us = (time.perf_counter() - t0) / reps * 1e6 / n_cases
+        e2e = {"value": e2e_us, "unit": "us",
+               "h2d_bytes_per_step": sum(2 * m * L.k for L in layers for m in MS),
+               "d2h_bytes_per_step": sum(2 * m * L.n for L in layers for m in MS),
+               "note": "eager calls of residue::nvfp4_linear (no CUDA graph): includes Python and launch overhead"}
+
+    detail = None
+    if not args.no_detail and tp == 1:
+        detail = measure_detail(torch, dev, layers, outs, nvfp4, ops, capture, timed, hbm_gbs)
+
+    cpu = None
+    if rank == 0 and tp == 1:
+        try:
+            cpu = cpu_eager_sample()
+        except Exception as e:                              # the oracle is optional equipment
+            cpu = {"value": None, "unit": "us", "cores": len(os.sched_getaffinity(0)), "kind": "port",
+                   "sample": f"failed: {type(e).__name__}: {e}"}
+
+    if rank == 0:
+        flops = sum(mext_flops(m, L.k_full, L.n_full) for L in layers for m in MS)
+        line = {
+            "metric": "mext_nvfp4_linear_latency", "value": us_per_op, "unit": "us", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": False,
+            "scaling": "strong", "vs_baseline": None,
+            "dtype": "nvfp4 (E2M1 x E4M3 block scales), fp32 accumulate", "data": "synthetic",
+            "config": workload_config(world), "clocks": clk.summary(), "gpu_launches": per_step_launches * args.steps,
+            "tflops": flops / (ms_step * 1e-3) / 1e12,
+            "hbm_gbs_algorithmic": sum(mext_bytes(m, L.k_full, L.n_full) for L in layers for m in MS) / (ms_step * 1e-3) / 1e9,
+            "e2e": e2e, "roofline": roofline, "cpu_baseline": cpu, "detail": detail,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def measure_detail(torch, dev, layers, outs, nvfp4, ops, capture, timed, hbm_gbs):
+    """Per-case latency (cold weights: rotating copies larger than L2) and a ResAttn decode point."""
+    cases = []
+    for L in layers:
+        for m in MS:
+            def one(L=L, m=m):
+                for _ in range(L.copies):
+                    c = L.next_copy()
+                    codes, sf = nvfp4.scaled_fp4_quant_mext_r1(L.x[m], L.gs_inv[m], layout_mode=1, enable_pdl=True)
+                    ops.fp4_gemm(codes, sf, L.w[c], L.w_sf[c], L.alpha[m], m=m, fmt="nvfp4", layout="row_pair",
+                                 out=outs[(L.name, m)])
+            rp = capture(one)
+            us = timed(rp, 10, 3) * 1e3 / L.copies
+            t_bound = mext_bytes(m, L.k, L.n) / (hbm_gbs * 1e9) * 1e6
+            cases.append({"shape": L.name, "m": m, "us": round(us, 2), "tflops": round(mext_flops(m, L.k, L.n) / us / 1e6, 1),
+                          "gbs": round(mext_bytes(m, L.k, L.n) / us / 1e3, 0), "frac_hbm_roofline": round(t_bound / us, 3)})
+    attn = []
+    try:
+        attn = measure_resattn(torch, dev, ops, capture, timed, hbm_gbs)
+    except Exception as e:
+        attn = [{"error": f"{type(e).__name__}: {e}"}]
+    return {"mext_nvfp4_cases": cases, "resattn": attn}
+
+
+def measure_resattn(torch, dev, ops, capture, timed, hbm_gbs):
+    from resinfer_b200.nvfp4.cute_attn.plan import select_decode_plan
+    res = []
+    hq, hkv, page = 64, 8, 16
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    for d, batch in ((128, 8), (128, 64), (256, 32)):
+        g = torch.Generator(device=dev).manual_seed(3)
+        lens = torch.randint(1024, 32769, (batch,), generator=g, device=dev, dtype=torch.int32)
+        pages_per = (lens + page - 1) // page
+        total = int(pages_per.sum())
+        pool = int(total * 1.1) + 1
+        perm = torch.randperm(pool, generator=g, device=dev)[:total].to(torch.int32)
+        bt = torch.zeros(batch, int(pages_per.max()), dtype=torch.int32, device=dev)
+        off = 0
+        for b in range(batch):
+            n = int(pages_per[b])
+            bt[b, :n] = perm[off:off + n]
+            off += n
+        kd = torch.randint(0, 256, (pool, hkv, page, d // 2), generator=g, device=dev, dtype=torch.uint8)
+        vd = torch.randint(0, 256, (pool, hkv, page, d // 2), generator=g, device=dev, dtype=torch.uint8)
+        ks = torch.randint(0x28, 0x48, (pool, hkv, page, d // 16), generator=g, device=dev, dtype=torch.uint8)
+        vs = torch.randint(0x28, 0x48, (pool, hkv, page, d // 16), generator=g, device=dev, dtype=torch.uint8)
+        q = torch.randn(batch, hq, d, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+        out = torch.empty(batch, hq, d, dtype=torch.bfloat16, device=dev)
+        splits, _ = select_decode_plan(batch, hkv, int(lens.max()), sms, head_dim=d)
+        rp = capture(lambda: ops.resattn_decode(q, kd, ks, vd, vs, bt, lens, d ** -0.5, 1.0, out, splits=splits))
+        us = timed(rp, 10, 3) * 1e3
+        tokens = int(lens.sum())
+        nbytes = tokens * hkv * d * 2 * (0.5 + 1 / 16) + 4 * batch * hq * d + 4 * total
+        res.append({"head_dim": d, "batch": batch, "page": page, "tokens": tokens, "splits": splits, "us": round(us, 1),
+                    "tbs": round(nbytes / us / 1e6, 3), "frac_hbm": round(nbytes / us / 1e3 / hbm_gbs, 3),
+                    "kv_bytes_gt_l2": bool(nbytes > L2_BYTES)})
+        del kd, vd, ks, vs
+    return res
+
+
+if __name__ == "__main__":
+    main()

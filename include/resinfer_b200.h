@@ -45,6 +45,7 @@ extern "C" {
 #define RI_MEXT_TILE8 2
 #define RI_MEXT_CONCAT_K 3
 #define RI_MEXT_ATTN_TILE8 4
+#define RI_MEXT_BASE_ONLY 5 /* this library's addition: base codes [M, K/2] only, no residue */
 
 /* activation layouts the GEMM accepts */
 #define RI_GEMM_PLAIN 0    /* act [M, K/2]: y = act . W^T (KEXT: K = K_base + S)            */

@@ -61,7 +61,10 @@ __global__ void __launch_bounds__(256) nvfp4_mext_kernel(const T* __restrict__ x
       for (int i = 0; i < 16; ++i) v[i] = 0.f;
     }
     BlockQ q = quant_mext16(v, gs, gs_res);
-    if (layout == 3) {   // concat_k: [M, 2K] elements, scales over Ktot = 2K
+    if (layout == 5) {   // base codes only (plain NVFP4 activation quantisation)
+      *reinterpret_cast<uint2*>(codes + int64_t(row) * (k / 2) + blk * 8) = q.base;
+      sf[sf_offset<16>(row, blk, k)] = q.sf;
+    } else if (layout == 3) {   // concat_k: [M, 2K] elements, scales over Ktot = 2K
       uint8_t* rowp = codes + int64_t(row) * k;
       *reinterpret_cast<uint2*>(rowp + blk * 8) = q.base;
       *reinterpret_cast<uint2*>(rowp + k / 2 + blk * 8) = q.res;
@@ -232,13 +235,13 @@ extern "C" int ri_nvfp4_quant_mext(const void* x, int dtype, int m, int k, int64
                                    void* stream) {
   RI_CHECK_ARG(dtype == RI_DTYPE_BF16 || dtype == RI_DTYPE_FP16, "Unsupported input data type for quantize_to_fp4.");
   RI_CHECK_ARG(m >= 0 && k > 0 && k % 16 == 0, "The N dimension must be multiple of 16.");
-  RI_CHECK_ARG(layout >= 0 && layout <= 4, "unknown MEXT layout mode %d", layout);
+  RI_CHECK_ARG(layout >= 0 && layout <= 5, "unknown MEXT layout mode %d", layout);
   RI_CHECK_ARG(n_gs >= 1 && n_gs <= 2, "input_sf must have 1 (single-alpha) or 2 (dual-alpha: [base, residue]) elements.");
   RI_CHECK_ARG(row_stride >= k && (row_stride * 2) % 16 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0,
                "input rows must be 16-byte aligned");
   const bool tile8 = layout == RI_MEXT_TILE8 || layout == RI_MEXT_ATTN_TILE8;
   const int64_t out_m = tile8 ? (int64_t(m) + 7) / 8 * 8 : m;
-  RI_CHECK_ARG(codes_bytes >= out_m * k,
+  RI_CHECK_ARG(codes_bytes >= (layout == RI_MEXT_BASE_ONLY ? out_m * k / 2 : out_m * k),
                "M-extension output tensor is too small for the derived output_m (caller buffer "
                "undersized for the padded row count).");
   int64_t m_tiles, k_tiles;
@@ -247,6 +250,9 @@ extern "C" int ri_nvfp4_quant_mext(const void* x, int dtype, int m, int k, int64
     k_tiles = (2 * int64_t(k) + 63) / 64;
   } else if (layout == RI_MEXT_ATTN_TILE8) {
     m_tiles = out_m / 8;
+    k_tiles = (int64_t(k) + 63) / 64;
+  } else if (layout == RI_MEXT_BASE_ONLY) {
+    m_tiles = (out_m + 127) / 128;
     k_tiles = (int64_t(k) + 63) / 64;
   } else {
     m_tiles = (2 * out_m + 127) / 128;

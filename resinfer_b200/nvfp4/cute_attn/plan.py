@@ -1,0 +1,79 @@
+"""Static launch selection for ResAttn decode: KV split count and reducer.
+
+Keeps the reference's selection interface and policy names (csrc/resattn/plan.py:21-93):
+``(splits, reducer)`` with reducer in {"none", "kernel", "cga_sharded", "gmem_fused"} and the
+RESIDUE_ATTN_REDUCTION policy {"legacy", "auto", "deterministic"}.  This library has one reducer -- the
+deterministic two-pass merge kernel -- so every plan whose split count is above one resolves to
+"kernel"; the cluster / fused reducers of the reference are accepted by ``validate_decode_plan`` for
+compatibility and executed as "kernel".  The split count itself is chosen for this library's kernel
+(four warps per CTA, several CTAs per SM): enough CTAs to cover the SMs a few times over while
+leaving every warp at least a few 16-token chunks.
+"""
+from __future__ import annotations
+
+import os
+
+_REDUCERS = ("none", "kernel", "cga_sharded", "gmem_fused")
+
+
+def _reduction_policy(value=None):
+    value = os.environ.get("RESIDUE_ATTN_REDUCTION", "legacy") if value is None else value
+    if value not in ("legacy", "auto", "deterministic"):
+        raise ValueError(f"unknown ResAttn reduction policy: {value}")
+    return value
+
+
+def _check_output_dimension(head_dim, output_nvfp4):
+    if head_dim not in (128, 256):
+        raise NotImplementedError("ResAttn supports head_dim=128 or 256")
+    if head_dim == 256 and output_nvfp4:
+        raise NotImplementedError("D256 supports BF16 output only")
+
+
+def _pow2_floor(v: int) -> int:
+    return 1 << (max(1, v).bit_length() - 1)
+
+
+def _select_splits(batch: int, heads: int, length: int, sms: int, ctas_per_sm: int = 3,
+                   min_chunks_per_warp: int = 4) -> int:
+    grid = max(1, batch * heads)
+    chunks = max(1, (length + 15) // 16)
+    want = _pow2_floor(max(1, (sms * ctas_per_sm) // grid))            # CTAs we can keep busy
+    cap = _pow2_floor(max(1, chunks // (4 * min_chunks_per_warp)))     # keep the warps fed
+    return max(1, min(want, cap, 64))
+
+
+def select_decode_plan(batch, num_kv_heads, max_kv_len, sm_count, *, output_nvfp4=False,
+                       grouped_head_tile=16, residue_fold=True, reduction_policy=None, head_dim=128):
+    """Select the static split/reducer, then apply the caller's reduction policy."""
+    _check_output_dimension(head_dim, output_nvfp4)
+    _reduction_policy(reduction_policy)
+    if not residue_fold or grouped_head_tile not in (8, 16):
+        raise NotImplementedError("production ResAttn requires residue Q8/Q16")
+    splits = _select_splits(batch, num_kv_heads, max_kv_len, sm_count)
+    return (1, "none") if splits == 1 else (splits, "kernel")
+
+
+def static_compile_plans(*, output_nvfp4=False, grouped_head_tile=16, residue_fold=True, head_dim=128):
+    """Enumerate decode kernel variants (nothing is compiled at run time here; kept for callers that
+    warm up one launch per plan)."""
+    if not residue_fold or grouped_head_tile not in (8, 16):
+        raise NotImplementedError("production ResAttn requires residue Q8/Q16")
+    _check_output_dimension(head_dim, output_nvfp4)
+    return ((1, "none"), (2, "kernel"), (4, "kernel"))
+
+
+def validate_decode_plan(plan, *, output_nvfp4=False, head_dim=128):
+    """Check launch constraints before workspace allocation."""
+    _check_output_dimension(head_dim, output_nvfp4)
+    splits, reducer = plan
+    if type(splits) is not int or splits < 1:
+        raise ValueError(f"decode plan splits must be a positive integer, got {splits!r}")
+    if reducer not in _REDUCERS:
+        raise ValueError(f"unsupported decode reducer: {reducer!r}")
+    if head_dim == 256 and reducer not in ("none", "kernel"):
+        raise NotImplementedError("D256 supports none/kernel reduction only")
+    if reducer == "none" and splits != 1:
+        raise ValueError("none reduction requires splits=1")
+    if splits > 256:
+        raise ValueError("at most 256 KV splits are supported")

@@ -1,0 +1,163 @@
+"""GPU parity of ResAttn decode against the CPU oracle (exact attention over the dequantised NVFP4 KV
+cache with the NVFP4 + residue query).  The reference kernel itself cannot be built on this toolchain,
+so this parity is a tolerance, not a bit-exact pin: FP32 output within 1e-3 relative Frobenius error (P is
+rounded to FP16 before the PV product), BF16 output within BF16 rounding."""
+import numpy as np
+import pytest
+import torch
+
+import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+TOL_F32 = 1e-3
+TOL_BF16 = 3e-3
+
+
+def rel_fro(a, b):
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30))
+
+
+def _run(dev, kv, q_np, sm, splits, out_dtype=torch.float32, q_residue=True, want_q=False):
+    from resinfer_b200 import ops
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    b, hq, d = q_np.shape
+    hkv = kv["k_data"].shape[1]
+    out = torch.zeros(b, hq, d, dtype=out_dtype, device=dev)
+    qp = qs = None
+    if want_q:
+        p = 8 if hq // hkv == 4 else 16
+        qp = torch.zeros(b, hkv, p, d // 2, dtype=torch.uint8, device=dev)
+        qs = torch.zeros(b * hkv * 128 * d // 16, dtype=torch.uint8, device=dev)
+    ops.resattn_decode(t(q_np).to(torch.bfloat16), t(kv["k_data"]), t(kv["k_sf"]), t(kv["v_data"]), t(kv["v_sf"]),
+                       t(np.maximum(kv["block_tables"], 0)), t(kv["seq_lens"]), sm * kv["k_global_scale"],
+                       kv["v_global_scale"], out, splits=splits, q_residue=q_residue, q_pack=qp, q_sf=qs)
+    torch.cuda.synchronize()
+    ops.check_status(dev)
+    return out, qp, qs
+
+
+@pytest.mark.parametrize("d,page,lens,hkv,g,splits", [
+    (128, 16, [100, 777], 2, 8, 1), (128, 16, [1, 16, 17, 3000], 2, 8, 4), (128, 128, [500, 129], 1, 8, 2),
+    (256, 16, [300, 64], 2, 8, 1), (128, 16, [333], 2, 4, 3), (256, 32, [1000], 1, 6, 5),
+    (128, 64, [2049, 5], 8, 8, 8), (128, 16, [0, 50], 1, 8, 2)])
+def test_decode_matches_oracle(cuda_device, device_rcp, d, page, lens, hkv, g, splits):
+    kv = O.make_paged_kv(lens, hkv, d, page, seed=d + page)
+    b, hq = len(lens), hkv * g
+    q_np = O.bf16_round(np.random.default_rng(9).standard_normal((b, hq, d)).astype(np.float32))
+    sm = d ** -0.5
+    ref = O.resattn_decode_reference(q_np, kv, sm, rcp=O.RecordingRcp(device_rcp))
+    ref32 = ref                                              # oracle output is BF16-rounded
+    out32, qp, qs = _run(cuda_device, kv, q_np, sm, splits, want_q=True)
+    got = out32.cpu().numpy()
+    assert not np.isnan(got).any()
+    assert rel_fro(got, ref32) < TOL_BF16                     # vs the BF16-rounded oracle
+    out16, _, _ = _run(cuda_device, kv, q_np, sm, splits, out_dtype=torch.bfloat16)
+    assert torch.equal(out16, out32.to(torch.bfloat16))
+    # the fused query quantiser is bit-identical to the grouped-Q quantiser
+    op, osf = O.nvfp4_quant_grouped_q(q_np.reshape(b, hkv, g, d), rcp=O.RecordingRcp(device_rcp))
+    assert np.array_equal(qp.cpu().numpy(), op) and np.array_equal(qs.cpu().numpy(), osf)
+    for i, L in enumerate(lens):
+        if L == 0:
+            assert not got[i].any()                           # empty sequence -> zeros
+
+
+def test_decode_unrounded_accuracy_and_residue_effect(cuda_device, device_rcp):
+    """FP32 output against a float64 oracle without output rounding; dropping the query residue moves
+    the result measurably away (the compensation is real), and split counts agree with each other."""
+    d, page, hkv, g = 128, 16, 2, 8
+    lens = [4097, 900]
+    kv = O.make_paged_kv(lens, hkv, d, page, seed=5)
+    q_np = O.bf16_round(np.random.default_rng(2).standard_normal((2, hkv * g, d)).astype(np.float32))
+    sm = d ** -0.5
+    # unrounded oracle: recompute in float64 from the oracle's pieces
+    qpk, qsf = O.nvfp4_quant_grouped_q(q_np.reshape(2, hkv, g, d), rcp=O.RecordingRcp(device_rcp))
+    qb, qr = O.dequant_grouped_q(qpk, qsf, g)
+    kd, vd = O.dequant_paged(kv["k_data"], kv["k_sf"]), O.dequant_paged(kv["v_data"], kv["v_sf"])
+    exact = np.zeros((2, hkv * g, d))
+    plain = np.zeros_like(exact)
+    for i, L in enumerate(lens):
+        n = (L + page - 1) // page
+        pages = kv["block_tables"][i, :n]
+        k = kd[pages].transpose(1, 0, 2, 3).reshape(hkv, n * page, d)[:, :L].astype(np.float64)
+        v = vd[pages].transpose(1, 0, 2, 3).reshape(hkv, n * page, d)[:, :L].astype(np.float64)
+        for qq, dst in (((qb[i] + qr[i]).astype(np.float64), exact), (qb[i].astype(np.float64), plain)):
+            s = np.einsum("hgd,htd->hgt", qq, k) * sm * kv["k_global_scale"]
+            p = np.exp(s - s.max(-1, keepdims=True))
+            dst[i] = (np.einsum("hgt,htd->hgd", p, v) / p.sum(-1, keepdims=True) * kv["v_global_scale"]).reshape(-1, d)
+    o1, _, _ = _run(cuda_device, kv, q_np, sm, 1)
+    o8, _, _ = _run(cuda_device, kv, q_np, sm, 8)
+    assert rel_fro(o1.cpu().numpy(), exact) < TOL_F32
+    assert rel_fro(o8.cpu().numpy(), exact) < TOL_F32
+    assert rel_fro(o8.cpu().numpy(), o1.cpu().numpy()) < TOL_F32
+    nores, _, _ = _run(cuda_device, kv, q_np, sm, 1, q_residue=False)
+    assert rel_fro(nores.cpu().numpy(), plain) < TOL_F32
+    assert rel_fro(nores.cpu().numpy(), exact) > 5 * rel_fro(o1.cpu().numpy(), exact)
+
+
+def test_reference_named_host_entry(cuda_device):
+    from resinfer_b200.nvfp4.cute_attn.host import (allocate_qmul4_reduction_workspace, plan_qmul4_decode,
+                                                     run_paged_fp4_decode_qmul4_tmem)
+    from resinfer_b200.nvfp4.cute_attn.kv_layout import NvFp4PagedKVPool
+    d, page, hkv, g = 128, 128, 2, 8
+    lens = [700, 1300, 128]
+    kv = O.make_paged_kv(lens, hkv, d, page, seed=11)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(cuda_device)
+    q_np = O.bf16_round(np.random.default_rng(3).standard_normal((3, hkv * g, d)).astype(np.float32))
+    pool = NvFp4PagedKVPool(hkv, d, t(kv["k_data"]), t(kv["v_data"]), t(kv["k_sf"]), t(kv["v_sf"]), page_size=page,
+                            k_global_scale=kv["k_global_scale"], v_global_scale=kv["v_global_scale"])
+    q = t(q_np).to(torch.bfloat16)
+    out = torch.empty(3, hkv * g, d, dtype=torch.bfloat16, device=cuda_device)
+    bt, sl = t(np.maximum(kv["block_tables"], 0)), t(kv["seq_lens"])
+    plan = plan_qmul4_decode(3, hkv, 1300, cuda_device, head_dim=d)
+    ws = allocate_qmul4_reduction_workspace(4, 3, hkv * g, d, cuda_device)
+    for pl, w in ((None, None), (plan, None), ((4, "kernel"), ws), ((1, "none"), None)):
+        out.zero_()
+        run_paged_fp4_decode_qmul4_tmem(q, pool, pool.v_data, pool.v_sf, bt, sl, d ** -0.5 * pool.k_global_scale, out,
+                                        value_scale=pool.v_global_scale, plan=pl, reduction_workspace=w)
+        ref = O.resattn_decode_reference(q_np, kv, d ** -0.5)
+        assert rel_fro(out.float().cpu().numpy(), ref) < TOL_BF16
+    with pytest.raises(ValueError, match="seq_lens"):
+        run_paged_fp4_decode_qmul4_tmem(q, pool, pool.v_data, pool.v_sf, bt, sl.long(), 0.1, out)
+    with pytest.raises(ValueError, match="v_data_hnd"):
+        run_paged_fp4_decode_qmul4_tmem(q, pool, pool.v_data[:, :1], pool.v_sf, bt, sl, 0.1, out)
+    with pytest.raises(NotImplementedError):
+        run_paged_fp4_decode_qmul4_tmem(q, pool, pool.v_data, pool.v_sf, bt, sl, 0.1, out, residue_fold=False)
+    with pytest.raises(ValueError, match="BF16"):
+        run_paged_fp4_decode_qmul4_tmem(q, pool, pool.v_data, pool.v_sf, bt, sl, 0.1, out.float())
+
+
+def test_decode_at_baseline_shape(cuda_device):
+    """BASELINE shape (64 query heads, 8 KV heads, page 16, contexts up to 32768) with random KV bytes:
+    properties only -- finite output, split invariance, and permuting the page pool together with the
+    block table leaves the result unchanged."""
+    from resinfer_b200 import ops
+    b, hq, hkv, d, page = 4, 64, 8, 128, 16
+    g = torch.Generator(device=cuda_device).manual_seed(0)
+    lens = torch.tensor([32768, 1024, 20000, 9999], dtype=torch.int32, device=cuda_device)
+    per = (lens + page - 1) // page
+    pool = int(per.sum()) + 7
+    perm = torch.randperm(pool, generator=g, device=cuda_device).to(torch.int32)
+    bt = torch.zeros(b, int(per.max()), dtype=torch.int32, device=cuda_device)
+    off = 0
+    for i in range(b):
+        bt[i, :int(per[i])] = perm[off:off + int(per[i])]
+        off += int(per[i])
+    rnd = lambda *s, lo=0, hi=256: torch.randint(lo, hi, s, generator=g, device=cuda_device, dtype=torch.uint8)
+    kd, vd = rnd(pool, hkv, page, d // 2), rnd(pool, hkv, page, d // 2)
+    ks, vs = rnd(pool, hkv, page, d // 16, lo=0x30, hi=0x40), rnd(pool, hkv, page, d // 16, lo=0x30, hi=0x40)
+    q = torch.randn(b, hq, d, generator=g, device=cuda_device).to(torch.bfloat16)
+    run = lambda kd_, ks_, vd_, vs_, bt_, s: ops.resattn_decode(
+        q, kd_, ks_, vd_, vs_, bt_, lens, d ** -0.5, 1.0, torch.empty(b, hq, d, dtype=torch.float32, device=cuda_device),
+        splits=s)
+    o1, o16 = run(kd, ks, vd, vs, bt, 1), run(kd, ks, vd, vs, bt, 16)
+    assert torch.isfinite(o1).all()
+    assert rel_fro(o16.cpu().numpy(), o1.cpu().numpy()) < TOL_F32
+    shuffle = torch.randperm(pool, generator=g, device=cuda_device)
+    inv = torch.empty_like(shuffle)
+    inv[shuffle] = torch.arange(pool, device=cuda_device)
+    o_perm = run(kd[shuffle], ks[shuffle], vd[shuffle], vs[shuffle], inv[bt.long()].to(torch.int32), 16)
+    assert torch.equal(o_perm, o16)
+    torch.cuda.synchronize()
+    ops.check_status(cuda_device)
