@@ -107,9 +107,13 @@ int ri_mxfp4_quant(const void* x, int dtype, int m, int k, int64_t row_stride, i
  * scales 128x4-swizzled.  `layout` is one of RI_GEMM_*; K is the weight's K in elements
  * (multiple of 64 for NVFP4, 128 for MXFP4, 256 for RI_GEMM_CONCAT_K).  alpha: device float[n_alpha] (n_alpha == 2, RI_GEMM_ROW_PAIR only:
  * separate factor for the residue term); NULL = 1.0 (MXFP4 has none).
- * splits: K partitions per output tile (0 = choose); splits > 1 needs `workspace` of
- * ri_fp4_gemm_workspace_bytes() bytes, whose first ri_fp4_gemm_counter_bytes() bytes must be zero
- * before the first use (the kernel leaves them zero).  out: bf16 or fp16 (or RI_DTYPE_F32) [M, out_row_stride].
+ * The kernel is persistent (one CTA per SM) and cuts the list of (output tile, K tile) units into
+ * equal contiguous ranges ("stream-K").  splits: 1 = cut at output-tile boundaries only (no K split,
+ * no workspace); 0 = choose; s > 1 = min(tiles * s, SMs) CTAs.  Any plan that splits K needs `workspace`
+ * of ri_fp4_gemm_workspace_bytes() bytes (FP32 partials + one ticket per tile), whose first
+ * ri_fp4_gemm_counter_bytes() bytes must be zero before the first use (the kernel leaves them zero);
+ * the parts of a tile are added in a fixed order, so results are deterministic.
+ * out: bf16 or fp16 (or RI_DTYPE_F32) [M, out_row_stride].
  * status: optional device word, set non-zero if a bounded wait inside the kernel expired.
  * Replaces mext_fold_gemm / kext_kloop_gemm_sm100 (csrc/common/fold/sm10x/host.py:190-334), the
  * MXFP4 gemm / fold_gemm (csrc/mxfp4/dense.py:35-66) and the flashinfer.mm_fp4 call of the KEXT
@@ -122,8 +126,13 @@ int ri_fp4_gemm(const uint8_t* act, int64_t act_row_bytes, const uint8_t* act_sf
                 void* stream);
 int64_t ri_fp4_gemm_workspace_bytes(int m, int n, int k, int fmt, int layout, int splits);
 int64_t ri_fp4_gemm_counter_bytes(int m, int n);
-/* The split count ri_fp4_gemm would choose for splits == 0 on the current device. */
+/* 1 if the plan ri_fp4_gemm chooses for splits == 0 on the current device does not split K
+ * (no workspace needed), a value > 1 otherwise. */
 int ri_fp4_gemm_auto_splits(int m, int n, int k, int fmt, int layout);
+
+/* Debugging aid: when set to a device buffer of 8 * (number of SMs) int64, every CTA of the next
+ * ri_fp4_gemm launches stores nanosecond time stamps of its phases there (NULL switches it off). */
+void ri_fp4_gemm_set_trace(int64_t* device_buffer);
 
 /* ResAttn: residue-compensated paged NVFP4-KV decode attention, one query token per sequence.
  * q [B,Hq,D] bf16; k_data/v_data [pages,Hkv,page_size,D/2]; k_sf/v_sf [pages,Hkv,page_size,D/16]

@@ -245,10 +245,10 @@ __device__ __forceinline__ BlockQ quant_mext16(const float (&x)[16], float gs, f
 
 
 // ------------------------------------------------------------------------------------------
-// mbarrier / bulk-copy helpers.  Every wait is bounded: it gives up after kWaitLimitNs (or as
+// mbarrier / bulk-copy helpers.  Every wait is bounded: it gives up after kWaitLimitCycles (or as
 // soon as another role of the CTA has given up) and reports that to the caller.
 // ------------------------------------------------------------------------------------------
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // 2 s
+constexpr long long kWaitLimitCycles = 4000000000ll;   // about 2 s at 2 GHz
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -266,24 +266,21 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
                : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ unsigned long long global_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-// Bounded wait.  Returns false when another role aborted or the time limit expired (then sets
-// the abort flag itself).
+// Bounded wait.  Returns false when another role aborted or the cycle limit expired (then sets
+// the abort flag itself).  The fast path is a plain try_wait loop; the SM cycle counter and the
+// abort flag are only looked at every 4096 failed polls.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try(bar, parity)) return true;
-  const unsigned long long t0 = global_ns();
-  for (;;) {
-#pragma unroll 1
-    for (int i = 0; i < 64; ++i)
-      if (mbar_try(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (global_ns() - t0 > kWaitLimitNs) {
-      *abort_flag = 1;
-      return false;
+  long long t0 = 0;
+  for (uint32_t spin = 1;; ++spin) {
+    if (mbar_try(bar, parity)) return true;
+    if ((spin & 4095u) == 0) {
+      if (*abort_flag) return false;
+      const long long now = clock64();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kWaitLimitCycles) {
+        *abort_flag = 1;
+        return false;
+      }
     }
   }
 }

@@ -23,6 +23,8 @@
 // csrc/common/fold/sm10x/kernel_sm100_fold.py) and the library GEMM of its KEXT route.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "resinfer_b200.h"
 
@@ -45,7 +47,10 @@ struct GemmParams {
   int n_tile;                   // accumulator columns per CTA
   int tok_per_tile;             // tokens per CTA tile
   int act_rows;                 // rows of the activation operand (M or 2M)
-  int k_tiles, k_tiles_per_split, splits;
+  int k_tiles;
+  int tiles, tok_tiles;         // output tiles (weight tiles x token tiles)
+  long long units;              // tiles * k_tiles
+  int grid, tile_granular;      // persistent CTAs; ranges cut at tile boundaries only
   int stages;
   int chunks;                   // 512-byte scale chunks per K tile (4 NVFP4, 2 MXFP4)
   int act_row_tiles;            // 128-row scale tiles the activation buffer holds
@@ -65,6 +70,7 @@ struct GemmParams {
   int32_t* status;
   // shared memory carve-up
   int smem_act_off, smem_sfa_off, smem_sfb_off, stage_bytes;
+  long long* trace;             // optional [grid][8] nanosecond stamps (debugging aid)
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -131,6 +137,30 @@ __device__ __forceinline__ void store_out(const GemmParams& p, int tok, int n, f
 // ---------------------------------------------------------------------------------------------
 // kernel
 // ---------------------------------------------------------------------------------------------
+// Work decomposition ("stream-K"): the K tiles of all output tiles form one linear list of units,
+// unit u = (output tile u / KT, K tile u % KT).  The grid is persistent, one CTA per SM, and CTA c
+// owns the contiguous unit range [start(c), start(c+1)), so every SM streams the same number of
+// weight bytes whatever the number of output tiles is.  A range that covers only part of a tile's K
+// yields an FP32 partial in the workspace; the CTA that delivers the last part of a tile (atomic
+// ticket, nobody waits) adds the parts in CTA order and writes the tile.  A CTA writes at most two
+// partials (its first and its last segment): slot 2c+1 when it is the first contributor of the tile,
+// slot 2c otherwise.
+__device__ __forceinline__ void stamp(const GemmParams& p, int slot) {
+  if (p.trace) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    p.trace[blockIdx.x * 8 + slot] = (long long)t;
+  }
+}
+__device__ __forceinline__ long long range_start(const GemmParams& p, int c) {
+  if (p.tile_granular) return ((long long)c * p.tiles / p.grid) * p.k_tiles;
+  return (long long)c * p.units / p.grid;
+}
+__device__ __forceinline__ int cta_of_unit(const GemmParams& p, long long u) {
+  if (p.tile_granular) return int((((u / p.k_tiles) + 1) * p.grid - 1) / p.tiles);
+  return int(((u + 1) * p.grid - 1) / p.units);
+}
+
 template <bool MX>
 __global__ void __launch_bounds__(kThreads, 1)
 fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap act_map,
@@ -138,7 +168,8 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[kMaxStages];
   __shared__ __align__(8) uint64_t bar_empty[kMaxStages];
-  __shared__ __align__(8) uint64_t bar_acc;
+  __shared__ __align__(8) uint64_t bar_acc_full[2];
+  __shared__ __align__(8) uint64_t bar_acc_empty[2];
   __shared__ uint32_t tmem_base_slot;
   __shared__ volatile int abort_flag;
   __shared__ int is_last_cta;
@@ -149,24 +180,25 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int w_tile = blockIdx.x;
-  const int tok_tile = blockIdx.y;
-  const int split = blockIdx.z;
-  const int kt_begin = split * p.k_tiles_per_split;
-  const int kt_end = min(kt_begin + p.k_tiles_per_split, p.k_tiles);
-  const int num_kt = kt_end - kt_begin;
+  const int cta = blockIdx.x;
+  const long long u_begin = range_start(p, cta);
+  const long long u_end = range_start(p, cta + 1);
   const bool kcat = p.layout == RI_GEMM_CONCAT_K;
   const int halves = kcat ? 2 : 1;
   const int row_tiles = (p.n_tile + 127) / 128;             // scale row tiles per activation tile
   const int act_tile_bytes = p.n_tile * kTileKBytes;
-  const int first_row_tile = (tok_tile * p.n_tile) / 128;
+  const int nbuf = p.n_tile <= 128 ? 2 : 1;                  // accumulator buffers in tensor memory
 
   if (threadIdx.x == 0) {
+    stamp(p, 0);
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);
       mbar_init(smem_u32(&bar_empty[s]), 1);
     }
-    mbar_init(smem_u32(&bar_acc), 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&bar_acc_full[b]), 1);
+      mbar_init(smem_u32(&bar_acc_empty[b]), 1);
+    }
     abort_flag = 0;
     is_last_cta = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -180,34 +212,37 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
+  if (threadIdx.x == 0) stamp(p, 1);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      // bytes per stage: W tile + scale chunks that exist + activation tile(s)
-      int valid_row_tiles = 0;
-      for (int t = 0; t < row_tiles; ++t)
-        if (first_row_tile + t < p.act_row_tiles) ++valid_row_tiles;
       const uint32_t sf_stride = p.chunks * 512;           // bytes of a full tile's scale chunks
-      const uint8_t* w_sf_row = p.w_sf + int64_t(w_tile) * p.w_sf_tile_stride;
       bool dep_synced = false;
-      for (int i = 0; i < num_kt; ++i) {
-        const int s = i % p.stages;
-        const int kt = kt_begin + i;
+      int it = 0;
+      for (long long u = u_begin; u < u_end; ++u, ++it) {
+        const int tile = int(u / p.k_tiles), kt = int(u % p.k_tiles);
+        const int w_tile = tile / p.tok_tiles, tok_tile = tile % p.tok_tiles;
+        const int first_row_tile = (tok_tile * p.n_tile) / 128;
+        int valid_row_tiles = 0;
+        for (int t = 0; t < row_tiles; ++t)
+          if (first_row_tile + t < p.act_row_tiles) ++valid_row_tiles;
+        const int s = it % p.stages;
         // the last K tile may hold fewer than four K64 steps: copy only the scale chunks that exist
         const int rem = p.k - kt * 256;
         const int n_mma = rem >= 256 ? kMmaPerTile : rem / 64;
         const uint32_t sf_bytes = uint32_t(MX ? (n_mma + 1) / 2 : n_mma) * 512;
         const uint32_t tx = kTileW * kTileKBytes + sf_bytes + halves * (act_tile_bytes + valid_row_tiles * sf_bytes);
-        if (i >= p.stages) {
-          if (!mbar_wait(smem_u32(&bar_empty[s]), ((i / p.stages) - 1) & 1, &abort_flag)) break;
+        if (it >= p.stages) {
+          if (!mbar_wait(smem_u32(&bar_empty[s]), ((it / p.stages) - 1) & 1, &abort_flag)) break;
         }
         uint8_t* st = smem + int64_t(s) * p.stage_bytes;
         const uint32_t full = smem_u32(&bar_full[s]);
         mbar_expect_tx(full, tx);
         // weights first: they do not depend on the quantiser that may still be running
         tma_load_2d(smem_u32(st), &w_map, kt * kTileKBytes, w_tile * kTileW, full);
-        bulk_load_1d(smem_u32(st + p.smem_sfa_off), w_sf_row + int64_t(kt) * sf_stride, sf_bytes, full);
+        bulk_load_1d(smem_u32(st + p.smem_sfa_off),
+                     p.w_sf + int64_t(w_tile) * p.w_sf_tile_stride + int64_t(kt) * sf_stride, sf_bytes, full);
         if (!dep_synced) {
           // programmatic dependent launch: the activation comes from the preceding kernel
           asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -224,6 +259,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
           }
         }
       }
+      stamp(p, 2);
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
@@ -232,65 +268,103 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
       const uint32_t idesc_base = (1u << 7) | (1u << 10) | (uint32_t(p.n_tile >> 3) << 17) |
                                   (MX ? (1u << 23) : 0u) | (uint32_t(kTileW >> 4) << 24);
       const uint32_t sf_stride = p.chunks * 512;
-      uint32_t accumulate = 0;
       bool ok = true;
-      for (int i = 0; i < num_kt && ok; ++i) {
-        const int s = i % p.stages;
-        if (!mbar_wait(smem_u32(&bar_full[s]), (i / p.stages) & 1, &abort_flag)) { ok = false; break; }
-        tc_fence_after();
-        uint8_t* st = smem + int64_t(s) * p.stage_bytes;
-        const int rem = p.k - (kt_begin + i) * 256;
-        const int n_mma = rem >= 256 ? kMmaPerTile : rem / 64;
-        const int n_chunks = MX ? (n_mma + 1) / 2 : n_mma;
-        // scales: shared memory -> tensor memory (4 columns per 512-byte chunk)
-        for (int c = 0; c < n_chunks; ++c) {
-          tmem_cp_sf(tmem_base + kSfaCol + 4 * c, desc_sf(smem_u32(st + p.smem_sfa_off + c * 512)));
-          for (int h = 0; h < halves; ++h)
-            for (int t = 0; t < row_tiles; ++t)
-              tmem_cp_sf(tmem_base + kSfbCol + ((h * p.chunks + c) * row_tiles + t) * 4,
-                         desc_sf(smem_u32(st + p.smem_sfb_off + (h * row_tiles + t) * sf_stride + c * 512)));
+      int it = 0, seg = 0;
+      long long u = u_begin;
+      while (u < u_end && ok) {
+        const long long tile_end = (u / p.k_tiles + 1) * p.k_tiles;
+        const long long seg_end = tile_end < u_end ? tile_end : u_end;
+        const int buf = seg % nbuf;
+        if (seg >= nbuf) {                          // the epilogue must have drained this buffer
+          if (!mbar_wait(smem_u32(&bar_acc_empty[buf]), ((seg / nbuf) - 1) & 1, &abort_flag)) { ok = false; break; }
+          tc_fence_after();
         }
-        const uint64_t a_desc = desc_sw128(smem_u32(st));
-        for (int h = 0; h < halves; ++h) {
-          const uint64_t b_desc = desc_sw128(smem_u32(st + p.smem_act_off + h * act_tile_bytes));
-#pragma unroll
-          for (int j = 0; j < kMmaPerTile; ++j) {
-            if (j >= n_mma) break;
-            // NVFP4: one chunk per instruction; MXFP4: one chunk per two instructions, the second
-            // uses scale bytes 2-3 of each column (scale-factor id 2)
-            const int c = MX ? (j >> 1) : j;
-            const uint32_t sf_id = MX ? uint32_t((j & 1) * 2) : 0u;
-            const uint32_t idesc = idesc_base | (sf_id << 4) | (sf_id << 29);
-            mma_fp4<MX>(tmem_base, a_desc + uint64_t(j * 2), b_desc + uint64_t(j * 2), idesc,
-                        tmem_base + kSfaCol + 4 * c,
-                        tmem_base + kSfbCol + ((h * p.chunks + c) * row_tiles) * 4, accumulate);
-            accumulate = 1;
+        const uint32_t d_tmem = tmem_base + buf * p.n_tile;
+        uint32_t accumulate = 0;
+        for (; u < seg_end; ++u, ++it) {
+          const int s = it % p.stages;
+          const int kt = int(u % p.k_tiles);
+          if (!mbar_wait(smem_u32(&bar_full[s]), (it / p.stages) & 1, &abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          if (it == 0) stamp(p, 3);
+          uint8_t* st = smem + int64_t(s) * p.stage_bytes;
+          const int rem = p.k - kt * 256;
+          const int n_mma = rem >= 256 ? kMmaPerTile : rem / 64;
+          const int n_chunks = MX ? (n_mma + 1) / 2 : n_mma;
+          // scales: shared memory -> tensor memory (4 columns per 512-byte chunk)
+          for (int c = 0; c < n_chunks; ++c) {
+            tmem_cp_sf(tmem_base + kSfaCol + 4 * c, desc_sf(smem_u32(st + p.smem_sfa_off + c * 512)));
+            for (int h = 0; h < halves; ++h)
+              for (int t = 0; t < row_tiles; ++t)
+                tmem_cp_sf(tmem_base + kSfbCol + ((h * p.chunks + c) * row_tiles + t) * 4,
+                           desc_sf(smem_u32(st + p.smem_sfb_off + (h * row_tiles + t) * sf_stride + c * 512)));
           }
+          const uint64_t a_desc = desc_sw128(smem_u32(st));
+          for (int h = 0; h < halves; ++h) {
+            const uint64_t b_desc = desc_sw128(smem_u32(st + p.smem_act_off + h * act_tile_bytes));
+#pragma unroll
+            for (int j = 0; j < kMmaPerTile; ++j) {
+              if (j >= n_mma) break;
+              // NVFP4: one chunk per instruction; MXFP4: one chunk per two instructions, the second
+              // uses scale bytes 2-3 of each column (scale-factor id 2)
+              const int c = MX ? (j >> 1) : j;
+              const uint32_t sf_id = MX ? uint32_t((j & 1) * 2) : 0u;
+              const uint32_t idesc = idesc_base | (sf_id << 4) | (sf_id << 29);
+              mma_fp4<MX>(d_tmem, a_desc + uint64_t(j * 2), b_desc + uint64_t(j * 2), idesc,
+                          tmem_base + kSfaCol + 4 * c,
+                          tmem_base + kSfbCol + ((h * p.chunks + c) * row_tiles) * 4, accumulate);
+              accumulate = 1;
+            }
+          }
+          mma_commit(smem_u32(&bar_empty[s]));     // frees the stage when these MMAs have read it
         }
-        mma_commit(smem_u32(&bar_empty[s]));       // frees the stage when these MMAs have read it
+        if (ok) mma_commit(smem_u32(&bar_acc_full[buf]));   // this segment's accumulator is complete
+        ++seg;
       }
-      if (ok) mma_commit(smem_u32(&bar_acc));      // accumulator complete
+      stamp(p, 4);
     }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int quarter = warp & 3;                  // tensor-memory lanes 32*quarter .. +31
-    const int n_row = w_tile * kTileW + quarter * 32 + lane;
-    // one thread waits for the accumulator so that all four warps take the same decision
-    if (warp == 2 && lane == 0) acc_ok = mbar_wait(smem_u32(&bar_acc), 0, &abort_flag) ? 1 : 0;
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-    const bool ok = acc_ok != 0;
-    tc_fence_after();
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    const float a0 = p.alpha ? __ldg(p.alpha) : 1.0f;
-    const float a1 = (p.alpha && p.n_alpha > 1) ? __ldg(p.alpha + 1) : a0;
+    const int row_in_tile = quarter * 32 + lane;
     const bool pair = p.layout == RI_GEMM_ROW_PAIR;
-    const uint32_t t_lane = tmem_base + (uint32_t(quarter * 32) << 16);
-    const int tok0 = tok_tile * p.tok_per_tile;
-    if (ok && p.splits == 1) {
+    const int64_t tile_elems = int64_t(kTileW) * p.n_tile;
+    float a0 = 1.f, a1 = 1.f;
+    bool alpha_read = false;
+    int seg = 0;
+    long long u = u_begin;
+    while (u < u_end) {
+      const int tile = int(u / p.k_tiles);
+      const long long tile_begin = (long long)tile * p.k_tiles, tile_end = tile_begin + p.k_tiles;
+      const long long seg_end = tile_end < u_end ? tile_end : u_end;
+      const bool complete = (u == tile_begin) && (seg_end == tile_end);
+      const int buf = seg % nbuf;
+      // one thread waits for the accumulator so that all four warps take the same decision
+      if (warp == 2 && lane == 0)
+        acc_ok = mbar_wait(smem_u32(&bar_acc_full[buf]), (seg / nbuf) & 1, &abort_flag) ? 1 : 0;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (!acc_ok) break;
+      tc_fence_after();
+      if (seg == 0 && threadIdx.x == 64) stamp(p, 5);
+      if (!alpha_read) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        a0 = p.alpha ? __ldg(p.alpha) : 1.0f;
+        a1 = (p.alpha && p.n_alpha > 1) ? __ldg(p.alpha + 1) : a0;
+        alpha_read = true;
+      }
+      const int w_tile = tile / p.tok_tiles, tok_tile = tile % p.tok_tiles;
+      const int n_row = w_tile * kTileW + row_in_tile;
+      const int tok0 = tok_tile * p.tok_per_tile;
+      const uint32_t t_lane = tmem_base + buf * p.n_tile + (uint32_t(quarter * 32) << 16);
+      const int c_first = cta_of_unit(p, tile_begin), c_last = cta_of_unit(p, tile_end - 1);
+      float* mine = p.ws_partial + (int64_t(cta) * 2 + (cta == c_first ? 1 : 0)) * tile_elems;
       for (int c0 = 0; c0 < p.n_tile; c0 += 16) {
         float v[16];
         tmem_ld16(t_lane + c0, v);
-        if (n_row < p.n) {
+        if (!complete) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) mine[int64_t(c0 + j) * kTileW + row_in_tile] = v[j];
+        } else if (n_row < p.n) {
           if (pair) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
@@ -308,49 +382,61 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
           }
         }
       }
-    } else if (ok) {
-      // split-K: park the FP32 partial tile, last CTA to arrive reduces all of them in order
-      const int tile_id = w_tile * gridDim.y + tok_tile;
-      const int64_t tile_elems = int64_t(kTileW) * p.n_tile;
-      float* mine = p.ws_partial + (int64_t(split) * gridDim.x * gridDim.y + tile_id) * tile_elems;
-      for (int c0 = 0; c0 < p.n_tile; c0 += 16) {
-        float v[16];
-        tmem_ld16(t_lane + c0, v);
-#pragma unroll
-        for (int j = 0; j < 16; ++j) mine[int64_t(c0 + j) * kTileW + quarter * 32 + lane] = v[j];
-      }
-      __threadfence();
+      // the accumulator buffer has been read: hand it back to the MMA warp
+      tc_fence_before();
+      if (!complete) __threadfence();
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (warp == 2 && lane == 0) {
-        const int ticket = atomicAdd(p.ws_counter + tile_id, 1);
-        const int last = ticket == p.splits - 1;
-        if (last) p.ws_counter[tile_id] = 0;       // ready for the next call
-        is_last_cta = last;
-        __threadfence();
-      }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (is_last_cta && n_row < p.n) {
-        const float* base = p.ws_partial + int64_t(tile_id) * tile_elems + quarter * 32 + lane;
-        const int64_t split_stride = int64_t(gridDim.x) * gridDim.y * tile_elems;
-        const int step = pair ? 2 : 1;
-        for (int c = 0; c < p.n_tile; c += step) {
-          float s0 = 0.f, s1 = 0.f;
-          for (int sp = 0; sp < p.splits; ++sp) {
-            const float* src = base + sp * split_stride + int64_t(c) * kTileW;
-            s0 += __ldcg(src);
-            if (pair) s1 += __ldcg(src + kTileW);
-          }
-          const int tok = tok0 + (pair ? (c >> 1) : c);
-          if (tok < p.m)
-            store_out(p, tok, n_row, pair ? (p.n_alpha > 1 ? a0 * s0 + a1 * s1 : a0 * (s0 + s1)) : a0 * s0);
+        mbar_arrive(smem_u32(&bar_acc_empty[buf]));
+        if (!complete) {
+          const int ticket = atomicAdd(p.ws_counter + tile, 1);
+          const int last = ticket == c_last - c_first;
+          if (last) p.ws_counter[tile] = 0;        // ready for the next call
+          is_last_cta = last;
+          __threadfence();
         }
       }
+      if (!complete) {
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (is_last_cta && n_row < p.n) {
+          // add the parts in CTA order (deterministic), four accumulator columns at a time
+          for (int c = 0; c < p.n_tile; c += 4) {
+            float s[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int cc = c_first; cc <= c_last; ++cc) {
+              const float* src = p.ws_partial + (int64_t(cc) * 2 + (cc == c_first ? 1 : 0)) * tile_elems +
+                                 int64_t(c) * kTileW + row_in_tile;
+#pragma unroll
+              for (int q = 0; q < 4; ++q) s[q] += __ldcg(src + q * kTileW);
+            }
+            if (pair) {
+#pragma unroll
+              for (int q = 0; q < 2; ++q) {
+                const int tok = tok0 + (c >> 1) + q;
+                if (tok < p.m)
+                  store_out(p, tok, n_row, p.n_alpha > 1 ? a0 * s[2 * q] + a1 * s[2 * q + 1]
+                                                          : a0 * (s[2 * q] + s[2 * q + 1]));
+              }
+            } else {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const int tok = tok0 + c + q;
+                if (tok < p.m) store_out(p, tok, n_row, a0 * s[q]);
+              }
+            }
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");    // is_last_cta is reused by the next segment
+      }
+      u = seg_end;
+      ++seg;
     }
+    if (threadIdx.x == 64) stamp(p, 6);
   }
 
   // ------------------------------------------------------------------ teardown
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) stamp(p, 7);
   if (abort_flag) {
     if (threadIdx.x == 0 && p.status) atomicExch(p.status, 1 + (int)blockIdx.x);
     __nanosleep(1000000);                          // let copies that are still in flight land
@@ -408,19 +494,15 @@ int make_map(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t ro
 }
 
 struct Plan {
-  int n_tile, tok_per_tile, tok_tiles, w_tiles, k_tiles, splits, k_tiles_per_split, stages;
+  int n_tile, tok_per_tile, tok_tiles, w_tiles, k_tiles, tiles, stages;
+  long long units;
+  int grid, tile_granular;      // persistent CTAs and how their unit ranges are cut
   int chunks, stage_bytes, smem_act_off, smem_sfa_off, smem_sfb_off, smem_total;
 };
 
-int auto_splits(int tiles, int k_tiles, int sm_count) {
-  if (tiles * 4 >= sm_count * 3) return 1;
-  int s = sm_count / tiles;
-  int cap = k_tiles / 2 > 0 ? k_tiles / 2 : 1;       // at least two K tiles per split
-  if (s > cap) s = cap;
-  if (s > 16) s = 16;
-  return s < 1 ? 1 : s;
-}
-
+// `splits`: 1 = ranges are cut at output-tile boundaries only (no K split, no workspace);
+// 0 = choose (stream-K over all SMs unless the tiles already balance); s > 1 = stream-K over
+// min(tiles * s, SMs) CTAs.
 int make_plan(int m, int n, int k, int fmt, int layout, int splits, int sm_count, Plan* pl) {
   const int act_rows = layout == RI_GEMM_ROW_PAIR ? 2 * m : m;
   pl->n_tile = act_rows <= 256 ? (act_rows + 15) / 16 * 16 : 256;
@@ -428,11 +510,28 @@ int make_plan(int m, int n, int k, int fmt, int layout, int splits, int sm_count
   pl->tok_tiles = (act_rows + pl->n_tile - 1) / pl->n_tile;
   pl->w_tiles = (n + kTileW - 1) / kTileW;
   pl->k_tiles = (k + 255) / 256;
+  pl->tiles = pl->w_tiles * pl->tok_tiles;
+  pl->units = (long long)pl->tiles * pl->k_tiles;
   pl->chunks = fmt == RI_FMT_NVFP4 ? 4 : 2;
-  if (splits <= 0) splits = auto_splits(pl->w_tiles * pl->tok_tiles, pl->k_tiles, sm_count);
-  if (splits > pl->k_tiles) splits = pl->k_tiles;
-  pl->k_tiles_per_split = (pl->k_tiles + splits - 1) / splits;
-  pl->splits = (pl->k_tiles + pl->k_tiles_per_split - 1) / pl->k_tiles_per_split;
+  if (splits == 1) {
+    pl->tile_granular = 1;
+    pl->grid = pl->tiles < sm_count ? pl->tiles : sm_count;
+  } else if (splits <= 0) {
+    // tiles that already fill the SMs evenly (or a very long tail-free list) need no K split
+    const bool balanced = pl->tiles % sm_count == 0 || pl->tiles >= 16 * sm_count;
+    pl->tile_granular = balanced ? 1 : 0;
+    long long g = sm_count;
+    if (!balanced && pl->units / 2 < g) g = pl->units / 2 > 0 ? pl->units / 2 : 1;   // >= 2 K tiles per CTA
+    if (balanced && pl->tiles < g) g = pl->tiles;
+    pl->grid = int(g);
+  } else {
+    pl->tile_granular = 0;
+    long long g = (long long)pl->tiles * splits;
+    if (g > sm_count) g = sm_count;
+    if (g > pl->units) g = pl->units;
+    pl->grid = int(g);
+  }
+  if (!pl->tile_granular && pl->grid <= pl->tiles && pl->tiles % pl->grid == 0) pl->tile_granular = 1;
   const int halves = layout == RI_GEMM_CONCAT_K ? 2 : 1;
   const int row_tiles = (pl->n_tile + 127) / 128;
   const int sf_bytes = pl->chunks * 512;
@@ -444,16 +543,28 @@ int make_plan(int m, int n, int k, int fmt, int layout, int splits, int sm_count
   const int budget = kMaxDynSmem - 1024;           // 1 KB of slack to align the tiles to 1024 bytes
   int stages = budget / pl->stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
+  if (const char* e = getenv("RI_GEMM_STAGES")) {        // development knob
+    int v = atoi(e);
+    if (v >= 2 && v < stages) stages = v;
+  }
   if (stages < 2) return RI_ERR_UNSUPPORTED;
   pl->stages = stages;
   pl->smem_total = stages * pl->stage_bytes + 1024;
   return RI_OK;
 }
 
+int64_t partial_bytes(const Plan& pl) {
+  return pl.tile_granular ? 0 : int64_t(pl.grid) * 2 * kTileW * pl.n_tile * 4;
+}
+
+long long* g_trace = nullptr;
+
 }  // namespace
 }  // namespace ri
 
 using namespace ri;
+
+extern "C" void ri_fp4_gemm_set_trace(int64_t* device_buffer) { g_trace = reinterpret_cast<long long*>(device_buffer); }
 
 extern "C" int64_t ri_fp4_gemm_counter_bytes(int m, int n) {
   (void)m;
@@ -468,14 +579,18 @@ extern "C" int ri_fp4_gemm_auto_splits(int m, int n, int k, int fmt, int layout)
   if (device_info(&di)) return -1;
   Plan pl;
   if (make_plan(m, n, k, fmt, layout, 0, di.sm_count, &pl)) return -1;
-  return pl.splits;
+  return pl.tile_granular ? 1 : (pl.grid + pl.tiles - 1) / pl.tiles + 1;
 }
 
 extern "C" int64_t ri_fp4_gemm_workspace_bytes(int m, int n, int k, int fmt, int layout, int splits) {
-  if (splits <= 1) return 0;
+  if (splits == 1) return 0;
+  DeviceInfo di;
+  int sms = 148;
+  if (device_info(&di) == 0 && di.sm_count > sms) sms = di.sm_count;
   Plan pl;
-  if (make_plan(m, n, k, fmt, layout, splits, 148, &pl)) return -1;
-  const int64_t partial = int64_t(pl.splits) * pl.w_tiles * pl.tok_tiles * kTileW * pl.n_tile * 4;
+  if (make_plan(m, n, k, fmt, layout, splits, sms, &pl)) return -1;
+  // sized for a grid of up to `sms` CTAs whatever the planner picks on the device in use
+  const int64_t partial = int64_t(sms) * 2 * kTileW * pl.n_tile * 4;
   return ri_fp4_gemm_counter_bytes(m, n) + partial;
 }
 
@@ -530,14 +645,14 @@ extern "C" int ri_fp4_gemm(const uint8_t* act, int64_t act_row_bytes, const uint
   }
   float* ws_partial = nullptr;
   int* ws_counter = nullptr;
-  if (pl.splits > 1) {
+  if (!pl.tile_granular) {
     const int64_t counter_bytes = ri_fp4_gemm_counter_bytes(m, n);
-    const int64_t partial = int64_t(pl.splits) * pl.w_tiles * pl.tok_tiles * kTileW * pl.n_tile * 4;
+    const int64_t partial = partial_bytes(pl);
     RI_CHECK_ARG(workspace != nullptr && workspace_bytes >= counter_bytes + partial,
-                 "split-K with %d splits needs a workspace of %lld bytes, got %lld", pl.splits,
-                 (long long)(counter_bytes + partial), (long long)workspace_bytes);
+                 "the K-split plan (%d CTAs over %d tiles) needs a workspace of %lld bytes, got %lld", pl.grid,
+                 pl.tiles, (long long)(counter_bytes + partial), (long long)workspace_bytes);
     RI_CHECK_ARG((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "workspace must be 256-byte aligned");
-    RI_CHECK_ARG(int64_t(pl.w_tiles) * pl.tok_tiles * 4 <= counter_bytes, "internal: counter area too small");
+    RI_CHECK_ARG(int64_t(pl.tiles) * 4 <= counter_bytes, "internal: counter area too small");
     ws_counter = static_cast<int*>(workspace);
     ws_partial = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + counter_bytes);
   }
@@ -551,7 +666,8 @@ extern "C" int ri_fp4_gemm(const uint8_t* act, int64_t act_row_bytes, const uint
   GemmParams p{};
   p.m = m; p.n = n; p.k = k; p.fmt = fmt; p.layout = layout;
   p.n_tile = pl.n_tile; p.tok_per_tile = pl.tok_per_tile; p.act_rows = act_rows;
-  p.k_tiles = pl.k_tiles; p.k_tiles_per_split = pl.k_tiles_per_split; p.splits = pl.splits;
+  p.k_tiles = pl.k_tiles; p.tiles = pl.tiles; p.tok_tiles = pl.tok_tiles; p.units = pl.units;
+  p.grid = pl.grid; p.tile_granular = pl.tile_granular;
   p.stages = pl.stages; p.chunks = pl.chunks;
   p.act_row_tiles = int(act_row_tiles);
   p.w_sf_tile_stride = w_chunks * 512;
@@ -563,6 +679,7 @@ extern "C" int ri_fp4_gemm(const uint8_t* act, int64_t act_row_bytes, const uint
   p.ws_partial = ws_partial; p.ws_counter = ws_counter; p.status = status;
   p.smem_act_off = pl.smem_act_off; p.smem_sfa_off = pl.smem_sfa_off; p.smem_sfb_off = pl.smem_sfb_off;
   p.stage_bytes = pl.stage_bytes;
+  p.trace = g_trace;
 
   auto kernel = fmt == RI_FMT_MXFP4 ? fp4_gemm_kernel<true> : fp4_gemm_kernel<false>;
   static bool attr_set[2] = {false, false};
@@ -571,7 +688,7 @@ extern "C" int ri_fp4_gemm(const uint8_t* act, int64_t act_row_bytes, const uint
     attr_set[fmt] = true;
   }
   cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(pl.w_tiles, pl.tok_tiles, pl.splits);
+  cfg.gridDim = dim3(pl.grid);
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = pl.smem_total;
   cfg.stream = static_cast<cudaStream_t>(stream);

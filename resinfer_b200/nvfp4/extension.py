@@ -64,7 +64,7 @@ def _scaled_fp4_quant_mext_r1(output, input, output_scale, input_scale, elts_mod
     _require(int(elts_mode) in (0, 8, 16), "elts_mode must be 0 (auto), 8 or 16")
     _require(input.dim() == 2 and input.stride(1) == 1, "input must be [M, K] with unit column stride")
     m, k = input.shape
-    layout = int(layout_mode) if int(layout_mode) in (0, 1, 2, 3, 4) else 0   # unknown -> concat
+    layout = int(layout_mode) if int(layout_mode) in (0, 1, 2, 3, 4, 5) else 0   # unknown -> concat
     with torch.cuda.device(input.device):
         st = _LIB.ri_nvfp4_quant_mext(
             input.data_ptr(), _cabi.torch_dtype_code(input.dtype), m, k, input.stride(0),

@@ -68,14 +68,11 @@ def fp4_gemm(act: torch.Tensor, act_sf: torch.Tensor, weight: torch.Tensor, weig
     if out is None:
         out = torch.empty((m, n), dtype=out_dtype, device=dev)
     with torch.cuda.device(dev):
-        if splits == 0:
-            splits = lib.ri_fp4_gemm_auto_splits(m, n, k, fmt_c, lay_c)
-            if splits < 1:
-                _cabi.check(_cabi.RI_ERR_ARG, "fp4_gemm plan")
         ws = None
-        ws_bytes = 0
-        if splits > 1:
-            ws_bytes = lib.ri_fp4_gemm_workspace_bytes(m, n, k, fmt_c, lay_c, splits)
+        ws_bytes = lib.ri_fp4_gemm_workspace_bytes(m, n, k, fmt_c, lay_c, splits)
+        if ws_bytes < 0:
+            _cabi.check(_cabi.RI_ERR_ARG, "fp4_gemm plan")
+        if ws_bytes > 0:
             ws = _workspace(dev, ws_bytes, "gemm", zero_prefix=lib.ri_fp4_gemm_counter_bytes(m, n))
         st = lib.ri_fp4_gemm(
             act.data_ptr(), act.stride(0), act_sf.data_ptr(), act_sf.numel(),
