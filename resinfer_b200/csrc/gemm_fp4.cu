@@ -15,8 +15,9 @@
 //     (W is read once, unlike a K loop over 2K);
 //   * split-K over CTAs for small grids: FP32 partials in a caller workspace, the CTA that arrives
 //     last (atomic ticket, nobody waits) reduces in split order, so the result is deterministic.
-// Warp roles: warp 0 = TMA producer, warp 1 = MMA issuer (owns tensor memory), warps 2-5 =
-// epilogue (one per 32-lane quarter of tensor memory).  Every mbarrier wait is bounded: on
+// Warp roles (11 warps): warp 0 = weight TMA producer, warp 10 = activation TMA producer, warp 1 =
+// MMA issuer (owns tensor memory), warps 2-5 = epilogue, warps 6-9 = scale warps that move the block
+// scales from shared to tensor memory with wide tcgen05.st (one warp per 32-lane quarter).  Every mbarrier wait is bounded: on
 // expiry the kernel records a status word, stops issuing and tears down normally.
 //
 // Stands in for the reference's CuTeDSL Fold kernel (ShawRong/ResInfer
@@ -34,10 +35,10 @@ namespace {
 constexpr int kTileW = 128;       // weight rows per CTA (MMA M)
 constexpr int kTileKBytes = 128;  // 256 FP4 per K tile
 constexpr int kMmaPerTile = 4;    // 4 x K64 instructions per K tile
-constexpr int kThreads = 192;
+constexpr int kThreads = 352;       // 11 warps: W producer, MMA, 4 epilogue, 4 scale, activation producer
 constexpr int kTmemCols = 512;
-constexpr int kSfaCol = 256;
-constexpr int kSfbCol = 272;
+constexpr int kSfCol = 256;        // first tensor-memory column of the block-scale sets
+constexpr int kMaxSfSets = 4;
 constexpr int kMaxStages = 10;
 constexpr int kMaxDynSmem = 227 * 1024 - 2048;    // 227 KB per CTA minus the static barriers / flags
 
@@ -52,6 +53,7 @@ struct GemmParams {
   long long units;              // tiles * k_tiles
   int grid, tile_granular;      // persistent CTAs; ranges cut at tile boundaries only
   int stages;
+  int sf_sets, sf_set_cols;     // scale sets in tensor memory: 16 columns for W + the activation's
   int chunks;                   // 512-byte scale chunks per K tile (4 NVFP4, 2 MXFP4)
   int act_row_tiles;            // 128-row scale tiles the activation buffer holds
   int64_t w_sf_tile_stride;     // bytes between 128-row tiles of the weight scales
@@ -108,6 +110,28 @@ __device__ __forceinline__ void mma_fp4(uint32_t d_tmem, uint64_t a_desc, uint64
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb) : "memory");
   }
 }
+// 32 lanes x 4 columns of this warp's quarter of tensor memory
+__device__ __forceinline__ void tmem_st4(uint32_t taddr, uint4 v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};"
+               ::"r"(taddr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint4 (&v)[2]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"r"(taddr), "r"(v[0].x), "r"(v[0].y), "r"(v[0].z), "r"(v[0].w), "r"(v[1].x), "r"(v[1].y),
+                 "r"(v[1].z), "r"(v[1].w) : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint4 (&v)[4]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(v[0].x), "r"(v[0].y), "r"(v[0].z), "r"(v[0].w), "r"(v[1].x), "r"(v[1].y), "r"(v[1].z),
+        "r"(v[1].w), "r"(v[2].x), "r"(v[2].y), "r"(v[2].z), "r"(v[2].w), "r"(v[3].x), "r"(v[3].y), "r"(v[3].z),
+        "r"(v[3].w) : "memory");
+}
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -161,6 +185,25 @@ __device__ __forceinline__ int cta_of_unit(const GemmParams& p, long long u) {
   return int(((u + 1) * p.grid - 1) / p.units);
 }
 
+// Position of a role in its CTA's unit list, advanced without divisions: output tile, K tile,
+// pipeline stage and scale set with their mbarrier phase parities.
+struct Walk {
+  int tile, kt, stage, set, it;
+  uint32_t stage_par, set_par;
+  __device__ __forceinline__ void init(const GemmParams& p, long long u) {
+    tile = int(u / p.k_tiles);
+    kt = int(u % p.k_tiles);
+    stage = set = it = 0;
+    stage_par = set_par = 0;
+  }
+  __device__ __forceinline__ void next(const GemmParams& p) {
+    if (++kt == p.k_tiles) { kt = 0; ++tile; }
+    if (++stage == p.stages) { stage = 0; stage_par ^= 1; }
+    if (++set == p.sf_sets) { set = 0; set_par ^= 1; }
+    ++it;
+  }
+};
+
 template <bool MX>
 __global__ void __launch_bounds__(kThreads, 1)
 fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap act_map,
@@ -170,6 +213,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
   __shared__ __align__(8) uint64_t bar_empty[kMaxStages];
   __shared__ __align__(8) uint64_t bar_acc_full[2];
   __shared__ __align__(8) uint64_t bar_acc_empty[2];
+  __shared__ __align__(8) uint64_t bar_sf_full[kMaxSfSets];
   __shared__ uint32_t tmem_base_slot;
   __shared__ volatile int abort_flag;
   __shared__ int is_last_cta;
@@ -190,7 +234,6 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
   const int nbuf = p.n_tile <= 128 ? 2 : 1;                  // accumulator buffers in tensor memory
 
   if (threadIdx.x == 0) {
-    stamp(p, 0);
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);
       mbar_init(smem_u32(&bar_empty[s]), 1);
@@ -198,6 +241,9 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&bar_acc_full[b]), 1);
       mbar_init(smem_u32(&bar_acc_empty[b]), 1);
+    }
+    for (int s = 0; s < kMaxSfSets; ++s) {
+      mbar_init(smem_u32(&bar_sf_full[s]), 4);     // one arrival per scale warp
     }
     abort_flag = 0;
     is_last_cta = 0;
@@ -212,93 +258,93 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
-  if (threadIdx.x == 0) stamp(p, 1);
 
-  if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
+  if (warp == 0 || warp == 10) {
+    // ------------------------------------------------------------------ TMA producers
+    // two issuing threads in different warps so that their issue costs overlap: warp 0 arms the
+    // barrier and loads the weight tile and its scales, warp 10 loads the activation tile(s) and
+    // their scales
+    const bool w_role = warp == 0;
     if (lane == 0) {
       const uint32_t sf_stride = p.chunks * 512;           // bytes of a full tile's scale chunks
-      bool dep_synced = false;
-      int it = 0;
-      for (long long u = u_begin; u < u_end; ++u, ++it) {
-        const int tile = int(u / p.k_tiles), kt = int(u % p.k_tiles);
-        const int w_tile = tile / p.tok_tiles, tok_tile = tile % p.tok_tiles;
-        const int first_row_tile = (tok_tile * p.n_tile) / 128;
-        int valid_row_tiles = 0;
-        for (int t = 0; t < row_tiles; ++t)
-          if (first_row_tile + t < p.act_row_tiles) ++valid_row_tiles;
-        const int s = it % p.stages;
+      const int n_units = int(u_end - u_begin);
+      Walk w;
+      w.init(p, u_begin);
+      int cur_tile = -1, w_tile = 0, tok_tile = 0, first_row_tile = 0, valid_row_tiles = 0;
+      const uint8_t* w_sf_tile = nullptr;
+      if (!w_role) asm volatile("griddepcontrol.wait;" ::: "memory");   // activations come from the previous kernel
+      for (int i = 0; i < n_units; ++i, w.next(p)) {
+        if (w.tile != cur_tile) {
+          cur_tile = w.tile;
+          w_tile = cur_tile / p.tok_tiles;
+          tok_tile = cur_tile - w_tile * p.tok_tiles;
+          first_row_tile = (tok_tile * p.n_tile) >> 7;
+          valid_row_tiles = 0;
+          for (int t = 0; t < row_tiles; ++t)
+            if (first_row_tile + t < p.act_row_tiles) ++valid_row_tiles;
+          w_sf_tile = p.w_sf + int64_t(w_tile) * p.w_sf_tile_stride;
+        }
         // the last K tile may hold fewer than four K64 steps: copy only the scale chunks that exist
-        const int rem = p.k - kt * 256;
-        const int n_mma = rem >= 256 ? kMmaPerTile : rem / 64;
-        const uint32_t sf_bytes = uint32_t(MX ? (n_mma + 1) / 2 : n_mma) * 512;
-        const uint32_t tx = kTileW * kTileKBytes + sf_bytes + halves * (act_tile_bytes + valid_row_tiles * sf_bytes);
-        if (it >= p.stages) {
-          if (!mbar_wait(smem_u32(&bar_empty[s]), ((it / p.stages) - 1) & 1, &abort_flag)) break;
+        const int rem = p.k - w.kt * 256;
+        const int n_mma = rem >= 256 ? kMmaPerTile : rem >> 6;
+        const uint32_t sf_bytes = uint32_t(MX ? (n_mma + 1) >> 1 : n_mma) * 512;
+        if (w.it >= p.stages) {
+          if (!mbar_wait(smem_u32(&bar_empty[w.stage]), w.stage_par ^ 1, &abort_flag)) break;
         }
-        uint8_t* st = smem + int64_t(s) * p.stage_bytes;
-        const uint32_t full = smem_u32(&bar_full[s]);
-        mbar_expect_tx(full, tx);
-        // weights first: they do not depend on the quantiser that may still be running
-        tma_load_2d(smem_u32(st), &w_map, kt * kTileKBytes, w_tile * kTileW, full);
-        bulk_load_1d(smem_u32(st + p.smem_sfa_off),
-                     p.w_sf + int64_t(w_tile) * p.w_sf_tile_stride + int64_t(kt) * sf_stride, sf_bytes, full);
-        if (!dep_synced) {
-          // programmatic dependent launch: the activation comes from the preceding kernel
-          asm volatile("griddepcontrol.wait;" ::: "memory");
-          dep_synced = true;
-        }
-        for (int h = 0; h < halves; ++h) {
-          tma_load_2d(smem_u32(st + p.smem_act_off + h * act_tile_bytes), &act_map,
-                      kt * kTileKBytes + h * p.act_res_col0, tok_tile * p.n_tile, full);
-          for (int t = 0; t < row_tiles; ++t) {
-            if (first_row_tile + t >= p.act_row_tiles) continue;
-            const uint8_t* src = p.act_sf + int64_t(first_row_tile + t) * p.act_sf_tile_stride +
-                                 (int64_t(kt) * p.chunks + h * p.act_res_chunk0) * 512;
-            bulk_load_1d(smem_u32(st + p.smem_sfb_off + (h * row_tiles + t) * sf_stride), src, sf_bytes, full);
+        uint8_t* st = smem + w.stage * p.stage_bytes;
+        const uint32_t full = smem_u32(&bar_full[w.stage]);
+        if (w_role) {
+          const uint32_t tx = kTileW * kTileKBytes + sf_bytes + halves * (act_tile_bytes + valid_row_tiles * sf_bytes);
+          mbar_expect_tx(full, tx);
+          tma_load_2d(smem_u32(st), &w_map, w.kt * kTileKBytes, w_tile * kTileW, full);
+          bulk_load_1d(smem_u32(st + p.smem_sfa_off), w_sf_tile + w.kt * sf_stride, sf_bytes, full);
+        } else {
+          for (int h = 0; h < halves; ++h) {
+            tma_load_2d(smem_u32(st + p.smem_act_off + h * act_tile_bytes), &act_map,
+                        w.kt * kTileKBytes + h * p.act_res_col0, tok_tile * p.n_tile, full);
+            for (int t = 0; t < row_tiles; ++t) {
+              if (first_row_tile + t >= p.act_row_tiles) continue;
+              const uint8_t* src = p.act_sf + int64_t(first_row_tile + t) * p.act_sf_tile_stride +
+                                   (w.kt * p.chunks + h * p.act_res_chunk0) * 512;
+              bulk_load_1d(smem_u32(st + p.smem_sfb_off + (h * row_tiles + t) * sf_stride), src, sf_bytes, full);
+            }
           }
         }
       }
-      stamp(p, 2);
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    {   // the whole warp walks the loop (converged); one elected lane issues the tcgen05 instructions
       // instruction descriptor: E2M1 x E2M1, K-major A and B, M = 128, N = n_tile
       const uint32_t idesc_base = (1u << 7) | (1u << 10) | (uint32_t(p.n_tile >> 3) << 17) |
                                   (MX ? (1u << 23) : 0u) | (uint32_t(kTileW >> 4) << 24);
-      const uint32_t sf_stride = p.chunks * 512;
       bool ok = true;
-      int it = 0, seg = 0;
-      long long u = u_begin;
-      while (u < u_end && ok) {
-        const long long tile_end = (u / p.k_tiles + 1) * p.k_tiles;
-        const long long seg_end = tile_end < u_end ? tile_end : u_end;
-        const int buf = seg % nbuf;
+      const int n_units = int(u_end - u_begin);
+      Walk w;
+      w.init(p, u_begin);
+      int seg = 0, i = 0;
+      while (i < n_units && ok) {
+        const int buf = nbuf == 2 ? (seg & 1) : 0;
         if (seg >= nbuf) {                          // the epilogue must have drained this buffer
-          if (!mbar_wait(smem_u32(&bar_acc_empty[buf]), ((seg / nbuf) - 1) & 1, &abort_flag)) { ok = false; break; }
+          const bool got = mbar_wait(smem_u32(&bar_acc_empty[buf]), ((seg / nbuf) - 1) & 1, &abort_flag);
+          if (!__all_sync(0xffffffffu, got)) { ok = false; break; }       // warp-uniform decision
           tc_fence_after();
         }
         const uint32_t d_tmem = tmem_base + buf * p.n_tile;
         uint32_t accumulate = 0;
-        for (; u < seg_end; ++u, ++it) {
-          const int s = it % p.stages;
-          const int kt = int(u % p.k_tiles);
-          if (!mbar_wait(smem_u32(&bar_full[s]), (it / p.stages) & 1, &abort_flag)) { ok = false; break; }
+        for (;;) {                                  // K tiles of this segment (same output tile)
+          bool got = mbar_wait(smem_u32(&bar_full[w.stage]), w.stage_par, &abort_flag);
+          // the scale warps have put this K tile's block scales into scale set `set` of tensor memory
+          got = got && mbar_wait(smem_u32(&bar_sf_full[w.set]), w.set_par, &abort_flag);
+          if (!__all_sync(0xffffffffu, got)) { ok = false; break; }       // warp-uniform decision
           tc_fence_after();
-          if (it == 0) stamp(p, 3);
-          uint8_t* st = smem + int64_t(s) * p.stage_bytes;
-          const int rem = p.k - kt * 256;
-          const int n_mma = rem >= 256 ? kMmaPerTile : rem / 64;
-          const int n_chunks = MX ? (n_mma + 1) / 2 : n_mma;
-          // scales: shared memory -> tensor memory (4 columns per 512-byte chunk)
-          for (int c = 0; c < n_chunks; ++c) {
-            tmem_cp_sf(tmem_base + kSfaCol + 4 * c, desc_sf(smem_u32(st + p.smem_sfa_off + c * 512)));
-            for (int h = 0; h < halves; ++h)
-              for (int t = 0; t < row_tiles; ++t)
-                tmem_cp_sf(tmem_base + kSfbCol + ((h * p.chunks + c) * row_tiles + t) * 4,
-                           desc_sf(smem_u32(st + p.smem_sfb_off + (h * row_tiles + t) * sf_stride + c * 512)));
-          }
+          if (w.it == 0 && lane == 0) stamp(p, 3);
+          const bool leader = elect_one();
+          uint8_t* st = smem + w.stage * p.stage_bytes;
+          const int rem = p.k - w.kt * 256;
+          const int n_mma = rem >= 256 ? kMmaPerTile : rem >> 6;
+          const uint32_t sfa_col = tmem_base + kSfCol + w.set * p.sf_set_cols;
+          const uint32_t sfb_col = sfa_col + 16;
           const uint64_t a_desc = desc_sw128(smem_u32(st));
           for (int h = 0; h < halves; ++h) {
             const uint64_t b_desc = desc_sw128(smem_u32(st + p.smem_act_off + h * act_tile_bytes));
@@ -310,35 +356,135 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
               const int c = MX ? (j >> 1) : j;
               const uint32_t sf_id = MX ? uint32_t((j & 1) * 2) : 0u;
               const uint32_t idesc = idesc_base | (sf_id << 4) | (sf_id << 29);
-              mma_fp4<MX>(d_tmem, a_desc + uint64_t(j * 2), b_desc + uint64_t(j * 2), idesc,
-                          tmem_base + kSfaCol + 4 * c,
-                          tmem_base + kSfbCol + ((h * p.chunks + c) * row_tiles) * 4, accumulate);
+              if (leader)
+                mma_fp4<MX>(d_tmem, a_desc + uint64_t(j * 2), b_desc + uint64_t(j * 2), idesc,
+                            sfa_col + 4 * c, sfb_col + ((h * p.chunks + c) * row_tiles) * 4, accumulate);
               accumulate = 1;
             }
           }
-          mma_commit(smem_u32(&bar_empty[s]));     // frees the stage when these MMAs have read it
+          if (leader) mma_commit(smem_u32(&bar_empty[w.stage]));   // frees the stage (and, later, its scale set)
+          __syncwarp();
+          const bool tile_done = w.kt == p.k_tiles - 1;
+          w.next(p);
+          ++i;
+          if (tile_done || i == n_units) break;
         }
-        if (ok) mma_commit(smem_u32(&bar_acc_full[buf]));   // this segment's accumulator is complete
+        if (ok && elect_one()) mma_commit(smem_u32(&bar_acc_full[buf]));   // this segment's accumulator is complete
+        __syncwarp();
         ++seg;
       }
-      stamp(p, 4);
+      if (lane == 0) stamp(p, 4);
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
-    const int quarter = warp & 3;                  // tensor-memory lanes 32*quarter .. +31
+    // ------------------------------------------------------ epilogue (warps 2..5), scales (warps 6..9)
+    // both roles walk the same list of segments; a warp touches tensor-memory lanes 32*(warp%4)..+31
+    const bool scale_role = warp >= 6;
+    const int quarter = warp & 3;
     const int row_in_tile = quarter * 32 + lane;
     const bool pair = p.layout == RI_GEMM_ROW_PAIR;
     const int64_t tile_elems = int64_t(kTileW) * p.n_tile;
     float a0 = 1.f, a1 = 1.f;
     bool alpha_read = false;
-    int seg = 0;
-    long long u = u_begin;
-    while (u < u_end) {
-      const int tile = int(u / p.k_tiles);
+    bool scale_alive = true;
+    const uint32_t sf_stride = p.chunks * 512;
+    const uint32_t q_lane = uint32_t(quarter * 32) << 16;
+    const int n_units = int(u_end - u_begin);
+    Walk w;
+    w.init(p, u_begin);
+    int seg = 0, i = 0;
+    int lag_stage = 0;
+    uint32_t lag_par = 0;
+    while (i < n_units) {
+      const int tile = w.tile;
       const long long tile_begin = (long long)tile * p.k_tiles, tile_end = tile_begin + p.k_tiles;
-      const long long seg_end = tile_end < u_end ? tile_end : u_end;
-      const bool complete = (u == tile_begin) && (seg_end == tile_end);
-      const int buf = seg % nbuf;
+      const int seg_units = min(p.k_tiles - w.kt, n_units - i);          // K tiles of this segment
+      const bool complete = seg_units == p.k_tiles;
+      const int buf = nbuf == 2 ? (seg & 1) : 0;
+      // ---- scale duty: copy the block scales of every K tile of this segment from shared memory
+      // into a scale set of tensor memory.  The 512-byte chunk of (128 rows x 4 k-groups) is laid
+      // out so that lane l reads 16 bytes = the 4 columns of rows l, l+32, l+64, l+96; every warp
+      // writes the same 32 x 4 columns into its own quarter (the MMA expects them replicated).
+      if (!scale_role) {
+        for (int j = 0; j < seg_units; ++j, ++i) w.next(p);
+      } else {
+      for (int j = 0; j < seg_units; ++j, ++i, w.next(p)) {
+        if (!scale_alive) continue;
+        const int rem = p.k - w.kt * 256;
+        const int n_mma = rem >= 256 ? kMmaPerTile : rem >> 6;
+        const int n_chunks = MX ? (n_mma + 1) >> 1 : n_mma;
+        bool got = mbar_wait(smem_u32(&bar_full[w.stage]), w.stage_par, &abort_flag);
+        if (got && w.it >= p.sf_sets) {
+          // scale set reuse: the MMAs of unit (it - sf_sets) must have completed, which is what the
+          // commit on that unit's stage barrier reports
+          got = mbar_wait(smem_u32(&bar_empty[lag_stage]), lag_par, &abort_flag);
+          if (++lag_stage == p.stages) { lag_stage = 0; lag_par ^= 1; }
+        }
+        if (!__all_sync(0xffffffffu, got)) { scale_alive = false; continue; }
+        tc_fence_after();
+        const uint8_t* st = smem + w.stage * p.stage_bytes;
+        const uint32_t col0 = tmem_base + q_lane + kSfCol + w.set * p.sf_set_cols;
+        const uint8_t* sfa_src = st + p.smem_sfa_off + lane * 16;
+        const uint8_t* sfb_src = st + p.smem_sfb_off + lane * 16;
+        if (n_chunks == p.chunks) {
+          // full K tile: 16-byte chunk slices are fetched first, then written with wide stores
+          // (4 chunks = 16 columns per instruction; MXFP4 has 2 chunks = 8 columns)
+          if constexpr (MX) {
+            uint4 a[2] = {*reinterpret_cast<const uint4*>(sfa_src), *reinterpret_cast<const uint4*>(sfa_src + 512)};
+            tmem_st8(col0, a);
+            for (int g8 = 0; g8 < halves * row_tiles; ++g8) {       // column order (h, c, t): pairs of chunks
+              const int h = g8 / row_tiles, tt = g8 % row_tiles;
+              // with two row tiles the column order interleaves them: c0t0 c0t1 c1t0 c1t1
+              if (row_tiles == 1) {
+                const uint8_t* s0 = sfb_src + h * sf_stride;
+                uint4 b[2] = {*reinterpret_cast<const uint4*>(s0), *reinterpret_cast<const uint4*>(s0 + 512)};
+                tmem_st8(col0 + 16 + h * 8, b);
+              } else {
+                const int c = tt;                                    // one chunk, both row tiles
+                const uint8_t* s0 = sfb_src + (h * 2) * sf_stride + c * 512;
+                uint4 b[2] = {*reinterpret_cast<const uint4*>(s0), *reinterpret_cast<const uint4*>(s0 + sf_stride)};
+                tmem_st8(col0 + 16 + (h * 2 + c) * 8, b);
+              }
+            }
+          } else {
+            uint4 a[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) a[c] = *reinterpret_cast<const uint4*>(sfa_src + c * 512);
+            tmem_st16(col0, a);
+            if (row_tiles == 1) {
+              for (int h = 0; h < halves; ++h) {
+                uint4 b[4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) b[c] = *reinterpret_cast<const uint4*>(sfb_src + h * sf_stride + c * 512);
+                tmem_st16(col0 + 16 + h * 16, b);
+              }
+            } else {
+              for (int h = 0; h < halves; ++h)
+                for (int cp = 0; cp < 2; ++cp) {                     // chunk pair: c, t order = c0t0 c0t1 c1t0 c1t1
+                  uint4 b[4];
+#pragma unroll
+                  for (int q = 0; q < 4; ++q)
+                    b[q] = *reinterpret_cast<const uint4*>(sfb_src + (h * 2 + (q & 1)) * sf_stride + (cp * 2 + (q >> 1)) * 512);
+                  tmem_st16(col0 + 16 + (h * 4 + cp * 2) * 8, b);
+                }
+            }
+          }
+        } else {
+          for (int c = 0; c < n_chunks; ++c) {
+            tmem_st4(col0 + 4 * c, *reinterpret_cast<const uint4*>(sfa_src + c * 512));
+            for (int h = 0; h < halves; ++h)
+              for (int t = 0; t < row_tiles; ++t)
+                tmem_st4(col0 + 16 + ((h * p.chunks + c) * row_tiles + t) * 4,
+                         *reinterpret_cast<const uint4*>(sfb_src + (h * row_tiles + t) * sf_stride + c * 512));
+          }
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        tc_fence_before();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_sf_full[w.set]));
+      }
+      ++seg;
+      continue;
+      }
+      // ---- epilogue duty for the segment
       // one thread waits for the accumulator so that all four warps take the same decision
       if (warp == 2 && lane == 0)
         acc_ok = mbar_wait(smem_u32(&bar_acc_full[buf]), (seg / nbuf) & 1, &abort_flag) ? 1 : 0;
@@ -346,6 +492,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
       if (!acc_ok) break;
       tc_fence_after();
       if (seg == 0 && threadIdx.x == 64) stamp(p, 5);
+      if (threadIdx.x == 64) stamp(p, 0);
       if (!alpha_read) {
         asm volatile("griddepcontrol.wait;" ::: "memory");
         a0 = p.alpha ? __ldg(p.alpha) : 1.0f;
@@ -362,8 +509,10 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
         float v[16];
         tmem_ld16(t_lane + c0, v);
         if (!complete) {
+          // partial tile, row-major [128][n_tile]: this thread's row, 16 columns = four 128-bit stores
+          float4* dst = reinterpret_cast<float4*>(mine + int64_t(row_in_tile) * p.n_tile + c0);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) mine[int64_t(c0 + j) * kTileW + row_in_tile] = v[j];
+          for (int j = 0; j < 4; ++j) __stcg(dst + j, make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
         } else if (n_row < p.n) {
           if (pair) {
 #pragma unroll
@@ -386,6 +535,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
       tc_fence_before();
       if (!complete) __threadfence();
       asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (threadIdx.x == 64) stamp(p, 1);
       if (warp == 2 && lane == 0) {
         mbar_arrive(smem_u32(&bar_acc_empty[buf]));
         if (!complete) {
@@ -398,19 +548,38 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
       }
       if (!complete) {
         asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 64) stamp(p, 2);
         if (is_last_cta && n_row < p.n) {
-          // add the parts in CTA order (deterministic), four accumulator columns at a time
-          for (int c = 0; c < p.n_tile; c += 4) {
-            float s[4] = {0.f, 0.f, 0.f, 0.f};
-            for (int cc = c_first; cc <= c_last; ++cc) {
-              const float* src = p.ws_partial + (int64_t(cc) * 2 + (cc == c_first ? 1 : 0)) * tile_elems +
-                                 int64_t(c) * kTileW + row_in_tile;
+          // add the parts in CTA order (deterministic); 16 columns at a time, the loads of two
+          // contributors in flight together
+          const int64_t row_off = int64_t(row_in_tile) * p.n_tile;
+          for (int c = 0; c < p.n_tile; c += 16) {
+            float s[16];
 #pragma unroll
-              for (int q = 0; q < 4; ++q) s[q] += __ldcg(src + q * kTileW);
+            for (int q = 0; q < 16; ++q) s[q] = 0.f;
+            for (int cc = c_first; cc <= c_last; cc += 2) {
+              const float4* s0 = reinterpret_cast<const float4*>(
+                  p.ws_partial + (int64_t(cc) * 2 + (cc == c_first ? 1 : 0)) * tile_elems + row_off + c);
+              const bool two = cc + 1 <= c_last;
+              const float4* s1 = reinterpret_cast<const float4*>(
+                  p.ws_partial + (int64_t(two ? cc + 1 : cc) * 2) * tile_elems + row_off + c);
+              float4 fa[4], fb[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) fa[q] = __ldcg(s0 + q);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) fb[q] = two ? __ldcg(s1 + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                s[4 * q] += fa[q].x; s[4 * q + 1] += fa[q].y; s[4 * q + 2] += fa[q].z; s[4 * q + 3] += fa[q].w;
+              }
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                s[4 * q] += fb[q].x; s[4 * q + 1] += fb[q].y; s[4 * q + 2] += fb[q].z; s[4 * q + 3] += fb[q].w;
+              }
             }
             if (pair) {
 #pragma unroll
-              for (int q = 0; q < 2; ++q) {
+              for (int q = 0; q < 8; ++q) {
                 const int tok = tok0 + (c >> 1) + q;
                 if (tok < p.m)
                   store_out(p, tok, n_row, p.n_alpha > 1 ? a0 * s[2 * q] + a1 * s[2 * q + 1]
@@ -418,7 +587,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
               }
             } else {
 #pragma unroll
-              for (int q = 0; q < 4; ++q) {
+              for (int q = 0; q < 16; ++q) {
                 const int tok = tok0 + c + q;
                 if (tok < p.m) store_out(p, tok, n_row, a0 * s[q]);
               }
@@ -427,7 +596,6 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");    // is_last_cta is reused by the next segment
       }
-      u = seg_end;
       ++seg;
     }
     if (threadIdx.x == 64) stamp(p, 6);
@@ -505,26 +673,44 @@ struct Plan {
 // min(tiles * s, SMs) CTAs.
 int make_plan(int m, int n, int k, int fmt, int layout, int splits, int sm_count, Plan* pl) {
   const int act_rows = layout == RI_GEMM_ROW_PAIR ? 2 * m : m;
-  pl->n_tile = act_rows <= 256 ? (act_rows + 15) / 16 * 16 : 256;
-  pl->tok_per_tile = layout == RI_GEMM_ROW_PAIR ? pl->n_tile / 2 : pl->n_tile;
-  pl->tok_tiles = (act_rows + pl->n_tile - 1) / pl->n_tile;
+  const int halves_c = layout == RI_GEMM_CONCAT_K ? 2 : 1;
   pl->w_tiles = (n + kTileW - 1) / kTileW;
   pl->k_tiles = (k + 255) / 256;
-  pl->tiles = pl->w_tiles * pl->tok_tiles;
-  pl->units = (long long)pl->tiles * pl->k_tiles;
   pl->chunks = fmt == RI_FMT_NVFP4 ? 4 : 2;
+  // accumulator columns per CTA: one tile for up to `cap` activation rows, tiles of `cap` rows above.
+  // Plans that split K use cap 128 (smaller FP32 partials, double-buffered accumulators), others 256.
+  auto geometry = [&](int cap) {
+    pl->n_tile = act_rows <= cap ? (act_rows + 15) / 16 * 16 : cap;
+    if (pl->n_tile < 16) pl->n_tile = 16;
+    pl->tok_per_tile = layout == RI_GEMM_ROW_PAIR ? pl->n_tile / 2 : pl->n_tile;
+    pl->tok_tiles = (act_rows + pl->n_tile - 1) / pl->n_tile;
+    pl->tiles = pl->w_tiles * pl->tok_tiles;
+    pl->units = (long long)pl->tiles * pl->k_tiles;
+  };
+  // measured cost model (microseconds): a unit (one K tile of one output tile) costs about
+  // 0.55 + 0.004 * columns; the exposed merge of a K-split plan about 4 + 0.08 * columns
+  auto unit_us = [&](int n_tile) { return 0.55 + 0.004 * n_tile * halves_c; };
   if (splits == 1) {
+    geometry(256);
     pl->tile_granular = 1;
     pl->grid = pl->tiles < sm_count ? pl->tiles : sm_count;
   } else if (splits <= 0) {
-    // tiles that already fill the SMs evenly (or a very long tail-free list) need no K split
-    const bool balanced = pl->tiles % sm_count == 0 || pl->tiles >= 16 * sm_count;
-    pl->tile_granular = balanced ? 1 : 0;
-    long long g = sm_count;
-    if (!balanced && pl->units / 2 < g) g = pl->units / 2 > 0 ? pl->units / 2 : 1;   // >= 2 K tiles per CTA
-    if (balanced && pl->tiles < g) g = pl->tiles;
-    pl->grid = int(g);
+    geometry(256);
+    const double t_tiles = double((pl->tiles + sm_count - 1) / sm_count) * pl->k_tiles * unit_us(pl->n_tile);
+    geometry(128);
+    const double t_stream = double(pl->units) / sm_count * unit_us(pl->n_tile) + 4.0 + 0.08 * pl->n_tile;
+    if (t_tiles <= t_stream || pl->units < 2) {
+      geometry(256);
+      pl->tile_granular = 1;
+      pl->grid = pl->tiles < sm_count ? pl->tiles : sm_count;
+    } else {
+      pl->tile_granular = 0;
+      long long g = sm_count;
+      if (pl->units / 2 < g) g = pl->units / 2;                 // at least two K tiles per CTA
+      pl->grid = int(g);
+    }
   } else {
+    geometry(128);
     pl->tile_granular = 0;
     long long g = (long long)pl->tiles * splits;
     if (g > sm_count) g = sm_count;
@@ -543,10 +729,6 @@ int make_plan(int m, int n, int k, int fmt, int layout, int splits, int sm_count
   const int budget = kMaxDynSmem - 1024;           // 1 KB of slack to align the tiles to 1024 bytes
   int stages = budget / pl->stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
-  if (const char* e = getenv("RI_GEMM_STAGES")) {        // development knob
-    int v = atoi(e);
-    if (v >= 2 && v < stages) stages = v;
-  }
   if (stages < 2) return RI_ERR_UNSUPPORTED;
   pl->stages = stages;
   pl->smem_total = stages * pl->stage_bytes + 1024;
@@ -570,7 +752,7 @@ extern "C" int64_t ri_fp4_gemm_counter_bytes(int m, int n) {
   (void)m;
   // one ticket per output tile; sized for the smallest tile the planner uses
   const int64_t w_tiles = (int64_t(n) + kTileW - 1) / kTileW;
-  const int64_t tok_tiles = (2 * int64_t(m) + 255) / 256 + 1;
+  const int64_t tok_tiles = (2 * int64_t(m) + 127) / 128;
   return (w_tiles * tok_tiles * 4 + 255) / 256 * 256;
 }
 
@@ -669,6 +851,13 @@ extern "C" int ri_fp4_gemm(const uint8_t* act, int64_t act_row_bytes, const uint
   p.k_tiles = pl.k_tiles; p.tiles = pl.tiles; p.tok_tiles = pl.tok_tiles; p.units = pl.units;
   p.grid = pl.grid; p.tile_granular = pl.tile_granular;
   p.stages = pl.stages; p.chunks = pl.chunks;
+  {
+    const int halves_h = layout == RI_GEMM_CONCAT_K ? 2 : 1;
+    const int row_tiles_h = (pl.n_tile + 127) / 128;
+    p.sf_set_cols = 16 + pl.chunks * halves_h * row_tiles_h * 4;
+    p.sf_sets = (kTmemCols - kSfCol) / p.sf_set_cols;
+    if (p.sf_sets > kMaxSfSets) p.sf_sets = kMaxSfSets;
+  }
   p.act_row_tiles = int(act_row_tiles);
   p.w_sf_tile_stride = w_chunks * 512;
   p.act_sf_tile_stride = act_chunks * 512;

@@ -40,12 +40,12 @@ def test_nvfp4_linear_ratio1_routes(cuda_device, m):
     a = O.dequant_operand(codes, sf, "nvfp4")
     wd = O.dequant_operand(prep["weight"].cpu().numpy(), prep["weight_scale"].cpu().numpy(), "nvfp4")
     ref = O.fp4_linear_reference(a[0::2] + a[1::2], wd, float(alpha.item()), False)
-    assert rel_fro(y.float().cpu().numpy(), ref) < 2.5e-3
+    assert rel_fro(y.detach().float().cpu().numpy(), ref) < 2.5e-3
     # and it beats plain W4A4 against the dense product
     y_plain = torch.ops.residue.nvfp4_linear(x, prep["weight"], gi, prep["weight_scale"], prep["weight_scale_base"],
                                              mask, alpha, k, 0, 0, n, False, False, False)
     dense = x_np.astype(np.float64) @ w_np.astype(np.float64).T
-    assert rel_fro(y.float().cpu().numpy(), dense) < rel_fro(y_plain.float().cpu().numpy(), dense)
+    assert rel_fro(y.detach().float().cpu().numpy(), dense) < rel_fro(y_plain.float().cpu().numpy(), dense)
 
 
 @pytest.mark.parametrize("m,per8", [(16, 1), (200, 2), (300, 4)])
@@ -67,7 +67,7 @@ def test_nvfp4_linear_selective_routes(cuda_device, m, per8):
     else:
         codes, sf, _ = O.nvfp4_quant_kext(x_np, gi.cpu().numpy()[0], mask.cpu().numpy(), per8)
         ref = O.fp4_linear_reference(O.dequant_operand(codes, sf, "nvfp4"), wd, float(alpha.item()), False)
-    assert rel_fro(y.float().cpu().numpy(), ref) < 3e-3
+    assert rel_fro(y.detach().float().cpu().numpy(), ref) < 3e-3
     empty = torch.ops.residue.nvfp4_linear(x[:0], prep["weight"], gi, prep["weight_scale"], prep["weight_scale_base"],
                                            mask, alpha, k, idx.numel(), 0, n, True, False, False)
     assert empty.shape == (0, n)
@@ -107,13 +107,13 @@ def test_registered_linear_modules(cuda_device):
     torch.manual_seed(0)
     lin = torch.nn.Linear(512, 256, bias=True).to(cuda_device).to(torch.bfloat16)
     x = torch.randn(3, 5, 512, device=cuda_device).to(torch.bfloat16)
-    dense = lin(x).float()
+    dense = lin(x).detach().float()
     errs = {}
     for name, kw in (("NVFP4Linear", {}), ("ResidueLinear", {"ratio": 0.25}), ("ResidueLinear", {})):
         mod = LinearRegistry.get(name).from_linear(lin, input_amax=float(x.float().abs().max()), **kw)
         y = mod(x)
         assert y.shape == dense.shape
-        errs[(name, kw.get("ratio", 1.0) if name == "ResidueLinear" else 0)] = rel_fro(y.float().cpu().numpy(),
+        errs[(name, kw.get("ratio", 1.0) if name == "ResidueLinear" else 0)] = rel_fro(y.detach().float().cpu().numpy(),
                                                                                       dense.cpu().numpy())
     assert errs[("ResidueLinear", 1.0)] < errs[("ResidueLinear", 0.25)] < errs[("NVFP4Linear", 0)] < 0.25
     with pytest.raises(NotImplementedError):
