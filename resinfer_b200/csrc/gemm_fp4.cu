@@ -771,6 +771,7 @@ extern "C" int64_t ri_fp4_gemm_workspace_bytes(int m, int n, int k, int fmt, int
   if (device_info(&di) == 0 && di.sm_count > sms) sms = di.sm_count;
   Plan pl;
   if (make_plan(m, n, k, fmt, layout, splits, sms, &pl)) return -1;
+  if (pl.tile_granular) return 0;
   // sized for a grid of up to `sms` CTAs whatever the planner picks on the device in use
   const int64_t partial = int64_t(sms) * 2 * kTileW * pl.n_tile * 4;
   return ri_fp4_gemm_counter_bytes(m, n) + partial;
