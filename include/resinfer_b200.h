@@ -130,6 +130,27 @@ int64_t ri_fp4_gemm_counter_bytes(int m, int n);
  * (no workspace needed), a value > 1 otherwise. */
 int ri_fp4_gemm_auto_splits(int m, int n, int k, int fmt, int layout);
 
+/* ri_fp4_gemm for callers that cannot provide a workspace.  No counterpart in the reference: its
+ * GEMMs always take their scratch from the torch caching allocator.  Same arguments and results as
+ * ri_fp4_gemm, minus `workspace` / `workspace_bytes`: the K-split scratch is a fixed array of
+ * RI_STATIC_SCRATCH_BYTES bytes that is part of the library's device image, so the call never
+ * allocates or frees memory.  Meant for callers that gave all free device memory to their own pool
+ * at start-up, or whose allocator cannot be reached through the binding.
+ *   - A problem whose plan needs more scratch than RI_STATIC_SCRATCH_BYTES (see
+ *     ri_fp4_gemm_workspace_bytes) is rejected with RI_ERR_ARG; nothing is launched.
+ *   - The array is shared by every call on a device and keeps its last contents; the ticket
+ *     counters are cleared on `stream` at the start of each call.  Calls on one device that overlap
+ *     in time race on it: order them (one stream, or events).
+ *   - The first call on each device looks up the array's device address; make it with the device
+ *     that owns `stream` current, and before any stream capture starts. */
+#define RI_STATIC_SCRATCH_BYTES (20 * 1024 * 1024)
+int ri_fp4_gemm_static_scratch(const uint8_t* act, int64_t act_row_bytes, const uint8_t* act_sf,
+                               int64_t act_sf_bytes, const uint8_t* w, int64_t w_row_bytes,
+                               const uint8_t* w_sf, int64_t w_sf_bytes, const float* alpha, int n_alpha,
+                               void* out, int out_dtype, int64_t out_row_stride, int m, int n, int k,
+                               int fmt, int layout, int splits, int32_t* status, int enable_pdl,
+                               void* stream);
+
 /* Debugging aid: when set to a device buffer of 8 * (number of SMs) int64, every CTA of the next
  * ri_fp4_gemm launches stores nanosecond time stamps of its phases there (NULL switches it off). */
 void ri_fp4_gemm_set_trace(int64_t* device_buffer);

@@ -32,6 +32,8 @@ SIGNATURES = {
     "ri_mxfp4_quant": (_i, [_vp, _i, _i, _i, _i64, _i64, _vp, _i, _vp, _i, _i, _vp, _i64, _i, _i, _i, _vp]),
     "ri_fp4_gemm": (_i, [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i, _vp, _i, _i64, _i, _i, _i,
                          _i, _i, _i, _vp, _i64, _vp, _i, _vp]),
+    "ri_fp4_gemm_static_scratch": (_i, [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i, _vp, _i, _i64, _i, _i,
+                                        _i, _i, _i, _i, _vp, _i, _vp]),
     "ri_fp4_gemm_workspace_bytes": (_i64, [_i, _i, _i, _i, _i, _i]),
     "ri_fp4_gemm_counter_bytes": (_i64, [_i, _i]),
     "ri_fp4_gemm_auto_splits": (_i, [_i, _i, _i, _i, _i]),

@@ -85,6 +85,31 @@ def fp4_gemm(act: torch.Tensor, act_sf: torch.Tensor, weight: torch.Tensor, weig
     return out
 
 
+def fp4_gemm_static_scratch(act: torch.Tensor, act_sf: torch.Tensor, weight: torch.Tensor,
+                            weight_sf: torch.Tensor, alpha: torch.Tensor | None, *, m: int, out: torch.Tensor,
+                            fmt: str = "nvfp4", layout: str = "plain", splits: int = 0,
+                            enable_pdl: bool = True) -> torch.Tensor:
+    """`fp4_gemm` through the entry point that allocates nothing: `out` is required, the K-split
+    scratch is the library's built-in per-device array (shared by all calls on the device, so calls
+    must not overlap in time), and sizes that need more than that array raise RuntimeError."""
+    lib = _cabi.load()
+    fmt_c = {"nvfp4": _cabi.FMT_NVFP4, "mxfp4": _cabi.FMT_MXFP4}[fmt]
+    lay_c = {"plain": _cabi.GEMM_PLAIN, "row_pair": _cabi.GEMM_ROW_PAIR, "concat_k": _cabi.GEMM_CONCAT_K}[layout]
+    n, kp = weight.shape
+    dev = weight.device
+    if weight.stride(1) != 1 or act.dim() != 2 or act.stride(1) != 1:
+        raise ValueError("operands must be K-contiguous rows")
+    with torch.cuda.device(dev):
+        st = lib.ri_fp4_gemm_static_scratch(
+            act.data_ptr(), act.stride(0), act_sf.data_ptr(), act_sf.numel(),
+            weight.data_ptr(), weight.stride(0), weight_sf.data_ptr(), weight_sf.numel(),
+            _cabi.ptr(alpha), 0 if alpha is None else alpha.numel(),
+            out.data_ptr(), _cabi.torch_dtype_code(out.dtype, allow_f32=True), out.stride(0), m, n, kp * 2,
+            fmt_c, lay_c, splits, status_word(dev).data_ptr(), int(enable_pdl), _cabi.current_stream(dev))
+    _cabi.check(st, "fp4_gemm_static_scratch")
+    return out
+
+
 def resattn_decode(q: torch.Tensor, k_data: torch.Tensor, k_sf: torch.Tensor, v_data: torch.Tensor,
                    v_sf: torch.Tensor, block_tables: torch.Tensor, seq_lens: torch.Tensor,
                    score_scale: float, out_scale: float, out: torch.Tensor, *, splits: int = 1,
