@@ -63,7 +63,25 @@ class ClockSampler:
     def __init__(self, index: int):
         self.index, self.samples, self._stop, self._t = index, [], threading.Event(), None
 
+    def _run_nvml(self):
+        """Read-only NVML polling every 2 ms (SM clock, max SM clock, clock event reasons)."""
+        import pynvml as N
+        N.nvmlInit()
+        h = N.nvmlDeviceGetHandleByIndex(self.index)
+        mx = N.nvmlDeviceGetMaxClockInfo(h, N.NVML_CLOCK_SM)
+        get_reasons = getattr(N, "nvmlDeviceGetCurrentClocksEventReasons", None) or N.nvmlDeviceGetCurrentClocksThrottleReasons
+        bits = (0x8, 0x40, 0x20, 0x4)        # hw_slowdown, hw_thermal_slowdown, sw_thermal_slowdown, sw_power_cap
+        while not self._stop.is_set():
+            r = int(get_reasons(h))
+            self.samples.append([str(N.nvmlDeviceGetClockInfo(h, N.NVML_CLOCK_SM)), str(mx)] +
+                                ["Active" if r & b else "Not Active" for b in bits])
+            self._stop.wait(0.002)
+
     def _run(self):
+        try:
+            return self._run_nvml()
+        except Exception:
+            pass
         while not self._stop.is_set():
             try:
                 out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
@@ -214,6 +232,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-detail", action="store_true", help="skip the per-case and ResAttn detail measurements")
+    ap.add_argument("--only", default=None,
+                    help="profiling aid: 'gemm:<shape>:<M>' times that single (shape, M) case, 'resattn:<index>' "
+                         "that single ResAttn point; no e2e, no CPU baseline, not a bench value")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
@@ -236,6 +257,19 @@ def main():
     from resinfer_b200.quant.vllm_integration import residue_linear_op  # noqa: F401
     nvfp4.ensure_loaded()
 
+    global SHAPES, MS
+    if args.only:
+        kind, _, rest = args.only.partition(":")
+        if kind == "resattn":
+            hbm_gbs, _ = load_peaks()
+            res = measure_resattn(torch, dev, ops, None, None, hbm_gbs, only=int(rest), steps=args.steps,
+                                  warmup=args.warmup)
+            print(json.dumps({"only": args.only, "resattn": res}), flush=True)
+            return
+        shape, _, m_only = rest.partition(":")
+        SHAPES = [s for s in SHAPES if s[0] == shape]
+        MS = [int(m_only)]
+        args.no_detail = True
     layers = [Layer(nm, k, n, par, tp, rank, dev) for nm, k, n, par in SHAPES]
     outs = {(L.name, m): torch.empty(m, L.n, dtype=torch.bfloat16, device=dev) for L in layers for m in MS}
     launches = {"n": 0}
@@ -324,7 +358,7 @@ def main():
 
     # ---- e2e through the public op with pinned host buffers
     e2e = None
-    if tp == 1:
+    if tp == 1 and not args.only:
         hx = {(L.name, m): L.x[m].cpu().pin_memory() for L in layers for m in MS}
         hy = {(L.name, m): torch.empty(m, L.n, dtype=torch.bfloat16).pin_memory() for L in layers for m in MS}
         zero_mask = torch.zeros(1, dtype=torch.uint8, device=dev)
@@ -356,7 +390,7 @@ def main():
         detail = measure_detail(torch, dev, layers, outs, nvfp4, ops, capture, timed, hbm_gbs)
 
     cpu = None
-    if rank == 0 and tp == 1:
+    if rank == 0 and tp == 1 and not args.only:
         try:
             cpu = cpu_eager_sample()
         except Exception as e:                              # the oracle is optional equipment
@@ -375,6 +409,8 @@ def main():
             "hbm_gbs_algorithmic": sum(mext_bytes(m, L.k_full, L.n_full) for L in layers for m in MS) / (ms_step * 1e-3) / 1e9,
             "e2e": e2e, "roofline": roofline, "cpu_baseline": cpu, "detail": detail,
         }
+        if args.only:
+            line["only"] = args.only
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -404,12 +440,14 @@ def measure_detail(torch, dev, layers, outs, nvfp4, ops, capture, timed, hbm_gbs
     return {"mext_nvfp4_cases": cases, "resattn": attn}
 
 
-def measure_resattn(torch, dev, ops, capture, timed, hbm_gbs):
+def measure_resattn(torch, dev, ops, capture, timed, hbm_gbs, only=None, steps=10, warmup=3):
     from resinfer_b200.nvfp4.cute_attn.plan import select_decode_plan
     res = []
     hq, hkv, page = 64, 8, 16
     sms = torch.cuda.get_device_properties(dev).multi_processor_count
-    for d, batch in ((128, 8), (128, 64), (256, 32)):
+    for idx, (d, batch) in enumerate(((128, 8), (128, 64), (256, 32))):
+        if only is not None and idx != only:
+            continue
         g = torch.Generator(device=dev).manual_seed(3)
         lens = torch.randint(1024, 32769, (batch,), generator=g, device=dev, dtype=torch.int32)
         pages_per = (lens + page - 1) // page
@@ -429,8 +467,19 @@ def measure_resattn(torch, dev, ops, capture, timed, hbm_gbs):
         q = torch.randn(batch, hq, d, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
         out = torch.empty(batch, hq, d, dtype=torch.bfloat16, device=dev)
         splits, _ = select_decode_plan(batch, hkv, int(lens.max()), sms, head_dim=d)
-        rp = capture(lambda: ops.resattn_decode(q, kd, ks, vd, vs, bt, lens, d ** -0.5, 1.0, out, splits=splits))
-        us = timed(rp, 10, 3) * 1e3
+        call = lambda: ops.resattn_decode(q, kd, ks, vd, vs, bt, lens, d ** -0.5, 1.0, out, splits=splits)  # noqa: E731
+        if capture is None:                                 # single-case mode: plain launches, CUDA events
+            for _ in range(warmup):
+                call()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                call()
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) / steps * 1e3
+        else:
+            us = timed(capture(call), 10, 3) * 1e3
         tokens = int(lens.sum())
         nbytes = tokens * hkv * d * 2 * (0.5 + 1 / 16) + 4 * batch * hq * d + 4 * total
         res.append({"head_dim": d, "batch": batch, "page": page, "tokens": tokens, "splits": splits, "us": round(us, 1),

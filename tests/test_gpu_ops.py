@@ -106,7 +106,9 @@ def test_registered_linear_modules(cuda_device):
     from resinfer_b200.quant.linear_registry import LinearRegistry
     torch.manual_seed(0)
     lin = torch.nn.Linear(512, 256, bias=True).to(cuda_device).to(torch.bfloat16)
-    x = torch.randn(3, 5, 512, device=cuda_device).to(torch.bfloat16)
+    # 150 tokens: above the decode threshold (128), so the ratio-0.25 layer takes the masked K-extension
+    # route while the ratio-1 layer stays on the fold route
+    x = torch.randn(3, 50, 512, device=cuda_device).to(torch.bfloat16)
     dense = lin(x).detach().float()
     errs = {}
     for name, kw in (("NVFP4Linear", {}), ("ResidueLinear", {"ratio": 0.25}), ("ResidueLinear", {})):
