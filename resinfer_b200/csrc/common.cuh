@@ -269,7 +269,7 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
 // Bounded wait.  Returns false when another role aborted or the cycle limit expired (then sets
 // the abort flag itself).  The fast path is a plain try_wait loop; the SM cycle counter and the
 // abort flag are only looked at every 4096 failed polls.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int site = 1) {
   long long t0 = 0;
   for (uint32_t spin = 1;; ++spin) {
     if (mbar_try(bar, parity)) return true;
@@ -278,7 +278,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       const long long now = clock64();
       if (t0 == 0) t0 = now;
       else if (now - t0 > kWaitLimitCycles) {
-        *abort_flag = 1;
+        *abort_flag = site;                     // which wait gave up (reported in the status word)
         return false;
       }
     }

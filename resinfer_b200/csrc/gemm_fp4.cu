@@ -41,6 +41,7 @@ constexpr int kSfCol = 256;        // first tensor-memory column of the block-sc
 constexpr int kMaxSfSets = 4;
 constexpr int kMaxStages = 10;
 constexpr int kMaxDynSmem = 227 * 1024 - 2048;    // 227 KB per CTA minus the static barriers / flags
+constexpr int kEpiStageBytes = 8 * 1024;          // epilogue staging: 16 token pairs x 128 outputs x 4 bytes
 
 struct GemmParams {
   int m, n, k;                  // tokens, weight rows, weight K (elements)
@@ -146,6 +147,16 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
 #pragma unroll
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {   // 32 lanes x 32 columns, waits for the data
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -175,6 +186,25 @@ __device__ __forceinline__ void stamp(const GemmParams& p, int slot) {
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     p.trace[blockIdx.x * 8 + slot] = (long long)t;
   }
+}
+// Cycle accounting for development builds (-DRI_GEMM_PROFILE): zero cost otherwise.
+__device__ __forceinline__ long long prof_clock() {
+#ifdef RI_GEMM_PROFILE
+  return clock64();
+#else
+  return 0;
+#endif
+}
+__device__ __forceinline__ void prof_store(const GemmParams& p, int slot, long long v) {
+#ifdef RI_GEMM_PROFILE
+  if (p.trace && blockIdx.x == 0) p.trace[8 * 148 + slot] = v;
+#endif
+}
+// per-unit event times of CTA 0 (development builds): row `ev`, first 24 units
+__device__ __forceinline__ void prof_event(const GemmParams& p, int ev, int unit) {
+#ifdef RI_GEMM_PROFILE
+  if (p.trace && blockIdx.x == 0 && unit < 24) p.trace[8 * 148 + 32 + ev * 24 + unit] = clock64();
+#endif
 }
 __device__ __forceinline__ long long range_start(const GemmParams& p, int c) {
   if (p.tile_granular) return ((long long)c * p.tiles / p.grid) * p.k_tiles;
@@ -225,6 +255,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int cta = blockIdx.x;
+  if (threadIdx.x == 0) stamp(p, 0);
   const long long u_begin = range_start(p, cta);
   const long long u_end = range_start(p, cta + 1);
   const bool kcat = p.layout == RI_GEMM_CONCAT_K;
@@ -233,31 +264,47 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
   const int act_tile_bytes = p.n_tile * kTileKBytes;
   const int nbuf = p.n_tile <= 128 ? 2 : 1;                  // accumulator buffers in tensor memory
 
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < p.stages; ++s) {
-      mbar_init(smem_u32(&bar_full[s]), 1);
-      mbar_init(smem_u32(&bar_empty[s]), 1);
+  // Set-up.  Warp 0 (the weight producer) initialises the barriers and only *arrives* at the set-up
+  // barrier, so its first loads are in flight while warp 1 allocates tensor memory; the dependent
+  // kernel of the stream may be scheduled from here on (it waits for this grid before it touches
+  // anything this grid writes).
+  uint32_t tmem_base = 0;
+  if (warp == 0) {
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&w_map)) : "memory");
+      for (int s = 0; s < p.stages; ++s) {
+        mbar_init(smem_u32(&bar_full[s]), 1);
+        mbar_init(smem_u32(&bar_empty[s]), 1);
+      }
+      for (int b = 0; b < 2; ++b) {
+        mbar_init(smem_u32(&bar_acc_full[b]), 1);
+        mbar_init(smem_u32(&bar_acc_empty[b]), 1);
+      }
+      for (int s = 0; s < kMaxSfSets; ++s) {
+        mbar_init(smem_u32(&bar_sf_full[s]), 4);     // one arrival per scale warp
+      }
+      abort_flag = 0;
+      is_last_cta = 0;
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(smem_u32(&bar_acc_full[b]), 1);
-      mbar_init(smem_u32(&bar_acc_empty[b]), 1);
+    __syncwarp();
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    __threadfence_block();
+    asm volatile("bar.arrive 2, %0;" ::"n"(kThreads) : "memory");
+  } else {
+    if (warp == 1) {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                   ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemCols) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    for (int s = 0; s < kMaxSfSets; ++s) {
-      mbar_init(smem_u32(&bar_sf_full[s]), 4);     // one arrival per scale warp
-    }
-    abort_flag = 0;
-    is_last_cta = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (warp == 10 && lane == 0)
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&act_map)) : "memory");
+    tc_fence_before();
+    asm volatile("bar.sync 2, %0;" ::"n"(kThreads) : "memory");
+    tc_fence_after();
+    tmem_base = tmem_base_slot;
   }
-  if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                 ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemCols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = tmem_base_slot;
+  if (threadIdx.x == 32) stamp(p, 1);
 
   if (warp == 0 || warp == 10) {
     // ------------------------------------------------------------------ TMA producers
@@ -272,6 +319,8 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
       w.init(p, u_begin);
       int cur_tile = -1, w_tile = 0, tok_tile = 0, first_row_tile = 0, valid_row_tiles = 0;
       const uint8_t* w_sf_tile = nullptr;
+      long long pf_wait = 0;
+      const long long pf_begin = prof_clock();
       if (!w_role) asm volatile("griddepcontrol.wait;" ::: "memory");   // activations come from the previous kernel
       for (int i = 0; i < n_units; ++i, w.next(p)) {
         if (w.tile != cur_tile) {
@@ -288,9 +337,13 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
         const int rem = p.k - w.kt * 256;
         const int n_mma = rem >= 256 ? kMmaPerTile : rem >> 6;
         const uint32_t sf_bytes = uint32_t(MX ? (n_mma + 1) >> 1 : n_mma) * 512;
+        const long long c0 = prof_clock();
         if (w.it >= p.stages) {
-          if (!mbar_wait(smem_u32(&bar_empty[w.stage]), w.stage_par ^ 1, &abort_flag)) break;
+          if (!mbar_wait(smem_u32(&bar_empty[w.stage]), w.stage_par ^ 1, &abort_flag, w_role ? 1 : 2)) break;
         }
+        const long long c1 = prof_clock();
+        pf_wait += c1 - c0;
+        if (w_role) prof_event(p, 0, i);
         uint8_t* st = smem + w.stage * p.stage_bytes;
         const uint32_t full = smem_u32(&bar_full[w.stage]);
         if (w_role) {
@@ -298,6 +351,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
           mbar_expect_tx(full, tx);
           tma_load_2d(smem_u32(st), &w_map, w.kt * kTileKBytes, w_tile * kTileW, full);
           bulk_load_1d(smem_u32(st + p.smem_sfa_off), w_sf_tile + w.kt * sf_stride, sf_bytes, full);
+          prof_event(p, 1, i);
         } else {
           for (int h = 0; h < halves; ++h) {
             tma_load_2d(smem_u32(st + p.smem_act_off + h * act_tile_bytes), &act_map,
@@ -311,6 +365,8 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
           }
         }
       }
+      prof_store(p, w_role ? 0 : 2, pf_wait);
+      prof_store(p, w_role ? 1 : 3, prof_clock() - pf_begin);
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
@@ -323,21 +379,27 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
       Walk w;
       w.init(p, u_begin);
       int seg = 0, i = 0;
+      long long pm_full = 0, pm_sf = 0, pm_mma = 0, pm_commit = 0;
+      const long long pm_begin = prof_clock();
       while (i < n_units && ok) {
         const int buf = nbuf == 2 ? (seg & 1) : 0;
         if (seg >= nbuf) {                          // the epilogue must have drained this buffer
-          const bool got = mbar_wait(smem_u32(&bar_acc_empty[buf]), ((seg / nbuf) - 1) & 1, &abort_flag);
+          const bool got = mbar_wait(smem_u32(&bar_acc_empty[buf]), ((seg / nbuf) - 1) & 1, &abort_flag, 3);
           if (!__all_sync(0xffffffffu, got)) { ok = false; break; }       // warp-uniform decision
           tc_fence_after();
         }
         const uint32_t d_tmem = tmem_base + buf * p.n_tile;
         uint32_t accumulate = 0;
         for (;;) {                                  // K tiles of this segment (same output tile)
-          bool got = mbar_wait(smem_u32(&bar_full[w.stage]), w.stage_par, &abort_flag);
+          const long long c0 = prof_clock();
+          bool got = mbar_wait(smem_u32(&bar_full[w.stage]), w.stage_par, &abort_flag, 4);
+          const long long c1 = prof_clock();
           // the scale warps have put this K tile's block scales into scale set `set` of tensor memory
-          got = got && mbar_wait(smem_u32(&bar_sf_full[w.set]), w.set_par, &abort_flag);
+          got = got && mbar_wait(smem_u32(&bar_sf_full[w.set]), w.set_par, &abort_flag, 5);
           if (!__all_sync(0xffffffffu, got)) { ok = false; break; }       // warp-uniform decision
           tc_fence_after();
+          const long long c2 = prof_clock();
+          if (lane == 0) prof_event(p, 5, i);
           if (w.it == 0 && lane == 0) stamp(p, 3);
           const bool leader = elect_one();
           uint8_t* st = smem + w.stage * p.stage_bytes;
@@ -362,8 +424,12 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
               accumulate = 1;
             }
           }
+          const long long c3 = prof_clock();
           if (leader) mma_commit(smem_u32(&bar_empty[w.stage]));   // frees the stage (and, later, its scale set)
           __syncwarp();
+          const long long c4 = prof_clock();
+          if (lane == 0) prof_event(p, 6, i);
+          pm_full += c1 - c0; pm_sf += c2 - c1; pm_mma += c3 - c2; pm_commit += c4 - c3;
           const bool tile_done = w.kt == p.k_tiles - 1;
           w.next(p);
           ++i;
@@ -373,7 +439,11 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
         __syncwarp();
         ++seg;
       }
-      if (lane == 0) stamp(p, 4);
+      if (lane == 0) {
+        stamp(p, 4);
+        prof_store(p, 4, pm_full); prof_store(p, 5, pm_sf); prof_store(p, 6, pm_mma); prof_store(p, 7, pm_commit);
+        prof_store(p, 8, prof_clock() - pm_begin); prof_store(p, 9, n_units);
+      }
     }
   } else {
     // ------------------------------------------------------ epilogue (warps 2..5), scales (warps 6..9)
@@ -384,7 +454,6 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
     const bool pair = p.layout == RI_GEMM_ROW_PAIR;
     const int64_t tile_elems = int64_t(kTileW) * p.n_tile;
     float a0 = 1.f, a1 = 1.f;
-    bool alpha_read = false;
     bool scale_alive = true;
     const uint32_t sf_stride = p.chunks * 512;
     const uint32_t q_lane = uint32_t(quarter * 32) << 16;
@@ -394,6 +463,16 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
     int seg = 0, i = 0;
     int lag_stage = 0;
     uint32_t lag_par = 0;
+    long long ps_full = 0, ps_lag = 0, ps_st = 0;
+    const int esz = p.out_fp16 == 2 ? 4 : 2;                  // output element size
+    const bool out_vec = ((reinterpret_cast<uintptr_t>(p.out) | uintptr_t(p.out_stride * esz)) & 15) == 0;
+    uint8_t* epi_stage = smem + p.stages * p.stage_bytes;     // kEpiStageBytes behind the pipeline stages
+    if (!scale_role) {
+      // global scales may come from the kernel before this one; fetch them while the main loop runs
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      a0 = p.alpha ? __ldg(p.alpha) : 1.0f;
+      a1 = (p.alpha && p.n_alpha > 1) ? __ldg(p.alpha + 1) : a0;
+    }
     while (i < n_units) {
       const int tile = w.tile;
       const long long tile_begin = (long long)tile * p.k_tiles, tile_end = tile_begin + p.k_tiles;
@@ -412,15 +491,21 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
         const int rem = p.k - w.kt * 256;
         const int n_mma = rem >= 256 ? kMmaPerTile : rem >> 6;
         const int n_chunks = MX ? (n_mma + 1) >> 1 : n_mma;
-        bool got = mbar_wait(smem_u32(&bar_full[w.stage]), w.stage_par, &abort_flag);
+        const long long c0 = prof_clock();
+        bool got = mbar_wait(smem_u32(&bar_full[w.stage]), w.stage_par, &abort_flag, 6);
+        const long long c1 = prof_clock();
+        if (warp == 6 && lane == 0) prof_event(p, 2, i);
         if (got && w.it >= p.sf_sets) {
           // scale set reuse: the MMAs of unit (it - sf_sets) must have completed, which is what the
           // commit on that unit's stage barrier reports
-          got = mbar_wait(smem_u32(&bar_empty[lag_stage]), lag_par, &abort_flag);
+          got = mbar_wait(smem_u32(&bar_empty[lag_stage]), lag_par, &abort_flag, 7);
           if (++lag_stage == p.stages) { lag_stage = 0; lag_par ^= 1; }
         }
         if (!__all_sync(0xffffffffu, got)) { scale_alive = false; continue; }
         tc_fence_after();
+        const long long c2 = prof_clock();
+        ps_full += c1 - c0; ps_lag += c2 - c1;
+        if (warp == 6 && lane == 0) prof_event(p, 3, i);
         const uint8_t* st = smem + w.stage * p.stage_bytes;
         const uint32_t col0 = tmem_base + q_lane + kSfCol + w.set * p.sf_set_cols;
         const uint8_t* sfa_src = st + p.smem_sfa_off + lane * 16;
@@ -480,65 +565,187 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         tc_fence_before();
         if (lane == 0) mbar_arrive(smem_u32(&bar_sf_full[w.set]));
+        ps_st += prof_clock() - c2;
+        if (warp == 6 && lane == 0) prof_event(p, 4, i);
+      }
+      if (warp == 6 && lane == 0 && i == n_units) {
+        prof_store(p, 10, ps_full); prof_store(p, 11, ps_lag); prof_store(p, 12, ps_st);
       }
       ++seg;
       continue;
       }
       // ---- epilogue duty for the segment
       // one thread waits for the accumulator so that all four warps take the same decision
-      if (warp == 2 && lane == 0)
-        acc_ok = mbar_wait(smem_u32(&bar_acc_full[buf]), (seg / nbuf) & 1, &abort_flag) ? 1 : 0;
+      const int c_first = cta_of_unit(p, tile_begin), c_last = cta_of_unit(p, tile_end - 1);
+      if (warp == 2 && lane == 0) {
+        // K-split tile: have all the other contributors delivered already?  (Usually true for a CTA's
+        // last segment: the rest of that tile was another CTA's first piece of work.)  Then this CTA
+        // is the one that finishes the tile and its own part never has to leave the SM.
+        int others = -1;
+        if (!complete) {
+          asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(others) : "l"(p.ws_counter + tile) : "memory");
+        }
+        acc_ok = mbar_wait(smem_u32(&bar_acc_full[buf]), (seg / nbuf) & 1, &abort_flag, 8) ? 1 : 0;
+        is_last_cta = (!complete && others == c_last - c_first) ? 2 : 0;
+      }
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (!acc_ok) break;
       tc_fence_after();
+      const bool finish_now = is_last_cta == 2;
       if (seg == 0 && threadIdx.x == 64) stamp(p, 5);
-      if (threadIdx.x == 64) stamp(p, 0);
-      if (!alpha_read) {
-        asm volatile("griddepcontrol.wait;" ::: "memory");
-        a0 = p.alpha ? __ldg(p.alpha) : 1.0f;
-        a1 = (p.alpha && p.n_alpha > 1) ? __ldg(p.alpha + 1) : a0;
-        alpha_read = true;
-      }
       const int w_tile = tile / p.tok_tiles, tok_tile = tile % p.tok_tiles;
-      const int n_row = w_tile * kTileW + row_in_tile;
+      const int n_row0 = w_tile * kTileW;
       const int tok0 = tok_tile * p.tok_per_tile;
       const uint32_t t_lane = tmem_base + buf * p.n_tile + (uint32_t(quarter * 32) << 16);
-      const int c_first = cta_of_unit(p, tile_begin), c_last = cta_of_unit(p, tile_end - 1);
       float* mine = p.ws_partial + (int64_t(cta) * 2 + (cta == c_first ? 1 : 0)) * tile_elems;
-      for (int c0 = 0; c0 < p.n_tile; c0 += 16) {
-        float v[16];
-        tmem_ld16(t_lane + c0, v);
-        if (!complete) {
-          // partial tile, row-major [128][n_tile]: this thread's row, 16 columns = four 128-bit stores
-          float4* dst = reinterpret_cast<float4*>(mine + int64_t(row_in_tile) * p.n_tile + c0);
+      const long long e1 = prof_clock();
+      long long pe_ld = 0, pe_stage = 0, pe_bar1 = 0, pe_copy = 0, pe_bar2 = 0;
+
+      // Output of one chunk of 32 accumulator columns (16 tokens with the row_pair layout, 32
+      // otherwise).  A thread owns one output column n (its weight row) and `ntok` token values.
+      // 16-bit outputs go through shared memory so that the global stores are 16-byte vectors along
+      // n: two tokens are packed into one 32-bit word, word [token pair][n]; a thread of the
+      // copy-out reads 8 words of a pair row and writes one vector for each of the two tokens.
+      // FP32 output (a debugging format) is stored element by element.
+      auto emit_chunk = [&](const float (&v)[32], int c0, int cols) {
+        const int ntok = pair ? cols >> 1 : cols;
+        const int tokc0 = tok0 + (pair ? c0 >> 1 : c0);
+        float o[32];
+        const long long q0 = prof_clock();
+        if (pair) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) __stcg(dst + j, make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
-        } else if (n_row < p.n) {
-          if (pair) {
+          for (int j = 0; j < 16; ++j) o[j] = p.n_alpha > 1 ? a0 * v[2 * j] + a1 * v[2 * j + 1] : a0 * (v[2 * j] + v[2 * j + 1]);
+        } else {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const int tok = tok0 + (c0 >> 1) + j;
-              if (tok < p.m)
-                store_out(p, tok, n_row, p.n_alpha > 1 ? a0 * v[2 * j] + a1 * v[2 * j + 1]
-                                                        : a0 * (v[2 * j] + v[2 * j + 1]));
+          for (int j = 0; j < 32; ++j) o[j] = a0 * v[j];
+        }
+        if (esz == 4) {
+          const int n = n_row0 + row_in_tile;
+          if (n < p.n) {
+            float* dst = static_cast<float*>(p.out) + int64_t(tokc0) * p.out_stride + n;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < ntok && tokc0 + j < p.m) dst[int64_t(j) * p.out_stride] = o[j];
+          }
+          return;
+        }
+        uint32_t* stage32 = reinterpret_cast<uint32_t*>(epi_stage);
+        const int npair = (ntok + 1) >> 1;
+#ifdef RI_GEMM_PROFILE
+        { uint32_t dummy; asm volatile("mov.b32 %0, %1;" : "=r"(dummy) : "f"(o[15])); asm volatile("mov.b32 %0, %1;" : "=r"(dummy) : "f"(o[0])); }
+        pe_bar2 -= prof_clock() - q0;     // (borrowed slot: minus the time to compute o[])
+#endif
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          if (i < npair) {
+            uint32_t wv;
+            if (p.out_fp16) {
+              const __half2 h = __floats2half2_rn(o[2 * i], o[2 * i + 1]);
+              wv = *reinterpret_cast<const uint32_t*>(&h);
+            } else {
+              const __nv_bfloat162 h = __floats2bfloat162_rn(o[2 * i], o[2 * i + 1]);
+              wv = *reinterpret_cast<const uint32_t*>(&h);
             }
+            stage32[i * kTileW + row_in_tile] = wv;
+          }
+        }
+        const long long q1 = prof_clock();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const long long q2 = prof_clock();
+        // copy-out: thread -> (pair row, vector of 8 outputs); 16 vectors per token row of the tile
+        const int et = int(threadIdx.x) - 64;
+        for (int pr = et >> 4; pr < npair; pr += 8) {
+          const int vc = et & 15;
+          const int n0 = n_row0 + vc * 8;
+          const int tok = tokc0 + 2 * pr;
+          if (tok >= p.m || n0 >= p.n) continue;
+          const uint4 lo4 = *reinterpret_cast<const uint4*>(stage32 + pr * kTileW + vc * 8);
+          const uint4 hi4 = *reinterpret_cast<const uint4*>(stage32 + pr * kTileW + vc * 8 + 4);
+          uint4 t0, t1;                                       // token `tok` (low halves), token `tok + 1` (high halves)
+          t0.x = __byte_perm(lo4.x, lo4.y, 0x5410); t0.y = __byte_perm(lo4.z, lo4.w, 0x5410);
+          t0.z = __byte_perm(hi4.x, hi4.y, 0x5410); t0.w = __byte_perm(hi4.z, hi4.w, 0x5410);
+          t1.x = __byte_perm(lo4.x, lo4.y, 0x7632); t1.y = __byte_perm(lo4.z, lo4.w, 0x7632);
+          t1.z = __byte_perm(hi4.x, hi4.y, 0x7632); t1.w = __byte_perm(hi4.z, hi4.w, 0x7632);
+          uint16_t* dst = static_cast<uint16_t*>(p.out) + int64_t(tok) * p.out_stride + n0;
+          const bool second = tok + 1 < p.m && 2 * pr + 1 < ntok;
+          if (out_vec && n0 + 8 <= p.n) {
+            *reinterpret_cast<uint4*>(dst) = t0;
+            if (second) *reinterpret_cast<uint4*>(dst + p.out_stride) = t1;
           } else {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int tok = tok0 + c0 + j;
-              if (tok < p.m) store_out(p, tok, n_row, a0 * v[j]);
+            const uint32_t a[4] = {t0.x, t0.y, t0.z, t0.w}, bq[4] = {t1.x, t1.y, t1.z, t1.w};
+            const int cnt = min(8, p.n - n0);
+            for (int e = 0; e < cnt; ++e) {
+              dst[e] = uint16_t(a[e >> 1] >> ((e & 1) * 16));
+              if (second) dst[p.out_stride + e] = uint16_t(bq[e >> 1] >> ((e & 1) * 16));
             }
           }
         }
+        const long long q3 = prof_clock();
+        asm volatile("bar.sync 1, 128;" ::: "memory");      // the stage is reused by the next chunk
+        pe_stage += q1 - q0; pe_bar1 += q2 - q1; pe_copy += q3 - q2; pe_bar2 += prof_clock() - q3;
+      };
+
+      for (int c0 = 0; c0 < p.n_tile; c0 += 32) {
+        const int cols = min(32, p.n_tile - c0);               // 32, or 16 for the last chunk
+        float v[32];
+        const long long l0 = prof_clock();
+        if (cols == 32) {
+          tmem_ld32(t_lane + c0, v);
+        } else {
+          float lo[16];
+          tmem_ld16(t_lane + c0, lo);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) { v[j] = lo[j]; v[16 + j] = 0.f; }
+        }
+#ifdef RI_GEMM_PROFILE
+        { uint32_t dummy; asm volatile("mov.b32 %0, %1;" : "=r"(dummy) : "f"(v[31])); asm volatile("mov.b32 %0, %1;" : "=r"(dummy) : "f"(v[0])); }
+#endif
+        pe_ld += prof_clock() - l0;
+        if (finish_now) {
+          // sum in CTA order, this CTA's part straight from tensor memory (same order and values as
+          // the reduction below, so the result does not depend on which path ran)
+          float s[32];
+#pragma unroll
+          for (int q = 0; q < 32; ++q) s[q] = 0.f;
+          const int64_t off = int64_t(c0) * kTileW + row_in_tile;
+          for (int cc = c_first; cc <= c_last; ++cc) {
+            if (cc == cta) {
+#pragma unroll
+              for (int q = 0; q < 32; ++q) s[q] += v[q];
+            } else {
+              const float* s0 = p.ws_partial + (int64_t(cc) * 2 + (cc == c_first ? 1 : 0)) * tile_elems + off;
+              float fa[32];
+#pragma unroll
+              for (int q = 0; q < 32; ++q) fa[q] = q < cols ? __ldcg(s0 + q * kTileW) : 0.f;
+#pragma unroll
+              for (int q = 0; q < 32; ++q) s[q] += fa[q];
+            }
+          }
+          emit_chunk(s, c0, cols);
+        } else if (!complete) {
+          // partial tile, column-major [n_tile][128]: a warp writes one full 128-byte line per column
+          float* dst = mine + int64_t(c0) * kTileW + row_in_tile;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) if (j < cols) __stcg(dst + j * kTileW, v[j]);
+        } else {
+          emit_chunk(v, c0, cols);
+        }
+      }
+      if (threadIdx.x == 64 && seg == 0) {
+        prof_store(p, 15, prof_clock() - e1); prof_store(p, 16, pe_ld); prof_store(p, 17, pe_stage);
+        prof_store(p, 18, pe_bar1); prof_store(p, 19, pe_copy); prof_store(p, 20, pe_bar2);
       }
       // the accumulator buffer has been read: hand it back to the MMA warp
       tc_fence_before();
-      if (!complete) __threadfence();
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (threadIdx.x == 64) stamp(p, 1);
       if (warp == 2 && lane == 0) {
         mbar_arrive(smem_u32(&bar_acc_empty[buf]));
-        if (!complete) {
+        if (finish_now) {
+          p.ws_counter[tile] = 0;                  // everybody else has arrived: ready for the next call
+        } else if (!complete) {
+          // the barrier above ordered every thread's partial stores before this thread; the fence
+          // publishes them device-wide before the ticket, and orders the reads after it
+          __threadfence();
           const int ticket = atomicAdd(p.ws_counter + tile, 1);
           const int last = ticket == c_last - c_first;
           if (last) p.ws_counter[tile] = 0;        // ready for the next call
@@ -546,52 +753,33 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
           __threadfence();
         }
       }
-      if (!complete) {
+      if (!complete && !finish_now) {
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (threadIdx.x == 64) stamp(p, 2);
-        if (is_last_cta && n_row < p.n) {
-          // add the parts in CTA order (deterministic); 16 columns at a time, the loads of two
-          // contributors in flight together
-          const int64_t row_off = int64_t(row_in_tile) * p.n_tile;
-          for (int c = 0; c < p.n_tile; c += 16) {
-            float s[16];
+        if (is_last_cta) {
+          // add the parts in CTA order (deterministic), 32 columns at a time with the loads of two
+          // contributors in flight together, then write the chunk like a complete tile's
+          for (int c0 = 0; c0 < p.n_tile; c0 += 32) {
+            const int cols = min(32, p.n_tile - c0);
+            float s[32];
 #pragma unroll
-            for (int q = 0; q < 16; ++q) s[q] = 0.f;
+            for (int q = 0; q < 32; ++q) s[q] = 0.f;
+            const int64_t off = int64_t(c0) * kTileW + row_in_tile;
             for (int cc = c_first; cc <= c_last; cc += 2) {
-              const float4* s0 = reinterpret_cast<const float4*>(
-                  p.ws_partial + (int64_t(cc) * 2 + (cc == c_first ? 1 : 0)) * tile_elems + row_off + c);
+              const float* s0 = p.ws_partial + (int64_t(cc) * 2 + (cc == c_first ? 1 : 0)) * tile_elems + off;
               const bool two = cc + 1 <= c_last;
-              const float4* s1 = reinterpret_cast<const float4*>(
-                  p.ws_partial + (int64_t(two ? cc + 1 : cc) * 2) * tile_elems + row_off + c);
-              float4 fa[4], fb[4];
+              const float* s1 = p.ws_partial + (int64_t(two ? cc + 1 : cc) * 2) * tile_elems + off;
+              float fa[32], fb[32];
 #pragma unroll
-              for (int q = 0; q < 4; ++q) fa[q] = __ldcg(s0 + q);
+              for (int q = 0; q < 32; ++q) fa[q] = q < cols ? __ldcg(s0 + q * kTileW) : 0.f;
 #pragma unroll
-              for (int q = 0; q < 4; ++q) fb[q] = two ? __ldcg(s1 + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+              for (int q = 0; q < 32; ++q) fb[q] = (two && q < cols) ? __ldcg(s1 + q * kTileW) : 0.f;
 #pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                s[4 * q] += fa[q].x; s[4 * q + 1] += fa[q].y; s[4 * q + 2] += fa[q].z; s[4 * q + 3] += fa[q].w;
-              }
+              for (int q = 0; q < 32; ++q) s[q] += fa[q];
 #pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                s[4 * q] += fb[q].x; s[4 * q + 1] += fb[q].y; s[4 * q + 2] += fb[q].z; s[4 * q + 3] += fb[q].w;
-              }
+              for (int q = 0; q < 32; ++q) s[q] += fb[q];
             }
-            if (pair) {
-#pragma unroll
-              for (int q = 0; q < 8; ++q) {
-                const int tok = tok0 + (c >> 1) + q;
-                if (tok < p.m)
-                  store_out(p, tok, n_row, p.n_alpha > 1 ? a0 * s[2 * q] + a1 * s[2 * q + 1]
-                                                          : a0 * (s[2 * q] + s[2 * q + 1]));
-              }
-            } else {
-#pragma unroll
-              for (int q = 0; q < 16; ++q) {
-                const int tok = tok0 + c + q;
-                if (tok < p.m) store_out(p, tok, n_row, a0 * s[q]);
-              }
-            }
+            emit_chunk(s, c0, cols);
           }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");    // is_last_cta is reused by the next segment
@@ -606,10 +794,9 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
   __syncthreads();
   if (threadIdx.x == 0) stamp(p, 7);
   if (abort_flag) {
-    if (threadIdx.x == 0 && p.status) atomicExch(p.status, 1 + (int)blockIdx.x);
+    if (threadIdx.x == 0 && p.status) atomicExch(p.status, 1 + (int)blockIdx.x + (abort_flag << 16));   // CTA and wait site
     __nanosleep(1000000);                          // let copies that are still in flight land
   }
-  asm volatile("griddepcontrol.launch_dependents;");
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
@@ -726,12 +913,12 @@ int make_plan(int m, int n, int k, int fmt, int layout, int splits, int sm_count
   pl->smem_sfb_off = pl->smem_sfa_off + sf_bytes;
   int stage = pl->smem_sfb_off + halves * row_tiles * sf_bytes;
   pl->stage_bytes = (stage + 1023) / 1024 * 1024;
-  const int budget = kMaxDynSmem - 1024;           // 1 KB of slack to align the tiles to 1024 bytes
+  const int budget = kMaxDynSmem - 1024 - kEpiStageBytes;   // 1 KB of slack to align the tiles to 1024 bytes
   int stages = budget / pl->stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) return RI_ERR_UNSUPPORTED;
   pl->stages = stages;
-  pl->smem_total = stages * pl->stage_bytes + 1024;
+  pl->smem_total = stages * pl->stage_bytes + kEpiStageBytes + 1024;
   return RI_OK;
 }
 
@@ -858,6 +1045,9 @@ extern "C" int ri_fp4_gemm(const uint8_t* act, int64_t act_row_bytes, const uint
     p.sf_set_cols = 16 + pl.chunks * halves_h * row_tiles_h * 4;
     p.sf_sets = (kTmemCols - kSfCol) / p.sf_set_cols;
     if (p.sf_sets > kMaxSfSets) p.sf_sets = kMaxSfSets;
+    // a scale set is recycled once the stage barrier of the unit that used it has completed; that
+    // barrier must not be able to run a whole phase ahead of the check, so sets <= stages
+    if (p.sf_sets > p.stages) p.sf_sets = p.stages;
   }
   p.act_row_tiles = int(act_row_tiles);
   p.w_sf_tile_stride = w_chunks * 512;

@@ -65,6 +65,9 @@ __global__ void __launch_bounds__(128) mxfp4_quant_kernel(
   const int groups_walk = sf_groups_out > groups_in ? sf_groups_out : groups_in;
   const int warps_per_row = (groups_walk + 31) / 32;
   const int total_warps = walk_rows * warps_per_row;
+  // let the dependent kernel (the GEMM) be scheduled now: it prefetches weights while this grid runs and
+  // waits for this grid (griddepcontrol.wait) before it reads the codes
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   for (int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; w < total_warps;
        w += (gridDim.x * blockDim.x) >> 5) {
@@ -204,7 +207,6 @@ __global__ void __launch_bounds__(128) mxfp4_quant_kernel(
       }
     }
   }
-  asm volatile("griddepcontrol.launch_dependents;");
 }
 
 template <typename T, int PER8>

@@ -46,6 +46,9 @@ __global__ void __launch_bounds__(256) nvfp4_mext_kernel(const T* __restrict__ x
                                                          uint8_t* __restrict__ sf, int layout) {
   const int blocks_per_row = k / 16;
   const int64_t total = int64_t(out_rows) * blocks_per_row;
+  // let the dependent kernel (the GEMM) be scheduled now: it prefetches weights while this grid runs and
+  // waits for this grid (griddepcontrol.wait) before it reads the codes
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");   // inputs may come from a kernel still running
   const float gs = gs_inv ? __ldg(gs_inv) : 1.0f;
   const float gs_res = (gs_inv && n_gs > 1) ? __ldg(gs_inv + 1) : gs;
@@ -79,9 +82,6 @@ __global__ void __launch_bounds__(256) nvfp4_mext_kernel(const T* __restrict__ x
       sf[sf_offset<16>(sr, blk, k)] = q.sf_res;
     }
   }
-  // let a dependent kernel (the GEMM) start its prologue; it still waits for this grid's
-  // memory with griddepcontrol.wait before it reads the codes
-  asm volatile("griddepcontrol.launch_dependents;");
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -104,6 +104,9 @@ __global__ void __launch_bounds__(256) nvfp4_kext_kernel(const T* __restrict__ x
   const int warps_per_row = (blocks_per_row + 31) / 32;
   const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int total_warps = rows_padded * warps_per_row;
+  // let the dependent kernel (the GEMM) be scheduled now: it prefetches weights while this grid runs and
+  // waits for this grid (griddepcontrol.wait) before it reads the codes
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   const float gs = gs_inv ? __ldg(gs_inv) : 1.0f;
   for (int w = warp_global; w < total_warps; w += (gridDim.x * blockDim.x) >> 5) {
@@ -168,7 +171,6 @@ __global__ void __launch_bounds__(256) nvfp4_kext_kernel(const T* __restrict__ x
       if ((lane % SF_THREADS) == 0) sf[sf_offset<16>(row, (k + res_start) / 16, n_ext)] = sfr;
     }
   }
-  asm volatile("griddepcontrol.launch_dependents;");
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -182,6 +184,9 @@ __global__ void __launch_bounds__(128) nvfp4_grouped_q_kernel(const __nv_bfloat1
   const int blocks_per_row = d / 16;
   const int per_group = g * blocks_per_row;
   const int64_t total = int64_t(groups) * per_group;
+  // let the dependent kernel (the GEMM) be scheduled now: it prefetches weights while this grid runs and
+  // waits for this grid (griddepcontrol.wait) before it reads the codes
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   for (int64_t t = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
        t += int64_t(gridDim.x) * blockDim.x) {
@@ -198,7 +203,6 @@ __global__ void __launch_bounds__(128) nvfp4_grouped_q_kernel(const __nv_bfloat1
     sfp[sf_offset<16>(row, blk, d)] = bq.sf;
     sfp[sf_offset<16>(p / 2 + row, blk, d)] = bq.sf_res;
   }
-  asm volatile("griddepcontrol.launch_dependents;");
 }
 
 template <typename K, typename... Args>
