@@ -874,26 +874,56 @@ int make_plan(int m, int n, int k, int fmt, int layout, int splits, int sm_count
     pl->tiles = pl->w_tiles * pl->tok_tiles;
     pl->units = (long long)pl->tiles * pl->k_tiles;
   };
-  // measured cost model (microseconds): a unit (one K tile of one output tile) costs about
-  // 0.55 + 0.004 * columns; the exposed merge of a K-split plan about 4 + 0.08 * columns
-  auto unit_us = [&](int n_tile) { return 0.55 + 0.004 * n_tile * halves_c; };
+  // Plan choice for splits == 0: a cost model fitted to measurements on B200 (microseconds).
+  //   * an SM pulls weight bytes (HBM) at about 42 GB/s while up to ~96 CTAs stream and 35 GB/s when
+  //     all SMs do (the HBM ceiling is shared), and activation tiles (L2) at about 120 GB/s;
+  //   * a plan that splits K pays for the exchange of FP32 partials: about 2 us + 0.02 us per
+  //     accumulator column when every CTA owns one even slice of one tile, 3 us + 0.05 us per column
+  //     for ragged ranges (more contributors per tile, two partials per CTA);
+  //   * the output pass costs about 0.75 us per 32 accumulator columns.
+  // Candidates: whole tiles per CTA; even K splits s = 2 .. SMs / tiles; ragged ranges on every SM.
+  const double w_unit_kb = (kTileW * kTileKBytes + pl->chunks * 512) / 1024.0;
+  auto act_unit_kb = [&](int n_tile) { return halves_c * (n_tile * kTileKBytes + pl->chunks * 512 * ((n_tile + 127) / 128)) / 1024.0; };
+  auto stream_us = [&](double units_per_cta, int ctas, int n_tile) {
+    const double rate = ctas <= 96 ? 42.0 : 35.0;
+    return units_per_cta * (w_unit_kb / rate + act_unit_kb(n_tile) / 120.0);     // KB / (GB/s) = us
+  };
+  auto epi_us = [&](int n_tile) { return 0.75 * ((n_tile + 31) / 32); };
   if (splits == 1) {
     geometry(256);
     pl->tile_granular = 1;
     pl->grid = pl->tiles < sm_count ? pl->tiles : sm_count;
   } else if (splits <= 0) {
     geometry(256);
-    const double t_tiles = double((pl->tiles + sm_count - 1) / sm_count) * pl->k_tiles * unit_us(pl->n_tile);
+    const int grid_t = pl->tiles < sm_count ? pl->tiles : sm_count;
+    const double waves = double((pl->tiles + grid_t - 1) / grid_t);
+    double best = stream_us(waves * pl->k_tiles, grid_t, pl->n_tile) + waves * epi_us(pl->n_tile);
+    int best_split = 1;                                   // 1 = whole tiles, -1 = ragged ranges, s > 1 = even split
     geometry(128);
-    const double t_stream = double(pl->units) / sm_count * unit_us(pl->n_tile) + 4.0 + 0.08 * pl->n_tile;
-    if (t_tiles <= t_stream || pl->units < 2) {
+    if (pl->units >= 2) {
+      for (int s = 2; s * pl->tiles <= sm_count && s <= pl->k_tiles; ++s) {
+        const double upc = double((pl->k_tiles + s - 1) / s);
+        const double c = stream_us(upc, s * pl->tiles, pl->n_tile) + epi_us(pl->n_tile) + 2.0 + 0.02 * pl->n_tile;
+        if (c < best) { best = c; best_split = s; }
+      }
+      long long g = sm_count;
+      if (pl->units / 2 < g) g = pl->units / 2;                 // at least two K tiles per CTA
+      if (g > 0 && pl->tiles % g != 0) {
+        const double c = stream_us(double(pl->units) / g, int(g), pl->n_tile) + epi_us(pl->n_tile) + 3.0 + 0.05 * pl->n_tile;
+        if (c < best) { best = c; best_split = -1; }
+      }
+    }
+    if (best_split == 1) {
       geometry(256);
       pl->tile_granular = 1;
-      pl->grid = pl->tiles < sm_count ? pl->tiles : sm_count;
+      pl->grid = grid_t;
+    } else if (best_split > 1) {
+      pl->tile_granular = 0;
+      pl->grid = best_split * pl->tiles;
     } else {
       pl->tile_granular = 0;
       long long g = sm_count;
-      if (pl->units / 2 < g) g = pl->units / 2;                 // at least two K tiles per CTA
+      if (pl->units / 2 < g) g = pl->units / 2;
       pl->grid = int(g);
     }
   } else {
@@ -945,10 +975,11 @@ extern "C" int64_t ri_fp4_gemm_counter_bytes(int m, int n) {
 
 extern "C" int ri_fp4_gemm_auto_splits(int m, int n, int k, int fmt, int layout) {
   DeviceInfo di;
-  if (device_info(&di)) return -1;
+  int sms = 148;                                   // planning without a visible device assumes a B200
+  if (device_info(&di) == 0) sms = di.sm_count;
   Plan pl;
-  if (make_plan(m, n, k, fmt, layout, 0, di.sm_count, &pl)) return -1;
-  return pl.tile_granular ? 1 : (pl.grid + pl.tiles - 1) / pl.tiles + 1;
+  if (make_plan(m, n, k, fmt, layout, 0, sms, &pl)) return -1;
+  return pl.tile_granular ? 1 : (pl.grid + pl.tiles - 1) / pl.tiles + (pl.grid % pl.tiles ? 1 : 0);
 }
 
 extern "C" int64_t ri_fp4_gemm_workspace_bytes(int m, int n, int k, int fmt, int layout, int splits) {
