@@ -1,30 +1,24 @@
 // ResAttn: residue-compensated paged NVFP4-KV decode attention (one query token per sequence).
 //
-// HBM-bound streaming kernel.  One CTA per (KV split, KV head, sequence), four independent
-// warps per CTA.  Each warp walks its own 16-token chunks of the sequence through a private ring
-// of shared-memory stages that one lane fills with bulk async copies (cp.async.bulk +
-// mbarrier::complete_tx) of the chunk's K codes, K scales, V codes and V scales -- 1-D TMA copies
-// of whole page slices, nothing else touches HBM.  Per chunk:
-//   * K and V nibbles are expanded to FP16 exactly (E2M1 x E4M3 fits FP16) and multiplied on
-//     the legacy tensor-core path (mma.sync m16n8k16, FP32 accumulate);
-//   * the 16 MMA rows hold the NVFP4 query in rows 0-7 and its NVFP4 residue in rows 8-15, so the
-//     base and residue scores of one head land in the same thread and the fold is one add;
-//   * online softmax with warp-shuffle row maxima and a lazy rescale (only when the maximum moves
-//     by more than 2^8), row sums kept in unrounded FP32.
-// The query is quantised in the CTA prologue with the same arithmetic as the grouped-Q quantiser
-// (bit-identical codes).  Warps merge through shared memory; KV splits write (o, l, m) partials that
-// a second kernel merges in split order (deterministic).
+// The query is quantised in the CTA prologue to NVFP4 plus an NVFP4 residue with the arithmetic of
+// the grouped-Q quantiser (bit-identical codes); the scores of both are added, so the K cache is read
+// once and nothing but the 4-bit KV codes and their E4M3 block scales crosses HBM.  The kernel below
+// computes the scores on the block-scaled FP4 tensor cores (tcgen05) and the P.V product on mma.sync
+// with an online softmax (lazy rescale: only when a row maximum moves by more than 2^8, row sums in
+// unrounded FP32).  KV splits write (o, l, m) partials that a second kernel merges in split order
+// (deterministic).
 //
 // Stands in for the reference's CuTeDSL decode kernel and its reducers (ShawRong/ResInfer
 // csrc/resattn/kernel_paged_decode.py:722-2433, 2729-2861).
+#include <cstdlib>
+
 #include "common.cuh"
 #include "resinfer_b200.h"
+#include "tc05.cuh"
 
 namespace ri {
 namespace {
 
-constexpr int kWarps = 4;
-constexpr int kChunk = 16;                 // tokens per pipeline stage
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLazyThreshold = 8.0f;     // rescale only when the row maximum grows by > 2^8
 
@@ -44,6 +38,7 @@ struct AttnParams {
   uint8_t* q_pack; uint8_t* q_sf;          // optional copies of the quantised query
   int splits, q_residue, stages;
   int32_t* status;
+  long long* trace;                        // development builds only (RI_ATTN_PROFILE)
 };
 
 __device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -64,69 +59,131 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// =================================================================================================
+// Tensor-memory version: Q.K^T on the block-scaled FP4 tensor cores (tcgen05), P.V on mma.sync.
+//
+// One CTA per (KV split, KV head, sequence), 24 warps, tiles of 128 tokens:
+//   warps 0-3  front end.  All four move the tile's K block scales from shared to tensor memory
+//              (one warp per 32-lane quarter); warp 0 then issues
+//              S^T[128 tokens x 16] = K[128 x D] . Qpack[16 x D]^T as D/64 tcgen05.mma
+//              kind::mxf4nvf4.block_scale instructions -- the K codes and E4M3 scales are consumed
+//              as stored, nothing is dequantised for the scores.  Qpack rows 0-7 are the NVFP4
+//              query heads of the group, rows 8-15 their NVFP4 residues.
+//   warps 4-7  copy producers: 16-byte cp.async copies of the K codes (written in the operand
+//              swizzle), V codes and both scale arrays, 32 rows of the tile per warp.
+//   warps 8-23 consumers.  A consumer reads its quarter of S^T from tensor memory, folds base +
+//              residue columns, runs the online softmax for 16 tokens (head_dim 128) or the 32 tokens
+//              of the quarter (head_dim 256) and accumulates P.V for 64 of the output columns, with V
+//              expanded to FP16 on the fly (exact) and multiplied on mma.sync m16n8k16.  Warps that
+//              share tokens repeat the (cheap) softmax so that sixteen warps hide each other's
+//              latencies; the accumulators of a warp are only 8 n-tiles.
+// S is double buffered in tensor memory, so the MMA of tile i+1 runs under the softmax of tile i.
+// Every mbarrier wait is bounded (status word + normal teardown on expiry).
+// =================================================================================================
+namespace tcattn {
+using namespace tc;
+// per-tile event times of CTA (0,0,0) in development builds: row `ev`, first 32 tiles
+__device__ __forceinline__ void attn_event(const AttnParams& p, int ev, int tile) {
+#ifdef RI_ATTN_PROFILE
+  if (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tile < 32) p.trace[ev * 32 + tile] = clock64();
+#endif
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+constexpr int kTile = 128;
+constexpr int kFront = 4, kCons = 16;
+constexpr int kProd = 4;                                    // copy producer warps, 32 rows of a tile each
+constexpr int kFirstCons = kFront + kProd;
+constexpr int kThreadsTc = (kFront + kProd + kCons) * 32;   // 768
+constexpr int kTmemColsTc = 128;
+constexpr int kColS = 0, kColSfa = 32, kColSfb = 64;
+constexpr int kMaxStagesTc = 12;
+constexpr int kHeaderBytes = 20 * 1024;       // Qpack operand (2 KB), its scales (1 KB), score staging (16 KB)
+constexpr int kColsPerWarp = 64;              // output columns a consumer accumulates
+
 template <int D>
-struct Cfg {
-  static constexpr int kKSteps = D / 16;            // QK k-steps
-  static constexpr int kNTiles = D / 8;             // PV n-tiles
+struct TCfg {
   static constexpr int kRowBytes = D / 2;
   static constexpr int kSfPerRow = D / 16;
-  static constexpr int kCodesBytes = kChunk * kRowBytes;
-  static constexpr int kSfBytes = kChunk * kSfPerRow;
-  static constexpr int kStageBytes = 2 * (kCodesBytes + kSfBytes);
-  static constexpr int kQFragBytes = kKSteps * 32 * 16;
+  static constexpr int kMma = D / 64;
+  static constexpr int kKBytes = kTile * kRowBytes;
+  static constexpr int kSfBytes = kTile * kSfPerRow;
+  static constexpr int kStageBytes = 2 * kKBytes + 2 * kSfBytes;
+  static constexpr int kOffV = kKBytes, kOffKsf = 2 * kKBytes, kOffVsf = 2 * kKBytes + kSfBytes;
+  static constexpr uint32_t kLayout = D == 128 ? 4u : 2u;      // 64-byte / 128-byte swizzle (row = D/2 bytes)
+  static constexpr uint32_t kSbo = 8 * kRowBytes;
+  static constexpr int kChunksPerWarp = D == 128 ? 1 : 2;      // 16-token chunks a consumer warp handles per tile
 };
 
+// byte offset of (row, byte) in a K-major operand tile with rows of D/2 bytes and the matching swizzle
 template <int D>
-__global__ void __launch_bounds__(kWarps * 32) resattn_decode_kernel(const AttnParams p) {
-  using C = Cfg<D>;
-  extern __shared__ __align__(128) uint8_t smem[];
-  __shared__ __align__(8) uint64_t bars[kWarps][8];
+__device__ __forceinline__ uint32_t swz_off(int row, int byte) {
+  const int chunk = byte >> 4;
+  if constexpr (D == 128) return row * 64 + (((chunk ^ ((row >> 1) & 3)) << 4) | (byte & 15));
+  else return row * 128 + (((chunk ^ (row & 7)) << 4) | (byte & 15));
+}
+
+template <int D>
+__global__ void __launch_bounds__(kThreadsTc, 1)
+resattn_tc_kernel(const AttnParams p) {
+  using C = TCfg<D>;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[kMaxStagesTc];
+  __shared__ __align__(8) uint64_t bar_empty[kMaxStagesTc];
+  __shared__ __align__(8) uint64_t bar_sfull[2];
+  __shared__ __align__(8) uint64_t bar_sempty[2];
+  __shared__ uint32_t tmem_slot;
   __shared__ volatile int abort_flag;
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* q_op = smem;                                        // [16][D/2] swizzled FP4 codes
+  uint8_t* qsf_s = smem + 2048;                                // [16][D/16] E4M3 scales
+  float* sbuf = reinterpret_cast<float*>(smem + 3072);         // [16 warps][32 tokens][8 heads]
+  uint8_t* stage0 = smem + kHeaderBytes;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tq = lane & 3, nq = lane >> 2;
   const int split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
   const int G = p.group;
+  const int S = p.stages;
 
-  uint4* q_frag = reinterpret_cast<uint4*>(smem);                       // [kKSteps][32] A fragments
-  uint8_t* stage_base = smem + C::kQFragBytes + warp * p.stages * C::kStageBytes;
-
-  if (threadIdx.x == 0) abort_flag = 0;
-  if (lane == 0) {
-    for (int s = 0; s < p.stages; ++s) mbar_init(smem_u32(&bars[warp][s]), 1);
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), kProd * 32);    // one arrival per producer lane
+      mbar_init(smem_u32(&bar_empty[s]), kCons);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&bar_sfull[s]), 1);
+      mbar_init(smem_u32(&bar_sempty[s]), kCons);
+    }
+    abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  // zero the fragment area (rows of heads >= G and, without residue, rows 8-15 stay zero)
-  for (int i = threadIdx.x; i < C::kQFragBytes / 16; i += blockDim.x) q_frag[i] = make_uint4(0, 0, 0, 0);
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_slot)), "r"(kTmemColsTc) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  for (int i = threadIdx.x; i < 3072 / 16; i += blockDim.x) reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  tc_fence_before();
   __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
 
   // ---------------------------------------------------------------- query prologue
-  // thread (g, blk) quantises one 16-block of head g to NVFP4 + NVFP4 residue (global scale 1)
-  // and scatters the dequantised FP16 values into mma A-fragment order:
-  //   value d of head g -> k-step s, lane g*4+tq, register {a0|a2} (base) / {a1|a3} (residue)
-  //   with d = (D/4)*tq + 4*s + e, e in 0..3  (the same permutation is applied to K below)
+  // thread (g, blk) quantises one 16-block of head g to NVFP4 + NVFP4 residue (global scale 1, the
+  // arithmetic of the grouped-Q quantiser) and stores the codes as the MMA B operand
   if (threadIdx.x < G * C::kSfPerRow) {
     const int g = threadIdx.x / C::kSfPerRow, blk = threadIdx.x % C::kSfPerRow;
     float v[16];
     load16(p.q + (int64_t(b) * p.hq + hkv * G + g) * D + blk * 16, v);
     BlockQ bq = quant_mext16(v, 1.0f, 1.0f);
-    const float sfb = decode_e4m3(bq.sf), sfr = decode_e4m3(bq.sf_res);
-    __half* qh = reinterpret_cast<__half*>(smem);
-    const uint32_t bc[2] = {bq.base.x, bq.base.y}, rc[2] = {bq.res.x, bq.res.y};
-#pragma unroll
-    for (int w = 0; w < 2; ++w) {
-      float hb[8], hr[8];
-      e2m1x8_to_float(bc[w], hb);
-      e2m1x8_to_float(rc[w], hr);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int d = blk * 16 + w * 8 + i;
-        const int t = d / (D / 4), within = d % (D / 4), s = within >> 2, e = within & 3;
-        const int base_idx = ((s * 32 + g * 4 + t) * 4 + (e >> 1) * 2) * 2 + (e & 1);   // in halves
-        qh[base_idx] = __float2half_rn(hb[i] * sfb);
-        if (p.q_residue) qh[base_idx + 2] = __float2half_rn(hr[i] * sfr);               // a1 / a3
-      }
+    *reinterpret_cast<uint2*>(q_op + swz_off<D>(g, blk * 8)) = bq.base;
+    qsf_s[g * C::kSfPerRow + blk] = bq.sf;
+    if (p.q_residue) {
+      *reinterpret_cast<uint2*>(q_op + swz_off<D>(8 + g, blk * 8)) = bq.res;
+      qsf_s[(8 + g) * C::kSfPerRow + blk] = bq.sf_res;
     }
     if (p.q_pack && split == 0) {
       const int P = G == 4 ? 8 : 16;
@@ -138,218 +195,313 @@ __global__ void __launch_bounds__(kWarps * 32) resattn_decode_kernel(const AttnP
       sfp[sf_offset<16>(P / 2 + g, blk, D)] = bq.sf_res;
     }
   }
+  // the operand was written with ordinary stores: make it visible to the tensor core's async reads
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   __syncthreads();
 
-  // ---------------------------------------------------------------- this CTA's chunk range
+  // ---------------------------------------------------------------- this CTA's tile range
   const int L = min(max(__ldg(p.seq_lens + b), 0), int(p.bt_stride) * p.page_size);
-  const int n_chunks = (L + kChunk - 1) / kChunk;
-  const int per_split = (n_chunks + p.splits - 1) / p.splits;
-  const int c_begin = min(split * per_split, n_chunks);
-  const int c_end = min(c_begin + per_split, n_chunks);
-  const int my_chunks = c_end > c_begin + warp ? (c_end - c_begin - warp + kWarps - 1) / kWarps : 0;
+  const int n_tiles = (L + kTile - 1) / kTile;
+  const int per_split = (n_tiles + p.splits - 1) / p.splits;
+  const int t_begin = min(split * per_split, n_tiles);
+  const int t_end = min(t_begin + per_split, n_tiles);
+  const int my_tiles = t_end - t_begin;
   const int32_t* bt = p.block_tables + int64_t(b) * p.bt_stride;
 
-  auto issue = [&](int i) {     // lane 0: fill stage i % stages with this warp's i-th chunk
-    const int chunk = c_begin + warp + i * kWarps;
-    const int t0 = chunk * kChunk;
-    int64_t page = __ldg(bt + t0 / p.page_size);
-    page = page < 0 ? 0 : (page >= p.num_pages ? p.num_pages - 1 : page);
-    const int64_t row = (page * p.hkv + hkv) * p.page_size + (t0 % p.page_size);
-    uint8_t* st = stage_base + (i % p.stages) * C::kStageBytes;
-    const uint32_t bar = smem_u32(&bars[warp][i % p.stages]);
-    mbar_expect_tx(bar, C::kStageBytes);
-    bulk_load_1d(smem_u32(st), p.k_data + row * C::kRowBytes, C::kCodesBytes, bar);
-    bulk_load_1d(smem_u32(st + C::kCodesBytes), p.v_data + row * C::kRowBytes, C::kCodesBytes, bar);
-    bulk_load_1d(smem_u32(st + 2 * C::kCodesBytes), p.k_sf + row * C::kSfPerRow, C::kSfBytes, bar);
-    bulk_load_1d(smem_u32(st + 2 * C::kCodesBytes + C::kSfBytes), p.v_sf + row * C::kSfPerRow, C::kSfBytes, bar);
-  };
-  if (lane == 0)
-    for (int i = 0; i < min(my_chunks, p.stages); ++i) issue(i);
-
-  // query fragments: registers for D = 128, re-read from shared memory for D = 256
-  uint32_t qreg[D == 128 ? C::kKSteps : 1][4];
-  if constexpr (D == 128) {
+  float oacc[8][4];
 #pragma unroll
-    for (int s = 0; s < C::kKSteps; ++s) {
-      uint4 f = q_frag[s * 32 + lane];
-      qreg[s][0] = f.x; qreg[s][1] = f.y; qreg[s][2] = f.z; qreg[s][3] = f.w;
+  for (int j = 0; j < 8; ++j) oacc[j][0] = oacc[j][1] = oacc[j][2] = oacc[j][3] = 0.f;
+  float m_run = -INFINITY, l_run = 0.f;
+  const int tq = lane & 3, nq = lane >> 2;
+  // consumer coordinates: tensor-memory quarter q, token half h (head_dim 128 only), column group e
+  const int cw = warp - kFirstCons;
+  const int cq = warp & 3, ck = cw >> 2;
+  const int ch_half = D == 128 ? (ck & 1) : 0;
+  const int ce = D == 128 ? (ck >> 1) : ck;
+
+  if (warp < kFront) {
+    // ============================================================ front end
+    const int q = warp;
+    const uint32_t lane_base = tmem_base + (uint32_t(q * 32) << 16);
+    // Qpack block scales -> tensor memory (rows 0-15 live in lanes 0-15 of column 0 of each group of 4)
+#pragma unroll
+    for (int j = 0; j < C::kMma; ++j) {
+      uint4 w = make_uint4(0, 0, 0, 0);
+      if (lane < 16) w.x = *reinterpret_cast<const uint32_t*>(qsf_s + lane * C::kSfPerRow + 4 * j);
+      tmem_st4(lane_base + kColSfb + 4 * j, w);
     }
-  }
-
-  float oacc[C::kNTiles][4];
-#pragma unroll
-  for (int j = 0; j < C::kNTiles; ++j) oacc[j][0] = oacc[j][1] = oacc[j][2] = oacc[j][3] = 0.f;
-  float m_run = -INFINITY, l_run = 0.f;     // row nq (head g = nq), log2 domain
-  bool alive = true;
-
-  for (int i = 0; i < my_chunks && alive; ++i) {
-    const int stg = i % p.stages;
-    const int chunk = c_begin + warp + i * kWarps;
-    const int t0 = chunk * kChunk;
-    const int valid = min(L - t0, kChunk);
-    // every lane polls the stage barrier; the warp takes one decision
-    const bool got = mbar_wait(smem_u32(&bars[warp][stg]), (i / p.stages) & 1, &abort_flag);
-    if (!__all_sync(0xffffffffu, got)) { alive = false; break; }
-    const uint8_t* st = stage_base + stg * C::kStageBytes;
-    const uint8_t* kc = st;
-    const uint8_t* vc = st + C::kCodesBytes;
-    const uint8_t* ksf = st + 2 * C::kCodesBytes;
-    const uint8_t* vsf = ksf + C::kSfBytes;
-
-    // ------------------------------------------------ S = K . (q + r)^T for 2 x 8 tokens
-    float sacc[2][4];
-#pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
-      sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
-      const int row = nt * 8 + nq;
-      // this lane's quarter of the token row: D/4 codes = D/8 bytes, D/64 scale bytes
-      constexpr int kWords = D / 32;                       // 32-bit words per lane
-      uint32_t w[kWords];
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+    const uint32_t idesc = (1u << 7) | (1u << 10) | (uint32_t(16 >> 3) << 17) | (uint32_t(kTile >> 4) << 24);
+    const uint64_t b_desc = desc_kmajor(smem_u32(q_op), C::kSbo, C::kLayout);
+    for (int i = 0; i < my_tiles; ++i) {
+      const int stg = i % S, sb = i & 1;
+      bool got = true;
+      if (lane == 0) {
+        got = mbar_wait(smem_u32(&bar_full[stg]), (i / S) & 1, &abort_flag, 2);
+        if (got && i >= 2) got = mbar_wait(smem_u32(&bar_sempty[sb]), ((i >> 1) - 1) & 1, &abort_flag, 3);
+      }
+      if (!__all_sync(0xffffffffu, got)) break;
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // cp.async data -> tensor-core reads
+      tc_fence_after();
+      if (warp == 0 && lane == 0) attn_event(p, 0, i);
+      const uint8_t* st = stage0 + stg * C::kStageBytes;
+      const uint8_t* ksf = st + C::kOffKsf;
+      // K block scales of the tile -> scale set sb: lane l supplies rows l, l+32, l+64, l+96
       if constexpr (D == 128) {
-        uint4 t = *reinterpret_cast<const uint4*>(kc + row * C::kRowBytes + tq * 16);
-        w[0] = t.x; w[1] = t.y; w[2] = t.z; w[3] = t.w;
+        uint2 r0 = *reinterpret_cast<const uint2*>(ksf + (lane) * 8), r1 = *reinterpret_cast<const uint2*>(ksf + (lane + 32) * 8);
+        uint2 r2 = *reinterpret_cast<const uint2*>(ksf + (lane + 64) * 8), r3 = *reinterpret_cast<const uint2*>(ksf + (lane + 96) * 8);
+        const uint4 a[2] = {make_uint4(r0.x, r1.x, r2.x, r3.x), make_uint4(r0.y, r1.y, r2.y, r3.y)};
+        tmem_st8(lane_base + kColSfa + sb * 16, a);
       } else {
-        const uint4* src = reinterpret_cast<const uint4*>(kc + row * C::kRowBytes + tq * 32);
-        uint4 t0v = src[0], t1v = src[1];
-        w[0] = t0v.x; w[1] = t0v.y; w[2] = t0v.z; w[3] = t0v.w;
-        w[4] = t1v.x; w[5] = t1v.y; w[6] = t1v.z; w[7] = t1v.w;
+        uint4 r0 = *reinterpret_cast<const uint4*>(ksf + (lane) * 16), r1 = *reinterpret_cast<const uint4*>(ksf + (lane + 32) * 16);
+        uint4 r2 = *reinterpret_cast<const uint4*>(ksf + (lane + 64) * 16), r3 = *reinterpret_cast<const uint4*>(ksf + (lane + 96) * 16);
+        const uint4 a[4] = {make_uint4(r0.x, r1.x, r2.x, r3.x), make_uint4(r0.y, r1.y, r2.y, r3.y),
+                            make_uint4(r0.z, r1.z, r2.z, r3.z), make_uint4(r0.w, r1.w, r2.w, r3.w)};
+        tmem_st16(lane_base + kColSfa + sb * 16, a);
       }
-      __half2 sc[D / 64];
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      tc_fence_before();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (warp == 0) {
+        tc_fence_after();
+        if (elect_one()) {
+          const uint64_t a_desc = desc_kmajor(smem_u32(st), C::kSbo, C::kLayout);
 #pragma unroll
-      for (int u = 0; u < D / 64; ++u) {
-        __half h = e4m3_to_half(ksf[row * C::kSfPerRow + tq * (D / 64) + u]);
-        sc[u] = __half2(h, h);
+          for (int j = 0; j < C::kMma; ++j)
+            mma_fp4<false>(tmem_base + kColS + sb * 16, a_desc + uint64_t(2 * j), b_desc + uint64_t(2 * j), idesc,
+                           tmem_base + kColSfa + sb * 16 + 4 * j, tmem_base + kColSfb + 4 * j, j > 0 ? 1u : 0u);
+          mma_commit(smem_u32(&bar_sfull[sb]));
+        }
+        __syncwarp();
+        if (lane == 0) attn_event(p, 1, i);
       }
+    }
+  } else if (warp < kFirstCons) {
+    // ============================================================ copy producers
+    // Ampere-style 16-byte async copies, one per lane and instruction: with 16-token pages a tile is
+    // 8 scattered slices x 4 arrays, far too many requests for the bulk-copy engine (measured: more
+    // than 100 cycles of issue time per bulk copy), while a warp of cp.async moves 512 bytes per
+    // instruction.  Producer warp w owns rows 32w..32w+31 of every tile (two page slices); the K
+    // codes are written in the operand swizzle by address arithmetic.
+    constexpr int kCpr = C::kRowBytes / 16;                    // 16-byte chunks per code row
+    const int pw = warp - kFront;
+    for (int i = 0; i < my_tiles; ++i) {
+      const int tile = t_begin + i, stg = i % S;
+      const int tok0 = tile * kTile + 32 * pw;
+      const int rows = min(max(((L - tok0) + 15) & ~15, 0), 32);     // rows of this warp that exist (0, 16 or 32)
+      // pool row of the first token of slice `lane` (looked up before the wait to hide the latency)
+      int64_t base_row = 0;
+      if (lane * 16 < rows) {
+        const int t0 = tok0 + lane * 16;
+        int64_t page = __ldg(bt + t0 / p.page_size);
+        page = page < 0 ? 0 : (page >= p.num_pages ? p.num_pages - 1 : page);
+        base_row = (page * p.hkv + hkv) * p.page_size + (t0 % p.page_size);
+      }
+      const int64_t base0 = __shfl_sync(0xffffffffu, base_row, 0), base1 = __shfl_sync(0xffffffffu, base_row, 1);
+      bool free_ok = true;
+      if (i >= S && lane == 0) free_ok = mbar_wait(smem_u32(&bar_empty[stg]), ((i / S) - 1) & 1, &abort_flag, 4);
+      if (!__all_sync(0xffffffffu, free_ok)) break;
+      uint8_t* st = stage0 + stg * C::kStageBytes;
 #pragma unroll
-      for (int s = 0; s < C::kKSteps; ++s) {
-        const uint32_t bits = (w[s >> 1] >> (16 * (s & 1))) & 0xFFFFu;   // 4 codes of this k-step
-        const __half2 scale = sc[s >> 2];
-        const uint32_t b0 = h2_bits(__hmul2(e2m1x2_to_half2(bits & 0xFFu), scale));
-        const uint32_t b1 = h2_bits(__hmul2(e2m1x2_to_half2(bits >> 8), scale));
-        if constexpr (D == 128) {
-          mma_f16(sacc[nt], qreg[s], b0, b1);
-        } else {
-          uint4 f = q_frag[s * 32 + lane];
-          const uint32_t a[4] = {f.x, f.y, f.z, f.w};
-          mma_f16(sacc[nt], a, b0, b1);
+      for (int it = 0; it < 32 * kCpr / 32; ++it) {
+        const int idx = it * 32 + lane;
+        const int r = idx / kCpr, chn = idx % kCpr;            // row inside this warp's 32
+        if (r < rows) {
+          const int row = 32 * pw + r;
+          const int64_t br = (r < 16 ? base0 : base1) + (r & 15);
+          cp_async16(smem_u32(st + swz_off<D>(row, chn * 16)), p.k_data + br * C::kRowBytes + chn * 16);
+          cp_async16(smem_u32(st + C::kOffV + row * C::kRowBytes + chn * 16), p.v_data + br * C::kRowBytes + chn * 16);
         }
       }
-    }
-    // fold residue rows (8-15) onto base rows (0-7): both live in this thread
-    float sv[4];
-    sv[0] = (sacc[0][0] + sacc[0][2]) * p.score_scale_log2;   // token 2tq
-    sv[1] = (sacc[0][1] + sacc[0][3]) * p.score_scale_log2;   // token 2tq+1
-    sv[2] = (sacc[1][0] + sacc[1][2]) * p.score_scale_log2;   // token 8+2tq
-    sv[3] = (sacc[1][1] + sacc[1][3]) * p.score_scale_log2;   // token 9+2tq
-    if (valid < kChunk) {
-      if (2 * tq >= valid) sv[0] = -INFINITY;
-      if (2 * tq + 1 >= valid) sv[1] = -INFINITY;
-      if (8 + 2 * tq >= valid) sv[2] = -INFINITY;
-      if (9 + 2 * tq >= valid) sv[3] = -INFINITY;
-    }
-    float mx = fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3]));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-    if (mx > m_run + kLazyThreshold || m_run == -INFINITY) {
-      const float f = fast_exp2(m_run - mx);                // 0 on the first chunk
-      m_run = mx;
-      l_run *= f;
+      {
+        const int byte = lane * 16;                            // 32 rows x D/16 scale bytes = 256 or 512 bytes
 #pragma unroll
-      for (int j = 0; j < C::kNTiles; ++j) { oacc[j][0] *= f; oacc[j][1] *= f; }
-    }
-    float pv[4];
-#pragma unroll
-    for (int e = 0; e < 4; ++e) pv[e] = fast_exp2(sv[e] - m_run);
-    l_run += (pv[0] + pv[1]) + (pv[2] + pv[3]);
-    uint32_t pa[4];
-    pa[0] = h2_bits(__floats2half2_rn(pv[0], pv[1]));
-    pa[1] = 0u;
-    pa[2] = h2_bits(__floats2half2_rn(pv[2], pv[3]));
-    pa[3] = 0u;
-
-    // ------------------------------------------------ O += P . V
-    // lane (tq, nq) owns token rows {2tq, 2tq+1, 2tq+8, 2tq+9} and the D/8 head-dim columns
-    // d = (D/8)*nq + j (one 16-wide (or two) scale block(s)); n-tile j, column nq <-> d
-    constexpr int kVWords = D / 64;                         // 32-bit words per row per lane
-    uint32_t vw[4][kVWords];
-    __half vs[4][D / 128];
-#pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      const int row = 2 * tq + (r & 1) + (r >> 1) * 8;
-      const bool ok = row < valid;
-      if constexpr (D == 128) {
-        uint2 t = ok ? *reinterpret_cast<const uint2*>(vc + row * C::kRowBytes + nq * 8) : make_uint2(0, 0);
-        vw[r][0] = t.x; vw[r][1] = t.y;
-      } else {
-        uint4 t = ok ? *reinterpret_cast<const uint4*>(vc + row * C::kRowBytes + nq * 16) : make_uint4(0, 0, 0, 0);
-        vw[r][0] = t.x; vw[r][1] = t.y; vw[r][2] = t.z; vw[r][3] = t.w;
+        for (int it = 0; it < 32 * C::kSfPerRow / 512; ++it) {
+          const int bb = byte + it * 512;
+          const int r = bb / C::kSfPerRow, within = bb % C::kSfPerRow;
+          if (bb < 32 * C::kSfPerRow && r < rows) {
+            const int64_t br = (r < 16 ? base0 : base1) + (r & 15);
+            const int dst = (32 * pw) * C::kSfPerRow + bb;
+            cp_async16(smem_u32(st + C::kOffKsf + dst), p.k_sf + br * C::kSfPerRow + within);
+            cp_async16(smem_u32(st + C::kOffVsf + dst), p.v_sf + br * C::kSfPerRow + within);
+          }
+        }
+        if constexpr (32 * C::kSfPerRow < 512) {
+          const int r = byte / C::kSfPerRow;
+          if (byte < 32 * C::kSfPerRow && r < rows) {
+            const int64_t br = (r < 16 ? base0 : base1) + (r & 15);
+            const int dst = (32 * pw) * C::kSfPerRow + byte;
+            cp_async16(smem_u32(st + C::kOffKsf + dst), p.k_sf + br * C::kSfPerRow);
+            cp_async16(smem_u32(st + C::kOffVsf + dst), p.v_sf + br * C::kSfPerRow);
+          }
+        }
       }
-#pragma unroll
-      for (int u = 0; u < D / 128; ++u)
-        vs[r][u] = ok ? e4m3_to_half(vsf[row * C::kSfPerRow + nq * (D / 128) + u]) : __half(0.f);
+      // every lane arrives once its own copies have landed (barrier count = producer lanes)
+      asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&bar_full[stg])) : "memory");
+      if (pw == 0 && lane == 0) attn_event(p, 2, i);
     }
+  } else {
+    // ============================================================ consumers
+    const uint32_t lane_base = tmem_base + (uint32_t(cq * 32) << 16);
+    float* my_s = sbuf + cw * 32 * 8;
+    for (int i = 0; i < my_tiles; ++i) {
+      const int stg = i % S, sb = i & 1;
+      const int tile = t_begin + i;
+      bool got = true;
+      if (lane == 0) {
+        got = mbar_wait(smem_u32(&bar_sfull[sb]), (i >> 1) & 1, &abort_flag, 5);
+        // the V codes and scales of the stage were written by the copy engine: observe its barrier too
+        if (got) got = mbar_wait(smem_u32(&bar_full[stg]), (i / S) & 1, &abort_flag, 6);
+      }
+      if (!__all_sync(0xffffffffu, got)) break;
+      tc_fence_after();
+      if (cw == 0 && lane == 0) attn_event(p, 3, i);
+      float r[16];
+      tmem_ld16(lane_base + kColS + sb * 16, r);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_sempty[sb]));
+      // fold the residue columns onto the base columns, move to the log2 domain, stage for the
+      // fragment-order reads below: token `lane` of the quarter, 8 heads
+      {
+        float4 lo, hi;
+        lo.x = (r[0] + r[8]) * p.score_scale_log2;  lo.y = (r[1] + r[9]) * p.score_scale_log2;
+        lo.z = (r[2] + r[10]) * p.score_scale_log2; lo.w = (r[3] + r[11]) * p.score_scale_log2;
+        hi.x = (r[4] + r[12]) * p.score_scale_log2; hi.y = (r[5] + r[13]) * p.score_scale_log2;
+        hi.z = (r[6] + r[14]) * p.score_scale_log2; hi.w = (r[7] + r[15]) * p.score_scale_log2;
+        if (D == 256 || (lane >> 4) == ch_half) {
+          reinterpret_cast<float4*>(my_s + lane * 8)[0] = lo;
+          reinterpret_cast<float4*>(my_s + lane * 8)[1] = hi;
+        }
+      }
+      __syncwarp();
+      if (cw == 0 && lane == 0) attn_event(p, 4, i);
+      const uint8_t* st = stage0 + stg * C::kStageBytes;
 #pragma unroll
-    for (int j = 0; j < C::kNTiles; j += 2) {
-      const int word = j >> 3, sh = (j & 7) * 4;            // byte j/2 of the lane's row slice
-      const int blk = j >> 4;                               // scale block inside the slice
-      const __half2 s01 = __halves2half2(vs[0][blk], vs[1][blk]);
-      const __half2 s89 = __halves2half2(vs[2][blk], vs[3][blk]);
-      const uint32_t x0 = h2_bits(e2m1x2_to_half2((vw[0][word] >> sh) & 0xFFu));   // row 2tq  : d, d+1
-      const uint32_t x1 = h2_bits(e2m1x2_to_half2((vw[1][word] >> sh) & 0xFFu));   // row 2tq+1
-      const uint32_t x8 = h2_bits(e2m1x2_to_half2((vw[2][word] >> sh) & 0xFFu));
-      const uint32_t x9 = h2_bits(e2m1x2_to_half2((vw[3][word] >> sh) & 0xFFu));
-      // regroup (d, d+1) pairs of two tokens into (token, token+1) pairs of one column
-      const uint32_t b0_lo = h2_bits(__hmul2(bits_h2(__byte_perm(x0, x1, 0x5410)), s01));
-      const uint32_t b0_hi = h2_bits(__hmul2(bits_h2(__byte_perm(x0, x1, 0x7632)), s01));
-      const uint32_t b1_lo = h2_bits(__hmul2(bits_h2(__byte_perm(x8, x9, 0x5410)), s89));
-      const uint32_t b1_hi = h2_bits(__hmul2(bits_h2(__byte_perm(x8, x9, 0x7632)), s89));
-      mma_f16(oacc[j], pa, b0_lo, b1_lo);
-      mma_f16(oacc[j + 1], pa, b0_hi, b1_hi);
+      for (int c = 0; c < C::kChunksPerWarp; ++c) {
+        const int tok_in_q = D == 128 ? 16 * ch_half : 16 * c;       // first token of the chunk inside the quarter
+        const int tok_in_tile = 32 * cq + tok_in_q;
+        const int valid = min(L - (tile * kTile + tok_in_tile), 16);
+        if (valid <= 0) continue;
+        float sv[4];
+        sv[0] = my_s[(tok_in_q + 2 * tq) * 8 + nq];
+        sv[1] = my_s[(tok_in_q + 2 * tq + 1) * 8 + nq];
+        sv[2] = my_s[(tok_in_q + 2 * tq + 8) * 8 + nq];
+        sv[3] = my_s[(tok_in_q + 2 * tq + 9) * 8 + nq];
+        if (valid < 16) {
+          if (2 * tq >= valid) sv[0] = -INFINITY;
+          if (2 * tq + 1 >= valid) sv[1] = -INFINITY;
+          if (8 + 2 * tq >= valid) sv[2] = -INFINITY;
+          if (9 + 2 * tq >= valid) sv[3] = -INFINITY;
+        }
+        float mx = fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        if (mx > m_run + kLazyThreshold || m_run == -INFINITY) {
+          const float f = fast_exp2(m_run - mx);                // 0 on the first chunk
+          m_run = mx;
+          l_run *= f;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) { oacc[j][0] *= f; oacc[j][1] *= f; }
+        }
+        float pv[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) pv[e] = fast_exp2(sv[e] - m_run);
+        l_run += (pv[0] + pv[1]) + (pv[2] + pv[3]);
+        uint32_t pa[4];
+        pa[0] = h2_bits(__floats2half2_rn(pv[0], pv[1]));
+        pa[1] = 0u;
+        pa[2] = h2_bits(__floats2half2_rn(pv[2], pv[3]));
+        pa[3] = 0u;
+        // O += P . V for this warp's 64 output columns: lane (tq, nq) owns token rows
+        // {2tq, 2tq+1, 2tq+8, 2tq+9} and the 8 columns 64 ce + 8 nq + j (half a scale block)
+        const int col_byte0 = 32 * ce + nq * 4;
+        const int sf_idx0 = 4 * ce + (nq >> 1);
+        uint32_t vw[4];
+        __half vs[4];
+        const uint8_t* vrow = st + C::kOffV + (tok_in_tile + 2 * tq) * C::kRowBytes + col_byte0;
+        const uint8_t* srow = st + C::kOffVsf + (tok_in_tile + 2 * tq) * C::kSfPerRow + sf_idx0;
+#pragma unroll
+        for (int rr = 0; rr < 4; ++rr) {
+          const int dr = (rr & 1) + (rr >> 1) * 8;              // rows 2tq, 2tq+1, 2tq+8, 2tq+9
+          vw[rr] = *reinterpret_cast<const uint32_t*>(vrow + dr * C::kRowBytes);
+          vs[rr] = e4m3_to_half(srow[dr * C::kSfPerRow]);
+        }
+        if (valid < 16) {                                       // rows past the sequence end hold stale bytes
+#pragma unroll
+          for (int rr = 0; rr < 4; ++rr)
+            if (2 * tq + (rr & 1) + (rr >> 1) * 8 >= valid) { vw[rr] = 0u; vs[rr] = __half(0.f); }
+        }
+        const __half2 s01 = __halves2half2(vs[0], vs[1]);
+        const __half2 s89 = __halves2half2(vs[2], vs[3]);
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) {
+          const int sh = j * 4;
+          const uint32_t x0 = h2_bits(e2m1x2_to_half2((vw[0] >> sh) & 0xFFu));
+          const uint32_t x1 = h2_bits(e2m1x2_to_half2((vw[1] >> sh) & 0xFFu));
+          const uint32_t x8 = h2_bits(e2m1x2_to_half2((vw[2] >> sh) & 0xFFu));
+          const uint32_t x9 = h2_bits(e2m1x2_to_half2((vw[3] >> sh) & 0xFFu));
+          const uint32_t b0_lo = h2_bits(__hmul2(bits_h2(__byte_perm(x0, x1, 0x5410)), s01));
+          const uint32_t b0_hi = h2_bits(__hmul2(bits_h2(__byte_perm(x0, x1, 0x7632)), s01));
+          const uint32_t b1_lo = h2_bits(__hmul2(bits_h2(__byte_perm(x8, x9, 0x5410)), s89));
+          const uint32_t b1_hi = h2_bits(__hmul2(bits_h2(__byte_perm(x8, x9, 0x7632)), s89));
+          mma_f16(oacc[j], pa, b0_lo, b1_lo);
+          mma_f16(oacc[j + 1], pa, b0_hi, b1_hi);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_empty[stg]));
+      if (cw == 0 && lane == 0) attn_event(p, 5, i);
     }
-
-    // stage consumed by every lane -> refill it
-    __syncwarp();
-    if (lane == 0 && i + p.stages < my_chunks) issue(i + p.stages);
   }
 
-  // ---------------------------------------------------------------- merge the four warps
+  // ---------------------------------------------------------------- merge the consumer warps
   l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
   l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+  tc_fence_before();
   __syncthreads();                                           // pipeline memory is free now
-  float* o_w = reinterpret_cast<float*>(smem + C::kQFragBytes);            // [warp][8][D]
-  float* m_w = o_w + kWarps * 8 * D;                                          // [warp][8]
-  float* l_w = m_w + kWarps * 8;
+  float* o_w = reinterpret_cast<float*>(stage0);              // [16 warps][8 heads][64 columns]
+  float* m_w = o_w + kCons * 8 * kColsPerWarp;
+  float* l_w = m_w + kCons * 8;
+  if (warp >= kFirstCons) {
 #pragma unroll
-  for (int j = 0; j < C::kNTiles; ++j) {
-    // accumulator columns 2tq / 2tq+1 of n-tile j are head-dim (D/8)*(2tq) + j and (D/8)*(2tq+1) + j
-    o_w[(warp * 8 + nq) * D + (D / 8) * (2 * tq) + j] = oacc[j][0];
-    o_w[(warp * 8 + nq) * D + (D / 8) * (2 * tq + 1) + j] = oacc[j][1];
-  }
-  if (tq == 0) {
-    m_w[warp * 8 + nq] = m_run;
-    l_w[warp * 8 + nq] = l_run;
+    for (int j = 0; j < 8; ++j) {
+      // accumulator columns 2tq / 2tq+1 of n-tile j are columns 8 * (2tq) + j and 8 * (2tq+1) + j of the group
+      o_w[(cw * 8 + nq) * kColsPerWarp + 8 * (2 * tq) + j] = oacc[j][0];
+      o_w[(cw * 8 + nq) * kColsPerWarp + 8 * (2 * tq + 1) + j] = oacc[j][1];
+    }
+    if (tq == 0) {
+      m_w[cw * 8 + nq] = m_run;
+      l_w[cw * 8 + nq] = l_run;
+    }
   }
   __syncthreads();
   const bool failed = abort_flag != 0;
   for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
     const int g = idx / D, d = idx % D;
+    const int e = d >> 6, dc = d & 63;
+    // consumer warps that own column group e: index k = cw >> 2 (k & 1 = token half, k >> 1 = e for
+    // head_dim 128; k = e for head_dim 256), all four quarters
     float mm = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < kWarps; ++w) mm = fmaxf(mm, m_w[w * 8 + g]);
+    for (int w = 0; w < kCons; ++w) {
+      const int k = w >> 2;
+      if ((D == 128 ? (k >> 1) : k) == e) mm = fmaxf(mm, m_w[w * 8 + g]);
+    }
     float o = 0.f, l = 0.f;
-#pragma unroll
-    for (int w = 0; w < kWarps; ++w) {
+    for (int w = 0; w < kCons; ++w) {
+      const int k = w >> 2;
+      if ((D == 128 ? (k >> 1) : k) != e) continue;
       const float mw = m_w[w * 8 + g];
       const float f = mw == -INFINITY ? 0.f : fast_exp2(mw - mm);
-      o += f * o_w[(w * 8 + g) * D + d];
+      o += f * o_w[(w * 8 + g) * kColsPerWarp + dc];
       l += f * l_w[w * 8 + g];
     }
     const int head = hkv * G + g;
     if (p.splits == 1) {
-      const float r = l > 0.f ? p.out_scale / l : 0.f;
+      const float rr = l > 0.f ? p.out_scale / l : 0.f;
       const int64_t oi = (int64_t(b) * p.hq + head) * D + d;
-      if (p.out_f32) static_cast<float*>(p.out)[oi] = o * r;
-      else static_cast<__nv_bfloat16*>(p.out)[oi] = __float2bfloat16_rn(o * r);
+      if (p.out_f32) static_cast<float*>(p.out)[oi] = o * rr;
+      else static_cast<__nv_bfloat16*>(p.out)[oi] = __float2bfloat16_rn(o * rr);
     } else {
       const int64_t slot = (int64_t(split) * p.batch + b) * p.hq + head;
       p.o_part[slot * D + d] = o;
@@ -359,9 +511,36 @@ __global__ void __launch_bounds__(kWarps * 32) resattn_decode_kernel(const AttnP
       }
     }
   }
-  if (failed && threadIdx.x == 0 && p.status) atomicExch(p.status, 1 + int(blockIdx.z));
-  asm volatile("griddepcontrol.launch_dependents;");
+  if (failed && threadIdx.x == 0 && p.status) atomicExch(p.status, 1 + int(blockIdx.z) + (abort_flag << 16));
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColsTc) : "memory");
+  }
 }
+
+template <int D>
+int launch_decode_tc(const AttnParams& p, cudaStream_t st) {
+  using C = TCfg<D>;
+  const int smem = kHeaderBytes + p.stages * C::kStageBytes + 1024;
+  static bool attr_done = false;
+  if (!attr_done) {
+    RI_CUDA(cudaFuncSetAttribute(resattn_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+    attr_done = true;
+  }
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(p.splits, p.hkv, p.batch);
+  cfg.blockDim = dim3(kThreadsTc);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr{};
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  return cuda_status(cudaLaunchKernelEx(&cfg, resattn_tc_kernel<D>, p), "resattn decode launch");
+}
+}  // namespace tcattn
 
 // out[b, h, :] = sum_s 2^(m_s - m) o_s / sum_s 2^(m_s - m) l_s * out_scale, splits in order
 __global__ void resattn_merge_kernel(const float* __restrict__ o_part, const float* __restrict__ l_part,
@@ -386,30 +565,6 @@ __global__ void resattn_merge_kernel(const float* __restrict__ o_part, const flo
     if (out_f32) static_cast<float*>(out)[row * d + c] = o * r;
     else static_cast<__nv_bfloat16*>(out)[row * d + c] = __float2bfloat16_rn(o * r);
   }
-}
-
-template <int D>
-int launch_decode(const AttnParams& p, cudaStream_t st) {
-  using C = Cfg<D>;
-  const int merge_bytes = (kWarps * 8 * D + 2 * kWarps * 8) * 4;
-  int pipe = kWarps * p.stages * C::kStageBytes;
-  const int smem = C::kQFragBytes + (pipe > merge_bytes ? pipe : merge_bytes);
-  static bool attr_done = false;
-  if (!attr_done) {
-    RI_CUDA(cudaFuncSetAttribute(resattn_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
-    attr_done = true;
-  }
-  cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(p.splits, p.hkv, p.batch);
-  cfg.blockDim = dim3(kWarps * 32);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = st;
-  cudaLaunchAttribute attr{};
-  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr.val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = &attr;
-  cfg.numAttrs = 1;
-  return cuda_status(cudaLaunchKernelEx(&cfg, resattn_decode_kernel<D>, p), "resattn decode launch");
 }
 
 }  // namespace
@@ -466,7 +621,10 @@ extern "C" int ri_resattn_decode(const void* q_bf16, const uint8_t* k_data, cons
   p.out_f32 = out_dtype == RI_DTYPE_F32;
   p.q_pack = q_pack; p.q_sf = q_sf;
   p.splits = splits; p.q_residue = q_residue; p.status = status;
-  p.stages = head_dim == 128 ? 6 : 4;
+#ifdef RI_ATTN_PROFILE
+  if (const char* e = getenv("RI_ATTN_TRACE_PTR")) p.trace = reinterpret_cast<long long*>(strtoull(e, nullptr, 16));
+#endif
+  p.stages = head_dim == 128 ? 8 : 4;
   if (splits > 1) {
     const int64_t need = ri_resattn_workspace_bytes(batch, num_q_heads, head_dim, splits);
     RI_CHECK_ARG(workspace != nullptr && workspace_bytes >= need && (reinterpret_cast<uintptr_t>(workspace) & 15) == 0,
@@ -478,7 +636,7 @@ extern "C" int ri_resattn_decode(const void* q_bf16, const uint8_t* k_data, cons
     p.m_part = p.l_part + rows;
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  s = head_dim == 128 ? launch_decode<128>(p, st) : launch_decode<256>(p, st);
+  s = head_dim == 128 ? tcattn::launch_decode_tc<128>(p, st) : tcattn::launch_decode_tc<256>(p, st);
   if (s) return s;
   if (splits > 1) {
     const int64_t rows = int64_t(batch) * num_q_heads;

