@@ -133,43 +133,68 @@ def mext_flops(m, k, n):
 # ------------------------------------------------------------------------------------------------
 # reference arm / CPU baseline: the torch-eager path on host cores
 # ------------------------------------------------------------------------------------------------
-def cpu_eager_sample(repeats: int = 3, shape=("qkv", 5120, 10240), m: int = 16):
-    """Times the eager quantise/dequantise/matmul path (oracle port of the reference's
-    ResidueQuantLinear._forward_residue_qdq) for one case on all host threads."""
+_CPU_INPUTS = {}
+
+
+def cpu_eager_step(m: int = 16):
+    """One bounded CPU step of the metric: the eager quantise/dequantise/matmul path (oracle port of the
+    reference's ResidueQuantLinear._forward_residue_qdq) for the four sweep shapes at one M on all host
+    threads.  Returns the mean microseconds per linear op and the thread count.  The CPU time hardly
+    depends on M (the weight is re-quantised on every call, as in the reference's eager path), so 4 of the
+    32 cases stand for the sweep."""
     import torch
     import oracle
     cores = len(os.sched_getaffinity(0))
     torch.set_num_threads(cores)
-    name, k, n = shape
-    x = torch.from_numpy(oracle.make_activation(m, k, seed=0)).to(torch.bfloat16)
-    w = torch.from_numpy(oracle.make_weight(n, k, seed=1)).to(torch.bfloat16)
-    oracle.eager_residue_linear(x, w)                      # warm-up
-    ts = []
-    for _ in range(repeats):
+    total = 0.0
+    for name, k, n, _ in SHAPES:
+        if (name, m) not in _CPU_INPUTS:
+            _CPU_INPUTS[(name, m)] = (torch.from_numpy(oracle.make_activation(m, k, seed=0)).to(torch.bfloat16),
+                                      torch.from_numpy(oracle.make_weight(n, k, seed=1)).to(torch.bfloat16))
+        x, w = _CPU_INPUTS[(name, m)]
         t0 = time.perf_counter()
         oracle.eager_residue_linear(x, w)
-        ts.append((time.perf_counter() - t0) * 1e6)
-    return {"value": statistics.median(ts), "unit": "us", "cores": cores, "kind": "port",
-            "sample": f"1 of 32 sweep cases: {name} {k}->{n}, M={m}, ratio 1.0, median of {repeats} runs"}
+        total += (time.perf_counter() - t0) * 1e6
+    return total / len(SHAPES), cores
+
+
+_CPU_SAMPLE = "4 of 32 sweep cases per step: qkv, o, gate_up, down at M=16, ratio 1.0"
+
+
+def cpu_eager_sample(repeats: int = 2):
+    """cpu_baseline of the GPU arm: one warm-up step, then the median of `repeats` steps."""
+    cpu_eager_step()
+    vals = []
+    cores = 0
+    for _ in range(repeats):
+        v, cores = cpu_eager_step()
+        vals.append(v)
+    return {"value": statistics.median(vals), "unit": "us", "cores": cores, "kind": "port",
+            "sample": _CPU_SAMPLE + f", median of {repeats} steps after one warm-up"}
 
 
 def run_reference_arm(args):
+    """`--impl reference`: the reference's CPU path (oracle port) for the same metric and config, on rank 0."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    ts = []
     for _ in range(max(1, args.warmup)):
-        cpu_eager_sample(repeats=1)
-    for _ in range(args.steps):
-        ts.append(cpu_eager_sample(repeats=1)["value"])
-    base = cpu_eager_sample(repeats=1)
+        cpu_eager_step()
+    ts = []
+    cores = 0
+    t_begin = time.perf_counter()
+    for _ in range(max(1, args.steps)):
+        v, cores = cpu_eager_step()
+        ts.append(v)
+        if time.perf_counter() - t_begin > 240:            # keep the whole run within a few minutes
+            break
     v = statistics.mean(ts)
     line = {
         "impl": "reference", "metric": "mext_nvfp4_linear_latency", "value": v, "unit": "us", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": v / 1e3, "higher_is_better": False,
+        "steps": len(ts), "warmup": max(1, args.warmup), "ms_per_step": v * len(SHAPES) / 1e3, "higher_is_better": False,
         "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4 (E2M1 x E4M3 block scales), fp32 accumulate",
         "data": "synthetic", "config": workload_config(args.gpus),
-        "cpu_baseline": {"value": v, "unit": "us", "cores": base["cores"], "kind": "port", "sample": base["sample"]},
+        "cpu_baseline": {"value": v, "unit": "us", "cores": cores, "kind": "port", "sample": _CPU_SAMPLE},
         "e2e": {"value": v, "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -250,8 +275,13 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
     tp = world
+
+    def note(msg):                                          # progress on stderr (rank 0), never on the JSON line
+        if rank == 0 and (world > 1 or os.environ.get("BENCH_VERBOSE")):
+            print(f"[bench] {msg}", file=sys.stderr, flush=True)
 
     from resinfer_b200 import nvfp4, ops
     from resinfer_b200.quant.vllm_integration import residue_linear_op  # noqa: F401
@@ -270,11 +300,13 @@ def main():
         SHAPES = [s for s in SHAPES if s[0] == shape]
         MS = [int(m_only)]
         args.no_detail = True
+    note("process group up; building layers")
     layers = [Layer(nm, k, n, par, tp, rank, dev) for nm, k, n, par in SHAPES]
+    note("layers built")
     outs = {(L.name, m): torch.empty(m, L.n, dtype=torch.bfloat16, device=dev) for L in layers for m in MS}
     launches = {"n": 0}
 
-    def run_case(L, m, quant=True, pre=None):
+    def run_case(L, m, quant=True, pre=None, reduce=True):
         c = L.next_copy()
         if quant:
             codes, sf = nvfp4.scaled_fp4_quant_mext_r1(L.x[m], L.gs_inv[m], layout_mode=1, enable_pdl=True)
@@ -284,14 +316,16 @@ def main():
         y = ops.fp4_gemm(codes, sf, L.w[c], L.w_sf[c], L.alpha[m], m=m, fmt="nvfp4", layout="row_pair",
                          out=outs[(L.name, m)])
         launches["n"] += 1
-        if tp > 1 and L.par == "row":
+        if tp > 1 and L.par == "row" and reduce:
             dist.all_reduce(y)
         return y
 
-    def sweep(quant=True, pre=None):
+    def sweep(quant=True, pre=None, reduce=True):
         for m in MS:
             for L in layers:
-                run_case(L, m, quant, None if pre is None else pre[(L.name, m)])
+                run_case(L, m, quant, None if pre is None else pre[(L.name, m)], reduce)
+
+    graphs = []
 
     def capture(fn):
         s = torch.cuda.Stream()
@@ -304,6 +338,7 @@ def main():
         try:
             with torch.cuda.graph(g):
                 fn()
+            graphs.append(g)
             return g.replay
         except Exception as e:                             # e.g. a collective that cannot be captured
             if rank == 0:
@@ -335,30 +370,35 @@ def main():
     n_cases = len(MS) * len(layers)
     # ---- headline: quantiser + GEMM over the sweep
     launches["n"] = 0
+    note("capturing the sweep")
     replay = capture(lambda: sweep(True))
+    note("captured; timing")
     per_step_launches = launches["n"] // 2                  # warm-up + capture both counted
     with ClockSampler(local) as clk:
         ms_step = timed(replay, args.steps, args.warmup)
     ops.check_status(dev)
+    note(f"timed: {ms_step:.3f} ms per step")
     us_per_op = ms_step * 1e3 / n_cases
 
     # ---- GEMM kernel alone (pre-quantised activations) for the roofline of the dominant kernel
     pre = {(L.name, m): nvfp4.scaled_fp4_quant_mext_r1(L.x[m], L.gs_inv[m], layout_mode=1) for L in layers for m in MS}
-    replay_g = capture(lambda: sweep(False, pre)) if tp == 1 else None
+    no_reduce = {"on": False}
+    replay_g = capture(lambda: sweep(False, pre, reduce=False))
     hbm_gbs, peak_kind = load_peaks()
     roofline = None
     if replay_g is not None:
         ms_gemm = timed(replay_g, args.steps, args.warmup)
         gbytes = sum(gemm_bytes(m, L.k, L.n) for L in layers for m in MS) / n_cases
         achieved = gbytes / (ms_gemm * 1e-3 / n_cases) / 1e9
-        roofline = {"kernel": "fp4_gemm_kernel (tcgen05 block-scaled, 32 launches per step)", "bound": "hbm",
+        roofline = {"kernel": "fp4_gemm_kernel (tcgen05 block-scaled, 32 launches per step"
+                              + (", this rank's shard, no all-reduce)" if tp > 1 else ")"), "bound": "hbm",
                     "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs,
                     "peak_source": peak_kind, "traffic": None,
                     "us_per_launch": ms_gemm * 1e3 / n_cases, "algorithmic_bytes_per_launch": gbytes}
 
     # ---- e2e through the public op with pinned host buffers
     e2e = None
-    if tp == 1 and not args.only:
+    if not args.only:
         hx = {(L.name, m): L.x[m].cpu().pin_memory() for L in layers for m in MS}
         hy = {(L.name, m): torch.empty(m, L.n, dtype=torch.bfloat16).pin_memory() for L in layers for m in MS}
         zero_mask = torch.zeros(1, dtype=torch.uint8, device=dev)
@@ -370,6 +410,8 @@ def main():
                     xd = hx[(L.name, m)].to(dev, non_blocking=True)
                     y = torch.ops.residue.nvfp4_linear(xd, L.w[c], L.gs_inv[m], L.w_sf[c], L.w_sf[c], zero_mask,
                                                        L.alpha[m], L.k, 0, 0, L.n, True, False, True)
+                    if tp > 1 and L.par == "row":
+                        dist.all_reduce(y)
                     hy[(L.name, m)].copy_(y, non_blocking=True)
             torch.cuda.synchronize()
 
@@ -380,9 +422,13 @@ def main():
         for _ in range(reps):
             e2e_sweep()
         e2e_us = (time.perf_counter() - t0) / reps * 1e6 / n_cases
+        if world > 1:
+            tt = torch.tensor([e2e_us], device=dev)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            e2e_us = float(tt.item())
         e2e = {"value": e2e_us, "unit": "us",
-               "h2d_bytes_per_step": sum(2 * m * L.k for L in layers for m in MS),
-               "d2h_bytes_per_step": sum(2 * m * L.n for L in layers for m in MS),
+               "h2d_bytes_per_step": world * sum(2 * m * L.k for L in layers for m in MS),
+               "d2h_bytes_per_step": world * sum(2 * m * L.n for L in layers for m in MS),
                "note": "eager calls of residue::nvfp4_linear (no CUDA graph): includes Python and launch overhead"}
 
     detail = None
@@ -413,7 +459,17 @@ def main():
             line["only"] = args.only
         print(json.dumps(line), flush=True)
     if world > 1:
+        # captured graphs hold NCCL kernels: release them before the communicator goes away, and do not
+        # let a slow communicator teardown keep the finished benchmark alive
+        graphs.clear()
+        import gc
+        gc.collect()
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        threading.Timer(20.0, lambda: os._exit(0)).start()
         dist.destroy_process_group()
+        os._exit(0)
 
 
 def measure_detail(torch, dev, layers, outs, nvfp4, ops, capture, timed, hbm_gbs):
