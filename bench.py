@@ -257,6 +257,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-detail", action="store_true", help="skip the per-case and ResAttn detail measurements")
+    ap.add_argument("--sweeps", action="store_true",
+                    help="measure the other sweeps of the three hot paths (MXFP4 MEXT, KEXT, ResAttn batch sizes) "
+                         "and print them as a second JSON line {\"sweeps\": ...}; N = 1 only")
     ap.add_argument("--only", default=None,
                     help="profiling aid: 'gemm:<shape>:<M>' times that single (shape, M) case, 'resattn:<index>' "
                          "that single ResAttn point; no e2e, no CPU baseline, not a bench value")
@@ -458,6 +461,9 @@ def main():
         if args.only:
             line["only"] = args.only
         print(json.dumps(line), flush=True)
+    if args.sweeps and tp == 1 and not args.only:
+        hbm_gbs2, _ = load_peaks()
+        print(json.dumps({"sweeps": measure_sweeps(torch, dev, capture, timed, hbm_gbs2)}), flush=True)
     if world > 1:
         # captured graphs hold NCCL kernels: release them before the communicator goes away, and do not
         # let a slow communicator teardown keep the finished benchmark alive
@@ -496,12 +502,97 @@ def measure_detail(torch, dev, layers, outs, nvfp4, ops, capture, timed, hbm_gbs
     return {"mext_nvfp4_cases": cases, "resattn": attn}
 
 
-def measure_resattn(torch, dev, ops, capture, timed, hbm_gbs, only=None, steps=10, warmup=3):
+def measure_sweeps(torch, dev, capture, timed, hbm_gbs):
+    """The sweeps beside the headline: MXFP4 MEXT (4 shapes x M), NVFP4 KEXT (4 shapes x M x ratio) and
+    ResAttn over batch sizes.  Every linear case is timed as quantiser + GEMM under a CUDA graph with
+    rotating weight copies (more than L2 in total), like the headline sweep."""
+    from resinfer_b200 import nvfp4, ops
+    from resinfer_b200.nvfp4 import mxfp4
+    from resinfer_b200.nvfp4.quant import indices_to_channel_masks
+    from resinfer_b200.quant import weight_prep
+    out = {"mxfp4_mext": [], "kext_nvfp4": [], "resattn": []}
+
+    def weights(k, n, fmt, idx=None):
+        g = torch.Generator(device=dev).manual_seed(5)
+        w = (torch.randn(n, k, generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+        prep = (weight_prep.quantize_weight_mxfp4 if fmt == "mxfp4" else weight_prep.quantize_weight_nvfp4)(w, idx)
+        del w
+        nbytes = prep["weight"].numel() + prep["weight_scale"].numel()
+        copies = max(2, min(8, -(-2 * L2_BYTES // nbytes)))
+        return prep, [prep["weight"].clone() for _ in range(copies)], [prep["weight_scale"].clone() for _ in range(copies)]
+
+    def act(m, k):
+        gx = torch.Generator(device=dev).manual_seed(0)
+        x = torch.randn(m, k, generator=gx, device=dev, dtype=torch.float32)
+        x[:, torch.randperm(k, generator=gx, device=dev)[: max(1, k // 100)]] *= 20.0
+        return x.to(torch.bfloat16)
+
+    def time_case(fn, copies):
+        rp = capture(lambda: [fn(c) for c in range(copies)])
+        return timed(rp, 10, 3) * 1e3 / copies
+
+    # ---- MXFP4 MEXT: online E8M0 quantiser (row_pair) + block32 fold GEMM
+    for name, k, n, _ in SHAPES:
+        prep, ws, sfs = weights(k, n, "mxfp4")
+        for m in MS:
+            x = act(m, k)
+
+            def fn(c, x=x, m=m):
+                a, a_sf = mxfp4.quantize_mext(x, pdl_mode="early")
+                return mxfp4.fold_gemm(a, ws[c], a_sf, sfs[c], out_dtype=torch.bfloat16)
+            us = time_case(fn, len(ws))
+            nbytes = 2 * m * k + n * k * (0.5 + 1 / 32) + 2 * m * n
+            out["mxfp4_mext"].append({"shape": name, "m": m, "us": round(us, 2), "tflops": round(4.0 * m * n * k / us / 1e6, 1),
+                                      "gbs": round(nbytes / us / 1e3), "frac_hbm_roofline": round(nbytes / us / 1e3 / hbm_gbs, 3)})
+        del prep, ws, sfs
+    # ---- KEXT NVFP4: masked residue along K + plain GEMM over K + S; ratio 1.0 = MEXT K-concat
+    for name, k, n, _ in SHAPES:
+        for ratio, per8 in ((0.125, 1), (0.25, 2), (0.5, 4), (1.0, 8)):
+            idx = None if per8 == 8 else weight_prep.salient_indices_per8(k, per8, device=dev)
+            prep, ws, sfs = weights(k, n, "nvfp4", idx)
+            s = 0 if idx is None else idx.numel()
+            mask = None if idx is None else indices_to_channel_masks(idx, k)
+            for m in (16, 128, 1024, 8192):
+                x = act(m, k)
+                gs = float(x.float().abs().max()) / (6.0 * 448.0)
+                gi = torch.tensor([1.0 / gs], dtype=torch.float32, device=dev)
+                alpha = (prep["weight_global_scale"] * gs).float().reshape(1)
+                y = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+
+                def fn(c, x=x, m=m, gi=gi, alpha=alpha, y=y):
+                    if per8 == 8:
+                        codes, sf = nvfp4.scaled_fp4_quant_mext_r1(x, gi, layout_mode=3)
+                        return ops.fp4_gemm(codes, sf, ws[c], sfs[c], alpha, m=m, fmt="nvfp4", layout="concat_k", out=y)
+                    codes, sf = nvfp4.scaled_fp4_quant_with_mask(x, gi, mask, s, use_swapped_residue=False)
+                    return ops.fp4_gemm(codes, sf, ws[c], sfs[c], alpha, m=m, fmt="nvfp4", layout="plain", out=y)
+                us = time_case(fn, len(ws))
+                k_eff = 2 * k if per8 == 8 else k + s
+                w_k = k if per8 == 8 else k + s                  # weight columns that are read
+                nbytes = 2 * m * k + k / 8 + n * w_k * 0.5625 + 2 * m * n
+                flops = 2.0 * m * n * k_eff
+                t_mem, t_tc = nbytes / (hbm_gbs * 1e9), flops / 9.0e15     # dense FP4 nominal 9 PFLOP/s
+                out["kext_nvfp4"].append({"shape": name, "ratio": ratio, "m": m, "us": round(us, 2),
+                                          "tflops": round(flops / us / 1e6, 1), "gbs": round(nbytes / us / 1e3),
+                                          "bound": "hbm" if t_mem >= t_tc else "tensor",
+                                          "frac_roofline": round(max(t_mem, t_tc) * 1e6 / us, 3)})
+            del prep, ws, sfs
+    # ---- ResAttn: batch sizes of the configuration, page 16, both head sizes
+    for d, batches in ((128, (1, 8, 32, 128, 256)), (256, (1, 8, 32, 128))):
+        for b in batches:
+            try:
+                out["resattn"] += measure_resattn(torch, dev, ops, capture, timed, hbm_gbs, custom=(d, b))
+            except Exception as e:                          # e.g. out of memory on a smaller part
+                out["resattn"].append({"head_dim": d, "batch": b, "error": f"{type(e).__name__}: {e}"})
+            torch.cuda.empty_cache()
+    return out
+
+
+def measure_resattn(torch, dev, ops, capture, timed, hbm_gbs, only=None, steps=10, warmup=3, custom=None):
     from resinfer_b200.nvfp4.cute_attn.plan import select_decode_plan
     res = []
     hq, hkv, page = 64, 8, 16
     sms = torch.cuda.get_device_properties(dev).multi_processor_count
-    for idx, (d, batch) in enumerate(((128, 8), (128, 64), (256, 32))):
+    for idx, (d, batch) in enumerate(((128, 8), (128, 64), (256, 32)) if custom is None else (custom,)):
         if only is not None and idx != only:
             continue
         g = torch.Generator(device=dev).manual_seed(3)

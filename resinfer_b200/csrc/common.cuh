@@ -266,14 +266,23 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
                : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
+// try_wait with a suspend-time hint: the thread may sleep in hardware for up to `hint_ns` and is woken
+// when the phase completes, so a waiting warp does not burn issue slots that working warps need
+__device__ __forceinline__ bool mbar_try_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(bar), "r"(parity), "r"(hint_ns) : "memory");
+  return ok != 0;
+}
 // Bounded wait.  Returns false when another role aborted or the cycle limit expired (then sets
-// the abort flag itself).  The fast path is a plain try_wait loop; the SM cycle counter and the
-// abort flag are only looked at every 4096 failed polls.
+// the abort flag itself).  The fast path is one try_wait; after that the thread sleeps in hardware
+// between polls; the SM cycle counter and the abort flag are looked at every 64 failed polls.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int site = 1) {
+  if (mbar_try(bar, parity)) return true;
   long long t0 = 0;
   for (uint32_t spin = 1;; ++spin) {
-    if (mbar_try(bar, parity)) return true;
-    if ((spin & 4095u) == 0) {
+    if (mbar_try_hint(bar, parity, 20000u)) return true;
+    if ((spin & 63u) == 0) {
       if (*abort_flag) return false;
       const long long now = clock64();
       if (t0 == 0) t0 = now;

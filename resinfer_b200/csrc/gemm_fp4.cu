@@ -169,7 +169,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
   __shared__ int acc_ok;
 
   // dynamic shared memory is only guaranteed 16-byte aligned: round up to the 1024-byte swizzle atom
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // stays a shared-space pointer
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;

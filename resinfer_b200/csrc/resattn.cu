@@ -30,6 +30,7 @@ struct AttnParams {
   const int32_t* seq_lens;
   int64_t num_pages;
   int batch, hq, hkv, group, page_size;
+  int page_shift;                          // log2(page_size) when it is a power of two, else -1
   float score_scale_log2;                  // sm_scale * k_global_scale * log2(e)
   float out_scale;
   void* out;                               // [B, Hq, D] bf16 (or fp32 when out_f32)
@@ -135,7 +136,7 @@ resattn_tc_kernel(const AttnParams p) {
   __shared__ __align__(8) uint64_t bar_sempty[2];
   __shared__ uint32_t tmem_slot;
   __shared__ volatile int abort_flag;
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // stays a shared-space pointer
   uint8_t* q_op = smem;                                        // [16][D/2] swizzled FP4 codes
   uint8_t* qsf_s = smem + 2048;                                // [16][D/16] E4M3 scales
   float* sbuf = reinterpret_cast<float*>(smem + 3072);         // [16 warps][32 tokens][8 heads]
@@ -233,11 +234,11 @@ resattn_tc_kernel(const AttnParams p) {
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
     const uint32_t idesc = (1u << 7) | (1u << 10) | (uint32_t(16 >> 3) << 17) | (uint32_t(kTile >> 4) << 24);
     const uint64_t b_desc = desc_kmajor(smem_u32(q_op), C::kSbo, C::kLayout);
-    for (int i = 0; i < my_tiles; ++i) {
-      const int stg = i % S, sb = i & 1;
+    for (int i = 0, stg = 0, ph = 0; i < my_tiles; ++i, stg = (stg + 1 == S ? 0 : stg + 1), ph ^= (stg == 0)) {
+      const int sb = i & 1;                                  // stg = i % S, ph = (i / S) & 1, kept without divisions
       bool got = true;
       if (lane == 0) {
-        got = mbar_wait(smem_u32(&bar_full[stg]), (i / S) & 1, &abort_flag, 2);
+        got = mbar_wait(smem_u32(&bar_full[stg]), ph, &abort_flag, 2);
         if (got && i >= 2) got = mbar_wait(smem_u32(&bar_sempty[sb]), ((i >> 1) - 1) & 1, &abort_flag, 3);
       }
       if (!__all_sync(0xffffffffu, got)) break;
@@ -284,57 +285,57 @@ resattn_tc_kernel(const AttnParams p) {
     // instruction.  Producer warp w owns rows 32w..32w+31 of every tile (two page slices); the K
     // codes are written in the operand swizzle by address arithmetic.
     constexpr int kCpr = C::kRowBytes / 16;                    // 16-byte chunks per code row
+    constexpr int kRowsPerIt = 32 / kCpr;                      // rows one warp instruction covers (8 or 4)
+    constexpr int kIters = 32 / kRowsPerIt;                    // instructions per array and tile (4 or 8)
     const int pw = warp - kFront;
-    for (int i = 0; i < my_tiles; ++i) {
-      const int tile = t_begin + i, stg = i % S;
-      const int tok0 = tile * kTile + 32 * pw;
+    // per-lane constants: row inside the instruction's row group, 16-byte chunk, scale row
+    const int r_lane = lane / kCpr, chn = lane % kCpr;
+    const int sf_row = D == 128 ? 2 * lane : lane;             // first row of this lane's 16 scale bytes
+    const bool sf_lane = D == 128 ? lane < 16 : true;
+    uint32_t k_dst[kIters];                                    // swizzled K offsets inside a stage
+#pragma unroll
+    for (int it = 0; it < kIters; ++it) k_dst[it] = swz_off<D>(32 * pw + it * kRowsPerIt + r_lane, chn * 16);
+    const uint32_t v_dst0 = C::kOffV + (32 * pw + r_lane) * C::kRowBytes + chn * 16;
+    const uint32_t sf_dst = (32 * pw + sf_row) * C::kSfPerRow;
+
+    // block-table entry of slice `lane` (lanes 0 and 1) of a tile, fetched one tile ahead
+    auto lookup = [&](int i) -> int {
+      if (lane >= 2 || i >= my_tiles) return 0;
+      const int t0 = (t_begin + i) * kTile + 32 * pw + lane * 16;
+      return t0 < L ? __ldg(bt + (p.page_shift >= 0 ? t0 >> p.page_shift : t0 / p.page_size)) : 0;
+    };
+    int page_next = lookup(0);
+    for (int i = 0, stg = 0, ph = 0; i < my_tiles; ++i, stg = (stg + 1 == S ? 0 : stg + 1), ph ^= (stg == 0)) {
+      const int tok0 = (t_begin + i) * kTile + 32 * pw;
       const int rows = min(max(((L - tok0) + 15) & ~15, 0), 32);     // rows of this warp that exist (0, 16 or 32)
-      // pool row of the first token of slice `lane` (looked up before the wait to hide the latency)
-      int64_t base_row = 0;
-      if (lane * 16 < rows) {
-        const int t0 = tok0 + lane * 16;
-        int64_t page = __ldg(bt + t0 / p.page_size);
-        page = page < 0 ? 0 : (page >= p.num_pages ? p.num_pages - 1 : page);
-        base_row = (page * p.hkv + hkv) * p.page_size + (t0 % p.page_size);
-      }
+      int64_t page = page_next;
+      page_next = lookup(i + 1);
+      page = page < 0 ? 0 : (page >= p.num_pages ? p.num_pages - 1 : page);
+      const int t0 = tok0 + lane * 16;
+      const int in_page = p.page_shift >= 0 ? (t0 & (p.page_size - 1)) : t0 % p.page_size;
+      const int64_t base_row = (page * p.hkv + hkv) * p.page_size + in_page;
       const int64_t base0 = __shfl_sync(0xffffffffu, base_row, 0), base1 = __shfl_sync(0xffffffffu, base_row, 1);
       bool free_ok = true;
-      if (i >= S && lane == 0) free_ok = mbar_wait(smem_u32(&bar_empty[stg]), ((i / S) - 1) & 1, &abort_flag, 4);
+      if (i >= S && lane == 0) free_ok = mbar_wait(smem_u32(&bar_empty[stg]), ph ^ 1, &abort_flag, 4);
       if (!__all_sync(0xffffffffu, free_ok)) break;
-      uint8_t* st = stage0 + stg * C::kStageBytes;
+      const uint32_t st = smem_u32(stage0 + stg * C::kStageBytes);
+      // rows 0-15 of this warp come from slice 0, rows 16-31 from slice 1
+      const uint8_t* kg[2] = {p.k_data + base0 * C::kRowBytes + chn * 16, p.k_data + base1 * C::kRowBytes + chn * 16};
+      const uint8_t* vg[2] = {p.v_data + base0 * C::kRowBytes + chn * 16, p.v_data + base1 * C::kRowBytes + chn * 16};
 #pragma unroll
-      for (int it = 0; it < 32 * kCpr / 32; ++it) {
-        const int idx = it * 32 + lane;
-        const int r = idx / kCpr, chn = idx % kCpr;            // row inside this warp's 32
-        if (r < rows) {
-          const int row = 32 * pw + r;
-          const int64_t br = (r < 16 ? base0 : base1) + (r & 15);
-          cp_async16(smem_u32(st + swz_off<D>(row, chn * 16)), p.k_data + br * C::kRowBytes + chn * 16);
-          cp_async16(smem_u32(st + C::kOffV + row * C::kRowBytes + chn * 16), p.v_data + br * C::kRowBytes + chn * 16);
+      for (int it = 0; it < kIters; ++it) {
+        const int r = it * kRowsPerIt + r_lane;                // row inside this warp's 32
+        if (it * kRowsPerIt < rows) {
+          const int sl = (it * kRowsPerIt) >> 4;               // compile-time slice of the instruction
+          const int off = (r & 15) * C::kRowBytes;
+          cp_async16(st + k_dst[it], kg[sl] + off);
+          cp_async16(st + v_dst0 + it * kRowsPerIt * C::kRowBytes, vg[sl] + off);
         }
       }
-      {
-        const int byte = lane * 16;                            // 32 rows x D/16 scale bytes = 256 or 512 bytes
-#pragma unroll
-        for (int it = 0; it < 32 * C::kSfPerRow / 512; ++it) {
-          const int bb = byte + it * 512;
-          const int r = bb / C::kSfPerRow, within = bb % C::kSfPerRow;
-          if (bb < 32 * C::kSfPerRow && r < rows) {
-            const int64_t br = (r < 16 ? base0 : base1) + (r & 15);
-            const int dst = (32 * pw) * C::kSfPerRow + bb;
-            cp_async16(smem_u32(st + C::kOffKsf + dst), p.k_sf + br * C::kSfPerRow + within);
-            cp_async16(smem_u32(st + C::kOffVsf + dst), p.v_sf + br * C::kSfPerRow + within);
-          }
-        }
-        if constexpr (32 * C::kSfPerRow < 512) {
-          const int r = byte / C::kSfPerRow;
-          if (byte < 32 * C::kSfPerRow && r < rows) {
-            const int64_t br = (r < 16 ? base0 : base1) + (r & 15);
-            const int dst = (32 * pw) * C::kSfPerRow + byte;
-            cp_async16(smem_u32(st + C::kOffKsf + dst), p.k_sf + br * C::kSfPerRow);
-            cp_async16(smem_u32(st + C::kOffVsf + dst), p.v_sf + br * C::kSfPerRow);
-          }
-        }
+      if (sf_lane && sf_row < rows) {
+        const int64_t br = (sf_row < 16 ? base0 : base1) + (sf_row & 15);
+        cp_async16(st + C::kOffKsf + sf_dst, p.k_sf + br * C::kSfPerRow);
+        cp_async16(st + C::kOffVsf + sf_dst, p.v_sf + br * C::kSfPerRow);
       }
       // every lane arrives once its own copies have landed (barrier count = producer lanes)
       asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&bar_full[stg])) : "memory");
@@ -344,14 +345,14 @@ resattn_tc_kernel(const AttnParams p) {
     // ============================================================ consumers
     const uint32_t lane_base = tmem_base + (uint32_t(cq * 32) << 16);
     float* my_s = sbuf + cw * 32 * 8;
-    for (int i = 0; i < my_tiles; ++i) {
-      const int stg = i % S, sb = i & 1;
+    for (int i = 0, stg = 0, ph = 0; i < my_tiles; ++i, stg = (stg + 1 == S ? 0 : stg + 1), ph ^= (stg == 0)) {
+      const int sb = i & 1;
       const int tile = t_begin + i;
       bool got = true;
       if (lane == 0) {
         got = mbar_wait(smem_u32(&bar_sfull[sb]), (i >> 1) & 1, &abort_flag, 5);
         // the V codes and scales of the stage were written by the copy engine: observe its barrier too
-        if (got) got = mbar_wait(smem_u32(&bar_full[stg]), (i / S) & 1, &abort_flag, 6);
+        if (got) got = mbar_wait(smem_u32(&bar_full[stg]), ph, &abort_flag, 6);
       }
       if (!__all_sync(0xffffffffu, got)) break;
       tc_fence_after();
@@ -383,6 +384,10 @@ resattn_tc_kernel(const AttnParams p) {
         const int tok_in_tile = 32 * cq + tok_in_q;
         const int valid = min(L - (tile * kTile + tok_in_tile), 16);
         if (valid <= 0) continue;
+#ifdef RI_ATTN_SKIP_CHUNK
+        oacc[0][0] += my_s[lane];
+        continue;
+#endif
         float sv[4];
         sv[0] = my_s[(tok_in_q + 2 * tq) * 8 + nq];
         sv[1] = my_s[(tok_in_q + 2 * tq + 1) * 8 + nq];
@@ -434,6 +439,7 @@ resattn_tc_kernel(const AttnParams p) {
         }
         const __half2 s01 = __halves2half2(vs[0], vs[1]);
         const __half2 s89 = __halves2half2(vs[2], vs[3]);
+#ifndef RI_ATTN_SKIP_PV
 #pragma unroll
         for (int j = 0; j < 8; j += 2) {
           const int sh = j * 4;
@@ -448,6 +454,9 @@ resattn_tc_kernel(const AttnParams p) {
           mma_f16(oacc[j], pa, b0_lo, b1_lo);
           mma_f16(oacc[j + 1], pa, b0_hi, b1_hi);
         }
+#else
+        oacc[0][0] += __uint_as_float(pa[0] ^ vw[0] ^ vw[1] ^ vw[2] ^ vw[3]) + __half2float(vs[0]) + __half2float(vs[1]) + __half2float(vs[2]) + __half2float(vs[3]);
+#endif
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_empty[stg]));
@@ -615,6 +624,9 @@ extern "C" int ri_resattn_decode(const void* q_bf16, const uint8_t* k_data, cons
   p.k_data = k_data; p.k_sf = k_sf; p.v_data = v_data; p.v_sf = v_sf;
   p.block_tables = block_tables; p.bt_stride = bt_stride; p.seq_lens = seq_lens; p.num_pages = num_pages;
   p.batch = batch; p.hq = num_q_heads; p.hkv = num_kv_heads; p.group = group; p.page_size = page_size;
+  p.page_shift = -1;
+  for (int sft = 4; sft < 31; ++sft)
+    if ((1 << sft) == page_size) p.page_shift = sft;
   p.score_scale_log2 = score_scale * kLog2e;
   p.out_scale = out_scale;
   p.out = out;
