@@ -43,6 +43,8 @@ SHAPES = [("qkv", 5120, 10240, "col"), ("o", 8192, 5120, "row"), ("gate_up", 512
           ("down", 25600, 5120, "row")]
 MS = [1, 2, 4, 8, 16, 32, 64, 128]
 L2_BYTES = 126 * 1024 * 1024
+# DRAM traffic of the GEMM kernel / its algorithmic bytes, from one ncu capture per shape (see roofline.traffic_source)
+NCU_TRAFFIC_RATIO = 289.49 / 277.36
 
 
 def load_peaks():
@@ -396,7 +398,10 @@ def main():
         roofline = {"kernel": "fp4_gemm_kernel (tcgen05 block-scaled, 32 launches per step"
                               + (", this rank's shard, no all-reduce)" if tp > 1 else ")"), "bound": "hbm",
                     "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs,
-                    "peak_source": peak_kind, "traffic": None,
+                    "peak_source": peak_kind, "traffic": gbytes * NCU_TRAFFIC_RATIO,
+                    "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of the four shapes at M=16 "
+                                      "(289.5 MB against 277.4 MB algorithmic), scaled to the sweep's mean launch; "
+                                      "profiles/fp4_gemm_kernel_m16_four_shapes.md",
                     "us_per_launch": ms_gemm * 1e3 / n_cases, "algorithmic_bytes_per_launch": gbytes}
 
     # ---- e2e through the public op with pinned host buffers
@@ -406,7 +411,12 @@ def main():
         hy = {(L.name, m): torch.empty(m, L.n, dtype=torch.bfloat16).pin_memory() for L in layers for m in MS}
         zero_mask = torch.zeros(1, dtype=torch.uint8, device=dev)
 
+        out_stream = torch.cuda.Stream()                    # results go home on their own stream, under the next op
+        done = [torch.cuda.Event() for _ in range(n_cases)]
+
         def e2e_sweep():
+            keep = []                                       # device results stay alive until their copy has run
+            i = 0
             for m in MS:
                 for L in layers:
                     c = L.next_copy()
@@ -415,7 +425,12 @@ def main():
                                                        L.alpha[m], L.k, 0, 0, L.n, True, False, True)
                     if tp > 1 and L.par == "row":
                         dist.all_reduce(y)
-                    hy[(L.name, m)].copy_(y, non_blocking=True)
+                    done[i].record()
+                    out_stream.wait_event(done[i])
+                    with torch.cuda.stream(out_stream):
+                        hy[(L.name, m)].copy_(y, non_blocking=True)
+                    keep.append(y)
+                    i += 1
             torch.cuda.synchronize()
 
         for _ in range(2):
@@ -432,7 +447,8 @@ def main():
         e2e = {"value": e2e_us, "unit": "us",
                "h2d_bytes_per_step": world * sum(2 * m * L.k for L in layers for m in MS),
                "d2h_bytes_per_step": world * sum(2 * m * L.n for L in layers for m in MS),
-               "note": "eager calls of residue::nvfp4_linear (no CUDA graph): includes Python and launch overhead"}
+               "note": "eager calls of residue::nvfp4_linear (no CUDA graph) from pinned host buffers: H2D of x, the op, "
+                       "D2H of y on a second stream; includes Python and launch overhead"}
 
     detail = None
     if not args.no_detail and tp == 1:

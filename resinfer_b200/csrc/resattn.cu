@@ -349,8 +349,10 @@ resattn_tc_kernel(const AttnParams p) {
       const int sb = i & 1;
       const int tile = t_begin + i;
       bool got = true;
+      if (cw == 0 && lane == 0) attn_event(p, 6, i);
       if (lane == 0) {
         got = mbar_wait(smem_u32(&bar_sfull[sb]), (i >> 1) & 1, &abort_flag, 5);
+        if (cw == 0) attn_event(p, 7, i);
         // the V codes and scales of the stage were written by the copy engine: observe its barrier too
         if (got) got = mbar_wait(smem_u32(&bar_full[stg]), ph, &abort_flag, 6);
       }
@@ -384,10 +386,6 @@ resattn_tc_kernel(const AttnParams p) {
         const int tok_in_tile = 32 * cq + tok_in_q;
         const int valid = min(L - (tile * kTile + tok_in_tile), 16);
         if (valid <= 0) continue;
-#ifdef RI_ATTN_SKIP_CHUNK
-        oacc[0][0] += my_s[lane];
-        continue;
-#endif
         float sv[4];
         sv[0] = my_s[(tok_in_q + 2 * tq) * 8 + nq];
         sv[1] = my_s[(tok_in_q + 2 * tq + 1) * 8 + nq];
@@ -439,7 +437,6 @@ resattn_tc_kernel(const AttnParams p) {
         }
         const __half2 s01 = __halves2half2(vs[0], vs[1]);
         const __half2 s89 = __halves2half2(vs[2], vs[3]);
-#ifndef RI_ATTN_SKIP_PV
 #pragma unroll
         for (int j = 0; j < 8; j += 2) {
           const int sh = j * 4;
@@ -454,9 +451,6 @@ resattn_tc_kernel(const AttnParams p) {
           mma_f16(oacc[j], pa, b0_lo, b1_lo);
           mma_f16(oacc[j + 1], pa, b0_hi, b1_hi);
         }
-#else
-        oacc[0][0] += __uint_as_float(pa[0] ^ vw[0] ^ vw[1] ^ vw[2] ^ vw[3]) + __half2float(vs[0]) + __half2float(vs[1]) + __half2float(vs[2]) + __half2float(vs[3]);
-#endif
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_empty[stg]));

@@ -14,6 +14,25 @@ from . import _cabi
 
 _WORKSPACES: dict[tuple, torch.Tensor] = {}
 _STATUS: dict[torch.device, torch.Tensor] = {}
+_GEMM_PLANS: dict[tuple, tuple] = {}
+
+
+class _on_device:
+    """``torch.cuda.device(dev)`` that costs nothing when ``dev`` is already current (the usual case)."""
+
+    __slots__ = ("ctx",)
+
+    def __init__(self, dev):
+        self.ctx = None if dev.index is None or torch.cuda.current_device() == dev.index else torch.cuda.device(dev)
+
+    def __enter__(self):
+        if self.ctx is not None:
+            self.ctx.__enter__()
+
+    def __exit__(self, *exc):
+        if self.ctx is not None:
+            self.ctx.__exit__(*exc)
+
 
 
 def _workspace(device, nbytes: int, tag: str, zero_prefix: int = 0) -> torch.Tensor:
@@ -67,13 +86,18 @@ def fp4_gemm(act: torch.Tensor, act_sf: torch.Tensor, weight: torch.Tensor, weig
         raise ValueError(f"activation must be compact rows; got stride {act.stride()}")
     if out is None:
         out = torch.empty((m, n), dtype=out_dtype, device=dev)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         ws = None
-        ws_bytes = lib.ri_fp4_gemm_workspace_bytes(m, n, k, fmt_c, lay_c, splits)
+        plan_key = (dev.index, m, n, k, fmt_c, lay_c, splits)
+        plan = _GEMM_PLANS.get(plan_key)
+        if plan is None:                                   # workspace size of a shape, asked once per device
+            plan = (lib.ri_fp4_gemm_workspace_bytes(m, n, k, fmt_c, lay_c, splits), lib.ri_fp4_gemm_counter_bytes(m, n))
+            _GEMM_PLANS[plan_key] = plan
+        ws_bytes = plan[0]
         if ws_bytes < 0:
             _cabi.check(_cabi.RI_ERR_ARG, "fp4_gemm plan")
         if ws_bytes > 0:
-            ws = _workspace(dev, ws_bytes, "gemm", zero_prefix=lib.ri_fp4_gemm_counter_bytes(m, n))
+            ws = _workspace(dev, ws_bytes, "gemm", zero_prefix=plan[1])
         st = lib.ri_fp4_gemm(
             act.data_ptr(), act.stride(0), act_sf.data_ptr(), act_sf.numel(),
             weight.data_ptr(), weight.stride(0), weight_sf.data_ptr(), weight_sf.numel(),

@@ -8,7 +8,6 @@ from __future__ import annotations
 import torch
 
 
-@torch.library.custom_op("residue::mxfp4_linear", mutates_args=())
 def mxfp4_linear(x: torch.Tensor, weight: torch.Tensor, weight_scale: torch.Tensor, indices: torch.Tensor,
                  masks: torch.Tensor, mode: str, output_dtype: torch.dtype,
                  bias: torch.Tensor | None = None) -> torch.Tensor:
@@ -35,6 +34,12 @@ def mxfp4_linear(x: torch.Tensor, weight: torch.Tensor, weight_scale: torch.Tens
     return out.reshape(out_shape)
 
 
-@mxfp4_linear.register_fake
 def _fake_mxfp4_linear(x, weight, weight_scale, indices, masks, mode, output_dtype, bias=None):
     return torch.empty((*x.shape[:-1], weight.shape[0]), device=x.device, dtype=output_dtype)
+
+
+_LIB = torch.library.Library("residue", "FRAGMENT")
+_LIB.define("mxfp4_linear(Tensor x, Tensor weight, Tensor weight_scale, Tensor indices, Tensor masks, str mode, "
+            "ScalarType output_dtype, Tensor? bias=None) -> Tensor")
+_LIB.impl("mxfp4_linear", mxfp4_linear, "CUDA")
+torch.library.register_fake("residue::mxfp4_linear", _fake_mxfp4_linear, lib=_LIB)

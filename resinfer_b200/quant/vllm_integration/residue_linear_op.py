@@ -37,12 +37,39 @@ def mext_fold_max_m_for(arch: str | None) -> int:
     return max(decode_max, configured if configured is not None else 512)
 
 
+_ARCH_BY_DEVICE: dict = {}
+
+
 def _sm10x_fold_arch(device=None) -> str | None:
     if settings().disable_sm10x:
         return None
-    major, minor = torch.cuda.get_device_capability(device)
-    from ...nvfp4.cute_fold.tactics import kernel_arch_for_capability
-    return kernel_arch_for_capability(major, minor) if major == 10 else None
+    key = None if device is None else torch.device(device).index
+    if key not in _ARCH_BY_DEVICE:                         # the capability of a device does not change
+        major, minor = torch.cuda.get_device_capability(device)
+        from ...nvfp4.cute_fold.tactics import kernel_arch_for_capability
+        _ARCH_BY_DEVICE[key] = kernel_arch_for_capability(major, minor) if major == 10 else None
+    return _ARCH_BY_DEVICE[key]
+
+
+def _quant_mext(x: torch.Tensor, scale_inv: torch.Tensor, layout: int):
+    """MEXT quantiser straight through the C ABI (same kernel and bytes as
+    ``nvfp4.scaled_fp4_quant_mext_r1``; the hot path skips that wrapper's option parsing and the second
+    dispatcher round trip)."""
+    from ... import _cabi
+    lib = _cabi.load()
+    m, k = x.shape
+    if k % 16 or x.stride(1) != 1:
+        raise ValueError(f"scaled_fp4_quant_mext_r1 requires compact rows with K multiple of 16, got {tuple(x.shape)}")
+    dev = x.device
+    codes = torch.empty((m, k) if layout == _LAYOUT_CONCAT_K else (2 * m, k // 2), dtype=torch.uint8, device=dev)
+    k_groups = ((2 * k if layout == _LAYOUT_CONCAT_K else k) + 63) // 64
+    rows = m if layout == _LAYOUT_CONCAT_K else 2 * m
+    sf = torch.empty(((rows + 127) // 128) * k_groups * 512, dtype=torch.uint8, device=dev)
+    st = lib.ri_nvfp4_quant_mext(x.data_ptr(), _cabi.torch_dtype_code(x.dtype), m, k, x.stride(0),
+                                 scale_inv.data_ptr(), scale_inv.numel(), codes.data_ptr(), codes.numel(),
+                                 sf.data_ptr(), sf.numel(), layout, 1, _cabi.current_stream(dev))
+    _cabi.check(st, "nvfp4::scaled_fp4_quant_mext_r1")
+    return codes, sf
 
 
 def _route(m: int, *, fold_eligible: bool, ratio1: bool, num_salient: int, arch: str | None,
@@ -81,10 +108,10 @@ def _nvfp4_linear_impl(x, weight, scale_inv, weight_scale, weight_scale_base, ma
     if route in ("sm10x_fold", "ratio1_prefill"):
         w_base = _base_weight_view(weight, k_base)
         if route == "sm10x_fold":
-            codes, sf = nvfp4.scaled_fp4_quant_mext_r1(x, scale_inv, layout_mode=_LAYOUT_ROW_PAIR)
+            codes, sf = _quant_mext(x, scale_inv, _LAYOUT_ROW_PAIR)
             return ops.fp4_gemm(codes, sf, w_base, weight_scale_base, alpha, m=m, fmt="nvfp4",
                                 layout="row_pair", out_dtype=x.dtype)
-        codes, sf = nvfp4.scaled_fp4_quant_mext_r1(x, scale_inv, layout_mode=_LAYOUT_CONCAT_K)
+        codes, sf = _quant_mext(x, scale_inv, _LAYOUT_CONCAT_K)
         return ops.fp4_gemm(codes, sf, w_base, weight_scale_base, alpha.reshape(-1)[:1], m=m, fmt="nvfp4",
                             layout="concat_k", out_dtype=x.dtype)
     if route == "plain":
@@ -97,7 +124,6 @@ def _nvfp4_linear_impl(x, weight, scale_inv, weight_scale, weight_scale_base, ma
                         out_dtype=x.dtype)
 
 
-@torch.library.custom_op("residue::nvfp4_linear", mutates_args=(), device_types="cuda")
 def nvfp4_linear(x: torch.Tensor, weight: torch.Tensor, input_global_scale_inv: torch.Tensor,
                  weight_scale: torch.Tensor, weight_scale_base: torch.Tensor, channel_mask: torch.Tensor,
                  alpha: torch.Tensor, k_base: int, num_salient: int, weights_padding_cols: int,
@@ -105,7 +131,7 @@ def nvfp4_linear(x: torch.Tensor, weight: torch.Tensor, input_global_scale_inv: 
     """y[M, N] = NVFP4 linear of x[M, K] with residue compensation (MEXT or KEXT by layer type and M)."""
     if x.shape[0] == 0:
         return x.new_empty((0, output_size if output_size > 0 else weight.shape[0]))
-    with torch.cuda.device(x.device):
+    with ops._on_device(x.device):
         out = _nvfp4_linear_impl(
             x, weight, input_global_scale_inv, weight_scale, weight_scale_base, channel_mask, alpha,
             k_base=int(k_base), num_salient=int(num_salient), padding=int(weights_padding_cols),
@@ -114,9 +140,18 @@ def nvfp4_linear(x: torch.Tensor, weight: torch.Tensor, input_global_scale_inv: 
     return out[:, :output_size].contiguous() if 0 < output_size < out.shape[1] else out
 
 
-@nvfp4_linear.register_fake
 def _nvfp4_linear_fake(x, weight, input_global_scale_inv, weight_scale, weight_scale_base, channel_mask, alpha,
                        k_base, num_salient, weights_padding_cols, output_size, fold_eligible, use_swap,
                        is_mext_r1):
     n = int(output_size) if int(output_size) > 0 else weight.shape[0]
     return torch.empty(x.shape[0], n, dtype=x.dtype, device=x.device)
+
+
+# Registered straight on the dispatcher (CUDA key + fake kernel): an opaque op for torch.compile like the
+# reference's, without the per-call Python wrapper layers of torch.library.custom_op (about 25 us per call).
+_LIB = torch.library.Library("residue", "FRAGMENT")
+_LIB.define("nvfp4_linear(Tensor x, Tensor weight, Tensor input_global_scale_inv, Tensor weight_scale, "
+            "Tensor weight_scale_base, Tensor channel_mask, Tensor alpha, int k_base, int num_salient, "
+            "int weights_padding_cols, int output_size, bool fold_eligible, bool use_swap, bool is_mext_r1) -> Tensor")
+_LIB.impl("nvfp4_linear", nvfp4_linear, "CUDA")
+torch.library.register_fake("residue::nvfp4_linear", _nvfp4_linear_fake, lib=_LIB)
