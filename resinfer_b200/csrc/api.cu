@@ -29,6 +29,7 @@ int device_info(DeviceInfo* out) {
   std::lock_guard<std::mutex> lock(mu);
   if (!have[dev]) {
     DeviceInfo d{};
+    d.ordinal = dev;
     RI_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev));
     RI_CUDA(cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev));
     RI_CUDA(cudaDeviceGetAttribute(&d.cc_minor, cudaDevAttrComputeCapabilityMinor, dev));

@@ -54,6 +54,7 @@ inline int cuda_status(cudaError_t e, const char* what) {
   } while (0)
 
 struct DeviceInfo {
+  int ordinal;                 // device the calling thread has current
   int sm_count;
   int cc_major, cc_minor;
   int max_smem_optin;

@@ -992,10 +992,10 @@ extern "C" int ri_fp4_gemm(const uint8_t* act, int64_t act_row_bytes, const uint
   p.trace = g_trace;
 
   auto kernel = fmt == RI_FMT_MXFP4 ? fp4_gemm_kernel<true> : fp4_gemm_kernel<false>;
-  static bool attr_set[2] = {false, false};
-  if (!attr_set[fmt]) {
+  static bool attr_set[64][2] = {};                 // function attributes are per device
+  if (!attr_set[di.ordinal][fmt]) {
     RI_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem));
-    attr_set[fmt] = true;
+    attr_set[di.ordinal][fmt] = true;
   }
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(pl.grid);

@@ -198,7 +198,9 @@ resattn_tc_kernel(const AttnParams p) {
   }
   // the operand was written with ordinary stores: make it visible to the tensor core's async reads
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  __syncthreads();
+  // everybody but the copy producers meets here; the producers are already filling the pipeline
+  if (warp < kFront || warp >= kFirstCons)
+    asm volatile("bar.sync 2, %0;" ::"n"(kThreadsTc - kProd * 32) : "memory");
 
   // ---------------------------------------------------------------- this CTA's tile range
   const int L = min(max(__ldg(p.seq_lens + b), 0), int(p.bt_stride) * p.page_size);
@@ -526,10 +528,13 @@ template <int D>
 int launch_decode_tc(const AttnParams& p, cudaStream_t st) {
   using C = TCfg<D>;
   const int smem = kHeaderBytes + p.stages * C::kStageBytes + 1024;
-  static bool attr_done = false;
-  if (!attr_done) {
+  static bool attr_done[64] = {};                    // function attributes are per device
+  int dev = 0;
+  RI_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (!attr_done[dev]) {
     RI_CUDA(cudaFuncSetAttribute(resattn_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-    attr_done = true;
+    attr_done[dev] = true;
   }
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(p.splits, p.hkv, p.batch);
