@@ -162,16 +162,19 @@ void ri_fp4_gemm_set_trace(int64_t* device_buffer);
  * score_scale = sm_scale * k_global_scale, out_scale = v_global_scale.  The query is quantised
  * to NVFP4 + NVFP4 residue inside the kernel (q_residue == 0 drops the residue rows); q_pack / q_sf
  * are optional (NULL) outputs that receive the quantised query in the layout of
- * ri_nvfp4_quant_grouped_q.  page_size is a multiple of 16.  splits > 1 (KV split per sequence)
- * uses `workspace` (ri_resattn_workspace_bytes) for the per-split partial (o, l, m) and a second,
- * deterministic merge kernel.  status: optional device word, set non-zero if a bounded wait inside
- * the kernel expired.
+ * ri_nvfp4_quant_grouped_q.  page_size is a multiple of 16.  splits > 1 cuts the KV range into
+ * `splits` pieces of ceil(ceil(max_kv_len / 128) / splits) 128-token tiles each -- the same piece
+ * size for every sequence, so long sequences use many splits and short ones few (CTAs of unused
+ * splits leave at once) -- and uses `workspace` (ri_resattn_workspace_bytes) for the per-split
+ * partial (o, l, m) and a second, deterministic merge kernel.  max_kv_len: upper bound of seq_lens
+ * for this call (0 = what the block table can hold, bt_stride * page_size).  status: optional
+ * device word, set non-zero if a bounded wait inside the kernel expired.
  * Replaces run_paged_fp4_decode_qmul4_tmem (csrc/resattn/host.py:489-606). */
 int ri_resattn_decode(const void* q_bf16, const uint8_t* k_data, const uint8_t* k_sf,
                       const uint8_t* v_data, const uint8_t* v_sf, int64_t num_pages,
                       const int32_t* block_tables, int64_t bt_stride, const int32_t* seq_lens,
                       int batch, int num_q_heads, int num_kv_heads, int head_dim, int page_size,
-                      float score_scale, float out_scale, void* out, int out_dtype, uint8_t* q_pack,
+                      int max_kv_len, float score_scale, float out_scale, void* out, int out_dtype, uint8_t* q_pack,
                       int64_t q_pack_bytes, uint8_t* q_sf, int64_t q_sf_bytes, int splits,
                       void* workspace, int64_t workspace_bytes, int q_residue, int32_t* status,
                       void* stream);

@@ -4,21 +4,23 @@
 //
 // The weight is the 128-row MMA-A operand, the tokens are the MMA-N operand (16..256 columns), so
 // decode-sized batches do not waste tensor-core rows and the kernel is a weight-streaming kernel:
-// every CTA pulls one 128 x K slice of W through a TMA pipeline exactly once.
+// every weight byte is pulled through a TMA pipeline exactly once.
 //   * operands: TMA (cp.async.bulk.tensor, 128B-swizzled K-major tiles of 256 FP4 = 128 bytes),
 //     no cluster multicast anywhere;
-//   * block scales: 1-D bulk copies of the 512-byte 128x4 chunks, tcgen05.cp into tensor memory;
+//   * block scales: 1-D bulk copies of the 512-byte 128x4 chunks into shared memory, moved to tensor
+//     memory by four scale warps with wide tcgen05.st (one warp per 32-lane quarter);
 //   * MMA: tcgen05.mma kind::mxf4nvf4.block_scale (block16 / UE4M3 for NVFP4) or kind::mxf4
-//     (block32 / UE8M0 for MXFP4), issued by one thread, FP32 accumulators in tensor memory;
+//     (block32 / UE8M0 for MXFP4), issued by one elected thread, FP32 accumulators in tensor memory;
 //   * residue fold: row_pair activations put base / residue in adjacent accumulator columns that
 //     the epilogue adds; concat_k activations issue two MMA groups per W tile into one accumulator
 //     (W is read once, unlike a K loop over 2K);
-//   * split-K over CTAs for small grids: FP32 partials in a caller workspace, the CTA that arrives
-//     last (atomic ticket, nobody waits) reduces in split order, so the result is deterministic.
+//   * work: the (output tile, K tile) units form one list that a persistent grid cuts into ranges --
+//     whole tiles, even K splits or ragged ranges, chosen by a measured cost model.  K-split tiles
+//     exchange FP32 partials through a caller workspace; the contributor that arrives last (atomic
+//     ticket, nobody waits) sums them in CTA order, so the result is deterministic.
 // Warp roles (11 warps): warp 0 = weight TMA producer, warp 10 = activation TMA producer, warp 1 =
-// MMA issuer (owns tensor memory), warps 2-5 = epilogue, warps 6-9 = scale warps that move the block
-// scales from shared to tensor memory with wide tcgen05.st (one warp per 32-lane quarter).  Every mbarrier wait is bounded: on
-// expiry the kernel records a status word, stops issuing and tears down normally.
+// MMA issuer (owns tensor memory), warps 2-5 = epilogue, warps 6-9 = scale warps.  Every mbarrier
+// wait is bounded: on expiry the kernel records a status word, stops issuing and tears down normally.
 //
 // Stands in for the reference's CuTeDSL Fold kernel (ShawRong/ResInfer
 // csrc/common/fold/sm10x/kernel_sm100_fold.py) and the library GEMM of its KEXT route.

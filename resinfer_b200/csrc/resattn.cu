@@ -31,6 +31,7 @@ struct AttnParams {
   int64_t num_pages;
   int batch, hq, hkv, group, page_size;
   int page_shift;                          // log2(page_size) when it is a power of two, else -1
+  int tiles_per_split;                     // 128-token tiles a KV split covers (the same for every sequence)
   float score_scale_log2;                  // sm_scale * k_global_scale * log2(e)
   float out_scale;
   void* out;                               // [B, Hq, D] bf16 (or fp32 when out_f32)
@@ -147,6 +148,26 @@ resattn_tc_kernel(const AttnParams p) {
   const int G = p.group;
   const int S = p.stages;
 
+  // ---------------------------------------------------------------- this CTA's tile range
+  // A split covers a fixed number of tiles, so long sequences use many splits and short ones few;
+  // a CTA whose range lies past the end of its sequence records an empty partial and leaves at once.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int L = min(max(__ldg(p.seq_lens + b), 0), int(p.bt_stride) * p.page_size);
+  const int n_tiles = (L + kTile - 1) / kTile;
+  const int t_begin = min(split * p.tiles_per_split, n_tiles);
+  const int t_end = min(t_begin + p.tiles_per_split, n_tiles);
+  const int my_tiles = t_end - t_begin;
+  if (my_tiles == 0 && p.splits > 1) {
+    if (threadIdx.x < G) {
+      const int64_t slot = (int64_t(split) * p.batch + b) * p.hq + hkv * G + threadIdx.x;
+      p.l_part[slot] = 0.f;
+      p.m_part[slot] = -INFINITY;                  // the merge skips partials with m = -inf
+    }
+    return;
+  }
+  const int32_t* bt = p.block_tables + int64_t(b) * p.bt_stride;
+
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(smem_u32(&bar_full[s]), kProd * 32);    // one arrival per producer lane
@@ -165,8 +186,6 @@ resattn_tc_kernel(const AttnParams p) {
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   for (int i = threadIdx.x; i < 3072 / 16; i += blockDim.x) reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  asm volatile("griddepcontrol.wait;" ::: "memory");
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -201,15 +220,6 @@ resattn_tc_kernel(const AttnParams p) {
   // everybody but the copy producers meets here; the producers are already filling the pipeline
   if (warp < kFront || warp >= kFirstCons)
     asm volatile("bar.sync 2, %0;" ::"n"(kThreadsTc - kProd * 32) : "memory");
-
-  // ---------------------------------------------------------------- this CTA's tile range
-  const int L = min(max(__ldg(p.seq_lens + b), 0), int(p.bt_stride) * p.page_size);
-  const int n_tiles = (L + kTile - 1) / kTile;
-  const int per_split = (n_tiles + p.splits - 1) / p.splits;
-  const int t_begin = min(split * per_split, n_tiles);
-  const int t_end = min(t_begin + per_split, n_tiles);
-  const int my_tiles = t_end - t_begin;
-  const int32_t* bt = p.block_tables + int64_t(b) * p.bt_stride;
 
   float oacc[8][4];
 #pragma unroll
@@ -568,7 +578,7 @@ __global__ void resattn_merge_kernel(const float* __restrict__ o_part, const flo
     float o = 0.f;
     for (int s = 0; s < splits; ++s) {
       const float ms = m_part[s * rows + row];
-      o += (ms == -INFINITY ? 0.f : fast_exp2(ms - mm)) * o_part[(s * rows + row) * d + c];
+      if (ms != -INFINITY) o += fast_exp2(ms - mm) * o_part[(s * rows + row) * d + c];   // empty partials hold no data
     }
     if (out_f32) static_cast<float*>(out)[row * d + c] = o * r;
     else static_cast<__nv_bfloat16*>(out)[row * d + c] = __float2bfloat16_rn(o * r);
@@ -590,7 +600,7 @@ extern "C" int ri_resattn_decode(const void* q_bf16, const uint8_t* k_data, cons
                                  const uint8_t* v_data, const uint8_t* v_sf, int64_t num_pages,
                                  const int32_t* block_tables, int64_t bt_stride, const int32_t* seq_lens,
                                  int batch, int num_q_heads, int num_kv_heads, int head_dim, int page_size,
-                                 float score_scale, float out_scale, void* out, int out_dtype, uint8_t* q_pack,
+                                 int max_kv_len, float score_scale, float out_scale, void* out, int out_dtype, uint8_t* q_pack,
                                  int64_t q_pack_bytes, uint8_t* q_sf, int64_t q_sf_bytes, int splits,
                                  void* workspace, int64_t workspace_bytes, int q_residue, int32_t* status,
                                  void* stream) {
@@ -604,6 +614,7 @@ extern "C" int ri_resattn_decode(const void* q_bf16, const uint8_t* k_data, cons
   RI_CHECK_ARG(page_size >= 16 && page_size % 16 == 0, "page size must be a multiple of 16, got %d", page_size);
   RI_CHECK_ARG(batch >= 0 && num_pages > 0 && bt_stride >= 1, "bad batch / page pool / block table");
   RI_CHECK_ARG(splits >= 1 && splits <= 256, "splits must be in [1, 256]");
+  RI_CHECK_ARG(max_kv_len >= 0, "max_kv_len must be non-negative");
   RI_CHECK_ARG((reinterpret_cast<uintptr_t>(k_data) & 15) == 0 && (reinterpret_cast<uintptr_t>(v_data) & 15) == 0 &&
                    (reinterpret_cast<uintptr_t>(k_sf) & 15) == 0 && (reinterpret_cast<uintptr_t>(v_sf) & 15) == 0 &&
                    (reinterpret_cast<uintptr_t>(q_bf16) & 15) == 0,
@@ -632,6 +643,13 @@ extern "C" int ri_resattn_decode(const void* q_bf16, const uint8_t* k_data, cons
   p.out_f32 = out_dtype == RI_DTYPE_F32;
   p.q_pack = q_pack; p.q_sf = q_sf;
   p.splits = splits; p.q_residue = q_residue; p.status = status;
+  {
+    const int64_t cap = bt_stride * page_size;
+    const int64_t bound = max_kv_len > 0 && max_kv_len < cap ? max_kv_len : cap;
+    const int64_t tiles = (bound + 127) / 128;
+    p.tiles_per_split = int((tiles + splits - 1) / splits);
+    if (p.tiles_per_split < 1) p.tiles_per_split = 1;
+  }
 #ifdef RI_ATTN_PROFILE
   if (const char* e = getenv("RI_ATTN_TRACE_PTR")) p.trace = reinterpret_cast<long long*>(strtoull(e, nullptr, 16));
 #endif

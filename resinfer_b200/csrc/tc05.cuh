@@ -1,8 +1,7 @@
 // Thin wrappers over the Blackwell (sm_100a) tensor-memory / tensor-core / TMA instructions that the
 // GEMM and the attention kernel share: tcgen05.mma (block-scaled FP4), tcgen05.ld / st / commit,
 // shared-memory matrix descriptors, tiled TMA loads, and the driver entry point that encodes tensor
-// maps.  Everything here is inline; include it inside a translation unit's own anonymous namespace
-// users via `namespace ri { namespace tc { ... } }`.
+// maps.  Everything here is inline and lives in namespace ri::tc.
 #pragma once
 #include <cuda.h>
 

@@ -147,7 +147,8 @@ def run_paged_fp4_decode_qmul4_tmem(q: torch.Tensor, pool: NvFp4PagedKVPool, v_d
         st = lib.ri_resattn_decode(
             q.data_ptr(), pool.k_data.data_ptr(), pool.k_sf.data_ptr(), v_data_hnd.data_ptr(),
             v_sf_bthd.data_ptr(), pool.k_data.shape[0], block_tables.data_ptr(), block_tables.stride(0),
-            seq_lens.data_ptr(), b, hq, h, d, page, float(sm_scale), float(value_scale), out.data_ptr(),
+            seq_lens.data_ptr(), b, hq, h, d, page, int(max_seq_len or 0), float(sm_scale), float(value_scale),
+            out.data_ptr(),
             _cabi.DTYPE_BF16, None, 0, None, 0, splits, ws_ptr, ws_bytes, 1,
             ops.status_word(q.device).data_ptr(), _cabi.current_stream(q.device))
     _cabi.check(st, "run_paged_fp4_decode_qmul4_tmem")

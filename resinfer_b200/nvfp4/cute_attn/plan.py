@@ -34,19 +34,22 @@ def _pow2_floor(v: int) -> int:
     return 1 << (max(1, v).bit_length() - 1)
 
 
-def _select_splits(batch: int, heads: int, length: int, sms: int, ctas_per_sm: int = 7,
-                   min_tiles_per_split: int = 4) -> int:
-    """One CTA per SM at a time, 128-token tiles.  Measured on B200: about seven CTAs per SM over the
-    run balance the tail of unequal sequence lengths against the fixed cost of a CTA (about 5 us:
-    tensor-memory allocation, query quantisation, merge), and beyond eight splits the partials start
-    to cost more than the balance gains."""
+def _select_splits(batch: int, heads: int, length: int, sms: int, min_tiles_per_split: int = 4) -> int:
+    """One CTA per SM at a time, 128-token tiles, and every split covers the same number of tiles
+    (ceil(tiles(length) / splits)) whatever the sequence: short sequences simply use fewer splits and
+    the CTAs of their unused splits leave at once.  Measured on B200, the best piece size is the one
+    that lets the working CTAs of the whole batch fit the SMs in one wave (a CTA costs about 5 us of
+    set-up and merge, a tile about 1 us), so the piece is the expected tile count of the batch divided
+    by the SM count, with 15 % head room; a batch of several sequences is assumed to average half of
+    the longest length."""
     grid = max(1, batch * heads)
     tiles = max(1, (length + 127) // 128)
-    want = _pow2_floor(max(1, (sms * ctas_per_sm) // grid))
-    if want >= 16:
-        want //= 2
-    cap = _pow2_floor(max(1, tiles // min_tiles_per_split))
-    return max(1, min(want, cap, 64))
+    total = grid * tiles * (0.5 if batch > 1 else 1.0)      # expected tiles of the whole batch
+    piece = max(min_tiles_per_split, -(-int(total * 1.15) // sms))
+    splits = -(-tiles // piece)
+    # many waves of unequal sequences: pieces of at most a third of the longest context even out the tail
+    splits = max(splits, min(3, tiles // 64))
+    return max(1, min(splits, 64))
 
 
 def select_decode_plan(batch, num_kv_heads, max_kv_len, sm_count, *, output_nvfp4=False,

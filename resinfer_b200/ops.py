@@ -138,7 +138,7 @@ def resattn_decode(q: torch.Tensor, k_data: torch.Tensor, k_sf: torch.Tensor, v_
                    v_sf: torch.Tensor, block_tables: torch.Tensor, seq_lens: torch.Tensor,
                    score_scale: float, out_scale: float, out: torch.Tensor, *, splits: int = 1,
                    q_residue: bool = True, q_pack: torch.Tensor | None = None,
-                   q_sf: torch.Tensor | None = None) -> torch.Tensor:
+                   q_sf: torch.Tensor | None = None, max_kv_len: int = 0) -> torch.Tensor:
     """Paged NVFP4-KV decode attention.  q bf16 [B,Hq,D]; k_data/v_data uint8 [pages,Hkv,page,D/2];
     k_sf/v_sf uint8 (or float8_e4m3fn) [pages,Hkv,page,D/16]; out bf16 [B,Hq,D] (written)."""
     lib = _cabi.load()
@@ -154,7 +154,7 @@ def resattn_decode(q: torch.Tensor, k_data: torch.Tensor, k_sf: torch.Tensor, v_
         st = lib.ri_resattn_decode(
             q.data_ptr(), k_data.data_ptr(), k_sf.data_ptr(), v_data.data_ptr(), v_sf.data_ptr(), pages,
             block_tables.data_ptr(), block_tables.stride(0), seq_lens.data_ptr(), b, hq, hkv, d, page,
-            float(score_scale), float(out_scale), out.data_ptr(),
+            int(max_kv_len), float(score_scale), float(out_scale), out.data_ptr(),
             _cabi.torch_dtype_code(out.dtype, allow_f32=True), _cabi.ptr(q_pack), 0 if q_pack is None else q_pack.numel(),
             _cabi.ptr(q_sf), 0 if q_sf is None else q_sf.numel(),
             splits, _cabi.ptr(ws), ws_bytes, int(q_residue), status_word(dev).data_ptr(),
