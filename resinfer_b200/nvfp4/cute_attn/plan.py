@@ -47,8 +47,10 @@ def _select_splits(batch: int, heads: int, length: int, sms: int, min_tiles_per_
     total = grid * tiles * (0.5 if batch > 1 else 1.0)      # expected tiles of the whole batch
     piece = max(min_tiles_per_split, -(-int(total * 1.15) // sms))
     splits = -(-tiles // piece)
-    # many waves of unequal sequences: pieces of at most a third of the longest context even out the tail
-    splits = max(splits, min(3, tiles // 64))
+    # a few waves of unequal sequences: pieces of at most a third of the longest context even out the
+    # tail (with very many CTAs the tail is short anyway and every extra CTA costs its set-up)
+    if grid <= 8 * sms:
+        splits = max(splits, min(3, tiles // 64))
     return max(1, min(splits, 64))
 
 

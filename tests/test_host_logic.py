@@ -62,7 +62,10 @@ def test_decode_plan_selection_and_validation():
     from resinfer_b200.nvfp4.cute_attn.plan import select_decode_plan, validate_decode_plan, static_compile_plans
     assert select_decode_plan(256, 8, 32768, 148) == (1, "none")
     s, r = select_decode_plan(1, 8, 32768, 148)
-    assert r == "kernel" and s > 1 and s & (s - 1) == 0
+    assert r == "kernel" and 8 <= s <= 64
+    # eight sequences of up to 32768 tokens: pieces sized so that the working CTAs fill the SMs once
+    assert select_decode_plan(8, 8, 32768, 148) == (4, "kernel")
+    assert select_decode_plan(64, 8, 32768, 148) == (3, "kernel")     # a few waves: thirds even out the tail
     assert select_decode_plan(1, 8, 64, 148) == (1, "none")          # too short to split
     assert (1, "none") in static_compile_plans()
     validate_decode_plan((4, "kernel"))
