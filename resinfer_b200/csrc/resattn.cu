@@ -158,7 +158,7 @@ resattn_tc_kernel(const AttnParams p) {
   const int t_begin = min(split * p.tiles_per_split, n_tiles);
   const int t_end = min(t_begin + p.tiles_per_split, n_tiles);
   const int my_tiles = t_end - t_begin;
-  if (my_tiles == 0 && p.splits > 1) {
+  if (my_tiles == 0 && p.splits > 1 && !(p.q_pack && split == 0)) {     // (split 0 also emits the quantised query)
     if (threadIdx.x < G) {
       const int64_t slot = (int64_t(split) * p.batch + b) * p.hq + hkv * G + threadIdx.x;
       p.l_part[slot] = 0.f;
