@@ -118,14 +118,17 @@ class ClockSampler:
 # ------------------------------------------------------------------------------------------------
 # algorithmic work
 # ------------------------------------------------------------------------------------------------
+SCALE_BLOCK = 16                     # elements per block scale: 16 (NVFP4) or 32 (MXFP4, set by --format)
+
+
 def mext_bytes(m, k, n):
     """x (bf16) + W codes and block scales + y (bf16): the bytes a fused MEXT linear must move."""
-    return 2 * m * k + n * k * (0.5 + 1.0 / 16.0) + 2 * m * n
+    return 2 * m * k + n * k * (0.5 + 1.0 / SCALE_BLOCK) + 2 * m * n
 
 
 def gemm_bytes(m, k, n):
     """GEMM kernel alone: activation codes+scales (base and residue), W codes+scales, y."""
-    return 2 * m * k * (0.5 + 1.0 / 16.0) + n * k * (0.5 + 1.0 / 16.0) + 2 * m * n
+    return 2 * m * k * (0.5 + 1.0 / SCALE_BLOCK) + n * k * (0.5 + 1.0 / SCALE_BLOCK) + 2 * m * n
 
 
 def mext_flops(m, k, n):
@@ -202,8 +205,8 @@ def run_reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
-def workload_config(n_gpus):
-    return {"workload": "MEXT NVFP4 sweep: qkv 5120->10240, o 8192->5120, gate_up 5120->51200, down 25600->5120; "
+def workload_config(n_gpus, fmt="nvfp4"):
+    return {"workload": "MEXT " + fmt.upper() + " sweep: qkv 5120->10240, o 8192->5120, gate_up 5120->51200, down 25600->5120; "
                         "M in {1,2,4,8,16,32,64,128}; online quantiser + folded GEMM per case",
             "l2": "inputs larger than L2: 274 MB of weights stream per pass over the four shapes, rotating copies",
             "parallelism": "tp%d" % n_gpus if n_gpus > 1 else "single GPU", "cuda_graph": True}
@@ -215,7 +218,7 @@ def workload_config(n_gpus):
 class Layer:
     """One projection on one rank: prequantised weight copies + activation buffers."""
 
-    def __init__(self, name, k, n, par, tp, rank, dev, copies_bytes=2 * L2_BYTES):
+    def __init__(self, name, k, n, par, tp, rank, dev, copies_bytes=2 * L2_BYTES, fmt="nvfp4"):
         import torch
         from resinfer_b200.quant import weight_prep
         self.name, self.par = name, par
@@ -224,13 +227,13 @@ class Layer:
         self.n = n // tp if par == "col" else n
         g = torch.Generator(device=dev).manual_seed(1 + rank)
         w = (torch.randn(self.n, self.k, generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
-        prep = weight_prep.quantize_weight_nvfp4(w)
+        prep = weight_prep.quantize_weight_mxfp4(w) if fmt == "mxfp4" else weight_prep.quantize_weight_nvfp4(w)
         del w
         wbytes = prep["weight"].numel() + prep["weight_scale"].numel()
         self.copies = max(1, min(8, -(-copies_bytes // wbytes)))
         self.w = [prep["weight"].clone() for _ in range(self.copies)]
         self.w_sf = [prep["weight_scale"].clone() for _ in range(self.copies)]
-        self.w_gs = prep["weight_global_scale"]
+        self.w_gs = prep.get("weight_global_scale", torch.ones(1, device=dev))   # MXFP4 has no global scale
         self.x, self.gs_inv, self.alpha = {}, {}, {}
         for m in MS:
             gx = torch.Generator(device=dev).manual_seed(0)
@@ -259,6 +262,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-detail", action="store_true", help="skip the per-case and ResAttn detail measurements")
+    ap.add_argument("--format", default="nvfp4", choices=["nvfp4", "mxfp4"],
+                    help="number format of the headline sweep (BASELINE configs[1] = nvfp4, configs[2] = mxfp4)")
     ap.add_argument("--sweeps", action="store_true",
                     help="measure the other sweeps of the three hot paths (MXFP4 MEXT, KEXT, ResAttn batch sizes) "
                          "and print them as a second JSON line {\"sweeps\": ...}; N = 1 only")
@@ -292,7 +297,8 @@ def main():
     from resinfer_b200.quant.vllm_integration import residue_linear_op  # noqa: F401
     nvfp4.ensure_loaded()
 
-    global SHAPES, MS
+    global SHAPES, MS, SCALE_BLOCK
+    SCALE_BLOCK = 32 if args.format == "mxfp4" else 16
     if args.only:
         kind, _, rest = args.only.partition(":")
         if kind == "resattn":
@@ -306,20 +312,26 @@ def main():
         MS = [int(m_only)]
         args.no_detail = True
     note("process group up; building layers")
-    layers = [Layer(nm, k, n, par, tp, rank, dev) for nm, k, n, par in SHAPES]
+    layers = [Layer(nm, k, n, par, tp, rank, dev, fmt=args.format) for nm, k, n, par in SHAPES]
     note("layers built")
+    mx = args.format == "mxfp4"
+    if mx:
+        from resinfer_b200.nvfp4 import mxfp4
     outs = {(L.name, m): torch.empty(m, L.n, dtype=torch.bfloat16, device=dev) for L in layers for m in MS}
     launches = {"n": 0}
 
     def run_case(L, m, quant=True, pre=None, reduce=True):
         c = L.next_copy()
         if quant:
-            codes, sf = nvfp4.scaled_fp4_quant_mext_r1(L.x[m], L.gs_inv[m], layout_mode=1, enable_pdl=True)
+            if mx:
+                codes, sf = mxfp4.quantize_mext(L.x[m], pdl_mode="early")
+            else:
+                codes, sf = nvfp4.scaled_fp4_quant_mext_r1(L.x[m], L.gs_inv[m], layout_mode=1, enable_pdl=True)
             launches["n"] += 1
         else:
             codes, sf = pre
-        y = ops.fp4_gemm(codes, sf, L.w[c], L.w_sf[c], L.alpha[m], m=m, fmt="nvfp4", layout="row_pair",
-                         out=outs[(L.name, m)])
+        y = ops.fp4_gemm(codes, sf, L.w[c], L.w_sf[c], None if mx else L.alpha[m], m=m, fmt=args.format,
+                         layout="row_pair", out=outs[(L.name, m)])
         launches["n"] += 1
         if tp > 1 and L.par == "row" and reduce:
             dist.all_reduce(y)
@@ -386,7 +398,8 @@ def main():
     us_per_op = ms_step * 1e3 / n_cases
 
     # ---- GEMM kernel alone (pre-quantised activations) for the roofline of the dominant kernel
-    pre = {(L.name, m): nvfp4.scaled_fp4_quant_mext_r1(L.x[m], L.gs_inv[m], layout_mode=1) for L in layers for m in MS}
+    pre = {(L.name, m): (mxfp4.quantize_mext(L.x[m]) if mx else
+                         nvfp4.scaled_fp4_quant_mext_r1(L.x[m], L.gs_inv[m], layout_mode=1)) for L in layers for m in MS}
     no_reduce = {"on": False}
     replay_g = capture(lambda: sweep(False, pre, reduce=False))
     hbm_gbs, peak_kind = load_peaks()
@@ -421,8 +434,12 @@ def main():
                 for L in layers:
                     c = L.next_copy()
                     xd = hx[(L.name, m)].to(dev, non_blocking=True)
-                    y = torch.ops.residue.nvfp4_linear(xd, L.w[c], L.gs_inv[m], L.w_sf[c], L.w_sf[c], zero_mask,
-                                                       L.alpha[m], L.k, 0, 0, L.n, True, False, True)
+                    if mx:
+                        y = torch.ops.residue.mxfp4_linear(xd, L.w[c], L.w_sf[c], zero_mask, zero_mask, "mext_r1",
+                                                           torch.bfloat16, None)
+                    else:
+                        y = torch.ops.residue.nvfp4_linear(xd, L.w[c], L.gs_inv[m], L.w_sf[c], L.w_sf[c], zero_mask,
+                                                           L.alpha[m], L.k, 0, 0, L.n, True, False, True)
                     if tp > 1 and L.par == "row":
                         dist.all_reduce(y)
                     done[i].record()
@@ -451,8 +468,20 @@ def main():
                        "D2H of y on a second stream; includes Python and launch overhead"}
 
     detail = None
-    if not args.no_detail and tp == 1:
+    if not args.no_detail and tp == 1 and not mx:
         detail = measure_detail(torch, dev, layers, outs, nvfp4, ops, capture, timed, hbm_gbs)
+    elif not args.no_detail and tp > 1 and 8 % tp == 0:
+        # ResAttn shards by KV head (8 / tp KV heads and 64 / tp query heads per rank, no collective);
+        # the time is the maximum over ranks, the bytes are those of all ranks
+        try:
+            ra = measure_resattn(torch, dev, ops, capture, timed, hbm_gbs, custom=(128, 64), heads=(64 // tp, 8 // tp))
+            for r in ra:
+                r["tbs"] = round(r["tbs"] * tp, 3)
+                r["frac_hbm"] = round(r["frac_hbm"], 3)
+                r["note"] = "KV heads sharded over %d GPUs; TB/s summed over ranks, frac_hbm per GPU" % tp
+            detail = {"resattn": ra}
+        except Exception as e:
+            detail = {"resattn": [{"error": f"{type(e).__name__}: {e}"}]}
 
     cpu = None
     if rank == 0 and tp == 1 and not args.only:
@@ -465,12 +494,12 @@ def main():
     if rank == 0:
         flops = sum(mext_flops(m, L.k_full, L.n_full) for L in layers for m in MS)
         line = {
-            "metric": "mext_nvfp4_linear_latency", "value": us_per_op, "unit": "us", "n_gpus": world,
+            "metric": "mext_%s_linear_latency" % args.format, "value": us_per_op, "unit": "us", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": False,
             "scaling": "strong", "vs_baseline": None,
-            "dtype": "nvfp4 (E2M1 x E4M3 block scales), fp32 accumulate", "data": "synthetic",
-            "config": workload_config(world), "clocks": clk.summary(), "gpu_launches": per_step_launches * args.steps,
-            "tflops": flops / (ms_step * 1e-3) / 1e12,
+            "dtype": ("mxfp4 (E2M1 x E8M0 block scales)" if mx else "nvfp4 (E2M1 x E4M3 block scales)") + ", fp32 accumulate",
+            "data": "synthetic", "config": workload_config(world, args.format), "clocks": clk.summary(), "gpu_launches": per_step_launches * args.steps,
+            "tflops": flops / (ms_step * 1e-3) / 1e12, "fp4_peak_frac": flops / (ms_step * 1e-3) / 9.0e15,
             "hbm_gbs_algorithmic": sum(mext_bytes(m, L.k_full, L.n_full) for L in layers for m in MS) / (ms_step * 1e-3) / 1e9,
             "e2e": e2e, "roofline": roofline, "cpu_baseline": cpu, "detail": detail,
         }
@@ -603,10 +632,11 @@ def measure_sweeps(torch, dev, capture, timed, hbm_gbs):
     return out
 
 
-def measure_resattn(torch, dev, ops, capture, timed, hbm_gbs, only=None, steps=10, warmup=3, custom=None):
+def measure_resattn(torch, dev, ops, capture, timed, hbm_gbs, only=None, steps=10, warmup=3, custom=None,
+                    heads=(64, 8)):
     from resinfer_b200.nvfp4.cute_attn.plan import select_decode_plan
     res = []
-    hq, hkv, page = 64, 8, 16
+    (hq, hkv), page = heads, 16
     sms = torch.cuda.get_device_properties(dev).multi_processor_count
     for idx, (d, batch) in enumerate(((128, 8), (128, 64), (256, 32)) if custom is None else (custom,)):
         if only is not None and idx != only:

@@ -31,6 +31,7 @@ _ALIASES = {
     "quant": "resinfer_b200.quant",
     "quant.linear_registry": "resinfer_b200.quant.linear_registry",
     "quant.mxfp4_linear": "resinfer_b200.quant.mxfp4_linear",
+    "quant.kernel_metadata": "resinfer_b200.quant.kernel_metadata",
     "quant.vllm_integration": "resinfer_b200.quant.vllm_integration",
     "quant.vllm_integration.residue_linear_op": "resinfer_b200.quant.vllm_integration.residue_linear_op",
     "quant.vllm_integration.residue_tp": "resinfer_b200.quant.vllm_integration.residue_tp",

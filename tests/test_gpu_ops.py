@@ -120,3 +120,26 @@ def test_registered_linear_modules(cuda_device):
     assert errs[("ResidueLinear", 1.0)] < errs[("ResidueLinear", 0.25)] < errs[("NVFP4Linear", 0)] < 0.25
     with pytest.raises(NotImplementedError):
         LinearRegistry.get("ResidueSwapLinear").from_linear(lin)
+
+
+def test_baseline_config0_mext_linear(cuda_device):
+    """The CPU-runnable configuration of the baseline: x BF16 [16, 5120] (N(0,1), 1 % of channels x20),
+    W BF16 [8192, 5120] (N(0, 0.02^2)), NVFP4 with FP32 global scales, y = deq(q(x)) deq(q(W))^T +
+    deq(q(r)) deq(q(W))^T in FP32, BF16 out.  The op must equal the oracle's contraction of the same codes
+    within BF16 rounding, and the torch-eager restatement of the reference's path within quantisation noise."""
+    from resinfer_b200.quant.vllm_integration import residue_linear_op  # noqa: F401
+    m, k, n = 16, 5120, 8192
+    x_np, w_np, x, prep, gi, alpha, _ = _setup(m, k, n, cuda_device)
+    mask = torch.zeros(1, dtype=torch.uint8, device=cuda_device)
+    y = torch.ops.residue.nvfp4_linear(x, prep["weight"], gi, prep["weight_scale"], prep["weight_scale_base"], mask,
+                                       alpha, k, 0, 0, n, True, False, True)
+    got = y.detach().float().cpu().numpy()
+    codes, sf, _ = O.nvfp4_quant_mext(x_np, gi.cpu().numpy()[0], 1)
+    a = O.dequant_operand(codes, sf, "nvfp4")
+    wd = O.dequant_operand(prep["weight"].cpu().numpy(), prep["weight_scale"].cpu().numpy(), "nvfp4")
+    ref = O.fp4_linear_reference(a[0::2] + a[1::2], wd, float(alpha.item()), False)
+    assert rel_fro(got, ref) < 2.5e-3
+    eager = O.eager_residue_linear(torch.from_numpy(x_np).to(torch.bfloat16), torch.from_numpy(w_np).to(torch.bfloat16))
+    assert rel_fro(got, eager.float().numpy()) < 2e-2
+    dense = x_np.astype(np.float64) @ w_np.astype(np.float64).T
+    assert rel_fro(got, dense) < 0.12
