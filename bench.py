@@ -294,6 +294,7 @@ def main():
             print(f"[bench] {msg}", file=sys.stderr, flush=True)
 
     from resinfer_b200 import nvfp4, ops
+    from resinfer_b200.quant import mxfp4_linear  # noqa: F401  (registers residue::mxfp4_linear)
     from resinfer_b200.quant.vllm_integration import residue_linear_op  # noqa: F401
     nvfp4.ensure_loaded()
 

@@ -34,6 +34,7 @@ extern "C" {
 #define RI_DTYPE_BF16 0
 #define RI_DTYPE_FP16 1
 #define RI_DTYPE_F32 2 /* outputs only: unrounded FP32 result, for accuracy checks */
+#define RI_DTYPE_NVFP4 3 /* ri_resattn_decode output only: packed E2M1 codes + E4M3 block scales */
 
 /* FP4 formats */
 #define RI_FMT_NVFP4 0 /* 16-element blocks, E4M3 block scale, FP32 global scale */
@@ -158,7 +159,11 @@ void ri_fp4_gemm_set_trace(int64_t* device_buffer);
 /* ResAttn: residue-compensated paged NVFP4-KV decode attention, one query token per sequence.
  * q [B,Hq,D] bf16; k_data/v_data [pages,Hkv,page_size,D/2]; k_sf/v_sf [pages,Hkv,page_size,D/16]
  * E4M3 bytes (linear); block_tables int32 [B, bt_stride]; seq_lens int32 [B]; out [B,Hq,D] bf16
- * (out_dtype RI_DTYPE_BF16; RI_DTYPE_F32 writes the unrounded result).
+ * (out_dtype RI_DTYPE_BF16; RI_DTYPE_F32 writes the unrounded result; RI_DTYPE_NVFP4 writes the
+ * activation format of the following projection: `out` = uint8 codes [B, Hq*D/2], out_block_scale =
+ * 128x4-swizzled E4M3 scales over rows = sequences and hidden = Hq*D, scale = e4m3(amax * g / 6) with
+ * g = *out_global_scale -- quantize_nvfp4_block16 / output_scale_offset, csrc/resattn/output.py:10-34,
+ * run_paged_fp4_decode_qmul4_tmem_nvfp4, quant/vllm_integration/attn/decode.py:55-101).
  * score_scale = sm_scale * k_global_scale, out_scale = v_global_scale.  The query is quantised
  * to NVFP4 + NVFP4 residue inside the kernel (q_residue == 0 drops the residue rows); q_pack / q_sf
  * are optional (NULL) outputs that receive the quantised query in the layout of
@@ -175,8 +180,9 @@ int ri_resattn_decode(const void* q_bf16, const uint8_t* k_data, const uint8_t* 
                       const int32_t* block_tables, int64_t bt_stride, const int32_t* seq_lens,
                       int batch, int num_q_heads, int num_kv_heads, int head_dim, int page_size,
                       int max_kv_len, float score_scale, float out_scale, void* out, int out_dtype, uint8_t* q_pack,
-                      int64_t q_pack_bytes, uint8_t* q_sf, int64_t q_sf_bytes, int splits,
-                      void* workspace, int64_t workspace_bytes, int q_residue, int32_t* status,
+                      int64_t q_pack_bytes, uint8_t* q_sf, int64_t q_sf_bytes,
+                      const float* out_global_scale, uint8_t* out_block_scale, int64_t out_block_scale_bytes,
+                      int splits, void* workspace, int64_t workspace_bytes, int q_residue, int32_t* status,
                       void* stream);
 int64_t ri_resattn_workspace_bytes(int batch, int num_q_heads, int head_dim, int splits);
 

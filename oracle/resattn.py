@@ -21,7 +21,7 @@ from .fp4_codec import (bf16_round, e2m1_decode, e4m3_decode, e4m3_encode, sf_of
 from .nvfp4_quant import nvfp4_quant_grouped_q, nvfp4_quant_plain
 
 __all__ = ["make_paged_kv", "dequant_paged", "resattn_decode_reference", "merge_splits",
-           "dequant_grouped_q"]
+           "dequant_grouped_q", "quantize_attention_output_nvfp4"]
 
 f32 = np.float32
 
@@ -155,3 +155,25 @@ def merge_splits(o_parts: np.ndarray, l_parts: np.ndarray, m_parts: np.ndarray, 
     o = (w[..., None] * o_parts).sum(axis=0)
     l = (w * l_parts).sum(axis=0)
     return o / l[..., None] * scale_o
+
+
+def quantize_attention_output_nvfp4(out: np.ndarray, global_scale, rcp=None):
+    """Packed NVFP4 form of an attention output ``out`` [B, Hq, D] (float32): codes uint8 [B, Hq*D/2] and the
+    128x4-swizzled E4M3 block-scale buffer over rows = sequences, hidden = Hq*D.
+
+    Arithmetic of quantize_nvfp4_block16 / output_scale_offset (csrc/resattn/output.py:10-34): per 16
+    consecutive values of the flattened hidden axis, scale = e4m3(amax * g * (1/6)) evaluated left to right
+    in float32, multiplier = g * rcp(scale) (0 for an all-zero block), codes = e2m1(value * multiplier)."""
+    from .fp4_codec import ExactRcp, e2m1_encode, e4m3_encode, pack_nibbles, swizzle_scales
+    rcp = rcp or ExactRcp()
+    b = out.shape[0]
+    hidden = int(np.prod(out.shape[1:]))
+    g = f32(global_scale)
+    v = np.ascontiguousarray(out, dtype=f32).reshape(b, hidden // 16, 16)
+    amax = np.abs(v).max(-1).astype(f32)
+    sfv = ((amax * g).astype(f32) * f32(1.0 / 6.0)).astype(f32)
+    sf_byte, sf_val = e4m3_encode(sfv)
+    safe = np.where(sf_val != 0, sf_val, f32(1.0)).astype(f32)
+    mult = np.where(sf_val != 0, (g * rcp(safe)).astype(f32), f32(0.0)).astype(f32)
+    codes = e2m1_encode((v * mult[..., None]).astype(f32)).reshape(b, hidden)
+    return pack_nibbles(codes), swizzle_scales(sf_byte.reshape(b, hidden // 16))

@@ -16,7 +16,7 @@ _PKG = Path(__file__).resolve().parent
 LIB_PATH = Path(os.environ.get("RESINFER_B200_LIB") or _PKG / "_lib" / "libresinfer_b200.so")
 
 RI_ERR_ARG, RI_ERR_UNSUPPORTED, RI_ERR_DEVICE, RI_ERR_TIMEOUT = -1, -2, -3, -4
-DTYPE_BF16, DTYPE_FP16, DTYPE_F32 = 0, 1, 2
+DTYPE_BF16, DTYPE_FP16, DTYPE_F32, DTYPE_NVFP4 = 0, 1, 2, 3
 FMT_NVFP4, FMT_MXFP4 = 0, 1
 GEMM_PLAIN, GEMM_ROW_PAIR, GEMM_CONCAT_K = 0, 1, 2
 
@@ -40,7 +40,7 @@ SIGNATURES = {
     "ri_fp4_gemm_auto_splits": (_i, [_i, _i, _i, _i, _i]),
     "ri_fp4_gemm_set_trace": (None, [_vp]),
     "ri_resattn_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _vp, _i, _i, _i, _i, _i, _i, _f, _f,
-                               _vp, _i, _vp, _i64, _vp, _i64, _i, _vp, _i64, _i, _vp, _vp]),
+                               _vp, _i, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i, _vp, _i64, _i, _vp, _vp]),
     "ri_resattn_workspace_bytes": (_i64, [_i, _i, _i, _i]),
     "ri_rcp_approx": (_i, [_vp, _vp, _i, _vp]),
 }

@@ -34,8 +34,11 @@ struct AttnParams {
   int tiles_per_split;                     // 128-token tiles a KV split covers (the same for every sequence)
   float score_scale_log2;                  // sm_scale * k_global_scale * log2(e)
   float out_scale;
-  void* out;                               // [B, Hq, D] bf16 (or fp32 when out_f32)
+  void* out;                               // [B, Hq, D] bf16 (or fp32 when out_f32), or NVFP4 codes [B, Hq*D/2]
   int out_f32;
+  int out_nvfp4;                           // packed NVFP4 output: codes in `out`, block scales in out_sf
+  const float* out_gs;                     // device FP32: global scale of the NVFP4 output (1 / global scale of the consumer)
+  uint8_t* out_sf;                         // 128x4-swizzled E4M3 block scales over [B, Hq*D]
   float* o_part; float* l_part; float* m_part;   // [splits, B, Hq, (D)]
   uint8_t* q_pack; uint8_t* q_sf;          // optional copies of the quantised query
   int splits, q_residue, stages;
@@ -82,6 +85,9 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // S is double buffered in tensor memory, so the MMA of tile i+1 runs under the softmax of tile i.
 // Every mbarrier wait is bounded (status word + normal teardown on expiry).
 // =================================================================================================
+__device__ __forceinline__ void store_nvfp4_out16(const float (&v)[16], float gs, uint8_t* codes_row, uint8_t* sf,
+                                                  int row, int block, int hidden);
+
 namespace tcattn {
 using namespace tc;
 // per-tile event times of CTA (0,0,0) in development builds: row `ev`, first 32 tiles
@@ -515,7 +521,8 @@ resattn_tc_kernel(const AttnParams p) {
     if (p.splits == 1) {
       const float rr = l > 0.f ? p.out_scale / l : 0.f;
       const int64_t oi = (int64_t(b) * p.hq + head) * D + d;
-      if (p.out_f32) static_cast<float*>(p.out)[oi] = o * rr;
+      if (p.out_nvfp4) sbuf[g * D + d] = o * rr;                 // quantised below, 16 values per thread
+      else if (p.out_f32) static_cast<float*>(p.out)[oi] = o * rr;
       else static_cast<__nv_bfloat16*>(p.out)[oi] = __float2bfloat16_rn(o * rr);
     } else {
       const int64_t slot = (int64_t(split) * p.batch + b) * p.hq + head;
@@ -528,6 +535,15 @@ resattn_tc_kernel(const AttnParams p) {
   }
   if (failed && threadIdx.x == 0 && p.status) atomicExch(p.status, 1 + int(blockIdx.z) + (abort_flag << 16));
   __syncthreads();
+  if (p.out_nvfp4 && p.splits == 1 && threadIdx.x < G * (D / 16)) {
+    const int g = threadIdx.x / (D / 16), blk = threadIdx.x % (D / 16);
+    float v[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = sbuf[g * D + blk * 16 + i];
+    const int head = hkv * G + g, hidden = p.hq * D;
+    store_nvfp4_out16(v, __ldg(p.out_gs), static_cast<uint8_t*>(p.out) + int64_t(b) * (hidden / 2), p.out_sf, b,
+                      head * (D / 16) + blk, hidden);
+  }
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColsTc) : "memory");
@@ -560,10 +576,28 @@ int launch_decode_tc(const AttnParams& p, cudaStream_t st) {
 }
 }  // namespace tcattn
 
+
+// One 16-element block of the attention output -> NVFP4 codes + E4M3 block scale, the arithmetic of the
+// reference's packed output path (ShawRong/ResInfer csrc/resattn/output.py:10-34):
+// scale = e4m3(amax * gs * (1/6)), multiplier = gs * rcp(scale) (0 for an all-zero block).
+__device__ __forceinline__ void store_nvfp4_out16(const float (&v)[16], float gs, uint8_t* codes_row, uint8_t* sf,
+                                                  int row, int block, int hidden) {
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  uint8_t sf_byte;
+  const float sfv = encode_e4m3(amax * gs * (1.0f / 6.0f), &sf_byte);
+  const float mult = sfv != 0.f ? gs * rcp_approx_ftz(sfv) : 0.f;
+  *reinterpret_cast<uint2*>(codes_row + block * 8) = quant_plain16(v, mult);
+  sf[sf_offset<16>(row, block, hidden)] = sf_byte;
+}
+
 // out[b, h, :] = sum_s 2^(m_s - m) o_s / sum_s 2^(m_s - m) l_s * out_scale, splits in order
 __global__ void resattn_merge_kernel(const float* __restrict__ o_part, const float* __restrict__ l_part,
                                      const float* __restrict__ m_part, void* __restrict__ out, int out_f32,
-                                     int splits, int64_t rows, int d, float out_scale) {
+                                     int splits, int64_t rows, int d, float out_scale, int out_nvfp4,
+                                     const float* __restrict__ out_gs, uint8_t* __restrict__ out_sf, int hq) {
+  __shared__ float row_vals[256];
   asm volatile("griddepcontrol.wait;" ::: "memory");
   const int64_t row = blockIdx.x;
   float mm = -INFINITY;
@@ -580,8 +614,20 @@ __global__ void resattn_merge_kernel(const float* __restrict__ o_part, const flo
       const float ms = m_part[s * rows + row];
       if (ms != -INFINITY) o += fast_exp2(ms - mm) * o_part[(s * rows + row) * d + c];   // empty partials hold no data
     }
-    if (out_f32) static_cast<float*>(out)[row * d + c] = o * r;
+    if (out_nvfp4) row_vals[c] = o * r;
+    else if (out_f32) static_cast<float*>(out)[row * d + c] = o * r;
     else static_cast<__nv_bfloat16*>(out)[row * d + c] = __float2bfloat16_rn(o * r);
+  }
+  if (out_nvfp4) {
+    __syncthreads();
+    if (threadIdx.x < d / 16) {
+      float v[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] = row_vals[threadIdx.x * 16 + i];
+      const int b = int(row / hq), head = int(row % hq), hidden = hq * d;
+      store_nvfp4_out16(v, __ldg(out_gs), static_cast<uint8_t*>(out) + int64_t(b) * (hidden / 2), out_sf, b,
+                        head * (d / 16) + int(threadIdx.x), hidden);
+    }
   }
 }
 
@@ -601,11 +647,22 @@ extern "C" int ri_resattn_decode(const void* q_bf16, const uint8_t* k_data, cons
                                  const int32_t* block_tables, int64_t bt_stride, const int32_t* seq_lens,
                                  int batch, int num_q_heads, int num_kv_heads, int head_dim, int page_size,
                                  int max_kv_len, float score_scale, float out_scale, void* out, int out_dtype, uint8_t* q_pack,
-                                 int64_t q_pack_bytes, uint8_t* q_sf, int64_t q_sf_bytes, int splits,
+                                 int64_t q_pack_bytes, uint8_t* q_sf, int64_t q_sf_bytes,
+                                 const float* out_global_scale, uint8_t* out_block_scale,
+                                 int64_t out_block_scale_bytes, int splits,
                                  void* workspace, int64_t workspace_bytes, int q_residue, int32_t* status,
                                  void* stream) {
   RI_CHECK_ARG(head_dim == 128 || head_dim == 256, "ResAttn supports head_dim=128 or 256");
-  RI_CHECK_ARG(out_dtype == RI_DTYPE_BF16 || out_dtype == RI_DTYPE_F32, "output must be bf16");
+  RI_CHECK_ARG(out_dtype == RI_DTYPE_BF16 || out_dtype == RI_DTYPE_F32 || out_dtype == RI_DTYPE_NVFP4,
+               "output must be bf16 (or packed NVFP4)");
+  if (out_dtype == RI_DTYPE_NVFP4) {
+    const int64_t hidden = int64_t(num_q_heads) * head_dim;
+    const int64_t need = ((int64_t(batch) + 127) / 128) * ((hidden + 63) / 64) * 512;
+    RI_CHECK_ARG(out_global_scale != nullptr && out_block_scale != nullptr && out_block_scale_bytes >= need,
+                 "NVFP4 output needs a global scale and a 128x4 block-scale buffer of %lld bytes, got %lld",
+                 (long long)need, (long long)out_block_scale_bytes);
+    RI_CHECK_ARG((reinterpret_cast<uintptr_t>(out) & 7) == 0, "NVFP4 output must be 8-byte aligned");
+  }
   RI_CHECK_ARG(num_kv_heads > 0 && num_q_heads % num_kv_heads == 0, "H_q=%d must be divisible by H_kv=%d",
                num_q_heads, num_kv_heads);
   const int group = num_q_heads / num_kv_heads;
@@ -641,6 +698,9 @@ extern "C" int ri_resattn_decode(const void* q_bf16, const uint8_t* k_data, cons
   p.out_scale = out_scale;
   p.out = out;
   p.out_f32 = out_dtype == RI_DTYPE_F32;
+  p.out_nvfp4 = out_dtype == RI_DTYPE_NVFP4;
+  p.out_gs = out_global_scale;
+  p.out_sf = out_block_scale;
   p.q_pack = q_pack; p.q_sf = q_sf;
   p.splits = splits; p.q_residue = q_residue; p.status = status;
   {
@@ -679,7 +739,8 @@ extern "C" int ri_resattn_decode(const void* q_bf16, const uint8_t* k_data, cons
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
     return cuda_status(cudaLaunchKernelEx(&cfg, resattn_merge_kernel, (const float*)p.o_part, (const float*)p.l_part,
-                                          (const float*)p.m_part, p.out, p.out_f32, splits, rows, head_dim, out_scale),
+                                          (const float*)p.m_part, p.out, p.out_f32, splits, rows, head_dim, out_scale, p.out_nvfp4,
+                                          p.out_gs, p.out_sf, num_q_heads),
                        "resattn merge launch");
   }
   return RI_OK;

@@ -149,7 +149,82 @@ def run_paged_fp4_decode_qmul4_tmem(q: torch.Tensor, pool: NvFp4PagedKVPool, v_d
             v_sf_bthd.data_ptr(), pool.k_data.shape[0], block_tables.data_ptr(), block_tables.stride(0),
             seq_lens.data_ptr(), b, hq, h, d, page, int(max_seq_len or 0), float(sm_scale), float(value_scale),
             out.data_ptr(),
-            _cabi.DTYPE_BF16, None, 0, None, 0, splits, ws_ptr, ws_bytes, 1,
+            _cabi.DTYPE_BF16, None, 0, None, 0, None, None, 0, splits, ws_ptr, ws_bytes, 1,
             ops.status_word(q.device).data_ptr(), _cabi.current_stream(q.device))
     _cabi.check(st, "run_paged_fp4_decode_qmul4_tmem")
     return out
+
+
+def plan_qmul4_decode_nvfp4(batch, num_qo_heads, num_kv_heads, max_kv_len, device, *, residue_fold=True):
+    """(splits, reducer) for a packed-NVFP4-output decode launch (head_dim 128 only, as in the reference:
+    csrc/resattn/host.py:94-106)."""
+    if not residue_fold:
+        raise NotImplementedError("ordinary QK is not supported")
+    return select_decode_plan(batch, num_kv_heads, max_kv_len, _sm_count(str(device)), output_nvfp4=True,
+                              grouped_head_tile=_residue_padded_group_size(num_qo_heads, num_kv_heads),
+                              residue_fold=residue_fold)
+
+
+def allocate_nvfp4_attention_output(batch: int, num_qo_heads: int, head_dim: int, device):
+    """Packed output [B, Hq*D/2] uint8 and its 128x4-swizzled E4M3 block scales, viewed
+    [ceil(B/128)*128, ceil(Hq*D/16 / 4)*4] like the reference's buffers."""
+    hidden = num_qo_heads * head_dim
+    out = torch.empty(batch, hidden // 2, dtype=torch.uint8, device=device)
+    sf = torch.zeros(((batch + 127) // 128) * 128, ((hidden // SF_VEC + 3) // 4) * 4, dtype=torch.float8_e4m3fn,
+                     device=device)
+    return out, sf
+
+
+def run_paged_fp4_decode_qmul4_tmem_nvfp4(q: torch.Tensor, pool: NvFp4PagedKVPool, v_data_hnd: torch.Tensor,
+                                          v_sf_bthd: torch.Tensor, block_tables: torch.Tensor,
+                                          seq_lens: torch.Tensor, sm_scale: float,
+                                          output_global_scale_inv: torch.Tensor, *, out: torch.Tensor | None = None,
+                                          output_block_scale: torch.Tensor | None = None, max_seq_len: int = 0,
+                                          k_sf_mode: str = "linear", value_scale: float = 1.0,
+                                          reduction_workspace: Qmul4ReductionWorkspace | None = None,
+                                          plan: tuple[int, str] | None = None, residue_fold: bool = True):
+    """Paged attention with the output quantised to NVFP4 in the kernel (the activation format of the
+    projection that follows).  Arguments, buffer shapes and errors follow the reference's
+    csrc/resattn/host.py:660-760; returns ``(out, output_block_scale)``."""
+    if not residue_fold:
+        raise NotImplementedError("ordinary QK is not supported")
+    if k_sf_mode != "linear":
+        raise NotImplementedError("production ResAttn uses linear K scales")
+    if q.ndim != 3 or q.dtype != torch.bfloat16 or not q.is_cuda:
+        raise ValueError("q must be CUDA BF16 [B, H_q, D]")
+    b, hq, d = q.shape
+    h = pool.num_kv_heads
+    if hq % h:
+        raise ValueError(f"H_q={hq} must be divisible by H_kv={h}")
+    page = pool.page_size
+    check_shape_supported(hq, h, d, prediction=1)
+    _check_decode_metadata(block_tables, seq_lens, b, q.device)
+    if v_data_hnd.shape != (pool.k_data.shape[0], h, page, d // 2):
+        raise ValueError(f"v_data_hnd must be [page, head, {page}, D/2], got {tuple(v_data_hnd.shape)}")
+    if v_sf_bthd.shape != (pool.k_data.shape[0], h, page, d // SF_VEC):
+        raise ValueError(f"v_sf_bthd must be [page, head, {page}, D/16], got {tuple(v_sf_bthd.shape)}")
+    gsi = output_global_scale_inv
+    if gsi.device != q.device or gsi.dtype != torch.float32 or gsi.numel() != 1:
+        raise ValueError("output_global_scale_inv must be a one-element CUDA float32 tensor")
+    if out is None or output_block_scale is None:
+        if out is not None or output_block_scale is not None:
+            raise ValueError("out and output_block_scale must be supplied together")
+        out, output_block_scale = allocate_nvfp4_attention_output(b, hq, d, q.device)
+    want_out = (b, hq * d // 2)
+    want_sf = (((b + 127) // 128) * 128, ((hq * d // SF_VEC + 3) // 4) * 4)
+    if tuple(out.shape) != want_out or out.dtype != torch.uint8 or out.device != q.device or not out.is_contiguous():
+        raise ValueError(f"out must be contiguous uint8 {want_out} on {q.device}")
+    if (tuple(output_block_scale.shape) != want_sf or output_block_scale.dtype != torch.float8_e4m3fn
+            or output_block_scale.device != q.device or not output_block_scale.is_contiguous()):
+        raise ValueError(f"output_block_scale must be contiguous E4M3 {want_sf} on {q.device}")
+    if plan is None:
+        max_len = max_seq_len or int(seq_lens.max().item())
+        splits, reduction = plan_qmul4_decode_nvfp4(b, hq, h, max_len, q.device, residue_fold=residue_fold)
+    else:
+        validate_decode_plan(plan, output_nvfp4=True, head_dim=d)
+        splits, reduction = plan
+    del reduction, reduction_workspace                # one reducer (the merge kernel) with its own cached workspace
+    ops.resattn_decode(q, pool.k_data, pool.k_sf, v_data_hnd, v_sf_bthd, block_tables, seq_lens, float(sm_scale),
+                       float(value_scale), out, splits=splits, max_kv_len=int(max_seq_len or 0),
+                       out_global_scale=gsi, out_block_scale=output_block_scale)
+    return out, output_block_scale

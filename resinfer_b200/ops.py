@@ -138,9 +138,13 @@ def resattn_decode(q: torch.Tensor, k_data: torch.Tensor, k_sf: torch.Tensor, v_
                    v_sf: torch.Tensor, block_tables: torch.Tensor, seq_lens: torch.Tensor,
                    score_scale: float, out_scale: float, out: torch.Tensor, *, splits: int = 1,
                    q_residue: bool = True, q_pack: torch.Tensor | None = None,
-                   q_sf: torch.Tensor | None = None, max_kv_len: int = 0) -> torch.Tensor:
+                   q_sf: torch.Tensor | None = None, max_kv_len: int = 0,
+                   out_global_scale: torch.Tensor | None = None,
+                   out_block_scale: torch.Tensor | None = None) -> torch.Tensor:
     """Paged NVFP4-KV decode attention.  q bf16 [B,Hq,D]; k_data/v_data uint8 [pages,Hkv,page,D/2];
-    k_sf/v_sf uint8 (or float8_e4m3fn) [pages,Hkv,page,D/16]; out bf16 [B,Hq,D] (written)."""
+    k_sf/v_sf uint8 (or float8_e4m3fn) [pages,Hkv,page,D/16]; out bf16 [B,Hq,D] (written) -- or, with
+    ``out_global_scale`` (float32[1]) and ``out_block_scale`` (128x4-swizzled E4M3 bytes), packed NVFP4:
+    out uint8 [B, Hq*D/2]."""
     lib = _cabi.load()
     b, hq, d = q.shape
     pages, hkv, page, _ = k_data.shape
@@ -155,8 +159,11 @@ def resattn_decode(q: torch.Tensor, k_data: torch.Tensor, k_sf: torch.Tensor, v_
             q.data_ptr(), k_data.data_ptr(), k_sf.data_ptr(), v_data.data_ptr(), v_sf.data_ptr(), pages,
             block_tables.data_ptr(), block_tables.stride(0), seq_lens.data_ptr(), b, hq, hkv, d, page,
             int(max_kv_len), float(score_scale), float(out_scale), out.data_ptr(),
-            _cabi.torch_dtype_code(out.dtype, allow_f32=True), _cabi.ptr(q_pack), 0 if q_pack is None else q_pack.numel(),
+            _cabi.DTYPE_NVFP4 if out_block_scale is not None else _cabi.torch_dtype_code(out.dtype, allow_f32=True),
+            _cabi.ptr(q_pack), 0 if q_pack is None else q_pack.numel(),
             _cabi.ptr(q_sf), 0 if q_sf is None else q_sf.numel(),
+            _cabi.ptr(out_global_scale), _cabi.ptr(out_block_scale),
+            0 if out_block_scale is None else out_block_scale.numel() * out_block_scale.element_size(),
             splits, _cabi.ptr(ws), ws_bytes, int(q_residue), status_word(dev).data_ptr(),
             _cabi.current_stream(dev))
     _cabi.check(st, "resattn_decode")

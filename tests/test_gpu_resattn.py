@@ -161,3 +161,50 @@ def test_decode_at_baseline_shape(cuda_device):
     assert torch.equal(o_perm, o16)
     torch.cuda.synchronize()
     ops.check_status(cuda_device)
+
+
+@pytest.mark.parametrize("lens,splits", [([100, 777, 16], 1), ([3000, 5, 700], 4)])
+def test_decode_nvfp4_output(cuda_device, device_rcp, lens, splits):
+    """Packed NVFP4 output: the codes and block scales equal the oracle's quantisation of the kernel's own
+    unrounded output bit for bit, through the reference-named host entry as well."""
+    from resinfer_b200 import ops
+    from resinfer_b200.nvfp4.cute_attn.host import (allocate_nvfp4_attention_output,
+                                                     run_paged_fp4_decode_qmul4_tmem_nvfp4)
+    from resinfer_b200.nvfp4.cute_attn.kv_layout import NvFp4PagedKVPool
+    d, page, hkv, g = 128, 16, 2, 8
+    kv = O.make_paged_kv(lens, hkv, d, page, seed=21)
+    b, hq = len(lens), hkv * g
+    q_np = O.bf16_round(np.random.default_rng(4).standard_normal((b, hq, d)).astype(np.float32))
+    sm = d ** -0.5
+    out32, _, _ = _run(cuda_device, kv, q_np, sm, splits)
+    gs = 6.0 * 448.0 / float(out32.abs().max())
+    want_codes, want_sf = O.quantize_attention_output_nvfp4(out32.cpu().numpy(), gs, rcp=O.RecordingRcp(device_rcp))
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(cuda_device)
+    gsi = torch.tensor([gs], dtype=torch.float32, device=cuda_device)
+    pool = NvFp4PagedKVPool(hkv, d, t(kv["k_data"]), t(kv["v_data"]), t(kv["k_sf"]), t(kv["v_sf"]), page_size=page,
+                            k_global_scale=kv["k_global_scale"], v_global_scale=kv["v_global_scale"])
+    codes, sf = run_paged_fp4_decode_qmul4_tmem_nvfp4(
+        t(q_np).to(torch.bfloat16), pool, pool.v_data, pool.v_sf, t(np.maximum(kv["block_tables"], 0)),
+        t(kv["seq_lens"]), sm * pool.k_global_scale, gsi, value_scale=pool.v_global_scale, plan=(splits, "kernel" if splits > 1 else "none"))
+    torch.cuda.synchronize()
+    ops.check_status(cuda_device)
+    assert codes.shape == (b, hq * d // 2) and sf.dtype == torch.float8_e4m3fn
+    assert np.array_equal(codes.cpu().numpy(), want_codes)
+    got_sf = sf.view(torch.uint8).reshape(-1).cpu().numpy()
+    # rows beyond the batch are never written (the buffer starts zeroed): compare the rows that exist
+    hidden = hq * d
+    for row in range(b):
+        for blk in range(0, hidden // 16, 37):
+            off = O.sf_offset(row, blk, hidden)
+            assert got_sf[off] == want_sf[off]
+    # dequantised output stays within FP4 error of the unrounded one
+    deq = O.nvfp4_dequant(codes.cpu().numpy(), O.unswizzle_scales(got_sf, b, hidden // 16), 1.0 / gs)
+    assert rel_fro(deq, out32.cpu().numpy().reshape(b, -1)) < 0.12
+    out_b, sf_b = allocate_nvfp4_attention_output(b, hq, d, cuda_device)
+    with pytest.raises(ValueError, match="supplied together"):
+        run_paged_fp4_decode_qmul4_tmem_nvfp4(t(q_np).to(torch.bfloat16), pool, pool.v_data, pool.v_sf,
+                                              t(np.maximum(kv["block_tables"], 0)), t(kv["seq_lens"]), 0.1, gsi, out=out_b)
+    with pytest.raises(ValueError, match="one-element"):
+        run_paged_fp4_decode_qmul4_tmem_nvfp4(t(q_np).to(torch.bfloat16), pool, pool.v_data, pool.v_sf,
+                                              t(np.maximum(kv["block_tables"], 0)), t(kv["seq_lens"]), 0.1,
+                                              torch.ones(2, device=cuda_device), out=out_b, output_block_scale=sf_b)
