@@ -141,6 +141,9 @@ def mext_flops(m, k, n):
 _CPU_INPUTS = {}
 
 
+FORMAT = "nvfp4"                     # set by --format
+
+
 def cpu_eager_step(m: int = 16):
     """One bounded CPU step of the metric: the eager quantise/dequantise/matmul path (oracle port of the
     reference's ResidueQuantLinear._forward_residue_qdq) for the four sweep shapes at one M on all host
@@ -158,7 +161,7 @@ def cpu_eager_step(m: int = 16):
                                       torch.from_numpy(oracle.make_weight(n, k, seed=1)).to(torch.bfloat16))
         x, w = _CPU_INPUTS[(name, m)]
         t0 = time.perf_counter()
-        oracle.eager_residue_linear(x, w)
+        oracle.eager_residue_linear(x, w, fmt=FORMAT)
         total += (time.perf_counter() - t0) * 1e6
     return total / len(SHAPES), cores
 
@@ -180,6 +183,8 @@ def cpu_eager_sample(repeats: int = 2):
 
 def run_reference_arm(args):
     """`--impl reference`: the reference's CPU path (oracle port) for the same metric and config, on rank 0."""
+    global FORMAT
+    FORMAT = args.format
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -195,10 +200,11 @@ def run_reference_arm(args):
             break
     v = statistics.mean(ts)
     line = {
-        "impl": "reference", "metric": "mext_nvfp4_linear_latency", "value": v, "unit": "us", "n_gpus": args.gpus,
+        "impl": "reference", "metric": "mext_%s_linear_latency" % args.format, "value": v, "unit": "us", "n_gpus": args.gpus,
         "steps": len(ts), "warmup": max(1, args.warmup), "ms_per_step": v * len(SHAPES) / 1e3, "higher_is_better": False,
-        "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4 (E2M1 x E4M3 block scales), fp32 accumulate",
-        "data": "synthetic", "config": workload_config(args.gpus),
+        "scaling": "strong", "vs_baseline": None,
+        "dtype": ("mxfp4 (E2M1 x E8M0 block scales)" if args.format == "mxfp4" else "nvfp4 (E2M1 x E4M3 block scales)") + ", fp32 accumulate",
+        "data": "synthetic", "config": workload_config(args.gpus, args.format),
         "cpu_baseline": {"value": v, "unit": "us", "cores": cores, "kind": "port", "sample": _CPU_SAMPLE},
         "e2e": {"value": v, "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -298,7 +304,8 @@ def main():
     from resinfer_b200.quant.vllm_integration import residue_linear_op  # noqa: F401
     nvfp4.ensure_loaded()
 
-    global SHAPES, MS, SCALE_BLOCK
+    global SHAPES, MS, SCALE_BLOCK, FORMAT
+    FORMAT = args.format
     SCALE_BLOCK = 32 if args.format == "mxfp4" else 16
     if args.only:
         kind, _, rest = args.only.partition(":")
@@ -465,8 +472,8 @@ def main():
         e2e = {"value": e2e_us, "unit": "us",
                "h2d_bytes_per_step": world * sum(2 * m * L.k for L in layers for m in MS),
                "d2h_bytes_per_step": world * sum(2 * m * L.n for L in layers for m in MS),
-               "note": "eager calls of residue::nvfp4_linear (no CUDA graph) from pinned host buffers: H2D of x, the op, "
-                       "D2H of y on a second stream; includes Python and launch overhead"}
+               "note": ("eager calls of residue::%s_linear (no CUDA graph) from pinned host buffers: H2D of x, the op, "
+                        "D2H of y on a second stream; includes Python and launch overhead") % args.format}
 
     detail = None
     if not args.no_detail and tp == 1 and not mx:
