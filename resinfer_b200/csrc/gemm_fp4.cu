@@ -41,7 +41,7 @@ constexpr int kMmaPerTile = 4;    // 4 x K64 instructions per K tile
 constexpr int kThreads = 352;       // 11 warps: W producer, MMA, 4 epilogue, 4 scale, activation producer
 constexpr int kTmemCols = 512;
 constexpr int kSfCol = 256;        // first tensor-memory column of the block-scale sets
-constexpr int kMaxSfSets = 4;
+constexpr int kMaxSfSets = 10;      // = kMaxStages: one scale set per pipeline stage when tensor memory allows
 constexpr int kMaxStages = 10;
 constexpr int kMaxDynSmem = 227 * 1024 - 2048;    // 227 KB per CTA minus the static barriers / flags
 constexpr int kEpiStageBytes = 8 * 1024;          // epilogue staging: 16 token pairs x 128 outputs x 4 bytes
@@ -416,9 +416,11 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
         bool got = mbar_wait(smem_u32(&bar_full[w.stage]), w.stage_par, &abort_flag, 6);
         const long long c1 = prof_clock();
         if (warp == 6 && lane == 0) prof_event(p, 2, i);
-        if (got && w.it >= p.sf_sets) {
-          // scale set reuse: the MMAs of unit (it - sf_sets) must have completed, which is what the
-          // commit on that unit's stage barrier reports
+        if (got && p.sf_sets < p.stages && w.it >= p.sf_sets) {
+          // fewer scale sets than stages: before a set is reused the MMAs of unit (it - sf_sets) must have
+          // completed, which is what the commit on that unit's stage barrier reports.  (With one set per
+          // stage the arrival of the stage's data already implies it: the stage was refilled only after
+          // that commit.)
           got = mbar_wait(smem_u32(&bar_empty[lag_stage]), lag_par, &abort_flag, 7);
           if (++lag_stage == p.stages) { lag_stage = 0; lag_par ^= 1; }
         }
@@ -975,11 +977,16 @@ extern "C" int ri_fp4_gemm(const uint8_t* act, int64_t act_row_bytes, const uint
     const int halves_h = layout == RI_GEMM_CONCAT_K ? 2 : 1;
     const int row_tiles_h = (pl.n_tile + 127) / 128;
     p.sf_set_cols = 16 + pl.chunks * halves_h * row_tiles_h * 4;
-    p.sf_sets = (kTmemCols - kSfCol) / p.sf_set_cols;
-    if (p.sf_sets > kMaxSfSets) p.sf_sets = kMaxSfSets;
-    // a scale set is recycled once the stage barrier of the unit that used it has completed; that
-    // barrier must not be able to run a whole phase ahead of the check, so sets <= stages
-    if (p.sf_sets > p.stages) p.sf_sets = p.stages;
+    // one scale set per pipeline stage if tensor memory has room for at least two (the scale warps then
+    // need no second wait per K tile); the stage count is trimmed to the sets that fit
+    const int sets_max = (kTmemCols - kSfCol) / p.sf_set_cols;
+    if (sets_max >= 2) {
+      if (p.stages > sets_max) p.stages = sets_max;
+      if (p.stages > kMaxSfSets) p.stages = kMaxSfSets;
+      p.sf_sets = p.stages;
+    } else {
+      p.sf_sets = 1;
+    }
   }
   p.act_row_tiles = int(act_row_tiles);
   p.w_sf_tile_stride = w_chunks * 512;
