@@ -1,0 +1,553 @@
+// ResAttn decode with both products on the tensor cores (head_dim 128).  Included by resattn.cu inside
+// namespace ri::<anon>::tcattn (it uses that file's AttnParams, cp_async16, swz_off, fast_exp2, ...).
+//
+//   S^T[128 tokens x 16] = K . Qpack^T     tcgen05.mma kind::mxf4nvf4.block_scale, K codes and E4M3 scales
+//                                          as stored (rows 0-7 of Qpack: NVFP4 heads, rows 8-15: residues)
+//   O^T[128 d x 16]     += V^T . P         tcgen05.mma kind::f16: V^T is the M-major A operand, written to
+//                                          shared memory as FP16 (code x block scale, exact) by the
+//                                          conversion warps; P (FP16) is the K-major B operand written
+//                                          by the softmax warps; FP32 accumulator in tensor memory
+//
+// One CTA per (KV split, KV head, sequence), two CTAs per SM, tiles of 128 tokens, 17 warps:
+//   warps 0-3   softmax: one thread per token of the tile (tensor-memory lane = token).  The running
+//               maximum of a head is shared by the CTA and only raised when a score exceeds it by more
+//               than 2^8 (then the accumulators in tensor memory are rescaled); row sums stay per
+//               thread until the end.
+//   warp 4      issues every MMA (scores of tile i+1 before the P.V of tile i), copies the K block scales
+//               of a tile from shared to tensor memory (tcgen05.cp) and owns tensor memory
+//   warps 5-8   cp.async producers: K codes and V codes in the 64-byte operand swizzle, V scales as
+//               stored, K scales in the layout of the tcgen05.cp 32x128b copy
+//   warps 9-16  V conversion: NVFP4 codes x E4M3 scale -> FP16, written in the 128-byte-swizzled M-major
+//               operand layout; rows past the end of the sequence are written as zeros
+// In every multi-warp role ONE lane polls the mbarriers and publishes its decision in shared memory;
+// the other warps of the role wait on a named barrier.  Polling lanes in every warp took half of all
+// issued instructions (measured: 1.6 -> 2.5 TB/s from this change alone).  Every mbarrier wait is
+// bounded; the decision slot makes all warps of a role leave their loop together on expiry.
+
+constexpr int kPvSoft = 4, kPvProd = 4, kPvConv = 8;
+constexpr int kPvMmaWarp = kPvSoft;
+constexpr int kPvFirstProd = kPvSoft + 1;
+constexpr int kPvFirstConv = kPvFirstProd + kPvProd;
+constexpr int kThreadsPv = (kPvSoft + 1 + kPvProd + kPvConv) * 32;     // 544
+// O^T accumulators: the eight P.V MMAs of a tile (16 tokens each) add into eight different accumulators,
+// 16 columns apart, which are summed at the end: MMAs into one accumulator execute one after the
+// other at full instruction latency, independent ones overlap
+constexpr int kPvColO = 128;
+constexpr int kPvAccs = 8;
+constexpr int kPvTmemCols = 256;
+constexpr int kPvOffMisc = 3072;                  // running maxima, rescale factors, flags
+// P: K-major B operand without swizzle.  A core matrix is 8 rows (heads) x 16 bytes (8 tokens); the
+// core matrices of consecutive 8-token groups are 144 bytes apart (not 128: the softmax warps then
+// write without bank conflicts).  Two buffers of one 8-row group each, followed by a group of zeros
+// that both use as rows 8-15.
+constexpr int kPvPLbo = 144;
+constexpr int kPvPGroup = 16 * kPvPLbo;           // 2304 bytes: one 8-row group over 128 tokens
+constexpr int kPvOffP = 4096;
+constexpr int kPvOffV = 11264;                    // [2 d-blocks][128 tokens][64 d] FP16, 128B swizzle, M-major
+constexpr int kPvVBytes = 128 * 128 * 2;
+#ifndef RI_PV_VBUFS
+#define RI_PV_VBUFS 2
+#define RI_PV_STAGES 2
+#define RI_PV_CTAS 2
+#endif
+constexpr int kPvVBufs = RI_PV_VBUFS;             // FP16 V tiles in flight
+constexpr int kPvHeaderBytes = kPvOffV + kPvVBufs * kPvVBytes;        // a multiple of 1024
+constexpr int kPvStages = RI_PV_STAGES;           // cp.async pipeline stages per CTA
+constexpr int kPvCtasPerSm = RI_PV_CTAS;
+
+__device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// shared-memory matrix descriptor with explicit leading / stride byte offsets (sm_100 encoding)
+__device__ __forceinline__ uint64_t desc_full(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout_type) {
+  return uint64_t((saddr & 0x3FFFFu) >> 4) | (uint64_t(lbo_bytes >> 4) << 16) | (uint64_t(sbo_bytes >> 4) << 32) |
+         (uint64_t(1) << 46) | (uint64_t(layout_type) << 61);
+}
+__device__ __forceinline__ void tmem_st16f(uint32_t taddr, const float (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+        "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
+        "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
+        "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+        "r"(__float_as_uint(v[15])) : "memory");
+}
+
+__global__ void __launch_bounds__(kThreadsPv, kPvCtasPerSm) resattn_pv_kernel(const AttnParams p) {
+  constexpr int D = 128;
+  using C = TCfg<D>;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[kPvStages];
+  __shared__ __align__(8) uint64_t bar_empty[kPvStages];
+  __shared__ __align__(8) uint64_t bar_sfull[2], bar_vpready[2], bar_pvdone[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ volatile int abort_flag;
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint8_t* q_op = smem;                                        // [16][64 B] swizzled FP4 codes
+  uint8_t* qsf_s = smem + 2048;                                // [16][8] E4M3 scales
+  float* m_sh = reinterpret_cast<float*>(smem + kPvOffMisc);   // [8] running maxima (log2 domain)
+  float* f_sh = m_sh + 8;                                      // [8] rescale factors of the current tile
+  float* wmax = m_sh + 16;                                     // [4 warps][8] tile maxima
+  volatile int* grow = reinterpret_cast<volatile int*>(m_sh + 48);   // [2] "a maximum moved" flag by tile parity
+  float* red = m_sh + 64;                                      // [4 warps][8] row-sum reduction
+  volatile int* soft_go = reinterpret_cast<volatile int*>(m_sh + 100);   // [3] decisions of the polling lanes
+  volatile int* conv_go = reinterpret_cast<volatile int*>(m_sh + 104);   // [2]
+  volatile int* prod_go = reinterpret_cast<volatile int*>(m_sh + 108);   // [2]
+  uint8_t* stage0 = smem + kPvHeaderBytes;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
+  const int G = p.group;
+  constexpr int S = kPvStages;
+
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int L = min(max(__ldg(p.seq_lens + b), 0), int(p.bt_stride) * p.page_size);
+  const int n_tiles = (L + kTile - 1) / kTile;
+  const int t_begin = min(split * p.tiles_per_split, n_tiles);
+  const int t_end = min(t_begin + p.tiles_per_split, n_tiles);
+  const int my_tiles = t_end - t_begin;
+  if (my_tiles == 0 && p.splits > 1 && !(p.q_pack && split == 0)) {
+    if (threadIdx.x < G) {
+      const int64_t slot = (int64_t(split) * p.batch + b) * p.hq + hkv * G + threadIdx.x;
+      p.l_part[slot] = 0.f;
+      p.m_part[slot] = -INFINITY;
+    }
+    return;
+  }
+  const int32_t* bt = p.block_tables + int64_t(b) * p.bt_stride;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), kPvProd * 32);
+      mbar_init(smem_u32(&bar_empty[s]), kPvConv + 1);         // conversion warps + the commit of the scores' MMAs
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&bar_sfull[s]), 1);
+      mbar_init(smem_u32(&bar_vpready[s]), kPvConv + kPvSoft);   // V tile converted and P written
+      mbar_init(smem_u32(&bar_pvdone[s]), 1);
+    }
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == kPvMmaWarp) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_slot)), "r"(kPvTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  // zero the query operand, its scales, the shared scalars and both P buffers (rows 8-15 of P stay zero)
+  for (int i = threadIdx.x; i < kPvOffV / 16; i += blockDim.x) reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  if (threadIdx.x < 8) m_sh[threadIdx.x] = -INFINITY;
+
+  // ---------------------------------------------------------------- query prologue (as in resattn_tc_kernel)
+  if (threadIdx.x < G * C::kSfPerRow) {
+    const int g = threadIdx.x / C::kSfPerRow, blk = threadIdx.x % C::kSfPerRow;
+    float v[16];
+    load16(p.q + (int64_t(b) * p.hq + hkv * G + g) * D + blk * 16, v);
+    BlockQ bq = quant_mext16(v, 1.0f, 1.0f);
+    *reinterpret_cast<uint2*>(q_op + swz_off<D>(g, blk * 8)) = bq.base;
+    qsf_s[g * C::kSfPerRow + blk] = bq.sf;
+    if (p.q_residue) {
+      *reinterpret_cast<uint2*>(q_op + swz_off<D>(8 + g, blk * 8)) = bq.res;
+      qsf_s[(8 + g) * C::kSfPerRow + blk] = bq.sf_res;
+    }
+    if (p.q_pack && split == 0) {
+      const int P = G == 4 ? 8 : 16;
+      uint8_t* pack = p.q_pack + (int64_t(b) * p.hkv + hkv) * P * (D / 2);
+      uint8_t* sfp = p.q_sf + (int64_t(b) * p.hkv + hkv) * 128 * C::kSfPerRow;
+      *reinterpret_cast<uint2*>(pack + int64_t(g) * (D / 2) + blk * 8) = bq.base;
+      *reinterpret_cast<uint2*>(pack + int64_t(P / 2 + g) * (D / 2) + blk * 8) = bq.res;
+      sfp[sf_offset<16>(g, blk, D)] = bq.sf;
+      sfp[sf_offset<16>(P / 2 + g, blk, D)] = bq.sf_res;
+    }
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  if (warp < kPvFirstProd || warp >= kPvFirstConv)
+    asm volatile("bar.sync 2, %0;" ::"n"(kThreadsPv - kPvProd * 32) : "memory");
+
+  float l_thr[8];
+#pragma unroll
+  for (int h = 0; h < 8; ++h) l_thr[h] = 0.f;
+
+  if (warp < kPvSoft) {
+    // ============================================================ softmax warps (and K scales -> tensor memory)
+    // Only lane 0 of warp 0 polls mbarriers; the four warps then meet on a named barrier, which
+    // costs the waiting warps no issue slots.
+    const int q = warp;
+    const uint32_t lane_base = tmem_base + (uint32_t(q * 32) << 16);
+#pragma unroll
+    for (int j = 0; j < C::kMma; ++j) {
+      uint4 w = make_uint4(0, 0, 0, 0);
+      if (lane < 16) w.x = *reinterpret_cast<const uint32_t*>(qsf_s + lane * C::kSfPerRow + 4 * j);
+      tmem_st4(lane_base + kColSfb + 4 * j, w);
+    }
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+    // the Q scales are in tensor memory: tell the MMA warp
+    tc_fence_before();
+    asm volatile("bar.sync 5, 160;" ::: "memory");
+    for (int i = 0; i < my_tiles; ++i) {
+      const int sb = i & 1;
+      const int tile = t_begin + i;
+      if (threadIdx.x == 0) {
+        soft_go[sb] = mbar_wait(smem_u32(&bar_sfull[sb]), (i >> 1) & 1, &abort_flag, 5) ? 1 : 0;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (!soft_go[sb]) break;                                  // the same decision in all four warps
+      tc_fence_after();
+      float s[8];
+      bool mine_grows = false;
+      {
+        float r[16];
+        tmem_ld16(lane_base + kColS + sb * 16, r);
+        tc_fence_before();
+        const bool valid = tile * kTile + 32 * q + lane < L;
+#pragma unroll
+        for (int h = 0; h < 8; ++h) {
+          s[h] = valid ? (r[h] + r[8 + h]) * p.score_scale_log2 : -INFINITY;
+          mine_grows |= s[h] > m_sh[h] + kLazyThreshold;       // also true while the maximum is still -inf
+        }
+        if (__any_sync(0xffffffffu, mine_grows) && lane == 0) grow[sb] = 1;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (grow[sb]) {
+        // ---- a maximum moved (always on the first tile): exact tile maxima, rescale the accumulators
+        float mx[8];
+#pragma unroll
+        for (int h = 0; h < 8; ++h) {
+          mx[h] = s[h];
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], o));
+        }
+        if (lane == 0) {
+#pragma unroll
+          for (int h = 0; h < 8; ++h) wmax[q * 8 + h] = mx[h];
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        float f[8];
+#pragma unroll
+        for (int h = 0; h < 8; ++h) {
+          const float old = m_sh[h];
+          const float nw = fmaxf(fmaxf(old, fmaxf(wmax[h], wmax[8 + h])), fmaxf(wmax[16 + h], wmax[24 + h]));
+          f[h] = old == -INFINITY ? 0.f : fast_exp2(old - nw);
+          l_thr[h] *= f[h];
+          mx[h] = nw;
+        }
+        if (i > 0) {
+          // the P.V of the previous tile must have landed before the accumulators are rescaled in place
+          bool got = true;
+          if (lane == 0) got = mbar_wait(smem_u32(&bar_pvdone[(i - 1) & 1]), ((i - 1) >> 1) & 1, &abort_flag, 7);
+          if (__all_sync(0xffffffffu, got)) {
+            tc_fence_after();
+#pragma unroll 1
+            for (int a = 0; a < kPvAccs; ++a) {
+              float o[16];
+              tmem_ld16(lane_base + kPvColO + 16 * a, o);
+#pragma unroll
+              for (int h = 0; h < 8; ++h) o[h] *= f[h];
+              tmem_st16f(lane_base + kPvColO + 16 * a, o);
+            }
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            tc_fence_before();
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");          // everybody has read the old maxima
+        if (threadIdx.x < 8) m_sh[threadIdx.x] = mx[threadIdx.x];
+        if (threadIdx.x == 8) grow[sb] = 0;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+      // ---- probabilities of this thread's token, FP16, into the K-major B operand of the P.V MMAs.
+      // (The P buffer is free: the commit behind s_full(i) was issued by the same thread after the P.V
+      // MMAs of tile i-2, so having seen it means those have read the buffer.)
+      {
+        const int t = 32 * q + lane;
+        __half* pb = reinterpret_cast<__half*>(smem + kPvOffP + sb * kPvPGroup + (t >> 3) * kPvPLbo) + (t & 7);
+#pragma unroll
+        for (int h = 0; h < 8; ++h) {
+          const float pv = fast_exp2(s[h] - m_sh[h]);          // 0 for tokens past the end (s = -inf)
+          l_thr[h] += pv;
+          pb[h * 8] = __float2half_rn(pv);
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_vpready[sb]));
+    }
+  } else if (warp == kPvMmaWarp) {
+    // ============================================================ MMA issuer
+    // One thread issues everything, the scores of tile i+1 before the P.V of tile i.  (Two issuing
+    // warps measured slower, and with one the commit behind s_full(i) also covers the P.V of tile i-2.)
+    const uint32_t idesc_qk = (1u << 7) | (1u << 10) | (uint32_t(16 >> 3) << 17) | (uint32_t(kTile >> 4) << 24);
+    // kind::f16: FP32 accumulate (bits 4-5 = 1), FP16 x FP16, A M-major (bit 15), B K-major, N = 16, M = 128
+    const uint32_t idesc_pv = (1u << 4) | (1u << 15) | (uint32_t(16 >> 3) << 17) | (uint32_t(128 >> 4) << 24);
+    const uint64_t bq_desc = desc_kmajor(smem_u32(q_op), C::kSbo, C::kLayout);
+    bool alive = true;
+    asm volatile("bar.sync 5, 160;" ::: "memory");              // the Q scales are in tensor memory
+    // Scores of tile i.  Its S buffer and scale set were last used by tile i-2, whose softmax finished
+    // before the P.V of tile i-2 was issued (by this thread, earlier).
+    auto issue_qk = [&](int i) {
+      const int stg = i % S, sb = i & 1;
+      bool got = true;
+      if (lane == 0) got = mbar_wait(smem_u32(&bar_full[stg]), (i / S) & 1, &abort_flag, 3);
+      if (!__all_sync(0xffffffffu, got)) { alive = false; return; }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // cp.async data -> tensor-core reads
+      tc_fence_after();
+      if (elect_one()) {
+        const uint32_t st_addr = smem_u32(stage0 + stg * C::kStageBytes);
+        const uint64_t a_desc = desc_kmajor(st_addr, C::kSbo, C::kLayout);
+        // K block scales: the producers store them as [64-column group][32 rows][4 quarters][4 bytes],
+        // the layout of one 32x128b copy per MMA
+#pragma unroll
+        for (int j = 0; j < C::kMma; ++j)
+          tmem_cp_sf(tmem_base + kColSfa + sb * 16 + 4 * j, desc_sf(st_addr + C::kOffKsf + j * 512));
+#pragma unroll
+        for (int j = 0; j < C::kMma; ++j)
+          mma_fp4<false>(tmem_base + kColS + sb * 16, a_desc + uint64_t(2 * j), bq_desc + uint64_t(2 * j), idesc_qk,
+                         tmem_base + kColSfa + sb * 16 + 4 * j, tmem_base + kColSfb + 4 * j, j > 0 ? 1u : 0u);
+        mma_commit(smem_u32(&bar_sfull[sb]));
+        mma_commit(smem_u32(&bar_empty[stg]));                 // the K codes of the stage have been read
+      }
+      __syncwarp();
+    };
+    if (my_tiles > 0) issue_qk(0);
+    for (int i = 0; i < my_tiles && alive; ++i) {
+      const int vb = i & 1;
+      if (i + 1 < my_tiles) issue_qk(i + 1);
+      if (!alive) break;
+      bool got = true;
+      if (lane == 0) got = mbar_wait(smem_u32(&bar_vpready[vb]), (i >> 1) & 1, &abort_flag, 9);
+      if (!__all_sync(0xffffffffu, got)) break;
+      tc_fence_after();
+      if (elect_one()) {
+        // A = V^T: M-major, 128-byte swizzle: 64-d blocks 16 KB apart (leading offset), 8-token groups 1 KB apart
+        const uint32_t va = smem_u32(smem + kPvOffV + (kPvVBufs == 2 ? vb * kPvVBytes : 0));
+        // B = P: K-major, no swizzle: 8-token core matrices kPvPLbo apart along K; rows 8-15 are the zero group
+        const uint32_t pa = smem_u32(smem + kPvOffP + vb * kPvPGroup);
+        const uint32_t p_sbo = (2 - vb) * kPvPGroup;
+#pragma unroll
+        for (int k16 = 0; k16 < kTile / 16; ++k16)
+          mma_f16_ss(tmem_base + kPvColO + 16 * k16, desc_full(va + k16 * 2048, 16384, 1024, 2),
+                     desc_full(pa + k16 * 2 * kPvPLbo, kPvPLbo, p_sbo, 0), idesc_pv, i > 0 ? 1u : 0u);
+        mma_commit(smem_u32(&bar_pvdone[vb]));
+      }
+      __syncwarp();
+    }
+  } else if (warp < kPvFirstConv) {
+    // ============================================================ copy producers (as in resattn_tc_kernel)
+    constexpr int kCpr = C::kRowBytes / 16;
+    constexpr int kRowsPerIt = 32 / kCpr;
+    constexpr int kIters = 32 / kRowsPerIt;
+    const int pw = warp - kPvFirstProd;
+    const int r_lane = lane / kCpr, chn = lane % kCpr;
+    const int sf_row = 2 * lane;
+    const bool sf_lane = lane < 16;
+    uint32_t k_dst[kIters];
+#pragma unroll
+    for (int it = 0; it < kIters; ++it) k_dst[it] = swz_off<D>(32 * pw + it * kRowsPerIt + r_lane, chn * 16);
+    const uint32_t sf_dst = (32 * pw + sf_row) * C::kSfPerRow;
+    auto lookup = [&](int i) -> int {
+      if (lane >= 2 || i >= my_tiles) return 0;
+      const int t0 = (t_begin + i) * kTile + 32 * pw + lane * 16;
+      return t0 < L ? __ldg(bt + (p.page_shift >= 0 ? t0 >> p.page_shift : t0 / p.page_size)) : 0;
+    };
+    int page_next = lookup(0);
+    for (int i = 0, stg = 0, ph = 0; i < my_tiles; ++i, stg = (stg + 1 == S ? 0 : stg + 1), ph ^= (stg == 0)) {
+      const int tok0 = (t_begin + i) * kTile + 32 * pw;
+      const int rows = min(max(((L - tok0) + 15) & ~15, 0), 32);
+      int64_t page = page_next;
+      page_next = lookup(i + 1);
+      page = page < 0 ? 0 : (page >= p.num_pages ? p.num_pages - 1 : page);
+      const int t0 = tok0 + lane * 16;
+      const int in_page = p.page_shift >= 0 ? (t0 & (p.page_size - 1)) : t0 % p.page_size;
+      const int64_t base_row = (page * p.hkv + hkv) * p.page_size + in_page;
+      const int64_t base0 = __shfl_sync(0xffffffffu, base_row, 0), base1 = __shfl_sync(0xffffffffu, base_row, 1);
+      if (i >= S) {                                            // one lane polls, the four warps meet on a named barrier
+        if (pw == 0 && lane == 0) prod_go[i & 1] = mbar_wait(smem_u32(&bar_empty[stg]), ph ^ 1, &abort_flag, 4) ? 1 : 0;
+        asm volatile("bar.sync 4, 128;" ::: "memory");
+        if (!prod_go[i & 1]) break;
+      }
+      const uint32_t st = smem_u32(stage0 + stg * C::kStageBytes);
+      const uint8_t* kg[2] = {p.k_data + base0 * C::kRowBytes + chn * 16, p.k_data + base1 * C::kRowBytes + chn * 16};
+      const uint8_t* vg[2] = {p.v_data + base0 * C::kRowBytes + chn * 16, p.v_data + base1 * C::kRowBytes + chn * 16};
+#pragma unroll
+      for (int it = 0; it < kIters; ++it) {
+        const int r = it * kRowsPerIt + r_lane;
+        if (it * kRowsPerIt < rows) {
+          const int sl = (it * kRowsPerIt) >> 4;
+          const int off = (r & 15) * C::kRowBytes;
+          cp_async16(st + k_dst[it], kg[sl] + off);
+          cp_async16(st + C::kOffV + k_dst[it], vg[sl] + off);
+        }
+      }
+      if (sf_lane && sf_row < rows) {
+        const int64_t br = (sf_row < 16 ? base0 : base1) + (sf_row & 15);
+        cp_async16(st + C::kOffVsf + sf_dst, p.v_sf + br * C::kSfPerRow);
+      }
+      if (lane < rows) {                                       // K scales of token 32 pw + lane, 4 bytes per MMA
+        const uint8_t* src = p.k_sf + ((lane < 16 ? base0 : base1) + (lane & 15)) * C::kSfPerRow;
+        const uint32_t dst = st + C::kOffKsf + lane * 16 + pw * 4;
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 512), "l"(src + 4) : "memory");
+      }
+      asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&bar_full[stg])) : "memory");
+    }
+  } else {
+    // ============================================================ V conversion warps
+    // warp c: tokens 32 (c / 2) .. +31, d-block c % 2 (64 head-dim values = 32 code bytes = 4 scale blocks)
+    const int cv = warp - kPvFirstConv;
+    const int tok = 32 * (cv >> 1) + lane, dblk = cv & 1;
+    for (int i = 0, stg = 0, ph = 0; i < my_tiles; ++i, stg = (stg + 1 == S ? 0 : stg + 1), ph ^= (stg == 0)) {
+      const int vb = i & 1;
+      if (cv == 0 && lane == 0) {                              // one lane polls, the eight warps meet on a named barrier
+        bool got = mbar_wait(smem_u32(&bar_full[stg]), ph, &abort_flag, 6);
+        if (kPvVBufs == 2) {
+          if (got && i >= 2) got = mbar_wait(smem_u32(&bar_pvdone[vb]), ((i >> 1) - 1) & 1, &abort_flag, 11);
+        } else {
+          if (got && i >= 1) got = mbar_wait(smem_u32(&bar_pvdone[vb ^ 1]), ((i - 1) >> 1) & 1, &abort_flag, 11);
+        }
+        conv_go[vb] = got ? 1 : 0;
+      }
+      asm volatile("bar.sync 3, 256;" ::: "memory");
+      if (!conv_go[vb]) break;
+      const uint8_t* st = stage0 + stg * C::kStageBytes;
+      if (cv == 0 && lane == 0) attn_event(p, 4, i);
+      const bool valid = (t_begin + i) * kTile + tok < L;
+      uint4 c0 = make_uint4(0, 0, 0, 0), c1 = c0;
+      uint32_t sfw = 0;
+      if (valid) {
+        // the producers store the V rows with the swizzle of the K operand (conflict-free 16-byte reads)
+        const uint8_t* row = st + C::kOffV + tok * C::kRowBytes;
+        const int sw = (tok >> 1) & 3;
+        c0 = *reinterpret_cast<const uint4*>(row + (((2 * dblk) ^ sw) << 4));
+        c1 = *reinterpret_cast<const uint4*>(row + (((2 * dblk + 1) ^ sw) << 4));
+        sfw = *reinterpret_cast<const uint32_t*>(st + C::kOffVsf + tok * C::kSfPerRow + dblk * 4);
+      }
+      const uint32_t words[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};   // 8 codes (= 8 d) per word
+      uint8_t* dst_row = smem + kPvOffV + (kPvVBufs == 2 ? vb * kPvVBytes : 0) + dblk * 16384 + (tok >> 3) * 1024 + (tok & 7) * 128;
+#pragma unroll
+      for (int w8 = 0; w8 < 8; ++w8) {                         // one 16-byte chunk = 8 FP16 per code word
+        const __half sc = e4m3_to_half((sfw >> (8 * (w8 >> 1))) & 0xFFu);
+        const __half2 sc2 = __halves2half2(sc, sc);
+        uint4 o;
+        o.x = h2_bits(__hmul2(e2m1x2_to_half2(words[w8] & 0xFFu), sc2));
+        o.y = h2_bits(__hmul2(e2m1x2_to_half2((words[w8] >> 8) & 0xFFu), sc2));
+        o.z = h2_bits(__hmul2(e2m1x2_to_half2((words[w8] >> 16) & 0xFFu), sc2));
+        o.w = h2_bits(__hmul2(e2m1x2_to_half2(words[w8] >> 24), sc2));
+        *reinterpret_cast<uint4*>(dst_row + ((w8 ^ (tok & 7)) << 4)) = o;
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(smem_u32(&bar_vpready[vb]));
+        mbar_arrive(smem_u32(&bar_empty[stg]));                // the V codes of the stage have been read
+        if (cv == 0) attn_event(p, 5, i);
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- output
+  // thread (softmax warp q, lane) owns head-dim column d = 32 q + lane of all heads
+  float* red_l = red;
+  float o_acc[16];
+#pragma unroll
+  for (int h = 0; h < 16; ++h) o_acc[h] = 0.f;
+  if (warp < kPvSoft) {
+    const uint32_t lane_base = tmem_base + (uint32_t(warp * 32) << 16);
+    if (my_tiles > 0) {
+      bool got = true;
+      if (lane == 0) got = mbar_wait(smem_u32(&bar_pvdone[(my_tiles - 1) & 1]), ((my_tiles - 1) >> 1) & 1, &abort_flag, 12);
+      if (__all_sync(0xffffffffu, got)) {
+        tc_fence_after();
+#pragma unroll 1
+        for (int a = 0; a < kPvAccs; ++a) {
+          float o[16];
+          tmem_ld16(lane_base + kPvColO + 16 * a, o);
+#pragma unroll
+          for (int h = 0; h < 8; ++h) o_acc[h] += o[h];
+        }
+      }
+    }
+#pragma unroll
+    for (int h = 0; h < 8; ++h) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) l_thr[h] += __shfl_xor_sync(0xffffffffu, l_thr[h], o);
+    }
+    if (lane == 0) {
+#pragma unroll
+      for (int h = 0; h < 8; ++h) red_l[warp * 8 + h] = l_thr[h];
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  const bool failed = abort_flag != 0;
+  float* stage_out = reinterpret_cast<float*>(smem + kPvOffV);      // [8 heads][128] for the NVFP4 output path
+  if (warp < kPvSoft) {
+    const int d = 32 * warp + lane;
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      if (g >= G) break;
+      const float l = (red_l[g] + red_l[8 + g]) + (red_l[16 + g] + red_l[24 + g]);
+      const int head = hkv * G + g;
+      if (p.splits == 1) {
+        const float rr = l > 0.f ? p.out_scale / l : 0.f;
+        const int64_t oi = (int64_t(b) * p.hq + head) * D + d;
+        if (p.out_nvfp4) stage_out[g * D + d] = o_acc[g] * rr;
+        else if (p.out_f32) static_cast<float*>(p.out)[oi] = o_acc[g] * rr;
+        else static_cast<__nv_bfloat16*>(p.out)[oi] = __float2bfloat16_rn(o_acc[g] * rr);
+      } else {
+        const int64_t slot = (int64_t(split) * p.batch + b) * p.hq + head;
+        p.o_part[slot * D + d] = o_acc[g];
+        if (d == 0) {
+          p.l_part[slot] = l;
+          p.m_part[slot] = my_tiles > 0 ? m_sh[g] : -INFINITY;
+        }
+      }
+    }
+  }
+  if (failed && threadIdx.x == 0 && p.status) atomicExch(p.status, 1 + int(blockIdx.z) + (abort_flag << 16));
+  __syncthreads();
+  if (p.out_nvfp4 && p.splits == 1 && threadIdx.x < G * (D / 16)) {
+    const int g = threadIdx.x / (D / 16), blk = threadIdx.x % (D / 16);
+    float v[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = stage_out[g * D + blk * 16 + i];
+    const int head = hkv * G + g, hidden = p.hq * D;
+    store_nvfp4_out16(v, __ldg(p.out_gs), static_cast<uint8_t*>(p.out) + int64_t(b) * (hidden / 2), p.out_sf, b,
+                      head * (D / 16) + blk, hidden);
+  }
+  if (warp == kPvMmaWarp) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kPvTmemCols) : "memory");
+  }
+}
+
+inline int launch_decode_pv(const AttnParams& p, cudaStream_t st) {
+  const int smem = kPvHeaderBytes + kPvStages * TCfg<128>::kStageBytes + 1024;
+  static bool attr_done[64] = {};
+  int dev = 0;
+  RI_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (!attr_done[dev]) {
+    RI_CUDA(cudaFuncSetAttribute(resattn_pv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    RI_CUDA(cudaFuncSetAttribute(resattn_pv_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
+    attr_done[dev] = true;
+  }
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(p.splits, p.hkv, p.batch);
+  cfg.blockDim = dim3(kThreadsPv);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr{};
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  return cuda_status(cudaLaunchKernelEx(&cfg, resattn_pv_kernel, p), "resattn decode launch");
+}

@@ -34,8 +34,10 @@ def _pow2_floor(v: int) -> int:
     return 1 << (max(1, v).bit_length() - 1)
 
 
-def _select_splits(batch: int, heads: int, length: int, sms: int, min_tiles_per_split: int = 4) -> int:
-    """One CTA per SM at a time, 128-token tiles, and every split covers the same number of tiles
+def _select_splits(batch: int, heads: int, length: int, sms: int, min_tiles_per_split: int = 4,
+                   ctas_per_sm: int = 1) -> int:
+    """`ctas_per_sm` CTAs per SM at a time (two for head_dim 128, one for 256), 128-token tiles, and every
+    split covers the same number of tiles
     (ceil(tiles(length) / splits)) whatever the sequence: short sequences simply use fewer splits and
     the CTAs of their unused splits leave at once.  Measured on B200, the best piece size is the one
     that lets the working CTAs of the whole batch fit the SMs in one wave (a CTA costs about 5 us of
@@ -45,11 +47,12 @@ def _select_splits(batch: int, heads: int, length: int, sms: int, min_tiles_per_
     grid = max(1, batch * heads)
     tiles = max(1, (length + 127) // 128)
     total = grid * tiles * (0.5 if batch > 1 else 1.0)      # expected tiles of the whole batch
-    piece = max(min_tiles_per_split, -(-int(total * 1.15) // sms))
+    slots = sms * ctas_per_sm
+    piece = max(min_tiles_per_split, -(-int(total * 1.15) // slots))
     splits = -(-tiles // piece)
     # a few waves of unequal sequences: pieces of at most a third of the longest context even out the
     # tail (with very many CTAs the tail is short anyway and every extra CTA costs its set-up)
-    if grid <= 8 * sms:
+    if grid <= 8 * slots:
         splits = max(splits, min(3, tiles // 64))
     return max(1, min(splits, 64))
 
@@ -61,7 +64,7 @@ def select_decode_plan(batch, num_kv_heads, max_kv_len, sm_count, *, output_nvfp
     _reduction_policy(reduction_policy)
     if not residue_fold or grouped_head_tile not in (8, 16):
         raise NotImplementedError("production ResAttn requires residue Q8/Q16")
-    splits = _select_splits(batch, num_kv_heads, max_kv_len, sm_count)
+    splits = _select_splits(batch, num_kv_heads, max_kv_len, sm_count, ctas_per_sm=2 if head_dim == 128 else 1)
     return (1, "none") if splits == 1 else (splits, "kernel")
 
 

@@ -60,11 +60,12 @@ def test_env_contract():
 # ---------------------------------------------------------------------------------- attention plan
 def test_decode_plan_selection_and_validation():
     from resinfer_b200.nvfp4.cute_attn.plan import select_decode_plan, validate_decode_plan, static_compile_plans
-    assert select_decode_plan(256, 8, 32768, 148) == (1, "none")
+    assert select_decode_plan(256, 8, 32768, 148, head_dim=256) == (1, "none")
     s, r = select_decode_plan(1, 8, 32768, 148)
     assert r == "kernel" and 8 <= s <= 64
     # eight sequences of up to 32768 tokens: pieces sized so that the working CTAs fill the SMs once
-    assert select_decode_plan(8, 8, 32768, 148) == (4, "kernel")
+    assert select_decode_plan(8, 8, 32768, 148, head_dim=256) == (4, "kernel")
+    assert select_decode_plan(8, 8, 32768, 148) == (8, "kernel")       # head_dim 128: two CTAs per SM
     assert select_decode_plan(64, 8, 32768, 148) == (3, "kernel")     # a few waves: thirds even out the tail
     assert select_decode_plan(1, 8, 64, 148) == (1, "none")          # too short to split
     assert (1, "none") in static_compile_plans()
