@@ -51,7 +51,13 @@ constexpr int kPvVBytes = 128 * 128 * 2;
 #define RI_PV_CTAS 2
 #endif
 constexpr int kPvVBufs = RI_PV_VBUFS;             // FP16 V tiles in flight
+#ifdef RI_PV_ALIAS_V   // timing experiment only (wrong results): both V buffers share memory
+constexpr int kPvVStride = 0;
+constexpr int kPvHeaderBytes = kPvOffV + kPvVBytes;
+#else
+constexpr int kPvVStride = kPvVBytes;
 constexpr int kPvHeaderBytes = kPvOffV + kPvVBufs * kPvVBytes;        // a multiple of 1024
+#endif
 constexpr int kPvStages = RI_PV_STAGES;           // cp.async pipeline stages per CTA
 constexpr int kPvCtasPerSm = RI_PV_CTAS;
 
@@ -197,7 +203,9 @@ __global__ void __launch_bounds__(kThreadsPv, kPvCtasPerSm) resattn_pv_kernel(co
       const int sb = i & 1;
       const int tile = t_begin + i;
       if (threadIdx.x == 0) {
+        attn_event(p, 0, i);
         soft_go[sb] = mbar_wait(smem_u32(&bar_sfull[sb]), (i >> 1) & 1, &abort_flag, 5) ? 1 : 0;
+        attn_event(p, 1, i);
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (!soft_go[sb]) break;                                  // the same decision in all four warps
@@ -279,6 +287,7 @@ __global__ void __launch_bounds__(kThreadsPv, kPvCtasPerSm) resattn_pv_kernel(co
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_vpready[sb]));
+      if (threadIdx.x == 0) attn_event(p, 2, i);
     }
   } else if (warp == kPvMmaWarp) {
     // ============================================================ MMA issuer
@@ -297,6 +306,7 @@ __global__ void __launch_bounds__(kThreadsPv, kPvCtasPerSm) resattn_pv_kernel(co
       bool got = true;
       if (lane == 0) got = mbar_wait(smem_u32(&bar_full[stg]), (i / S) & 1, &abort_flag, 3);
       if (!__all_sync(0xffffffffu, got)) { alive = false; return; }
+      if (lane == 0) attn_event(p, 3, i);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // cp.async data -> tensor-core reads
       tc_fence_after();
       if (elect_one()) {
@@ -315,6 +325,7 @@ __global__ void __launch_bounds__(kThreadsPv, kPvCtasPerSm) resattn_pv_kernel(co
         mma_commit(smem_u32(&bar_empty[stg]));                 // the K codes of the stage have been read
       }
       __syncwarp();
+      if (lane == 0) attn_event(p, 6, i);
     };
     if (my_tiles > 0) issue_qk(0);
     for (int i = 0; i < my_tiles && alive; ++i) {
@@ -324,10 +335,11 @@ __global__ void __launch_bounds__(kThreadsPv, kPvCtasPerSm) resattn_pv_kernel(co
       bool got = true;
       if (lane == 0) got = mbar_wait(smem_u32(&bar_vpready[vb]), (i >> 1) & 1, &abort_flag, 9);
       if (!__all_sync(0xffffffffu, got)) break;
+      if (lane == 0) attn_event(p, 7, i);
       tc_fence_after();
       if (elect_one()) {
         // A = V^T: M-major, 128-byte swizzle: 64-d blocks 16 KB apart (leading offset), 8-token groups 1 KB apart
-        const uint32_t va = smem_u32(smem + kPvOffV + (kPvVBufs == 2 ? vb * kPvVBytes : 0));
+        const uint32_t va = smem_u32(smem + kPvOffV + (kPvVBufs == 2 ? vb * kPvVStride : 0));
         // B = P: K-major, no swizzle: 8-token core matrices kPvPLbo apart along K; rows 8-15 are the zero group
         const uint32_t pa = smem_u32(smem + kPvOffP + vb * kPvPGroup);
         const uint32_t p_sbo = (2 - vb) * kPvPGroup;
@@ -338,6 +350,7 @@ __global__ void __launch_bounds__(kThreadsPv, kPvCtasPerSm) resattn_pv_kernel(co
         mma_commit(smem_u32(&bar_pvdone[vb]));
       }
       __syncwarp();
+      if (lane == 0) attn_event(p, 8, i);
     }
   } else if (warp < kPvFirstConv) {
     // ============================================================ copy producers (as in resattn_tc_kernel)
@@ -430,17 +443,30 @@ __global__ void __launch_bounds__(kThreadsPv, kPvCtasPerSm) resattn_pv_kernel(co
         sfw = *reinterpret_cast<const uint32_t*>(st + C::kOffVsf + tok * C::kSfPerRow + dblk * 4);
       }
       const uint32_t words[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};   // 8 codes (= 8 d) per word
-      uint8_t* dst_row = smem + kPvOffV + (kPvVBufs == 2 ? vb * kPvVBytes : 0) + dblk * 16384 + (tok >> 3) * 1024 + (tok & 7) * 128;
+      // the four block scales of this thread's 64 values as FP16 pairs (s, s)
+      uint32_t sc2[4];
+      {
+        uint32_t lo, hi;                                       // (s0, s1), (s2, s3) as FP16 pairs
+        asm("{\n\t.reg .b16 a, b;\n\tmov.b32 {a, b}, %2;\n\tcvt.rn.f16x2.e4m3x2 %0, a;\n\tcvt.rn.f16x2.e4m3x2 %1, b;\n\t}"
+            : "=r"(lo), "=r"(hi) : "r"(sfw));
+        sc2[0] = __byte_perm(lo, 0, 0x1010); sc2[1] = __byte_perm(lo, 0, 0x3232);
+        sc2[2] = __byte_perm(hi, 0, 0x1010); sc2[3] = __byte_perm(hi, 0, 0x3232);
+      }
+      // destination row of this token in the swizzled M-major tile; chunk w goes to (w ^ (tok & 7)) << 4,
+      // which is an XOR on the address because the row is 128-byte aligned
+      const uint32_t dst0 = smem_u32(smem + kPvOffV + (kPvVBufs == 2 ? vb * kPvVStride : 0) + dblk * 16384 +
+                                     (tok >> 3) * 1024 + (tok & 7) * 128) | ((tok & 7) << 4);
 #pragma unroll
       for (int w8 = 0; w8 < 8; ++w8) {                         // one 16-byte chunk = 8 FP16 per code word
-        const __half sc = e4m3_to_half((sfw >> (8 * (w8 >> 1))) & 0xFFu);
-        const __half2 sc2 = __halves2half2(sc, sc);
-        uint4 o;
-        o.x = h2_bits(__hmul2(e2m1x2_to_half2(words[w8] & 0xFFu), sc2));
-        o.y = h2_bits(__hmul2(e2m1x2_to_half2((words[w8] >> 8) & 0xFFu), sc2));
-        o.z = h2_bits(__hmul2(e2m1x2_to_half2((words[w8] >> 16) & 0xFFu), sc2));
-        o.w = h2_bits(__hmul2(e2m1x2_to_half2(words[w8] >> 24), sc2));
-        *reinterpret_cast<uint4*>(dst_row + ((w8 ^ (tok & 7)) << 4)) = o;
+        uint32_t h0, h1, h2, h3;
+        asm("{\n\t.reg .b8 a, b, c, d;\n\tmov.b32 {a, b, c, d}, %4;\n\t"
+            "cvt.rn.f16x2.e2m1x2 %0, a;\n\tcvt.rn.f16x2.e2m1x2 %1, b;\n\t"
+            "cvt.rn.f16x2.e2m1x2 %2, c;\n\tcvt.rn.f16x2.e2m1x2 %3, d;\n\t}"
+            : "=r"(h0), "=r"(h1), "=r"(h2), "=r"(h3) : "r"(words[w8]));
+        const __half2 s2 = bits_h2(sc2[w8 >> 1]);
+        const uint32_t o0 = h2_bits(__hmul2(bits_h2(h0), s2)), o1 = h2_bits(__hmul2(bits_h2(h1), s2));
+        const uint32_t o2 = h2_bits(__hmul2(bits_h2(h2), s2)), o3 = h2_bits(__hmul2(bits_h2(h3), s2));
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst0 ^ (w8 << 4)), "r"(o0), "r"(o1), "r"(o2), "r"(o3) : "memory");
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
