@@ -727,11 +727,11 @@ extern "C" int ri_resattn_decode(const void* q_bf16, const uint8_t* k_data, cons
     p.m_part = p.l_part + rows;
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // head_dim 128 runs the kernel with both products on the tensor cores; RI_ATTN_PV=0 selects the
-  // mma.sync P.V kernel (kept for head_dim 256) for comparisons
+  // Both head dimensions run the kernel with both products on the tensor cores; RI_ATTN_PV=0 selects the
+  // mma.sync P.V kernel for comparisons
   static const bool use_pv = [] { const char* e = getenv("RI_ATTN_PV"); return !(e && e[0] == '0'); }();
-  s = head_dim == 128 ? (use_pv ? tcattn::launch_decode_pv(p, st) : tcattn::launch_decode_tc<128>(p, st))
-                      : tcattn::launch_decode_tc<256>(p, st);
+  s = head_dim == 128 ? (use_pv ? tcattn::launch_decode_pv<128>(p, st) : tcattn::launch_decode_tc<128>(p, st))
+                      : (use_pv ? tcattn::launch_decode_pv<256>(p, st) : tcattn::launch_decode_tc<256>(p, st));
   if (s) return s;
   if (splits > 1) {
     const int64_t rows = int64_t(batch) * num_q_heads;

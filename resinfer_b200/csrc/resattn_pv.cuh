@@ -24,17 +24,14 @@
 // issued instructions (measured: 1.6 -> 2.5 TB/s from this change alone).  Every mbarrier wait is
 // bounded; the decision slot makes all warps of a role leave their loop together on expiry.
 
-constexpr int kPvSoft = 4, kPvProd = 4, kPvConv = 8;
+constexpr int kPvSoft = 4, kPvProd = 4;
 constexpr int kPvMmaWarp = kPvSoft;
 constexpr int kPvFirstProd = kPvSoft + 1;
 constexpr int kPvFirstConv = kPvFirstProd + kPvProd;
-constexpr int kThreadsPv = (kPvSoft + 1 + kPvProd + kPvConv) * 32;     // 544
 // O^T accumulators: the eight P.V MMAs of a tile (16 tokens each) add into eight different accumulators,
-// 16 columns apart, which are summed at the end: MMAs into one accumulator execute one after the
-// other at full instruction latency, independent ones overlap
+// 16 columns apart, which are summed at the end (head_dim 256: two sets, one per 128 output rows)
 constexpr int kPvColO = 128;
 constexpr int kPvAccs = 8;
-constexpr int kPvTmemCols = 256;
 constexpr int kPvOffMisc = 3072;                  // running maxima, rescale factors, flags
 // P: K-major B operand without swizzle.  A core matrix is 8 rows (heads) x 16 bytes (8 tokens); the
 // core matrices of consecutive 8-token groups are 144 bytes apart (not 128: the softmax warps then
@@ -43,23 +40,37 @@ constexpr int kPvOffMisc = 3072;                  // running maxima, rescale fac
 constexpr int kPvPLbo = 144;
 constexpr int kPvPGroup = 16 * kPvPLbo;           // 2304 bytes: one 8-row group over 128 tokens
 constexpr int kPvOffP = 4096;
-constexpr int kPvOffV = 11264;                    // [2 d-blocks][128 tokens][64 d] FP16, 128B swizzle, M-major
-constexpr int kPvVBytes = 128 * 128 * 2;
+constexpr int kPvOffV = 11264;                    // [D/64 d-blocks][128 tokens][64 d] FP16, 128B swizzle, M-major
 #ifndef RI_PV_VBUFS
 #define RI_PV_VBUFS 2
 #define RI_PV_STAGES 2
 #define RI_PV_CTAS 2
 #endif
-constexpr int kPvVBufs = RI_PV_VBUFS;             // FP16 V tiles in flight
-#ifdef RI_PV_ALIAS_V   // timing experiment only (wrong results): both V buffers share memory
-constexpr int kPvVStride = 0;
-constexpr int kPvHeaderBytes = kPvOffV + kPvVBytes;
-#else
-constexpr int kPvVStride = kPvVBytes;
-constexpr int kPvHeaderBytes = kPvOffV + kPvVBufs * kPvVBytes;        // a multiple of 1024
+#ifndef RI_PV256_VBUFS
+#define RI_PV256_VBUFS 2
+#define RI_PV256_STAGES 2
 #endif
-constexpr int kPvStages = RI_PV_STAGES;           // cp.async pipeline stages per CTA
-constexpr int kPvCtasPerSm = RI_PV_CTAS;
+// head_dim 128: two CTAs of 17 warps per SM; head_dim 256: one CTA of 25 warps (the FP16 V tile is 64 KB)
+template <int D>
+struct PvCfg {
+  static constexpr int kConv = D == 128 ? 8 : 16;                     // conversion warps
+  static constexpr int kVBufs = D == 128 ? RI_PV_VBUFS : RI_PV256_VBUFS;        // FP16 V tiles in flight
+  static constexpr int kStages = D == 128 ? RI_PV_STAGES : RI_PV256_STAGES;     // cp.async pipeline stages
+  static constexpr int kCtasPerSm = D == 128 ? RI_PV_CTAS : 1;
+  static constexpr int kDBlocks = D / 64;                             // 64-wide blocks of the head dimension
+  static constexpr int kHalves = D / 128;                             // 128-row halves of O^T (M of one MMA)
+  static constexpr int kVBytes = 128 * D * 2;
+#ifdef RI_PV_ALIAS_V   // timing experiment only (wrong results): both V buffers share memory
+  static constexpr int kVStride = 0;
+  static constexpr int kHeaderBytes = kPvOffV + kVBytes;
+#else
+  static constexpr int kVStride = kVBytes;
+  static constexpr int kHeaderBytes = kPvOffV + kVBufs * kVBytes;      // a multiple of 1024
+#endif
+  static constexpr int kThreads = (kPvSoft + 1 + kPvProd + kConv) * 32;
+  static constexpr int kTmemCols = D == 128 ? 256 : 512;
+  static constexpr int kSmemBytes = kHeaderBytes + kStages * TCfg<D>::kStageBytes + 1024;
+};
 
 __device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                            uint32_t accumulate) {
@@ -83,9 +94,12 @@ __device__ __forceinline__ void tmem_st16f(uint32_t taddr, const float (&v)[16])
         "r"(__float_as_uint(v[15])) : "memory");
 }
 
-__global__ void __launch_bounds__(kThreadsPv, kPvCtasPerSm) resattn_pv_kernel(const AttnParams p) {
-  constexpr int D = 128;
+template <int D>
+__global__ void __launch_bounds__(PvCfg<D>::kThreads, PvCfg<D>::kCtasPerSm) resattn_pv_kernel(const AttnParams p) {
   using C = TCfg<D>;
+  using PC = PvCfg<D>;
+  constexpr int kPvConv = PC::kConv, kPvVBufs = PC::kVBufs, kPvStages = PC::kStages, kThreadsPv = PC::kThreads;
+  constexpr int kPvTmemCols = PC::kTmemCols, kPvVStride = PC::kVStride, kPvHeaderBytes = PC::kHeaderBytes;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[kPvStages];
   __shared__ __align__(8) uint64_t bar_empty[kPvStages];
@@ -255,7 +269,7 @@ __global__ void __launch_bounds__(kThreadsPv, kPvCtasPerSm) resattn_pv_kernel(co
           if (__all_sync(0xffffffffu, got)) {
             tc_fence_after();
 #pragma unroll 1
-            for (int a = 0; a < kPvAccs; ++a) {
+            for (int a = 0; a < kPvAccs * PC::kHalves; ++a) {
               float o[16];
               tmem_ld16(lane_base + kPvColO + 16 * a, o);
 #pragma unroll
@@ -344,9 +358,12 @@ __global__ void __launch_bounds__(kThreadsPv, kPvCtasPerSm) resattn_pv_kernel(co
         const uint32_t pa = smem_u32(smem + kPvOffP + vb * kPvPGroup);
         const uint32_t p_sbo = (2 - vb) * kPvPGroup;
 #pragma unroll
-        for (int k16 = 0; k16 < kTile / 16; ++k16)
-          mma_f16_ss(tmem_base + kPvColO + 16 * k16, desc_full(va + k16 * 2048, 16384, 1024, 2),
-                     desc_full(pa + k16 * 2 * kPvPLbo, kPvPLbo, p_sbo, 0), idesc_pv, i > 0 ? 1u : 0u);
+        for (int hf = 0; hf < PC::kHalves; ++hf)
+#pragma unroll
+          for (int k16 = 0; k16 < kTile / 16; ++k16)
+            mma_f16_ss(tmem_base + kPvColO + 16 * (hf * kPvAccs + k16),
+                       desc_full(va + hf * 2 * 16384 + k16 * 2048, 16384, 1024, 2),
+                       desc_full(pa + k16 * 2 * kPvPLbo, kPvPLbo, p_sbo, 0), idesc_pv, i > 0 ? 1u : 0u);
         mma_commit(smem_u32(&bar_pvdone[vb]));
       }
       __syncwarp();
@@ -359,8 +376,8 @@ __global__ void __launch_bounds__(kThreadsPv, kPvCtasPerSm) resattn_pv_kernel(co
     constexpr int kIters = 32 / kRowsPerIt;
     const int pw = warp - kPvFirstProd;
     const int r_lane = lane / kCpr, chn = lane % kCpr;
-    const int sf_row = 2 * lane;
-    const bool sf_lane = lane < 16;
+    const int sf_row = D == 128 ? 2 * lane : lane;             // first row of this lane's 16 scale bytes
+    const bool sf_lane = D == 128 ? lane < 16 : true;
     uint32_t k_dst[kIters];
 #pragma unroll
     for (int it = 0; it < kIters; ++it) k_dst[it] = swz_off<D>(32 * pw + it * kRowsPerIt + r_lane, chn * 16);
@@ -406,16 +423,17 @@ __global__ void __launch_bounds__(kThreadsPv, kPvCtasPerSm) resattn_pv_kernel(co
       if (lane < rows) {                                       // K scales of token 32 pw + lane, 4 bytes per MMA
         const uint8_t* src = p.k_sf + ((lane < 16 ? base0 : base1) + (lane & 15)) * C::kSfPerRow;
         const uint32_t dst = st + C::kOffKsf + lane * 16 + pw * 4;
-        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
-        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 512), "l"(src + 4) : "memory");
+#pragma unroll
+        for (int j = 0; j < C::kMma; ++j)
+          asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 512 * j), "l"(src + 4 * j) : "memory");
       }
       asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&bar_full[stg])) : "memory");
     }
   } else {
     // ============================================================ V conversion warps
-    // warp c: tokens 32 (c / 2) .. +31, d-block c % 2 (64 head-dim values = 32 code bytes = 4 scale blocks)
+    // warp c: tokens 32 (c / blocks) .. +31, d-block c % blocks (64 head-dim values = 32 code bytes = 4 scale blocks)
     const int cv = warp - kPvFirstConv;
-    const int tok = 32 * (cv >> 1) + lane, dblk = cv & 1;
+    const int tok = 32 * (cv / PC::kDBlocks) + lane, dblk = cv % PC::kDBlocks;
     for (int i = 0, stg = 0, ph = 0; i < my_tiles; ++i, stg = (stg + 1 == S ? 0 : stg + 1), ph ^= (stg == 0)) {
       const int vb = i & 1;
       if (cv == 0 && lane == 0) {                              // one lane polls, the eight warps meet on a named barrier
@@ -427,7 +445,7 @@ __global__ void __launch_bounds__(kThreadsPv, kPvCtasPerSm) resattn_pv_kernel(co
         }
         conv_go[vb] = got ? 1 : 0;
       }
-      asm volatile("bar.sync 3, 256;" ::: "memory");
+      asm volatile("bar.sync 3, %0;" ::"n"(kPvConv * 32) : "memory");
       if (!conv_go[vb]) break;
       const uint8_t* st = stage0 + stg * C::kStageBytes;
       if (cv == 0 && lane == 0) attn_event(p, 4, i);
@@ -437,7 +455,7 @@ __global__ void __launch_bounds__(kThreadsPv, kPvCtasPerSm) resattn_pv_kernel(co
       if (valid) {
         // the producers store the V rows with the swizzle of the K operand (conflict-free 16-byte reads)
         const uint8_t* row = st + C::kOffV + tok * C::kRowBytes;
-        const int sw = (tok >> 1) & 3;
+        const int sw = D == 128 ? (tok >> 1) & 3 : tok & 7;
         c0 = *reinterpret_cast<const uint4*>(row + (((2 * dblk) ^ sw) << 4));
         c1 = *reinterpret_cast<const uint4*>(row + (((2 * dblk + 1) ^ sw) << 4));
         sfw = *reinterpret_cast<const uint32_t*>(st + C::kOffVsf + tok * C::kSfPerRow + dblk * 4);
@@ -479,26 +497,29 @@ __global__ void __launch_bounds__(kThreadsPv, kPvCtasPerSm) resattn_pv_kernel(co
   }
 
   // ---------------------------------------------------------------- output
-  // thread (softmax warp q, lane) owns head-dim column d = 32 q + lane of all heads
+  // thread (softmax warp q, lane) owns head-dim columns 128 half + 32 q + lane of all heads
   float* red_l = red;
-  float o_acc[16];
+  bool have_o = false;
+  float o_acc[8];
 #pragma unroll
-  for (int h = 0; h < 16; ++h) o_acc[h] = 0.f;
-  if (warp < kPvSoft) {
+  for (int h = 0; h < 8; ++h) o_acc[h] = 0.f;
+  auto load_half = [&](int hf) {          // sum of the eight accumulators of output rows 128 hf .. 128 hf + 127
     const uint32_t lane_base = tmem_base + (uint32_t(warp * 32) << 16);
+    tc_fence_after();
+#pragma unroll 1
+    for (int a = 0; a < kPvAccs; ++a) {
+      float o[16];
+      tmem_ld16(lane_base + kPvColO + 16 * (hf * kPvAccs + a), o);
+#pragma unroll
+      for (int h = 0; h < 8; ++h) o_acc[h] += o[h];
+    }
+  };
+  if (warp < kPvSoft) {
     if (my_tiles > 0) {
       bool got = true;
       if (lane == 0) got = mbar_wait(smem_u32(&bar_pvdone[(my_tiles - 1) & 1]), ((my_tiles - 1) >> 1) & 1, &abort_flag, 12);
-      if (__all_sync(0xffffffffu, got)) {
-        tc_fence_after();
-#pragma unroll 1
-        for (int a = 0; a < kPvAccs; ++a) {
-          float o[16];
-          tmem_ld16(lane_base + kPvColO + 16 * a, o);
-#pragma unroll
-          for (int h = 0; h < 8; ++h) o_acc[h] += o[h];
-        }
-      }
+      have_o = __all_sync(0xffffffffu, got);
+      if (have_o) load_half(0);
     }
 #pragma unroll
     for (int h = 0; h < 8; ++h) {
@@ -513,26 +534,34 @@ __global__ void __launch_bounds__(kThreadsPv, kPvCtasPerSm) resattn_pv_kernel(co
   tc_fence_before();
   __syncthreads();
   const bool failed = abort_flag != 0;
-  float* stage_out = reinterpret_cast<float*>(smem + kPvOffV);      // [8 heads][128] for the NVFP4 output path
+  float* stage_out = reinterpret_cast<float*>(smem + kPvOffV);      // [8 heads][D] for the NVFP4 output path
   if (warp < kPvSoft) {
-    const int d = 32 * warp + lane;
 #pragma unroll
-    for (int g = 0; g < 8; ++g) {
-      if (g >= G) break;
-      const float l = (red_l[g] + red_l[8 + g]) + (red_l[16 + g] + red_l[24 + g]);
-      const int head = hkv * G + g;
-      if (p.splits == 1) {
-        const float rr = l > 0.f ? p.out_scale / l : 0.f;
-        const int64_t oi = (int64_t(b) * p.hq + head) * D + d;
-        if (p.out_nvfp4) stage_out[g * D + d] = o_acc[g] * rr;
-        else if (p.out_f32) static_cast<float*>(p.out)[oi] = o_acc[g] * rr;
-        else static_cast<__nv_bfloat16*>(p.out)[oi] = __float2bfloat16_rn(o_acc[g] * rr);
-      } else {
-        const int64_t slot = (int64_t(split) * p.batch + b) * p.hq + head;
-        p.o_part[slot * D + d] = o_acc[g];
-        if (d == 0) {
-          p.l_part[slot] = l;
-          p.m_part[slot] = my_tiles > 0 ? m_sh[g] : -INFINITY;
+    for (int hf = 0; hf < PC::kHalves; ++hf) {
+      if (hf > 0) {
+#pragma unroll
+        for (int h = 0; h < 8; ++h) o_acc[h] = 0.f;
+        if (have_o) load_half(hf);
+      }
+      const int d = 128 * hf + 32 * warp + lane;
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {
+        if (g >= G) break;
+        const float l = (red_l[g] + red_l[8 + g]) + (red_l[16 + g] + red_l[24 + g]);
+        const int head = hkv * G + g;
+        if (p.splits == 1) {
+          const float rr = l > 0.f ? p.out_scale / l : 0.f;
+          const int64_t oi = (int64_t(b) * p.hq + head) * D + d;
+          if (p.out_nvfp4) stage_out[g * D + d] = o_acc[g] * rr;
+          else if (p.out_f32) static_cast<float*>(p.out)[oi] = o_acc[g] * rr;
+          else static_cast<__nv_bfloat16*>(p.out)[oi] = __float2bfloat16_rn(o_acc[g] * rr);
+        } else {
+          const int64_t slot = (int64_t(split) * p.batch + b) * p.hq + head;
+          p.o_part[slot * D + d] = o_acc[g];
+          if (d == 0) {
+            p.l_part[slot] = l;
+            p.m_part[slot] = my_tiles > 0 ? m_sh[g] : -INFINITY;
+          }
         }
       }
     }
@@ -554,26 +583,27 @@ __global__ void __launch_bounds__(kThreadsPv, kPvCtasPerSm) resattn_pv_kernel(co
   }
 }
 
-inline int launch_decode_pv(const AttnParams& p, cudaStream_t st) {
-  const int smem = kPvHeaderBytes + kPvStages * TCfg<128>::kStageBytes + 1024;
+template <int D>
+int launch_decode_pv(const AttnParams& p, cudaStream_t st) {
+  using PC = PvCfg<D>;
   static bool attr_done[64] = {};
   int dev = 0;
   RI_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) dev = 0;
   if (!attr_done[dev]) {
-    RI_CUDA(cudaFuncSetAttribute(resattn_pv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    RI_CUDA(cudaFuncSetAttribute(resattn_pv_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
+    RI_CUDA(cudaFuncSetAttribute(resattn_pv_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, PC::kSmemBytes));
+    RI_CUDA(cudaFuncSetAttribute(resattn_pv_kernel<D>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
     attr_done[dev] = true;
   }
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(p.splits, p.hkv, p.batch);
-  cfg.blockDim = dim3(kThreadsPv);
-  cfg.dynamicSmemBytes = smem;
+  cfg.blockDim = dim3(PC::kThreads);
+  cfg.dynamicSmemBytes = PC::kSmemBytes;
   cfg.stream = st;
   cudaLaunchAttribute attr{};
   attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr.val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  return cuda_status(cudaLaunchKernelEx(&cfg, resattn_pv_kernel, p), "resattn decode launch");
+  return cuda_status(cudaLaunchKernelEx(&cfg, resattn_pv_kernel<D>, p), "resattn decode launch");
 }
