@@ -1,4 +1,4 @@
-// ResAttn decode with both products on the tensor cores (head_dim 128).  Included by resattn.cu inside
+// ResAttn decode with both products on the tensor cores (head_dim 128 and 256).  Included by resattn.cu inside
 // namespace ri::<anon>::tcattn (it uses that file's AttnParams, cp_async16, swz_off, fast_exp2, ...).
 //
 //   S^T[128 tokens x 16] = K . Qpack^T     tcgen05.mma kind::mxf4nvf4.block_scale, K codes and E4M3 scales
@@ -8,26 +8,25 @@
 //                                          conversion warps; P (FP16) is the K-major B operand written
 //                                          by the softmax warps; FP32 accumulator in tensor memory
 //
-// One CTA per (KV split, KV head, sequence), two CTAs per SM, tiles of 128 tokens, 17 warps:
-//   warps 0-3   softmax: one thread per token of the tile (tensor-memory lane = token).  The running
-//               maximum of a head is shared by the CTA and only raised when a score exceeds it by more
-//               than 2^8 (then the accumulators in tensor memory are rescaled); row sums stay per
-//               thread until the end.
-//   warp 4      issues every MMA (scores of tile i+1 before the P.V of tile i), copies the K block scales
-//               of a tile from shared to tensor memory (tcgen05.cp) and owns tensor memory
-//   warps 5-8   cp.async producers: K codes and V codes in the 64-byte operand swizzle, V scales as
+// One CTA per (KV split, KV head, sequence), tiles of 128 tokens.  head_dim 128: two CTAs of 21 warps per SM;
+// head_dim 256: one CTA of 29 warps (its FP16 V tile is 64 KB).  Roles:
+//   softmax     eight warps, warp (q, hh): tokens 32 q .. 32 q + 31 of the tile (tensor-memory lane = token),
+//               heads 4 hh .. 4 hh + 3.  The running maximum of a head is shared by the CTA and only raised
+//               when a score exceeds it by more than 2^8 (then the accumulators in tensor memory are
+//               rescaled); row sums stay per thread until the end.  (Four warps with eight heads per thread
+//               measured 7-9 % slower: the softmax of a tile is the longest dependency chain of the CTA.)
+//   MMA         one warp issues every MMA (scores of tile i+1 before the P.V of tile i), copies the K block
+//               scales of a tile from shared to tensor memory (tcgen05.cp) and owns tensor memory
+//   producers   four warps of cp.async: K codes and V codes in the operand swizzle of K, V scales as
 //               stored, K scales in the layout of the tcgen05.cp 32x128b copy
-//   warps 9-16  V conversion: NVFP4 codes x E4M3 scale -> FP16, written in the 128-byte-swizzled M-major
+//   conversion  8 / 16 warps: NVFP4 codes x E4M3 scale -> FP16, written in the 128-byte-swizzled M-major
 //               operand layout; rows past the end of the sequence are written as zeros
 // In every multi-warp role ONE lane polls the mbarriers and publishes its decision in shared memory;
 // the other warps of the role wait on a named barrier.  Polling lanes in every warp took half of all
 // issued instructions (measured: 1.6 -> 2.5 TB/s from this change alone).  Every mbarrier wait is
 // bounded; the decision slot makes all warps of a role leave their loop together on expiry.
 
-constexpr int kPvSoft = 4, kPvProd = 4;
-constexpr int kPvMmaWarp = kPvSoft;
-constexpr int kPvFirstProd = kPvSoft + 1;
-constexpr int kPvFirstConv = kPvFirstProd + kPvProd;
+constexpr int kPvProd = 4;
 // O^T accumulators: the eight P.V MMAs of a tile (16 tokens each) add into eight different accumulators,
 // 16 columns apart, which are summed at the end (head_dim 256: two sets, one per 128 output rows)
 constexpr int kPvColO = 128;
@@ -50,9 +49,17 @@ constexpr int kPvOffV = 11264;                    // [D/64 d-blocks][128 tokens]
 #define RI_PV256_VBUFS 2
 #define RI_PV256_STAGES 2
 #endif
+#ifndef RI_PV256_SOFT
+#define RI_PV256_SOFT 8
+#endif
+#ifndef RI_PV_SOFT
+#define RI_PV_SOFT 8
+#endif
 // head_dim 128: two CTAs of 17 warps per SM; head_dim 256: one CTA of 25 warps (the FP16 V tile is 64 KB)
 template <int D>
 struct PvCfg {
+  static constexpr int kSoft = D == 128 ? RI_PV_SOFT : RI_PV256_SOFT;          // softmax warps: 4 (8 heads per thread) or 8 (4 heads)
+  static constexpr int kHpt = 32 / kSoft;                             // heads a softmax thread handles
   static constexpr int kConv = D == 128 ? 8 : 16;                     // conversion warps
   static constexpr int kVBufs = D == 128 ? RI_PV_VBUFS : RI_PV256_VBUFS;        // FP16 V tiles in flight
   static constexpr int kStages = D == 128 ? RI_PV_STAGES : RI_PV256_STAGES;     // cp.async pipeline stages
@@ -67,7 +74,7 @@ struct PvCfg {
   static constexpr int kVStride = kVBytes;
   static constexpr int kHeaderBytes = kPvOffV + kVBufs * kVBytes;      // a multiple of 1024
 #endif
-  static constexpr int kThreads = (kPvSoft + 1 + kPvProd + kConv) * 32;
+  static constexpr int kThreads = (kSoft + 1 + kPvProd + kConv) * 32;
   static constexpr int kTmemCols = D == 128 ? 256 : 512;
   static constexpr int kSmemBytes = kHeaderBytes + kStages * TCfg<D>::kStageBytes + 1024;
 };
@@ -83,6 +90,12 @@ __device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uin
 __device__ __forceinline__ uint64_t desc_full(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout_type) {
   return uint64_t((saddr & 0x3FFFFu) >> 4) | (uint64_t(lbo_bytes >> 4) << 16) | (uint64_t(sbo_bytes >> 4) << 32) |
          (uint64_t(1) << 46) | (uint64_t(layout_type) << 61);
+}
+__device__ __forceinline__ void tmem_ld4f(uint32_t taddr, float (&v)[4]) {   // 32 lanes x 4 columns, waits for the data
+  uint32_t r0, r1, r2, r3;
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];\n\ttcgen05.wait::ld.sync.aligned;"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(taddr) : "memory");
+  v[0] = __uint_as_float(r0); v[1] = __uint_as_float(r1); v[2] = __uint_as_float(r2); v[3] = __uint_as_float(r3);
 }
 __device__ __forceinline__ void tmem_st16f(uint32_t taddr, const float (&v)[16]) {
   asm volatile(
@@ -100,6 +113,8 @@ __global__ void __launch_bounds__(PvCfg<D>::kThreads, PvCfg<D>::kCtasPerSm) resa
   using PC = PvCfg<D>;
   constexpr int kPvConv = PC::kConv, kPvVBufs = PC::kVBufs, kPvStages = PC::kStages, kThreadsPv = PC::kThreads;
   constexpr int kPvTmemCols = PC::kTmemCols, kPvVStride = PC::kVStride, kPvHeaderBytes = PC::kHeaderBytes;
+  constexpr int kPvSoft = PC::kSoft, kHpt = PC::kHpt;
+  constexpr int kPvMmaWarp = kPvSoft, kPvFirstProd = kPvSoft + 1, kPvFirstConv = kPvFirstProd + kPvProd;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[kPvStages];
   __shared__ __align__(8) uint64_t bar_empty[kPvStages];
@@ -193,26 +208,29 @@ __global__ void __launch_bounds__(PvCfg<D>::kThreads, PvCfg<D>::kCtasPerSm) resa
   if (warp < kPvFirstProd || warp >= kPvFirstConv)
     asm volatile("bar.sync 2, %0;" ::"n"(kThreadsPv - kPvProd * 32) : "memory");
 
-  float l_thr[8];
+  float l_thr[kHpt];
 #pragma unroll
-  for (int h = 0; h < 8; ++h) l_thr[h] = 0.f;
+  for (int h = 0; h < kHpt; ++h) l_thr[h] = 0.f;
 
   if (warp < kPvSoft) {
-    // ============================================================ softmax warps (and K scales -> tensor memory)
-    // Only lane 0 of warp 0 polls mbarriers; the four warps then meet on a named barrier, which
-    // costs the waiting warps no issue slots.
-    const int q = warp;
+    // ============================================================ softmax warps
+    // Warp (q, hh): tensor-memory quarter q = tokens 32 q .. 32 q + 31 of the tile, heads kHpt hh .. + kHpt - 1.
+    // Only lane 0 of warp 0 polls mbarriers; the warps then meet on a named barrier, which costs the
+    // waiting warps no issue slots.
+    const int q = warp & 3, hh = warp >> 2, g0 = hh * kHpt;
     const uint32_t lane_base = tmem_base + (uint32_t(q * 32) << 16);
+    if (hh == 0) {
 #pragma unroll
-    for (int j = 0; j < C::kMma; ++j) {
-      uint4 w = make_uint4(0, 0, 0, 0);
-      if (lane < 16) w.x = *reinterpret_cast<const uint32_t*>(qsf_s + lane * C::kSfPerRow + 4 * j);
-      tmem_st4(lane_base + kColSfb + 4 * j, w);
+      for (int j = 0; j < C::kMma; ++j) {
+        uint4 w = make_uint4(0, 0, 0, 0);
+        if (lane < 16) w.x = *reinterpret_cast<const uint32_t*>(qsf_s + lane * C::kSfPerRow + 4 * j);
+        tmem_st4(lane_base + kColSfb + 4 * j, w);
+      }
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
     }
-    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
     // the Q scales are in tensor memory: tell the MMA warp
     tc_fence_before();
-    asm volatile("bar.sync 5, 160;" ::: "memory");
+    asm volatile("bar.sync 5, %0;" ::"n"(kPvSoft * 32 + 32) : "memory");
     for (int i = 0; i < my_tiles; ++i) {
       const int sb = i & 1;
       const int tile = t_begin + i;
@@ -221,43 +239,51 @@ __global__ void __launch_bounds__(PvCfg<D>::kThreads, PvCfg<D>::kCtasPerSm) resa
         soft_go[sb] = mbar_wait(smem_u32(&bar_sfull[sb]), (i >> 1) & 1, &abort_flag, 5) ? 1 : 0;
         attn_event(p, 1, i);
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (!soft_go[sb]) break;                                  // the same decision in all four warps
+      asm volatile("bar.sync 1, %0;" ::"n"(kPvSoft * 32) : "memory");
+      if (!soft_go[sb]) break;                                  // the same decision in all softmax warps
       tc_fence_after();
-      float s[8];
+      float s[kHpt];
       bool mine_grows = false;
       {
-        float r[16];
-        tmem_ld16(lane_base + kColS + sb * 16, r);
-        tc_fence_before();
         const bool valid = tile * kTile + 32 * q + lane < L;
+        if constexpr (kHpt == 8) {
+          float r[16];
+          tmem_ld16(lane_base + kColS + sb * 16, r);
 #pragma unroll
-        for (int h = 0; h < 8; ++h) {
-          s[h] = valid ? (r[h] + r[8 + h]) * p.score_scale_log2 : -INFINITY;
-          mine_grows |= s[h] > m_sh[h] + kLazyThreshold;       // also true while the maximum is still -inf
+          for (int h = 0; h < 8; ++h) s[h] = valid ? (r[h] + r[8 + h]) * p.score_scale_log2 : -INFINITY;
+        } else {
+          float r0[4], r1[4];
+          tmem_ld4f(lane_base + kColS + sb * 16 + g0, r0);
+          tmem_ld4f(lane_base + kColS + sb * 16 + 8 + g0, r1);
+#pragma unroll
+          for (int h = 0; h < 4; ++h) s[h] = valid ? (r0[h] + r1[h]) * p.score_scale_log2 : -INFINITY;
         }
+        tc_fence_before();
+#pragma unroll
+        for (int h = 0; h < kHpt; ++h) mine_grows |= s[h] > m_sh[g0 + h] + kLazyThreshold;   // also true while the maximum is -inf
         if (__any_sync(0xffffffffu, mine_grows) && lane == 0) grow[sb] = 1;
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      asm volatile("bar.sync 1, %0;" ::"n"(kPvSoft * 32) : "memory");
       if (grow[sb]) {
         // ---- a maximum moved (always on the first tile): exact tile maxima, rescale the accumulators
-        float mx[8];
+        float mx[kHpt];
 #pragma unroll
-        for (int h = 0; h < 8; ++h) {
+        for (int h = 0; h < kHpt; ++h) {
           mx[h] = s[h];
 #pragma unroll
           for (int o = 16; o > 0; o >>= 1) mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], o));
         }
         if (lane == 0) {
 #pragma unroll
-          for (int h = 0; h < 8; ++h) wmax[q * 8 + h] = mx[h];
+          for (int h = 0; h < kHpt; ++h) wmax[q * 8 + g0 + h] = mx[h];
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        float f[8];
+        asm volatile("bar.sync 1, %0;" ::"n"(kPvSoft * 32) : "memory");
+        float f[kHpt];
 #pragma unroll
-        for (int h = 0; h < 8; ++h) {
-          const float old = m_sh[h];
-          const float nw = fmaxf(fmaxf(old, fmaxf(wmax[h], wmax[8 + h])), fmaxf(wmax[16 + h], wmax[24 + h]));
+        for (int h = 0; h < kHpt; ++h) {
+          const int g = g0 + h;
+          const float old = m_sh[g];
+          const float nw = fmaxf(fmaxf(old, fmaxf(wmax[g], wmax[8 + g])), fmaxf(wmax[16 + g], wmax[24 + g]));
           f[h] = old == -INFINITY ? 0.f : fast_exp2(old - nw);
           l_thr[h] *= f[h];
           mx[h] = nw;
@@ -270,30 +296,42 @@ __global__ void __launch_bounds__(PvCfg<D>::kThreads, PvCfg<D>::kCtasPerSm) resa
             tc_fence_after();
 #pragma unroll 1
             for (int a = 0; a < kPvAccs * PC::kHalves; ++a) {
-              float o[16];
-              tmem_ld16(lane_base + kPvColO + 16 * a, o);
+              if constexpr (kHpt == 8) {
+                float o[16];
+                tmem_ld16(lane_base + kPvColO + 16 * a, o);
 #pragma unroll
-              for (int h = 0; h < 8; ++h) o[h] *= f[h];
-              tmem_st16f(lane_base + kPvColO + 16 * a, o);
+                for (int h = 0; h < 8; ++h) o[h] *= f[h];
+                tmem_st16f(lane_base + kPvColO + 16 * a, o);
+              } else {                                          // this warp's four heads = four columns of the accumulator
+                float o[4];
+                tmem_ld4f(lane_base + kPvColO + 16 * a + g0, o);
+                tmem_st4(lane_base + kPvColO + 16 * a + g0,
+                         make_uint4(__float_as_uint(o[0] * f[0]), __float_as_uint(o[1] * f[1]),
+                                    __float_as_uint(o[2] * f[2]), __float_as_uint(o[3] * f[3])));
+              }
             }
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             tc_fence_before();
           }
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");          // everybody has read the old maxima
-        if (threadIdx.x < 8) m_sh[threadIdx.x] = mx[threadIdx.x];
+        asm volatile("bar.sync 1, %0;" ::"n"(kPvSoft * 32) : "memory");   // everybody has read the old maxima
+        if (q == 0) {
+#pragma unroll
+          for (int h = 0; h < kHpt; ++h)
+            if (lane == h) m_sh[g0 + h] = mx[h];
+        }
         if (threadIdx.x == 8) grow[sb] = 0;
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(kPvSoft * 32) : "memory");
       }
       // ---- probabilities of this thread's token, FP16, into the K-major B operand of the P.V MMAs.
       // (The P buffer is free: the commit behind s_full(i) was issued by the same thread after the P.V
       // MMAs of tile i-2, so having seen it means those have read the buffer.)
       {
         const int t = 32 * q + lane;
-        __half* pb = reinterpret_cast<__half*>(smem + kPvOffP + sb * kPvPGroup + (t >> 3) * kPvPLbo) + (t & 7);
+        __half* pb = reinterpret_cast<__half*>(smem + kPvOffP + sb * kPvPGroup + (t >> 3) * kPvPLbo) + (t & 7) + g0 * 8;
 #pragma unroll
-        for (int h = 0; h < 8; ++h) {
-          const float pv = fast_exp2(s[h] - m_sh[h]);          // 0 for tokens past the end (s = -inf)
+        for (int h = 0; h < kHpt; ++h) {
+          const float pv = fast_exp2(s[h] - m_sh[g0 + h]);     // 0 for tokens past the end (s = -inf)
           l_thr[h] += pv;
           pb[h * 8] = __float2half_rn(pv);
         }
@@ -312,7 +350,7 @@ __global__ void __launch_bounds__(PvCfg<D>::kThreads, PvCfg<D>::kCtasPerSm) resa
     const uint32_t idesc_pv = (1u << 4) | (1u << 15) | (uint32_t(16 >> 3) << 17) | (uint32_t(128 >> 4) << 24);
     const uint64_t bq_desc = desc_kmajor(smem_u32(q_op), C::kSbo, C::kLayout);
     bool alive = true;
-    asm volatile("bar.sync 5, 160;" ::: "memory");              // the Q scales are in tensor memory
+    asm volatile("bar.sync 5, %0;" ::"n"(kPvSoft * 32 + 32) : "memory");   // the Q scales are in tensor memory
     // Scores of tile i.  Its S buffer and scale set were last used by tile i-2, whose softmax finished
     // before the P.V of tile i-2 was issued (by this thread, earlier).
     auto issue_qk = [&](int i) {
@@ -515,27 +553,27 @@ __global__ void __launch_bounds__(PvCfg<D>::kThreads, PvCfg<D>::kCtasPerSm) resa
     }
   };
   if (warp < kPvSoft) {
-    if (my_tiles > 0) {
+    if (warp < 4 && my_tiles > 0) {                            // the first four softmax warps write the output
       bool got = true;
       if (lane == 0) got = mbar_wait(smem_u32(&bar_pvdone[(my_tiles - 1) & 1]), ((my_tiles - 1) >> 1) & 1, &abort_flag, 12);
       have_o = __all_sync(0xffffffffu, got);
       if (have_o) load_half(0);
     }
 #pragma unroll
-    for (int h = 0; h < 8; ++h) {
+    for (int h = 0; h < kHpt; ++h) {
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) l_thr[h] += __shfl_xor_sync(0xffffffffu, l_thr[h], o);
     }
     if (lane == 0) {
 #pragma unroll
-      for (int h = 0; h < 8; ++h) red_l[warp * 8 + h] = l_thr[h];
+      for (int h = 0; h < kHpt; ++h) red_l[(warp & 3) * 8 + (warp >> 2) * kHpt + h] = l_thr[h];
     }
   }
   tc_fence_before();
   __syncthreads();
   const bool failed = abort_flag != 0;
   float* stage_out = reinterpret_cast<float*>(smem + kPvOffV);      // [8 heads][D] for the NVFP4 output path
-  if (warp < kPvSoft) {
+  if (warp < 4) {
 #pragma unroll
     for (int hf = 0; hf < PC::kHalves; ++hf) {
       if (hf > 0) {
