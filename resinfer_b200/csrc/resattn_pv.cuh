@@ -498,6 +498,11 @@ __global__ void __launch_bounds__(PvCfg<D>::kThreads, PvCfg<D>::kCtasPerSm) resa
         c1 = *reinterpret_cast<const uint4*>(row + (((2 * dblk + 1) ^ sw) << 4));
         sfw = *reinterpret_cast<const uint32_t*>(st + C::kOffVsf + tok * C::kSfPerRow + dblk * 4);
       }
+      // The codes and scales are in registers: give the stage back before converting, so that its
+      // refill (about 2600 cycles of memory latency) starts a conversion earlier.  (The arrive is a
+      // release; __syncwarp orders the other lanes' loads before it.)
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_empty[stg]));
       const uint32_t words[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};   // 8 codes (= 8 d) per word
       // the four block scales of this thread's 64 values as FP16 pairs (s, s)
       uint32_t sc2[4];
@@ -528,7 +533,6 @@ __global__ void __launch_bounds__(PvCfg<D>::kThreads, PvCfg<D>::kCtasPerSm) resa
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(smem_u32(&bar_vpready[vb]));
-        mbar_arrive(smem_u32(&bar_empty[stg]));                // the V codes of the stage have been read
         if (cv == 0) attn_event(p, 5, i);
       }
     }
