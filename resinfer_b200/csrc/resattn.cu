@@ -2,11 +2,13 @@
 //
 // The query is quantised in the CTA prologue to NVFP4 plus an NVFP4 residue with the arithmetic of
 // the grouped-Q quantiser (bit-identical codes); the scores of both are added, so the K cache is read
-// once and nothing but the 4-bit KV codes and their E4M3 block scales crosses HBM.  The kernel below
-// computes the scores on the block-scaled FP4 tensor cores (tcgen05) and the P.V product on mma.sync
-// with an online softmax (lazy rescale: only when a row maximum moves by more than 2^8, row sums in
-// unrounded FP32).  KV splits write (o, l, m) partials that a second kernel merges in split order
-// (deterministic).
+// once and nothing but the 4-bit KV codes and their E4M3 block scales crosses HBM.  Both kernels compute
+// the scores on the block-scaled FP4 tensor cores (tcgen05) with an online softmax (lazy rescale: only
+// when a row maximum moves by more than 2^8, row sums in unrounded FP32).  resattn_pv_kernel
+// (resattn_pv.cuh, the one that runs) also does P.V on tcgen05, with V expanded to an FP16 operand tile in
+// shared memory; resattn_tc_kernel below does P.V on mma.sync with V expanded in registers and is kept for
+// comparisons (RI_ATTN_PV=0).  KV splits write (o, l, m) partials that a second kernel merges in split
+// order (deterministic).
 //
 // Stands in for the reference's CuTeDSL decode kernel and its reducers (ShawRong/ResInfer
 // csrc/resattn/kernel_paged_decode.py:722-2433, 2729-2861).

@@ -344,7 +344,7 @@ __global__ void __launch_bounds__(PvCfg<D>::kThreads, PvCfg<D>::kCtasPerSm) resa
   } else if (warp == kPvMmaWarp) {
     // ============================================================ MMA issuer
     // One thread issues everything, the scores of tile i+1 before the P.V of tile i.  (Two issuing
-    // warps measured slower, and with one the commit behind s_full(i) also covers the P.V of tile i-2.)
+    // warps measured 4-7 % slower, twice, and with one the commit behind s_full(i) also covers the P.V of tile i-2.)
     const uint32_t idesc_qk = (1u << 7) | (1u << 10) | (uint32_t(16 >> 3) << 17) | (uint32_t(kTile >> 4) << 24);
     // kind::f16: FP32 accumulate (bits 4-5 = 1), FP16 x FP16, A M-major (bit 15), B K-major, N = 16, M = 128
     const uint32_t idesc_pv = (1u << 4) | (1u << 15) | (uint32_t(16 >> 3) << 17) | (uint32_t(128 >> 4) << 24);
@@ -379,14 +379,11 @@ __global__ void __launch_bounds__(PvCfg<D>::kThreads, PvCfg<D>::kCtasPerSm) resa
       __syncwarp();
       if (lane == 0) attn_event(p, 6, i);
     };
-    if (my_tiles > 0) issue_qk(0);
-    for (int i = 0; i < my_tiles && alive; ++i) {
+    auto issue_pv = [&](int i) -> bool {
       const int vb = i & 1;
-      if (i + 1 < my_tiles) issue_qk(i + 1);
-      if (!alive) break;
       bool got = true;
       if (lane == 0) got = mbar_wait(smem_u32(&bar_vpready[vb]), (i >> 1) & 1, &abort_flag, 9);
-      if (!__all_sync(0xffffffffu, got)) break;
+      if (!__all_sync(0xffffffffu, got)) return false;
       if (lane == 0) attn_event(p, 7, i);
       tc_fence_after();
       if (elect_one()) {
@@ -406,6 +403,12 @@ __global__ void __launch_bounds__(PvCfg<D>::kThreads, PvCfg<D>::kCtasPerSm) resa
       }
       __syncwarp();
       if (lane == 0) attn_event(p, 8, i);
+      return true;
+    };
+    if (my_tiles > 0) issue_qk(0);
+    for (int i = 0; i < my_tiles && alive; ++i) {
+      if (i + 1 < my_tiles) issue_qk(i + 1);
+      if (!alive || !issue_pv(i)) break;
     }
   } else if (warp < kPvFirstConv) {
     // ============================================================ copy producers (as in resattn_tc_kernel)
