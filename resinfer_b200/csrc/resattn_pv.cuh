@@ -26,7 +26,6 @@
 // issued instructions (measured: 1.6 -> 2.5 TB/s from this change alone).  Every mbarrier wait is
 // bounded; the decision slot makes all warps of a role leave their loop together on expiry.
 
-constexpr int kPvProd = 4;
 // O^T accumulators: the eight P.V MMAs of a tile (16 tokens each) add into eight different accumulators,
 // 16 columns apart, which are summed at the end (head_dim 256: two sets, one per 128 output rows)
 constexpr int kPvColO = 128;
@@ -55,11 +54,15 @@ constexpr int kPvOffV = 11264;                    // [D/64 d-blocks][128 tokens]
 #ifndef RI_PV_SOFT
 #define RI_PV_SOFT 8
 #endif
+#ifndef RI_PV_PROD
+#define RI_PV_PROD 4
+#endif
 // head_dim 128: two CTAs of 17 warps per SM; head_dim 256: one CTA of 25 warps (the FP16 V tile is 64 KB)
 template <int D>
 struct PvCfg {
   static constexpr int kSoft = D == 128 ? RI_PV_SOFT : RI_PV256_SOFT;          // softmax warps: 4 (8 heads per thread) or 8 (4 heads)
   static constexpr int kHpt = 32 / kSoft;                             // heads a softmax thread handles
+  static constexpr int kProd = D == 128 ? RI_PV_PROD : 4;             // copy producer warps, 128 / kProd rows of a tile each
   static constexpr int kConv = D == 128 ? 8 : 16;                     // conversion warps
   static constexpr int kVBufs = D == 128 ? RI_PV_VBUFS : RI_PV256_VBUFS;        // FP16 V tiles in flight
   static constexpr int kStages = D == 128 ? RI_PV_STAGES : RI_PV256_STAGES;     // cp.async pipeline stages
@@ -74,7 +77,7 @@ struct PvCfg {
   static constexpr int kVStride = kVBytes;
   static constexpr int kHeaderBytes = kPvOffV + kVBufs * kVBytes;      // a multiple of 1024
 #endif
-  static constexpr int kThreads = (kSoft + 1 + kPvProd + kConv) * 32;
+  static constexpr int kThreads = (kSoft + 1 + kProd + kConv) * 32;
   static constexpr int kTmemCols = D == 128 ? 256 : 512;
   static constexpr int kSmemBytes = kHeaderBytes + kStages * TCfg<D>::kStageBytes + 1024;
 };
@@ -113,7 +116,7 @@ __global__ void __launch_bounds__(PvCfg<D>::kThreads, PvCfg<D>::kCtasPerSm) resa
   using PC = PvCfg<D>;
   constexpr int kPvConv = PC::kConv, kPvVBufs = PC::kVBufs, kPvStages = PC::kStages, kThreadsPv = PC::kThreads;
   constexpr int kPvTmemCols = PC::kTmemCols, kPvVStride = PC::kVStride, kPvHeaderBytes = PC::kHeaderBytes;
-  constexpr int kPvSoft = PC::kSoft, kHpt = PC::kHpt;
+  constexpr int kPvSoft = PC::kSoft, kHpt = PC::kHpt, kPvProd = PC::kProd;
   constexpr int kPvMmaWarp = kPvSoft, kPvFirstProd = kPvSoft + 1, kPvFirstConv = kPvFirstProd + kPvProd;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[kPvStages];
@@ -414,24 +417,25 @@ __global__ void __launch_bounds__(PvCfg<D>::kThreads, PvCfg<D>::kCtasPerSm) resa
     // ============================================================ copy producers (as in resattn_tc_kernel)
     constexpr int kCpr = C::kRowBytes / 16;
     constexpr int kRowsPerIt = 32 / kCpr;
-    constexpr int kIters = 32 / kRowsPerIt;
+    constexpr int kRowsW = kTile / kPvProd;                    // rows of a tile per producer warp (32 or 16)
+    constexpr int kIters = kRowsW / kRowsPerIt;
     const int pw = warp - kPvFirstProd;
     const int r_lane = lane / kCpr, chn = lane % kCpr;
     const int sf_row = D == 128 ? 2 * lane : lane;             // first row of this lane's 16 scale bytes
-    const bool sf_lane = D == 128 ? lane < 16 : true;
+    const bool sf_lane = D == 128 ? lane < kRowsW / 2 : lane < kRowsW;
     uint32_t k_dst[kIters];
 #pragma unroll
-    for (int it = 0; it < kIters; ++it) k_dst[it] = swz_off<D>(32 * pw + it * kRowsPerIt + r_lane, chn * 16);
-    const uint32_t sf_dst = (32 * pw + sf_row) * C::kSfPerRow;
+    for (int it = 0; it < kIters; ++it) k_dst[it] = swz_off<D>(kRowsW * pw + it * kRowsPerIt + r_lane, chn * 16);
+    const uint32_t sf_dst = (kRowsW * pw + sf_row) * C::kSfPerRow;
     auto lookup = [&](int i) -> int {
-      if (lane >= 2 || i >= my_tiles) return 0;
-      const int t0 = (t_begin + i) * kTile + 32 * pw + lane * 16;
+      if (lane >= kRowsW / 16 || i >= my_tiles) return 0;
+      const int t0 = (t_begin + i) * kTile + kRowsW * pw + lane * 16;
       return t0 < L ? __ldg(bt + (p.page_shift >= 0 ? t0 >> p.page_shift : t0 / p.page_size)) : 0;
     };
     int page_next = lookup(0);
     for (int i = 0, stg = 0, ph = 0; i < my_tiles; ++i, stg = (stg + 1 == S ? 0 : stg + 1), ph ^= (stg == 0)) {
-      const int tok0 = (t_begin + i) * kTile + 32 * pw;
-      const int rows = min(max(((L - tok0) + 15) & ~15, 0), 32);
+      const int tok0 = (t_begin + i) * kTile + kRowsW * pw;
+      const int rows = min(max(((L - tok0) + 15) & ~15, 0), kRowsW);
       int64_t page = page_next;
       page_next = lookup(i + 1);
       page = page < 0 ? 0 : (page >= p.num_pages ? p.num_pages - 1 : page);
@@ -441,7 +445,7 @@ __global__ void __launch_bounds__(PvCfg<D>::kThreads, PvCfg<D>::kCtasPerSm) resa
       const int64_t base0 = __shfl_sync(0xffffffffu, base_row, 0), base1 = __shfl_sync(0xffffffffu, base_row, 1);
       if (i >= S) {                                            // one lane polls, the four warps meet on a named barrier
         if (pw == 0 && lane == 0) prod_go[i & 1] = mbar_wait(smem_u32(&bar_empty[stg]), ph ^ 1, &abort_flag, 4) ? 1 : 0;
-        asm volatile("bar.sync 4, 128;" ::: "memory");
+        asm volatile("bar.sync 4, %0;" ::"n"(kPvProd * 32) : "memory");
         if (!prod_go[i & 1]) break;
       }
       const uint32_t st = smem_u32(stage0 + stg * C::kStageBytes);
@@ -461,9 +465,10 @@ __global__ void __launch_bounds__(PvCfg<D>::kThreads, PvCfg<D>::kCtasPerSm) resa
         const int64_t br = (sf_row < 16 ? base0 : base1) + (sf_row & 15);
         cp_async16(st + C::kOffVsf + sf_dst, p.v_sf + br * C::kSfPerRow);
       }
-      if (lane < rows) {                                       // K scales of token 32 pw + lane, 4 bytes per MMA
+      if (lane < rows) {                                       // K scales of token kRowsW pw + lane, 4 bytes per MMA
         const uint8_t* src = p.k_sf + ((lane < 16 ? base0 : base1) + (lane & 15)) * C::kSfPerRow;
-        const uint32_t dst = st + C::kOffKsf + lane * 16 + pw * 4;
+        const int tk = kRowsW * pw + lane;
+        const uint32_t dst = st + C::kOffKsf + (tk & 31) * 16 + (tk >> 5) * 4;
 #pragma unroll
         for (int j = 0; j < C::kMma; ++j)
           asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 512 * j), "l"(src + 4 * j) : "memory");
