@@ -208,3 +208,31 @@ def test_decode_nvfp4_output(cuda_device, device_rcp, lens, splits):
         run_paged_fp4_decode_qmul4_tmem_nvfp4(t(q_np).to(torch.bfloat16), pool, pool.v_data, pool.v_sf,
                                               t(np.maximum(kv["block_tables"], 0)), t(kv["seq_lens"]), 0.1,
                                               torch.ones(2, device=cuda_device), out=out_b, output_block_scale=sf_b)
+
+
+@pytest.mark.parametrize("d,splits", [(128, 1), (128, 2), (256, 1), (256, 3)])
+def test_decode_late_maxima_rescale_accumulators(cuda_device, device_rcp, d, splits):
+    """Scores that grow along the sequence: the K block scales of later 128-token tiles are raised by a
+    few E4M3 exponent steps, so the running maximum of every head moves by far more than the lazy
+    threshold (2^8) on several tiles after the first one and the accumulated P.V has to be rescaled in
+    place each time.  Checked against the oracle like every other case."""
+    page, hkv, g = 16, 2, 8
+    lens = [1500, 700]
+    kv = O.make_paged_kv(lens, hkv, d, page, seed=11)
+    ks = kv["k_sf"].copy()
+    for b, L in enumerate(lens):
+        for t in range(L):
+            bump = (t // 128) // 2                           # 0, 0, 1, 1, 2, 2, ... exponent steps of 2 each
+            if bump:
+                pg = kv["block_tables"][b, t // page]
+                row = ks[pg, :, t % page, :].astype(np.int32)
+                ks[pg, :, t % page, :] = np.minimum(row + 16 * bump, 0x7E).astype(np.uint8)   # E4M3: +16 = x4
+    kv["k_sf"] = ks
+    b, hq = len(lens), hkv * g
+    q_np = O.bf16_round((4.0 * np.random.default_rng(5).standard_normal((b, hq, d))).astype(np.float32))
+    sm = d ** -0.5
+    ref = O.resattn_decode_reference(q_np, kv, sm, rcp=O.RecordingRcp(device_rcp))
+    out32, _, _ = _run(cuda_device, kv, q_np, sm, splits)
+    got = out32.cpu().numpy()
+    assert np.isfinite(got).all()
+    assert rel_fro(got, ref) < TOL_BF16
