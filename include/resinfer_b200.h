@@ -152,6 +152,27 @@ int ri_fp4_gemm_static_scratch(const uint8_t* act, int64_t act_row_bytes, const 
                                int fmt, int layout, int splits, int32_t* status, int enable_pdl,
                                void* stream);
 
+/* One-shot all-reduce (sum) of a small BF16 tensor over peer memory, for the partial outputs of row-parallel
+ * linears in a tensor-parallel decode step on one node.  Stands where the reference relies on vLLM's
+ * RowParallelLinear all-reduce after its rank-local linear (quant/vllm_integration/linear/
+ * nvfp4_linear_adapter.py:120-176 returns the partial).
+ *   rank_data[r]   this process's mapping of rank r's partial (`numel` BF16 values, 16-byte aligned; for
+ *                  r == rank the local buffer itself); the partial must have been written by earlier work on
+ *                  `stream`
+ *   rank_flags[r]  this process's mapping of rank r's flag array (ri_peer_allreduce_flag_bytes() bytes,
+ *                  zeroed once before the first call, owned by this library afterwards)
+ *   state          local device memory, ri_peer_allreduce_state_bytes() bytes, zeroed once
+ *   out            local result, `numel` BF16 values, 16-byte aligned, not one of the mapped partials
+ * Every rank of the group must make the same sequence of calls.  A rank's partial buffer may be
+ * overwritten again after its NEXT call of this function has completed (alternate between two
+ * buffers).  The wait for the peers is bounded (about a second); on expiry `status` receives
+ * 0x40000000 | missing_rank << 8 | rank and the output is not written.  The sum is taken in rank
+ * order with FP32 accumulation, so every rank holds the same bits. */
+int64_t ri_peer_allreduce_flag_bytes(void);
+int64_t ri_peer_allreduce_state_bytes(void);
+int ri_peer_allreduce_bf16(const void* const* rank_data, void* const* rank_flags, int rank, int world,
+                           int64_t numel, void* out, void* state, int32_t* status, void* stream);
+
 /* Debugging aid: when set to a device buffer of 8 * (number of SMs) int64, every CTA of the next
  * ri_fp4_gemm launches stores nanosecond time stamps of its phases there (NULL switches it off). */
 void ri_fp4_gemm_set_trace(int64_t* device_buffer);

@@ -42,6 +42,9 @@ SIGNATURES = {
     "ri_resattn_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _vp, _i, _i, _i, _i, _i, _i, _f, _f,
                                _vp, _i, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i, _vp, _i64, _i, _vp, _vp]),
     "ri_resattn_workspace_bytes": (_i64, [_i, _i, _i, _i]),
+    "ri_peer_allreduce_flag_bytes": (_i64, []),
+    "ri_peer_allreduce_state_bytes": (_i64, []),
+    "ri_peer_allreduce_bf16": (_i, [_vp, _vp, _i, _i, _i64, _vp, _vp, _vp, _vp]),
     "ri_rcp_approx": (_i, [_vp, _vp, _i, _vp]),
 }
 

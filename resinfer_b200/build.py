@@ -23,7 +23,7 @@ INCLUDE = PKG.parent / "include"
 OUT_DIR = PKG / "_lib"
 LIB = OUT_DIR / "libresinfer_b200.so"
 
-SOURCES = ["api.cu", "quant_nvfp4.cu", "quant_mxfp4.cu", "gemm_fp4.cu", "gemm_static_scratch.cu", "resattn.cu"]
+SOURCES = ["api.cu", "quant_nvfp4.cu", "quant_mxfp4.cu", "gemm_fp4.cu", "gemm_static_scratch.cu", "resattn.cu", "peer_allreduce.cu"]
 
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-lineinfo",

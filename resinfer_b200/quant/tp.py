@@ -64,3 +64,96 @@ def finish_output(y: torch.Tensor, parallel: str, group=None, gather: bool = Fal
         dist.all_gather(parts, y.contiguous(), group=group)
         return torch.cat(parts, dim=-1)
     return y
+
+
+class PeerAllReduce:
+    """One-shot all-reduce of small BF16 partials over peer memory (``ri_peer_allreduce_bf16``).
+
+    Every rank allocates ``slots`` partial buffers of ``max_numel`` BF16 values and a flag array in one
+    device allocation, exports it to the other ranks of the node through CUDA IPC (handles travel over the
+    process group as Python objects) and maps theirs.  ``partial(shape)`` hands out the next buffer as a
+    tensor for the GEMM to write into; ``reduce(partial, out)`` sums the same slot of every rank into
+    ``out``.  Buffers are used round-robin; with two or more slots a buffer is only written again after
+    this rank's next reduce has completed, which is what the kernel's contract asks for.
+
+    All ranks must call ``partial`` / ``reduce`` in the same order.  Raises RuntimeError if peer mapping is
+    not possible (ranks on different nodes, IPC disabled); callers then stay with NCCL."""
+
+    def __init__(self, max_numel: int, group=None, slots: int = 2, device=None):
+        from .. import _cabi
+        if not (dist.is_available() and dist.is_initialized()):
+            raise RuntimeError("PeerAllReduce needs an initialised process group")
+        if slots < 2:
+            raise ValueError("at least two partial buffers are needed (a buffer must outlive the next reduce)")
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if not 2 <= self.world <= 8:
+            raise RuntimeError(f"PeerAllReduce supports 2..8 ranks, got {self.world}")
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.lib = _cabi.load()
+        self.max_numel = (int(max_numel) + 7) // 8 * 8
+        self.slots = slots
+        self.slot_bytes = (2 * self.max_numel + 255) // 256 * 256
+        flag_bytes = int(self.lib.ri_peer_allreduce_flag_bytes())
+        self.flag_off = self.slots * self.slot_bytes
+        total = self.flag_off + (flag_bytes + 255) // 256 * 256
+        # a private allocation (not a slice of a cached block that other tensors share)
+        self.local = torch.zeros(total, dtype=torch.uint8, device=self.device)
+        self.state = torch.zeros(int(self.lib.ri_peer_allreduce_state_bytes()), dtype=torch.uint8, device=self.device)
+        torch.cuda.synchronize(self.device)
+        handle = self.local.untyped_storage()._share_cuda_()
+        handles = [None] * self.world
+        dist.all_gather_object(handles, handle, group=group)
+        self._peer_storages = []
+        self.bases = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                self.bases.append(self.local.data_ptr())
+                continue
+            try:
+                with torch.cuda.device(self.device):
+                    st = torch.UntypedStorage._new_shared_cuda(self.device.index, *h[1:])
+            except Exception as e:                            # not on this node, no peer access, IPC refused
+                raise RuntimeError(f"cannot map the buffer of rank {r}: {type(e).__name__}: {e}") from e
+            self._peer_storages.append(st)
+            self.bases.append(st.data_ptr())
+        import ctypes
+        self._ct = ctypes
+        self._flag_ptrs = (ctypes.c_void_p * self.world)(*[b + self.flag_off for b in self.bases])
+        self._data_ptrs = [(ctypes.c_void_p * self.world)(*[b + s * self.slot_bytes for b in self.bases])
+                           for s in range(self.slots)]
+        self._next = 0
+        dist.barrier(group=group)                              # every rank has mapped every buffer
+
+    def partial(self, shape, dtype=torch.bfloat16) -> torch.Tensor:
+        """The next partial buffer of this rank as a tensor of ``shape`` (row-major, BF16)."""
+        if dtype != torch.bfloat16:
+            raise ValueError("PeerAllReduce sums BF16 partials")
+        n = 1
+        for s in shape:
+            n *= int(s)
+        if n > self.max_numel or n % 8:
+            raise ValueError(f"{n} elements: at most {self.max_numel}, a multiple of 8")
+        slot = self._next
+        self._next = (self._next + 1) % self.slots
+        off = slot * self.slot_bytes
+        t = self.local[off:off + 2 * n].view(torch.bfloat16).view(*shape)
+        t._ri_slot = slot
+        return t
+
+    def reduce(self, partial: torch.Tensor, out: torch.Tensor | None = None, status: torch.Tensor | None = None) -> torch.Tensor:
+        """Sum ``partial`` (a tensor from ``partial()``) over the ranks into ``out`` (local BF16, same shape)."""
+        from .. import _cabi
+        slot = getattr(partial, "_ri_slot", None)
+        if slot is None:
+            raise ValueError("reduce() takes a tensor handed out by partial()")
+        if out is None:
+            out = torch.empty(partial.shape, dtype=torch.bfloat16, device=self.device)
+        if out.dtype != torch.bfloat16 or out.numel() != partial.numel() or not out.is_contiguous():
+            raise ValueError("out must be a contiguous BF16 tensor of the partial's size")
+        st = self.lib.ri_peer_allreduce_bf16(self._data_ptrs[slot], self._flag_ptrs, self.rank, self.world,
+                                             partial.numel(), out.data_ptr(), self.state.data_ptr(),
+                                             0 if status is None else status.data_ptr(),
+                                             _cabi.current_stream(self.device))
+        _cabi.check(st, "peer all-reduce")
+        return out
