@@ -270,6 +270,9 @@ def main():
     ap.add_argument("--no-detail", action="store_true", help="skip the per-case and ResAttn detail measurements")
     ap.add_argument("--format", default="nvfp4", choices=["nvfp4", "mxfp4"],
                     help="number format of the headline sweep (BASELINE configs[1] = nvfp4, configs[2] = mxfp4)")
+    ap.add_argument("--allreduce", choices=("peer", "nccl"), default="peer",
+                    help="N > 1: how the row-parallel partials are summed (this library's one-shot all-reduce over "
+                         "peer memory, or NCCL)")
     ap.add_argument("--sweeps", action="store_true",
                     help="measure the other sweeps of the three hot paths (MXFP4 MEXT, KEXT, ResAttn batch sizes) "
                          "and print them as a second JSON line {\"sweeps\": ...}; N = 1 only")
@@ -327,6 +330,30 @@ def main():
         from resinfer_b200.nvfp4 import mxfp4
     outs = {(L.name, m): torch.empty(m, L.n, dtype=torch.bfloat16, device=dev) for L in layers for m in MS}
     launches = {"n": 0}
+    # N > 1: the partial outputs of the row-parallel layers are summed by this library's one-shot all-reduce
+    # over peer memory (a kernel per rank, plain NVLink loads); NCCL if the peers cannot be mapped or
+    # --allreduce nccl is given.  The GEMM writes its partial straight into the exported buffer.
+    peer_ar = None
+    if tp > 1 and args.allreduce == "peer":
+        try:
+            from resinfer_b200.quant.tp import PeerAllReduce
+            peer_ar = PeerAllReduce(max(MS) * max(L.n for L in layers if L.par == "row"), slots=2)
+        except Exception as e:
+            note(f"peer all-reduce unavailable ({type(e).__name__}: {e}); using NCCL")
+    ar_status = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def gemm_out(L, m, reduce):
+        if peer_ar is not None and L.par == "row" and reduce:
+            return peer_ar.partial((m, L.n))
+        return outs[(L.name, m)]
+
+    def finish(L, m, y, reduce):
+        if tp > 1 and L.par == "row" and reduce:
+            if peer_ar is not None:
+                launches["n"] += 1
+                return peer_ar.reduce(y, outs[(L.name, m)], status=ar_status)
+            dist.all_reduce(y)
+        return y
 
     def run_case(L, m, quant=True, pre=None, reduce=True):
         c = L.next_copy()
@@ -339,11 +366,9 @@ def main():
         else:
             codes, sf = pre
         y = ops.fp4_gemm(codes, sf, L.w[c], L.w_sf[c], None if mx else L.alpha[m], m=m, fmt=args.format,
-                         layout="row_pair", out=outs[(L.name, m)])
+                         layout="row_pair", out=gemm_out(L, m, reduce))
         launches["n"] += 1
-        if tp > 1 and L.par == "row" and reduce:
-            dist.all_reduce(y)
-        return y
+        return finish(L, m, y, reduce)
 
     def sweep(quant=True, pre=None, reduce=True):
         for m in MS:
@@ -449,7 +474,12 @@ def main():
                         y = torch.ops.residue.nvfp4_linear(xd, L.w[c], L.gs_inv[m], L.w_sf[c], L.w_sf[c], zero_mask,
                                                            L.alpha[m], L.k, 0, 0, L.n, True, False, True)
                     if tp > 1 and L.par == "row":
-                        dist.all_reduce(y)
+                        if peer_ar is not None:             # the op's output is copied into the exported buffer first
+                            pbuf = peer_ar.partial(tuple(y.shape))
+                            pbuf.copy_(y)
+                            y = peer_ar.reduce(pbuf, status=ar_status)
+                        else:
+                            dist.all_reduce(y)
                     done[i].record()
                     out_stream.wait_event(done[i])
                     with torch.cuda.stream(out_stream):
@@ -568,7 +598,11 @@ def main():
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": False,
             "scaling": "strong", "vs_baseline": None,
             "dtype": ("mxfp4 (E2M1 x E8M0 block scales)" if mx else "nvfp4 (E2M1 x E4M3 block scales)") + ", fp32 accumulate",
-            "data": "synthetic", "config": workload_config(world, args.format), "clocks": clk.summary(), "gpu_launches": per_step_launches * args.steps,
+            "data": "synthetic",
+            "config": dict(workload_config(world, args.format),
+                           **({"allreduce": "one-shot over peer memory (ri_peer_allreduce_bf16)" if peer_ar is not None
+                               else "NCCL"} if tp > 1 else {})),
+            "clocks": clk.summary(), "gpu_launches": per_step_launches * args.steps,
             "tflops": flops / (ms_step * 1e-3) / 1e12, "fp4_peak_frac": flops / (ms_step * 1e-3) / 9.0e15,
             "hbm_gbs_algorithmic": sum(mext_bytes(m, L.k_full, L.n_full) for L in layers for m in MS) / (ms_step * 1e-3) / 1e9,
             "e2e": e2e, "roofline": roofline, "cpu_baseline": cpu, "detail": detail,
