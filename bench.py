@@ -602,7 +602,8 @@ def main():
             "config": dict(workload_config(world, args.format),
                            **({"allreduce": "one-shot over peer memory (ri_peer_allreduce_bf16)" if peer_ar is not None
                                else "NCCL"} if tp > 1 else {})),
-            "clocks": clk.summary(), "gpu_launches": per_step_launches * args.steps,
+            "clocks": clk.summary(),
+            **({"allreduce_status": int(ar_status.item())} if tp > 1 else {}), "gpu_launches": per_step_launches * args.steps,
             "tflops": flops / (ms_step * 1e-3) / 1e12, "fp4_peak_frac": flops / (ms_step * 1e-3) / 9.0e15,
             "hbm_gbs_algorithmic": sum(mext_bytes(m, L.k_full, L.n_full) for L in layers for m in MS) / (ms_step * 1e-3) / 1e9,
             "e2e": e2e, "roofline": roofline, "cpu_baseline": cpu, "detail": detail,
