@@ -504,7 +504,7 @@ def main():
         reps = max(3, min(args.steps, 10))
         eager_us = wall_us(e2e_sweep, reps)
         e2e_us, how = eager_us, "eager"
-        if tp == 1:
+        if tp == 1 or peer_ar is not None:                  # (NCCL collectives stay out of this graph)
             # The way a serving stack drives decode: the whole sweep (every H2D copy of x from pinned memory,
             # every call of the public op, every D2H copy of y on a second stream) captured once in a CUDA
             # graph and replayed per step; the wall clock covers replay + synchronize.
@@ -536,6 +536,10 @@ def main():
                         else:
                             y = torch.ops.residue.nvfp4_linear(xd, L.w[c], L.gs_inv[m], L.w_sf[c], L.w_sf[c], zero_mask,
                                                                L.alpha[m], L.k, 0, 0, L.n, True, False, True)
+                        if tp > 1 and L.par == "row":
+                            pbuf = peer_ar.partial(tuple(y.shape))
+                            pbuf.copy_(y)
+                            y = peer_ar.reduce(pbuf, status=ar_status)
                         side.wait_stream(cur)
                         with torch.cuda.stream(side):
                             hy[(L.name, m)].copy_(y, non_blocking=True)
@@ -551,8 +555,15 @@ def main():
                     replay()
                     torch.cuda.synchronize()
                 ref_y = {k: v.clone() for k, v in hy.items()}      # eager results, for a sanity check
+                if world > 1:                               # the peers' kernels wait for each other (bounded): start together
+                    torch.cuda.synchronize()
+                    dist.barrier()
                 graphed_step()
                 same = all(torch.equal(ref_y[k], hy[k]) for k in hy)
+                if world > 1:                               # one decision for all ranks
+                    flag = torch.tensor([1 if same else 0], device=dev)
+                    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+                    same = bool(flag.item())
                 if same:
                     e2e_us, how = wall_us(graphed_step, reps), "graph"
                 elif rank == 0:
