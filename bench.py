@@ -375,6 +375,33 @@ def main():
             for L in layers:
                 run_case(L, m, quant, None if pre is None else pre[(L.name, m)], reduce)
 
+    if peer_ar is not None:
+        # self-check before anything is timed: one eager sweep against NCCL on the same partials; any rank
+        # that sees a time-out status or a different sum sends every rank back to NCCL
+        torch.cuda.synchronize()
+        dist.barrier()
+        sweep()
+        bad = int(ar_status.item()) != 0
+        for L in layers:
+            if L.par == "row" and not bad:
+                m = MS[-1]
+                part = run_case(L, m, reduce=False).clone()
+                want = part.float()
+                dist.all_reduce(want)
+                pbuf = peer_ar.partial((m, L.n))
+                pbuf.copy_(part)
+                got = peer_ar.reduce(pbuf, status=ar_status)
+                pbuf2 = peer_ar.partial((m, L.n))            # keep the buffers alternating in pairs
+                pbuf2.copy_(part)
+                peer_ar.reduce(pbuf2, status=ar_status)
+                torch.cuda.synchronize()
+                bad = bad or int(ar_status.item()) != 0 or not torch.allclose(got.float(), want, rtol=2e-2, atol=1e-2)
+        flag = torch.tensor([1 if bad else 0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+        if int(flag.item()):
+            note("peer all-reduce failed its self-check; using NCCL")
+            peer_ar = None
+            ar_status.zero_()
     graphs = []
 
     def capture(fn):
