@@ -5,11 +5,12 @@
 
 Workload (N = 1): the NVFP4 MEXT sweep over the four Qwen3-32B-shaped projections
 (K->N: qkv 5120->10240, o 8192->5120, gate_up 5120->51200, down 25600->5120) and tokens
-M in {1,2,4,8,16,32,64,128}.  One *step* is one pass over all 32 (shape, M) cases; each case is
-two kernels of this library (quantiser, GEMM).  The step is captured in a CUDA graph (the
-reference measures under CUDA graphs as well) and timed with CUDA events on the launching
-stream.  Successive cases stream different weights (274 MB per pass over the four shapes, more
-than the 126 MB L2), so every weight read comes from HBM.
+M in {1,2,4,8,16,32,64,128}.  One pass over all 32 (shape, M) cases is captured in a CUDA graph (the
+reference measures under CUDA graphs as well); each case is two kernels of this library (quantiser,
+GEMM).  One *step* replays that graph SWEEPS_PER_STEP times, so that the timed region of the default
+run lasts about half a second, and is timed with CUDA events on the launching stream.  Successive
+cases stream different weights (274 MB per pass over the four shapes, more than the 126 MB L2), so
+every weight read comes from HBM.
 
 Printed JSON (one line, rank 0):
   value / ms_per_step   mean microseconds per linear op over the sweep (lower is better)
@@ -43,6 +44,8 @@ SHAPES = [("qkv", 5120, 10240, "col"), ("o", 8192, 5120, "row"), ("gate_up", 512
           ("down", 25600, 5120, "row")]
 MS = [1, 2, 4, 8, 16, 32, 64, 128]
 L2_BYTES = 126 * 1024 * 1024
+SWEEPS_PER_STEP = 40                 # replays of the 32-case sweep graph per step
+CPU_MS = (1, 16, 128)                # token counts the CPU arm runs (4 shapes each)
 # DRAM traffic of the GEMM kernel / its algorithmic bytes, from one ncu capture per shape (see roofline.traffic_source)
 NCU_TRAFFIC_RATIO = 289.49 / 277.36
 
@@ -144,41 +147,39 @@ _CPU_INPUTS = {}
 FORMAT = "nvfp4"                     # set by --format
 
 
-def cpu_eager_step(m: int = 16):
+def cpu_eager_step(ms=CPU_MS):
     """One bounded CPU step of the metric: the eager quantise/dequantise/matmul path (oracle port of the
-    reference's ResidueQuantLinear._forward_residue_qdq) for the four sweep shapes at one M on all host
-    threads.  Returns the mean microseconds per linear op and the thread count.  The CPU time hardly
-    depends on M (the weight is re-quantised on every call, as in the reference's eager path), so 4 of the
-    32 cases stand for the sweep."""
+    reference's ResidueQuantLinear._forward_residue_qdq) for the four sweep shapes at the token counts
+    `ms` on all host threads.  Returns the mean microseconds per linear op and the thread count.  The CPU
+    time hardly depends on M (the weight is re-quantised on every call, as in the reference's eager path),
+    so 12 of the 32 cases (M = 1, 16, 128) stand for the sweep."""
     import torch
     import oracle
     cores = len(os.sched_getaffinity(0))
     torch.set_num_threads(cores)
-    total = 0.0
-    for name, k, n, _ in SHAPES:
-        if (name, m) not in _CPU_INPUTS:
-            _CPU_INPUTS[(name, m)] = (torch.from_numpy(oracle.make_activation(m, k, seed=0)).to(torch.bfloat16),
-                                      torch.from_numpy(oracle.make_weight(n, k, seed=1)).to(torch.bfloat16))
-        x, w = _CPU_INPUTS[(name, m)]
-        t0 = time.perf_counter()
-        oracle.eager_residue_linear(x, w, fmt=FORMAT)
-        total += (time.perf_counter() - t0) * 1e6
-    return total / len(SHAPES), cores
+    total, n = 0.0, 0
+    for m in ms:
+        for name, k, nn, _ in SHAPES:
+            if (name, m) not in _CPU_INPUTS:
+                _CPU_INPUTS[(name, m)] = (torch.from_numpy(oracle.make_activation(m, k, seed=0)).to(torch.bfloat16),
+                                          torch.from_numpy(oracle.make_weight(nn, k, seed=1)).to(torch.bfloat16))
+            x, w = _CPU_INPUTS[(name, m)]
+            t0 = time.perf_counter()
+            oracle.eager_residue_linear(x, w, fmt=FORMAT)
+            total += (time.perf_counter() - t0) * 1e6
+            n += 1
+    return total / n, cores
 
 
-_CPU_SAMPLE = "4 of 32 sweep cases per step: qkv, o, gate_up, down at M=16, ratio 1.0"
+_CPU_SAMPLE = "12 of 32 sweep cases per step: qkv, o, gate_up, down at M in {1, 16, 128}, ratio 1.0"
 
 
-def cpu_eager_sample(repeats: int = 2):
-    """cpu_baseline of the GPU arm: one warm-up step, then the median of `repeats` steps."""
-    cpu_eager_step()
-    vals = []
-    cores = 0
-    for _ in range(repeats):
-        v, cores = cpu_eager_step()
-        vals.append(v)
-    return {"value": statistics.median(vals), "unit": "us", "cores": cores, "kind": "port",
-            "sample": _CPU_SAMPLE + f", median of {repeats} steps after one warm-up"}
+def cpu_eager_sample():
+    """cpu_baseline of the GPU arm: a warm-up over the four shapes at M = 16, then one step (12 cases)."""
+    cpu_eager_step((16,))
+    v, cores = cpu_eager_step()
+    return {"value": v, "unit": "us", "cores": cores, "kind": "port",
+            "sample": _CPU_SAMPLE + ", one step after a warm-up pass over the four shapes"}
 
 
 def run_reference_arm(args):
@@ -188,7 +189,8 @@ def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    for _ in range(max(1, args.warmup)):
+    cpu_eager_step((16,))                                    # warm-up: thread pool, allocator, one pass over the shapes
+    for _ in range(max(0, args.warmup - 1)):
         cpu_eager_step()
     ts = []
     cores = 0
@@ -201,7 +203,7 @@ def run_reference_arm(args):
     v = statistics.mean(ts)
     line = {
         "impl": "reference", "metric": "mext_%s_linear_latency" % args.format, "value": v, "unit": "us", "n_gpus": args.gpus,
-        "steps": len(ts), "warmup": max(1, args.warmup), "ms_per_step": v * len(SHAPES) / 1e3, "higher_is_better": False,
+        "steps": len(ts), "warmup": max(1, args.warmup), "ms_per_step": v * len(SHAPES) * len(CPU_MS) / 1e3, "higher_is_better": False,
         "scaling": "strong", "vs_baseline": None,
         "dtype": ("mxfp4 (E2M1 x E8M0 block scales)" if args.format == "mxfp4" else "nvfp4 (E2M1 x E4M3 block scales)") + ", fp32 accumulate",
         "data": "synthetic", "config": workload_config(args.gpus, args.format),
@@ -214,6 +216,8 @@ def run_reference_arm(args):
 def workload_config(n_gpus, fmt="nvfp4"):
     return {"workload": "MEXT " + fmt.upper() + " sweep: qkv 5120->10240, o 8192->5120, gate_up 5120->51200, down 25600->5120; "
                         "M in {1,2,4,8,16,32,64,128}; online quantiser + folded GEMM per case",
+            "step": "%d replays of the 32-case sweep graph (GPU arm); the CPU arm runs 12 of the 32 cases per step, "
+                    "M in {1, 16, 128}" % SWEEPS_PER_STEP,
             "l2": "inputs larger than L2: 274 MB of weights stream per pass over the four shapes, rotating copies",
             "parallelism": "tp%d" % n_gpus if n_gpus > 1 else "single GPU", "cuda_graph": True}
 
@@ -269,7 +273,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-detail", action="store_true", help="skip the per-case and ResAttn detail measurements")
     ap.add_argument("--format", default="nvfp4", choices=["nvfp4", "mxfp4"],
-                    help="number format of the headline sweep (BASELINE configs[1] = nvfp4, configs[2] = mxfp4)")
+                    help="number format of the headline sweep (NVFP4 MEXT is the headline configuration, MXFP4 MEXT "
+                         "the second one)")
     ap.add_argument("--allreduce", choices=("peer", "nccl"), default="peer",
                     help="N > 1: how the row-parallel partials are summed (this library's one-shot all-reduce over "
                          "peer memory, or NCCL)")
@@ -335,6 +340,7 @@ def main():
     # --allreduce nccl is given.  The GEMM writes its partial straight into the exported buffer.
     peer_ar = None
     if tp > 1 and args.allreduce == "peer":
+        # the constructor exchanges its outcome among the ranks: it raises on all of them or on none
         try:
             from resinfer_b200.quant.tp import PeerAllReduce
             peer_ar = PeerAllReduce(max(MS) * max(L.n for L in layers if L.par == "row"), slots=2)
@@ -376,26 +382,34 @@ def main():
                 run_case(L, m, quant, None if pre is None else pre[(L.name, m)], reduce)
 
     if peer_ar is not None:
-        # self-check before anything is timed: one eager sweep against NCCL on the same partials; any rank
-        # that sees a time-out status or a different sum sends every rank back to NCCL
+        # Self-check before anything is timed: one eager sweep, then every row-parallel layer's reduction
+        # against the rank-ordered FP32 sum of the same partials (gathered with NCCL), which the kernel must
+        # reproduce bit for bit.  Every rank runs the same sequence of collectives whatever it observes; the
+        # verdicts are combined once at the end, and a failure on any rank sends all of them to NCCL.
         torch.cuda.synchronize()
         dist.barrier()
         sweep()
-        bad = int(ar_status.item()) != 0
+        bad = False
         for L in layers:
-            if L.par == "row" and not bad:
-                m = MS[-1]
-                part = run_case(L, m, reduce=False).clone()
-                want = part.float()
-                dist.all_reduce(want)
-                pbuf = peer_ar.partial((m, L.n))
-                pbuf.copy_(part)
-                got = peer_ar.reduce(pbuf, status=ar_status)
-                pbuf2 = peer_ar.partial((m, L.n))            # keep the buffers alternating in pairs
-                pbuf2.copy_(part)
-                peer_ar.reduce(pbuf2, status=ar_status)
-                torch.cuda.synchronize()
-                bad = bad or int(ar_status.item()) != 0 or not torch.allclose(got.float(), want, rtol=2e-2, atol=1e-2)
+            if L.par != "row":
+                continue
+            m = MS[-1]
+            part = run_case(L, m, reduce=False).clone()
+            parts = [torch.empty_like(part) for _ in range(tp)]
+            dist.all_gather(parts, part)
+            want = torch.zeros_like(part, dtype=torch.float32)
+            for q in parts:                                  # rank order, FP32: the kernel's own order
+                want += q.float()
+            want = want.to(torch.bfloat16)
+            pbuf = peer_ar.partial((m, L.n))
+            pbuf.copy_(part)
+            got = peer_ar.reduce(pbuf, status=ar_status)
+            pbuf2 = peer_ar.partial((m, L.n))                # keep the buffers alternating in pairs
+            pbuf2.copy_(part)
+            peer_ar.reduce(pbuf2, status=ar_status)
+            torch.cuda.synchronize()
+            bad = bad or not torch.equal(got, want)
+        bad = bad or int(ar_status.item()) != 0
         flag = torch.tensor([1 if bad else 0], device=dev)
         dist.all_reduce(flag, op=dist.ReduceOp.MAX)
         if int(flag.item()):
@@ -445,36 +459,51 @@ def main():
         return ms
 
     n_cases = len(MS) * len(layers)
+    inner = 1 if args.only else SWEEPS_PER_STEP            # sweep-graph replays per step
+
+    def step_of(replay_one):
+        def step():
+            for _ in range(inner):
+                replay_one()
+        return step
+
     # ---- headline: quantiser + GEMM over the sweep
     launches["n"] = 0
     note("capturing the sweep")
     replay = capture(lambda: sweep(True))
     note("captured; timing")
-    per_step_launches = launches["n"] // 2                  # warm-up + capture both counted
+    per_sweep_launches = launches["n"] // 2                 # warm-up + capture both counted
     with ClockSampler(local) as clk:
-        ms_step = timed(replay, args.steps, args.warmup)
+        ms_step = timed(step_of(replay), args.steps, args.warmup)
     ops.check_status(dev)
     note(f"timed: {ms_step:.3f} ms per step")
-    us_per_op = ms_step * 1e3 / n_cases
+    us_per_op = ms_step * 1e3 / (n_cases * inner)
+
+    # ---- N > 1: the same sweep without the all-reduce of the row-parallel layers, for the cost of one reduction
+    allreduce_us = None
+    if tp > 1:
+        replay_nr = capture(lambda: sweep(True, reduce=False))
+        ms_nr = timed(step_of(replay_nr), args.steps, args.warmup)
+        n_row_ops = len(MS) * sum(1 for L in layers if L.par == "row")
+        allreduce_us = (ms_step - ms_nr) * 1e3 / (inner * max(1, n_row_ops))
 
     # ---- GEMM kernel alone (pre-quantised activations) for the roofline of the dominant kernel
     pre = {(L.name, m): (mxfp4.quantize_mext(L.x[m]) if mx else
                          nvfp4.scaled_fp4_quant_mext_r1(L.x[m], L.gs_inv[m], layout_mode=1)) for L in layers for m in MS}
-    no_reduce = {"on": False}
     replay_g = capture(lambda: sweep(False, pre, reduce=False))
     hbm_gbs, peak_kind = load_peaks()
     roofline = None
     if replay_g is not None:
-        ms_gemm = timed(replay_g, args.steps, args.warmup)
+        ms_gemm = timed(step_of(replay_g), args.steps, args.warmup) / inner     # one sweep of GEMM launches
         gbytes = sum(gemm_bytes(m, L.k, L.n) for L in layers for m in MS) / n_cases
         achieved = gbytes / (ms_gemm * 1e-3 / n_cases) / 1e9
-        roofline = {"kernel": "fp4_gemm_kernel (tcgen05 block-scaled, 32 launches per step"
+        roofline = {"kernel": "fp4_gemm_kernel (tcgen05 block-scaled, %d launches per step" % (n_cases * inner)
                               + (", this rank's shard, no all-reduce)" if tp > 1 else ")"), "bound": "hbm",
                     "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs,
                     "peak_source": peak_kind, "traffic": gbytes * NCU_TRAFFIC_RATIO,
-                    "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of the four shapes at M=16 "
-                                      "(289.5 MB against 277.4 MB algorithmic), scaled to the sweep's mean launch; "
-                                      "profiles/fp4_gemm_kernel_m16_four_shapes.md",
+                    "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of single launches of the four "
+                                      "shapes at M=16 (the weights dominate at every M <= 128, so traffic grows in "
+                                      "proportion), scaled to the sweep's mean launch",
                     "us_per_launch": ms_gemm * 1e3 / n_cases, "algorithmic_bytes_per_launch": gbytes}
 
     # ---- e2e through the public op with pinned host buffers
@@ -528,7 +557,7 @@ def main():
                 us = float(tt.item())
             return us
 
-        reps = max(3, min(args.steps, 10))
+        reps = max(3, min(args.steps, 10)) * 4             # sweeps per wall-clock measurement
         eager_us = wall_us(e2e_sweep, reps)
         e2e_us, how = eager_us, "eager"
         if tp == 1 or peer_ar is not None:                  # (NCCL collectives stay out of this graph)
@@ -596,8 +625,9 @@ def main():
                 elif rank == 0:
                     print("[bench] graphed e2e results differ from the eager ones; reporting the eager time", file=sys.stderr)
         e2e = {"value": e2e_us, "unit": "us",
-               "h2d_bytes_per_step": world * sum(2 * m * L.k for L in layers for m in MS),
-               "d2h_bytes_per_step": world * sum(2 * m * L.n for L in layers for m in MS),
+               "h2d_bytes_per_step": inner * world * sum(2 * m * L.k for L in layers for m in MS),
+               "d2h_bytes_per_step": inner * world * sum(2 * m * L.n for L in layers for m in MS),
+               "sweeps_timed": reps,
                "eager_us": eager_us, "mode": how,
                "note": ("residue::%s_linear from pinned host buffers: H2D of x, the op, D2H of y on a second stream. "
                         "mode=graph: the whole sweep captured once in a CUDA graph (inputs on an inbound stream, results on an "
@@ -612,7 +642,7 @@ def main():
         # ResAttn shards by KV head (8 / tp KV heads and 64 / tp query heads per rank, no collective);
         # the time is the maximum over ranks, the bytes are those of all ranks
         try:
-            ra = measure_resattn(torch, dev, ops, capture, timed, hbm_gbs, custom=(128, 64), heads=(64 // tp, 8 // tp))
+            ra = measure_resattn(torch, dev, ops, capture, timed, hbm_gbs, custom=(128, 64, 16), heads=(64 // tp, 8 // tp))
             for r in ra:
                 r["tbs"] = round(r["tbs"] * tp, 3)
                 r["frac_hbm"] = round(r["frac_hbm"], 3)
@@ -631,6 +661,11 @@ def main():
 
     if rank == 0:
         flops = sum(mext_flops(m, L.k_full, L.n_full) for L in layers for m in MS)
+        # the ResAttn point that the documents quote, as a top-level key (records may cut the detail short)
+        attn_key = {}
+        for r in (detail or {}).get("resattn", []):
+            if r.get("head_dim") == 128 and r.get("batch") == 64 and r.get("page") == 16:
+                attn_key = {"resattn_d128_b64_page16": {k: r[k] for k in ("us", "tbs", "frac_hbm", "splits") if k in r}}
         line = {
             "metric": "mext_%s_linear_latency" % args.format, "value": us_per_op, "unit": "us", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": False,
@@ -641,10 +676,11 @@ def main():
                            **({"allreduce": "one-shot over peer memory (ri_peer_allreduce_bf16)" if peer_ar is not None
                                else "NCCL"} if tp > 1 else {})),
             "clocks": clk.summary(),
-            **({"allreduce_status": int(ar_status.item())} if tp > 1 else {}), "gpu_launches": per_step_launches * args.steps,
-            "tflops": flops / (ms_step * 1e-3) / 1e12, "fp4_peak_frac": flops / (ms_step * 1e-3) / 9.0e15,
-            "hbm_gbs_algorithmic": sum(mext_bytes(m, L.k_full, L.n_full) for L in layers for m in MS) / (ms_step * 1e-3) / 1e9,
-            "e2e": e2e, "roofline": roofline, "cpu_baseline": cpu, "detail": detail,
+            **({"allreduce_status": int(ar_status.item()), "allreduce_us": allreduce_us} if tp > 1 else {}),
+            "gpu_launches": per_sweep_launches * inner * args.steps,
+            "tflops": flops * inner / (ms_step * 1e-3) / 1e12, "fp4_peak_frac": flops * inner / (ms_step * 1e-3) / 9.0e15,
+            "hbm_gbs_algorithmic": sum(mext_bytes(m, L.k_full, L.n_full) for L in layers for m in MS) * inner / (ms_step * 1e-3) / 1e9,
+            "e2e": e2e, "roofline": roofline, "cpu_baseline": cpu, **attn_key, "detail": detail,
         }
         if args.only:
             line["only"] = args.only
@@ -698,7 +734,7 @@ def measure_sweeps(torch, dev, capture, timed, hbm_gbs):
     from resinfer_b200.nvfp4 import mxfp4
     from resinfer_b200.nvfp4.quant import indices_to_channel_masks
     from resinfer_b200.quant import weight_prep
-    out = {"mxfp4_mext": [], "kext_nvfp4": [], "resattn": []}
+    out = {"mxfp4_mext": [], "kext_nvfp4": [], "resattn": [], "stock_mm_fp4": []}
 
     def weights(k, n, fmt, idx=None):
         g = torch.Generator(device=dev).manual_seed(5)
@@ -724,10 +760,38 @@ def measure_sweeps(torch, dev, capture, timed, hbm_gbs):
     for d, batches in ((128, (1, 8, 32, 128, 256)), (256, (1, 8, 32, 128))):
         for b in batches:
             try:
-                out["resattn"] += measure_resattn(torch, dev, ops, capture, timed, hbm_gbs, custom=(d, b))
+                out["resattn"] += measure_resattn(torch, dev, ops, capture, timed, hbm_gbs, custom=(d, b, 16))
             except Exception as e:                          # e.g. out of memory on a smaller part
                 out["resattn"].append({"head_dim": d, "batch": b, "error": f"{type(e).__name__}: {e}"})
             torch.cuda.empty_cache()
+    # ---- stock anchor: FlashInfer's plain NVFP4 W4A4 GEMM (no residue) behind this library's plain
+    # quantiser, on the four shapes.  A comparison kernel, never part of the product path: the reference
+    # publishes its MEXT latency as a ratio to this stock kernel.
+    try:
+        from flashinfer import mm_fp4
+        out["stock_mm_fp4"] = []
+        for name, k, n, _ in SHAPES:
+            prep, ws, sfs = weights(k, n, "nvfp4")
+            w_sf_v = [t.view(torch.float8_e4m3fn).view(((n + 127) // 128) * 128, (k // 64) * 4) for t in sfs]
+            for m in MS:
+                x = act(m, k)
+                gs = float(x.float().abs().max()) / (6.0 * 448.0)
+                gi = torch.tensor([1.0 / gs], dtype=torch.float32, device=dev)
+                alpha = (prep["weight_global_scale"] * gs).float().reshape(1)
+                codes = torch.empty((m, k // 2), dtype=torch.uint8, device=dev)
+                sf = torch.zeros(((m + 127) // 128) * ((k + 63) // 64) * 512, dtype=torch.uint8, device=dev)
+                sf_v = sf.view(torch.float8_e4m3fn).view(((m + 127) // 128) * 128, (k // 64) * 4)
+                y = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+
+                def fn(c, x=x, gi=gi, alpha=alpha, codes=codes, sf=sf, sf_v=sf_v, y=y):
+                    torch.ops.nvfp4.scaled_fp4_quant_mext_r1(codes, x, sf, gi, 0, 5, True)      # base codes only
+                    return mm_fp4(codes, ws[c].T, sf_v, w_sf_v[c].T, alpha, torch.bfloat16, out=y, backend="cudnn")
+                us = time_case(fn, len(ws))
+                out["stock_mm_fp4"].append({"shape": name, "m": m, "us": round(us, 2), "backend": "cudnn",
+                                            "what": "plain NVFP4 quantiser of this library + flashinfer.mm_fp4, no residue"})
+            del prep, ws, sfs, w_sf_v
+    except Exception as e:                                  # the comparison kernel is optional equipment
+        out["stock_mm_fp4"] = [{"error": f"{type(e).__name__}: {str(e)[:300]}"}]
     # ---- MXFP4 MEXT: online E8M0 quantiser (row_pair) + block32 fold GEMM
     for name, k, n, _ in SHAPES:
         prep, ws, sfs = weights(k, n, "mxfp4")
@@ -776,13 +840,25 @@ def measure_sweeps(torch, dev, capture, timed, hbm_gbs):
     return out
 
 
+# ResAttn decode points of the driver-run line: (head_dim, batch, page size).  The first three are the ones
+# `--only resattn:<index>` addresses.
+RESATTN_POINTS = ((128, 8, 16), (128, 64, 16), (256, 32, 16),
+                  (128, 1, 16), (128, 32, 16), (128, 128, 16), (128, 256, 16),
+                  (256, 1, 16), (256, 8, 16), (256, 128, 16), (256, 256, 16),
+                  (128, 1, 128), (128, 8, 128), (128, 64, 128), (128, 256, 128), (256, 32, 128), (256, 128, 128))
+
+
 def measure_resattn(torch, dev, ops, capture, timed, hbm_gbs, only=None, steps=10, warmup=3, custom=None,
-                    heads=(64, 8)):
+                    heads=(64, 8), points=RESATTN_POINTS):
+    """ResAttn decode: 64 query heads, 8 KV heads, context lengths uniform in [1024, 32768], block tables a
+    random permutation of the page pool.  The KV tensors are uniform random code bytes with E4M3 scale bytes
+    in 0x28-0x48 (timing inputs: the kernel's work does not depend on the values); quantised N(0,1) K/V are
+    what the parity tests use."""
     from resinfer_b200.nvfp4.cute_attn.plan import select_decode_plan
     res = []
-    (hq, hkv), page = heads, 16
+    hq, hkv = heads
     sms = torch.cuda.get_device_properties(dev).multi_processor_count
-    for idx, (d, batch) in enumerate(((128, 8), (128, 64), (256, 32)) if custom is None else (custom,)):
+    for idx, (d, batch, page) in enumerate(points if custom is None else (custom,)):
         if only is not None and idx != only:
             continue
         g = torch.Generator(device=dev).manual_seed(3)
@@ -822,7 +898,8 @@ def measure_resattn(torch, dev, ops, capture, timed, hbm_gbs, only=None, steps=1
         res.append({"head_dim": d, "batch": batch, "page": page, "tokens": tokens, "splits": splits, "us": round(us, 1),
                     "tbs": round(nbytes / us / 1e6, 3), "frac_hbm": round(nbytes / us / 1e3 / hbm_gbs, 3),
                     "kv_bytes_gt_l2": bool(nbytes > L2_BYTES)})
-        del kd, vd, ks, vs
+        del kd, vd, ks, vs, q, out, bt
+        torch.cuda.empty_cache()
     return res
 
 

@@ -154,8 +154,8 @@ int ri_fp4_gemm_static_scratch(const uint8_t* act, int64_t act_row_bytes, const 
 
 /* One-shot all-reduce (sum) of a small BF16 tensor over peer memory, for the partial outputs of row-parallel
  * linears in a tensor-parallel decode step on one node.  Stands where the reference relies on vLLM's
- * RowParallelLinear all-reduce after its rank-local linear (quant/vllm_integration/linear/
- * nvfp4_linear_adapter.py:120-176 returns the partial).
+ * RowParallelLinear all-reduce after its rank-local linear (`apply` of quant/vllm_integration/
+ * linear_method_v2.py and linear_method_mxfp4.py returns the partial).
  *   rank_data[r]   this process's mapping of rank r's partial (`numel` BF16 values, 16-byte aligned; for
  *                  r == rank the local buffer itself); the partial must have been written by earlier work on
  *                  `stream`
@@ -165,17 +165,19 @@ int ri_fp4_gemm_static_scratch(const uint8_t* act, int64_t act_row_bytes, const 
  *   out            local result, `numel` BF16 values, 16-byte aligned, not one of the mapped partials
  * Every rank of the group must make the same sequence of calls.  A rank's partial buffer may be
  * overwritten again after its NEXT call of this function has completed (alternate between two
- * buffers).  The wait for the peers is bounded (about a second); on expiry `status` receives
- * 0x40000000 | missing_rank << 8 | rank and the output is not written.  The sum is taken in rank
- * order with FP32 accumulation, so every rank holds the same bits. */
+ * buffers).  The wait for the peers is bounded (ten seconds unless ri_peer_allreduce_set_wait_ms
+ * says otherwise; measured on the GPU's nanosecond timer); on expiry `status` (optional) receives
+ * 0x40000000 | missing_rank << 8 | rank and `out` receives this rank's own partial -- a defined value,
+ * not the sum -- so callers must look at the status word where that matters.  The sum is taken in
+ * rank order with FP32 accumulation, so every rank holds the same bits.  enable_pdl != 0 launches
+ * with programmatic stream serialisation: the kernel's launch overlaps the tail of the kernel that
+ * wrote the partial and its first instruction waits for that kernel's completion. */
 int64_t ri_peer_allreduce_flag_bytes(void);
 int64_t ri_peer_allreduce_state_bytes(void);
+void ri_peer_allreduce_set_wait_ms(int milliseconds);
 int ri_peer_allreduce_bf16(const void* const* rank_data, void* const* rank_flags, int rank, int world,
-                           int64_t numel, void* out, void* state, int32_t* status, void* stream);
-
-/* Debugging aid: when set to a device buffer of 8 * (number of SMs) int64, every CTA of the next
- * ri_fp4_gemm launches stores nanosecond time stamps of its phases there (NULL switches it off). */
-void ri_fp4_gemm_set_trace(int64_t* device_buffer);
+                           int64_t numel, void* out, void* state, int32_t* status, void* stream,
+                           int enable_pdl);
 
 /* ResAttn: residue-compensated paged NVFP4-KV decode attention, one query token per sequence.
  * q [B,Hq,D] bf16; k_data/v_data [pages,Hkv,page_size,D/2]; k_sf/v_sf [pages,Hkv,page_size,D/16]
@@ -192,7 +194,12 @@ void ri_fp4_gemm_set_trace(int64_t* device_buffer);
  * `splits` pieces of ceil(ceil(max_kv_len / 128) / splits) 128-token tiles each -- the same piece
  * size for every sequence, so long sequences use many splits and short ones few (CTAs of unused
  * splits leave at once) -- and uses `workspace` (ri_resattn_workspace_bytes) for the per-split
- * partial (o, l, m) and a second, deterministic merge kernel.  max_kv_len: upper bound of seq_lens
+ * partial (o, l, m).  The merge is part of the same launch: every CTA takes a ticket per (sequence,
+ * KV head) and the one that draws the last ticket sums the partials in split order (deterministic;
+ * the reference's fused reducer spins instead, csrc/resattn/kernel_paged_decode.py:2365-2431).  The
+ * first ri_resattn_counter_bytes(batch, num_q_heads) bytes of the workspace are those tickets: they
+ * must be zero before the first call and the kernel leaves them zero, so a workspace may be reused
+ * by calls that do not overlap on the GPU.  max_kv_len: upper bound of seq_lens
  * for this call (0 = what the block table can hold, bt_stride * page_size).  status: optional
  * device word, set non-zero if a bounded wait inside the kernel expired.
  * Replaces run_paged_fp4_decode_qmul4_tmem (csrc/resattn/host.py:489-606). */
@@ -206,6 +213,7 @@ int ri_resattn_decode(const void* q_bf16, const uint8_t* k_data, const uint8_t* 
                       int splits, void* workspace, int64_t workspace_bytes, int q_residue, int32_t* status,
                       void* stream);
 int64_t ri_resattn_workspace_bytes(int batch, int num_q_heads, int head_dim, int splits);
+int64_t ri_resattn_counter_bytes(int batch, int num_q_heads);
 
 /* Test helper: out[i] = rcp.approx.ftz.f32(in[i]) on the device (the quantisers' reciprocal). */
 int ri_rcp_approx(const float* in, float* out, int n, void* stream);

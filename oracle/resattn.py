@@ -27,11 +27,14 @@ f32 = np.float32
 
 
 def make_paged_kv(seq_lens, num_kv_heads: int, head_dim: int, page_size: int, seed: int = 3,
-                  extra_pages: float = 0.1):
+                  extra_pages: float = 0.1, scale_range: float = 6.0 * 448.0):
     """Seeded synthetic NVFP4 paged KV cache.
 
     K, V ~ N(0,1) in BF16, quantised to NVFP4 (16-blocks along head_dim, per-tensor global scale
-    amax/(6*448)).  Pages of all sequences are a random permutation of the pool.  Returns a dict
+    amax/scale_range: 6*448 uses the whole E4M3 range for the block scales; 448 is the convention of an
+    FP8-range cache, where code x block scale never exceeds 448 -- the range the reference's E4M3
+    expansion of V, mul.rn.satfinite.e4m3x4 in csrc/resattn/qmul4.py:45, can hold without saturating).
+    Pages of all sequences are a random permutation of the pool.  Returns a dict
     with k_data/v_data uint8 [pages, Hkv, page, D/2], k_sf/v_sf uint8 [pages, Hkv, page, D/16]
     (linear E4M3 bytes), block_tables int32 [B, max_pages] (-1 = unused), seq_lens int32 [B],
     k_global_scale, v_global_scale."""
@@ -49,7 +52,7 @@ def make_paged_kv(seq_lens, num_kv_heads: int, head_dim: int, page_size: int, se
     out = {}
     for name in ("k", "v"):
         x = bf16_round(rng.standard_normal((pool * num_kv_heads * page_size, head_dim), dtype=f32))
-        gs = f32(np.abs(x).max() / (6.0 * 448.0))
+        gs = f32(np.abs(x).max() / scale_range)
         codes, sf_sw = nvfp4_quant_plain(x, f32(1.0) / gs)
         rows = np.arange(x.shape[0])[:, None]
         sf_lin = sf_sw[sf_offset(rows, np.arange(head_dim // 16)[None, :], head_dim)]

@@ -38,13 +38,14 @@ SIGNATURES = {
     "ri_fp4_gemm_workspace_bytes": (_i64, [_i, _i, _i, _i, _i, _i]),
     "ri_fp4_gemm_counter_bytes": (_i64, [_i, _i]),
     "ri_fp4_gemm_auto_splits": (_i, [_i, _i, _i, _i, _i]),
-    "ri_fp4_gemm_set_trace": (None, [_vp]),
     "ri_resattn_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _vp, _i, _i, _i, _i, _i, _i, _f, _f,
                                _vp, _i, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i, _vp, _i64, _i, _vp, _vp]),
     "ri_resattn_workspace_bytes": (_i64, [_i, _i, _i, _i]),
+    "ri_resattn_counter_bytes": (_i64, [_i, _i]),
     "ri_peer_allreduce_flag_bytes": (_i64, []),
     "ri_peer_allreduce_state_bytes": (_i64, []),
-    "ri_peer_allreduce_bf16": (_i, [_vp, _vp, _i, _i, _i64, _vp, _vp, _vp, _vp]),
+    "ri_peer_allreduce_set_wait_ms": (None, [_i]),
+    "ri_peer_allreduce_bf16": (_i, [_vp, _vp, _i, _i, _i64, _vp, _vp, _vp, _vp, _i]),
     "ri_rcp_approx": (_i, [_vp, _vp, _i, _vp]),
 }
 

@@ -76,7 +76,7 @@ struct GemmParams {
   int32_t* status;
   // shared memory carve-up
   int smem_act_off, smem_sfa_off, smem_sfb_off, stage_bytes;
-  long long* trace;             // optional [grid][8] nanosecond stamps (debugging aid)
+  long long* trace;             // development builds: [grid][8] nanosecond stamps
 };
 
 using namespace tc;
@@ -101,30 +101,14 @@ __device__ __forceinline__ void store_out(const GemmParams& p, int tok, int n, f
 // ticket, nobody waits) adds the parts in CTA order and writes the tile.  A CTA writes at most two
 // partials (its first and its last segment): slot 2c+1 when it is the first contributor of the tile,
 // slot 2c otherwise.
+// Development builds (-DRI_GEMM_TRACE) record nanosecond stamps of the phases of every CTA.
 __device__ __forceinline__ void stamp(const GemmParams& p, int slot) {
+#ifdef RI_GEMM_TRACE
   if (p.trace) {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     p.trace[blockIdx.x * 8 + slot] = (long long)t;
   }
-}
-// Cycle accounting for development builds (-DRI_GEMM_PROFILE): zero cost otherwise.
-__device__ __forceinline__ long long prof_clock() {
-#ifdef RI_GEMM_PROFILE
-  return clock64();
-#else
-  return 0;
-#endif
-}
-__device__ __forceinline__ void prof_store(const GemmParams& p, int slot, long long v) {
-#ifdef RI_GEMM_PROFILE
-  if (p.trace && blockIdx.x == 0) p.trace[8 * 148 + slot] = v;
-#endif
-}
-// per-unit event times of CTA 0 (development builds): row `ev`, first 24 units
-__device__ __forceinline__ void prof_event(const GemmParams& p, int ev, int unit) {
-#ifdef RI_GEMM_PROFILE
-  if (p.trace && blockIdx.x == 0 && unit < 24) p.trace[8 * 148 + 32 + ev * 24 + unit] = clock64();
 #endif
 }
 __device__ __forceinline__ long long range_start(const GemmParams& p, int c) {
@@ -240,8 +224,6 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
       w.init(p, u_begin);
       int cur_tile = -1, w_tile = 0, tok_tile = 0, first_row_tile = 0, valid_row_tiles = 0;
       const uint8_t* w_sf_tile = nullptr;
-      long long pf_wait = 0;
-      const long long pf_begin = prof_clock();
       if (!w_role) asm volatile("griddepcontrol.wait;" ::: "memory");   // activations come from the previous kernel
       for (int i = 0; i < n_units; ++i, w.next(p)) {
         if (w.tile != cur_tile) {
@@ -258,13 +240,9 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
         const int rem = p.k - w.kt * 256;
         const int n_mma = rem >= 256 ? kMmaPerTile : rem >> 6;
         const uint32_t sf_bytes = uint32_t(MX ? (n_mma + 1) >> 1 : n_mma) * 512;
-        const long long c0 = prof_clock();
         if (w.it >= p.stages) {
           if (!mbar_wait(smem_u32(&bar_empty[w.stage]), w.stage_par ^ 1, &abort_flag, w_role ? 1 : 2)) break;
         }
-        const long long c1 = prof_clock();
-        pf_wait += c1 - c0;
-        if (w_role) prof_event(p, 0, i);
         uint8_t* st = smem + w.stage * p.stage_bytes;
         const uint32_t full = smem_u32(&bar_full[w.stage]);
         if (w_role) {
@@ -272,7 +250,6 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
           mbar_expect_tx(full, tx);
           tma_load_2d(smem_u32(st), &w_map, w.kt * kTileKBytes, w_tile * kTileW, full);
           bulk_load_1d(smem_u32(st + p.smem_sfa_off), w_sf_tile + w.kt * sf_stride, sf_bytes, full);
-          prof_event(p, 1, i);
         } else {
           for (int h = 0; h < halves; ++h) {
             tma_load_2d(smem_u32(st + p.smem_act_off + h * act_tile_bytes), &act_map,
@@ -286,8 +263,6 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
           }
         }
       }
-      prof_store(p, w_role ? 0 : 2, pf_wait);
-      prof_store(p, w_role ? 1 : 3, prof_clock() - pf_begin);
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
@@ -300,8 +275,6 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
       Walk w;
       w.init(p, u_begin);
       int seg = 0, i = 0;
-      long long pm_full = 0, pm_sf = 0, pm_mma = 0, pm_commit = 0;
-      const long long pm_begin = prof_clock();
       while (i < n_units && ok) {
         const int buf = nbuf == 2 ? (seg & 1) : 0;
         if (seg >= nbuf) {                          // the epilogue must have drained this buffer
@@ -312,15 +285,11 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
         const uint32_t d_tmem = tmem_base + buf * p.n_tile;
         uint32_t accumulate = 0;
         for (;;) {                                  // K tiles of this segment (same output tile)
-          const long long c0 = prof_clock();
           bool got = mbar_wait(smem_u32(&bar_full[w.stage]), w.stage_par, &abort_flag, 4);
-          const long long c1 = prof_clock();
           // the scale warps have put this K tile's block scales into scale set `set` of tensor memory
           got = got && mbar_wait(smem_u32(&bar_sf_full[w.set]), w.set_par, &abort_flag, 5);
           if (!__all_sync(0xffffffffu, got)) { ok = false; break; }       // warp-uniform decision
           tc_fence_after();
-          const long long c2 = prof_clock();
-          if (lane == 0) prof_event(p, 5, i);
           if (w.it == 0 && lane == 0) stamp(p, 3);
           const bool leader = elect_one();
           uint8_t* st = smem + w.stage * p.stage_bytes;
@@ -345,12 +314,8 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
               accumulate = 1;
             }
           }
-          const long long c3 = prof_clock();
           if (leader) mma_commit(smem_u32(&bar_empty[w.stage]));   // frees the stage (and, later, its scale set)
           __syncwarp();
-          const long long c4 = prof_clock();
-          if (lane == 0) prof_event(p, 6, i);
-          pm_full += c1 - c0; pm_sf += c2 - c1; pm_mma += c3 - c2; pm_commit += c4 - c3;
           const bool tile_done = w.kt == p.k_tiles - 1;
           w.next(p);
           ++i;
@@ -362,8 +327,6 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
       }
       if (lane == 0) {
         stamp(p, 4);
-        prof_store(p, 4, pm_full); prof_store(p, 5, pm_sf); prof_store(p, 6, pm_mma); prof_store(p, 7, pm_commit);
-        prof_store(p, 8, prof_clock() - pm_begin); prof_store(p, 9, n_units);
       }
     }
   } else {
@@ -384,7 +347,6 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
     int seg = 0, i = 0;
     int lag_stage = 0;
     uint32_t lag_par = 0;
-    long long ps_full = 0, ps_lag = 0, ps_st = 0;
     const int esz = p.out_fp16 == 2 ? 4 : 2;                  // output element size
     const bool out_vec = ((reinterpret_cast<uintptr_t>(p.out) | uintptr_t(p.out_stride * esz)) & 15) == 0;
     uint8_t* epi_stage = smem + p.stages * p.stage_bytes;     // kEpiStageBytes behind the pipeline stages
@@ -412,10 +374,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
         const int rem = p.k - w.kt * 256;
         const int n_mma = rem >= 256 ? kMmaPerTile : rem >> 6;
         const int n_chunks = MX ? (n_mma + 1) >> 1 : n_mma;
-        const long long c0 = prof_clock();
         bool got = mbar_wait(smem_u32(&bar_full[w.stage]), w.stage_par, &abort_flag, 6);
-        const long long c1 = prof_clock();
-        if (warp == 6 && lane == 0) prof_event(p, 2, i);
         if (got && p.sf_sets < p.stages && w.it >= p.sf_sets) {
           // fewer scale sets than stages: before a set is reused the MMAs of unit (it - sf_sets) must have
           // completed, which is what the commit on that unit's stage barrier reports.  (With one set per
@@ -426,9 +385,6 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
         }
         if (!__all_sync(0xffffffffu, got)) { scale_alive = false; continue; }
         tc_fence_after();
-        const long long c2 = prof_clock();
-        ps_full += c1 - c0; ps_lag += c2 - c1;
-        if (warp == 6 && lane == 0) prof_event(p, 3, i);
         const uint8_t* st = smem + w.stage * p.stage_bytes;
         const uint32_t col0 = tmem_base + q_lane + kSfCol + w.set * p.sf_set_cols;
         const uint8_t* sfa_src = st + p.smem_sfa_off + lane * 16;
@@ -488,11 +444,6 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         tc_fence_before();
         if (lane == 0) mbar_arrive(smem_u32(&bar_sf_full[w.set]));
-        ps_st += prof_clock() - c2;
-        if (warp == 6 && lane == 0) prof_event(p, 4, i);
-      }
-      if (warp == 6 && lane == 0 && i == n_units) {
-        prof_store(p, 10, ps_full); prof_store(p, 11, ps_lag); prof_store(p, 12, ps_st);
       }
       ++seg;
       continue;
@@ -521,8 +472,6 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
       const int tok0 = tok_tile * p.tok_per_tile;
       const uint32_t t_lane = tmem_base + buf * p.n_tile + (uint32_t(quarter * 32) << 16);
       float* mine = p.ws_partial + (int64_t(cta) * 2 + (cta == c_first ? 1 : 0)) * tile_elems;
-      const long long e1 = prof_clock();
-      long long pe_ld = 0, pe_stage = 0, pe_bar1 = 0, pe_copy = 0, pe_bar2 = 0;
 
       // Output of one chunk of 32 accumulator columns (16 tokens with the row_pair layout, 32
       // otherwise).  A thread owns one output column n (its weight row) and `ntok` token values.
@@ -534,7 +483,6 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
         const int ntok = pair ? cols >> 1 : cols;
         const int tokc0 = tok0 + (pair ? c0 >> 1 : c0);
         float o[32];
-        const long long q0 = prof_clock();
         if (pair) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) o[j] = p.n_alpha > 1 ? a0 * v[2 * j] + a1 * v[2 * j + 1] : a0 * (v[2 * j] + v[2 * j + 1]);
@@ -554,10 +502,6 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
         }
         uint32_t* stage32 = reinterpret_cast<uint32_t*>(epi_stage);
         const int npair = (ntok + 1) >> 1;
-#ifdef RI_GEMM_PROFILE
-        { uint32_t dummy; asm volatile("mov.b32 %0, %1;" : "=r"(dummy) : "f"(o[15])); asm volatile("mov.b32 %0, %1;" : "=r"(dummy) : "f"(o[0])); }
-        pe_bar2 -= prof_clock() - q0;     // (borrowed slot: minus the time to compute o[])
-#endif
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           if (i < npair) {
@@ -572,9 +516,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
             stage32[i * kTileW + row_in_tile] = wv;
           }
         }
-        const long long q1 = prof_clock();
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        const long long q2 = prof_clock();
         // copy-out: thread -> (pair row, vector of 8 outputs); 16 vectors per token row of the tile
         const int et = int(threadIdx.x) - 64;
         for (int pr = et >> 4; pr < npair; pr += 8) {
@@ -603,15 +545,12 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
             }
           }
         }
-        const long long q3 = prof_clock();
         asm volatile("bar.sync 1, 128;" ::: "memory");      // the stage is reused by the next chunk
-        pe_stage += q1 - q0; pe_bar1 += q2 - q1; pe_copy += q3 - q2; pe_bar2 += prof_clock() - q3;
       };
 
       for (int c0 = 0; c0 < p.n_tile; c0 += 32) {
         const int cols = min(32, p.n_tile - c0);               // 32, or 16 for the last chunk
         float v[32];
-        const long long l0 = prof_clock();
         if (cols == 32) {
           tmem_ld32(t_lane + c0, v);
         } else {
@@ -620,10 +559,6 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
 #pragma unroll
           for (int j = 0; j < 16; ++j) { v[j] = lo[j]; v[16 + j] = 0.f; }
         }
-#ifdef RI_GEMM_PROFILE
-        { uint32_t dummy; asm volatile("mov.b32 %0, %1;" : "=r"(dummy) : "f"(v[31])); asm volatile("mov.b32 %0, %1;" : "=r"(dummy) : "f"(v[0])); }
-#endif
-        pe_ld += prof_clock() - l0;
         if (finish_now) {
           // sum in CTA order, this CTA's part straight from tensor memory (same order and values as
           // the reduction below, so the result does not depend on which path ran)
@@ -655,8 +590,6 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
         }
       }
       if (threadIdx.x == 64 && seg == 0) {
-        prof_store(p, 15, prof_clock() - e1); prof_store(p, 16, pe_ld); prof_store(p, 17, pe_stage);
-        prof_store(p, 18, pe_bar1); prof_store(p, 19, pe_copy); prof_store(p, 20, pe_bar2);
       }
       // the accumulator buffer has been read: hand it back to the MMA warp
       tc_fence_before();
@@ -859,14 +792,18 @@ int64_t partial_bytes(const Plan& pl) {
   return pl.tile_granular ? 0 : int64_t(pl.grid) * 2 * kTileW * pl.n_tile * 4;
 }
 
+#ifdef RI_GEMM_TRACE
 long long* g_trace = nullptr;
+#endif
 
 }  // namespace
 }  // namespace ri
 
 using namespace ri;
 
+#ifdef RI_GEMM_TRACE
 extern "C" void ri_fp4_gemm_set_trace(int64_t* device_buffer) { g_trace = reinterpret_cast<long long*>(device_buffer); }
+#endif
 
 extern "C" int64_t ri_fp4_gemm_counter_bytes(int m, int n) {
   (void)m;
@@ -887,15 +824,21 @@ extern "C" int ri_fp4_gemm_auto_splits(int m, int n, int k, int fmt, int layout)
 
 extern "C" int64_t ri_fp4_gemm_workspace_bytes(int m, int n, int k, int fmt, int layout, int splits) {
   if (splits == 1) return 0;
+  // The plan depends on the SM count.  The size returned covers the plan of the device in use (when one
+  // is visible) and the plan of a full 148-SM part, so that a launch never finds the workspace short.
   DeviceInfo di;
-  int sms = 148;
-  if (device_info(&di) == 0 && di.sm_count > sms) sms = di.sm_count;
-  Plan pl;
-  if (make_plan(m, n, k, fmt, layout, splits, sms, &pl)) return -1;
-  if (pl.tile_granular) return 0;
-  // sized for a grid of up to `sms` CTAs whatever the planner picks on the device in use
-  const int64_t partial = int64_t(sms) * 2 * kTileW * pl.n_tile * 4;
-  return ri_fp4_gemm_counter_bytes(m, n) + partial;
+  int counts[2] = {148, 148};
+  if (device_info(&di) == 0) counts[1] = di.sm_count;
+  int64_t partial = 0;
+  for (int i = 0; i < 2; ++i) {
+    Plan pl;
+    if (make_plan(m, n, k, fmt, layout, splits, counts[i], &pl)) return -1;
+    if (pl.tile_granular) continue;
+    const int sms = counts[i] > 148 ? counts[i] : 148;     // room for a grid of every SM, whatever the planner picks
+    const int64_t bytes = int64_t(sms) * 2 * kTileW * pl.n_tile * 4;
+    if (bytes > partial) partial = bytes;
+  }
+  return partial ? ri_fp4_gemm_counter_bytes(m, n) + partial : 0;
 }
 
 extern "C" int ri_fp4_gemm(const uint8_t* act, int64_t act_row_bytes, const uint8_t* act_sf,
@@ -998,7 +941,9 @@ extern "C" int ri_fp4_gemm(const uint8_t* act, int64_t act_row_bytes, const uint
   p.ws_partial = ws_partial; p.ws_counter = ws_counter; p.status = status;
   p.smem_act_off = pl.smem_act_off; p.smem_sfa_off = pl.smem_sfa_off; p.smem_sfb_off = pl.smem_sfb_off;
   p.stage_bytes = pl.stage_bytes;
+#ifdef RI_GEMM_TRACE
   p.trace = g_trace;
+#endif
 
   auto kernel = fmt == RI_FMT_MXFP4 ? fp4_gemm_kernel<true> : fp4_gemm_kernel<false>;
   static bool attr_set[64][2] = {};                 // function attributes are per device

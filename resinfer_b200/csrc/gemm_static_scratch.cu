@@ -84,8 +84,9 @@ extern "C" int ri_fp4_gemm_static_scratch(const uint8_t* act, int64_t act_row_by
   void* scratch = nullptr;
   int s = scratch_for_current_device(&scratch);
   if (s) return s;
-  if (need > 0 && m > 0) {
-    // tickets must read zero when the kernel starts; the previous call may have been cut short
+  if (m > 0 && splits != 1) {
+    // tickets must read zero when the kernel starts; the previous call may have been cut short.  (Cleared
+    // whenever the launch may choose a K-split plan, whatever the size query above planned.)
     const int64_t counters = ri_fp4_gemm_counter_bytes(m, n);
     cudaError_t e = cudaMemsetAsync(scratch, 0, size_t(counters), static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return ri::cuda_status(e, "clearing the static scratch tickets");

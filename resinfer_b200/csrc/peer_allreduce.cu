@@ -7,9 +7,9 @@
 // the BF16 result to local memory.  The sum is bit-identical on every rank.
 //
 // No multicast, no multimem, no NCCL.  Only ranks on DIFFERENT GPUs ever wait for each other.
-// The reference leaves this step to vLLM's tensor-parallel linear layers (quant/vllm_integration/
-// linear/nvfp4_linear_adapter.py:120-176 return the rank-local partial; the all-reduce follows in
-// vLLM's RowParallelLinear).
+// The reference leaves this step to vLLM's tensor-parallel linear layers (its linear methods,
+// quant/vllm_integration/linear_method_v2.py and linear_method_mxfp4.py, return the rank-local partial
+// from `apply`; the all-reduce follows in vLLM's RowParallelLinear).
 #include "common.cuh"
 #include "resinfer_b200.h"
 
@@ -26,8 +26,15 @@ struct PeerArParams {
   uint32_t* state;                  // local: [0] calls completed so far, [1] block ticket
   int32_t* status;
   int64_t n16;                      // 16-byte units (8 BF16 values) to reduce
+  long long wait_ns;                // how long a block waits for the peers before it gives up
   int rank, world;
 };
+
+__device__ __forceinline__ long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return (long long)t;
+}
 
 __device__ __forceinline__ void add8(float (&acc)[8], uint4 v) {
   const uint32_t w[4] = {v.x, v.y, v.z, v.w};
@@ -40,6 +47,9 @@ __device__ __forceinline__ void add8(float (&acc)[8], uint4 v) {
 
 __global__ void __launch_bounds__(kArThreads) peer_allreduce_kernel(const PeerArParams p) {
   __shared__ int ok;
+  // launched with programmatic stream serialisation: the partial is the previous kernel's output
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(p.state) + 1;
   if (threadIdx.x == 0) ok = 1;
   __syncthreads();
@@ -51,14 +61,14 @@ __global__ void __launch_bounds__(kArThreads) peer_allreduce_kernel(const PeerAr
       __threadfence_system();
       asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.flags[r] + p.rank), "r"(epoch) : "memory");
     }
-    // ... and every block waits until every rank has announced this call: at most about a second.
+    // ... and every block waits until every rank has announced this call, for at most p.wait_ns.
     const uint32_t* mine = p.flags[p.rank] + r;
-    const long long t0 = clock64();
+    const long long t0 = global_ns();
     for (uint32_t spin = 0;; ++spin) {
       uint32_t seen;
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
       if (int32_t(seen - epoch) >= 0) break;
-      if ((spin & 255u) == 255u && clock64() - t0 > 2000000000ll) {
+      if ((spin & 255u) == 255u && global_ns() - t0 > p.wait_ns) {
         ok = 0;
         if (p.status) atomicExch(p.status, 0x40000000 | (r << 8) | p.rank);    // which peer never arrived
         break;
@@ -84,6 +94,11 @@ __global__ void __launch_bounds__(kArThreads) peer_allreduce_kernel(const PeerAr
       }
       p.out[i] = o;
     }
+  } else {
+    // a peer never arrived: the status word says which one; the output gets a defined value, this rank's
+    // own partial, instead of whatever the buffer held
+    for (int64_t i = int64_t(blockIdx.x) * kArThreads + threadIdx.x; i < p.n16; i += int64_t(gridDim.x) * kArThreads)
+      p.out[i] = p.data[p.rank][i];
   }
   // the last block to finish closes the call: the next launch on this rank sees epoch as "completed"
   __syncthreads();
@@ -101,11 +116,21 @@ __global__ void __launch_bounds__(kArThreads) peer_allreduce_kernel(const PeerAr
 }  // namespace
 }  // namespace ri
 
+namespace ri {
+namespace {
+long long g_wait_ns = 10ll * 1000 * 1000 * 1000;       // ten seconds: rank skew from a first-call module load or a host stall
+}
+}  // namespace ri
+
+extern "C" void ri_peer_allreduce_set_wait_ms(int milliseconds) {
+  ri::g_wait_ns = (long long)(milliseconds < 1 ? 1 : milliseconds) * 1000000ll;
+}
 extern "C" int64_t ri_peer_allreduce_flag_bytes(void) { return ri::kMaxRanks * 4; }
 extern "C" int64_t ri_peer_allreduce_state_bytes(void) { return 8; }
 
 extern "C" int ri_peer_allreduce_bf16(const void* const* rank_data, void* const* rank_flags, int rank, int world,
-                                      int64_t numel, void* out, void* state, int32_t* status, void* stream) {
+                                      int64_t numel, void* out, void* state, int32_t* status, void* stream,
+                                      int enable_pdl) {
   using namespace ri;
   RI_CHECK_ARG(world >= 2 && world <= kMaxRanks && rank >= 0 && rank < world, "bad rank %d / world %d (2..%d ranks)",
                rank, world, kMaxRanks);
@@ -125,11 +150,22 @@ extern "C" int ri_peer_allreduce_bf16(const void* const* rank_data, void* const*
   p.n16 = numel / 8;
   p.rank = rank;
   p.world = world;
+  p.wait_ns = g_wait_ns;
   DeviceInfo di;
   int s = device_info(&di);
   if (s) return s;
   const int64_t want = (p.n16 + kArThreads - 1) / kArThreads;
   const int grid = int(want < 1 ? 1 : (want > di.sm_count ? di.sm_count : want));
-  peer_allreduce_kernel<<<grid, kArThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
-  return cuda_status(cudaGetLastError(), "peer all-reduce launch");
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kArThreads);
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr{};
+  if (enable_pdl) {                  // its launch latency then hides under the tail of the kernel that wrote the partial
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+  }
+  return cuda_status(cudaLaunchKernelEx(&cfg, peer_allreduce_kernel, p), "peer all-reduce launch");
 }

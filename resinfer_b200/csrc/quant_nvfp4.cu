@@ -36,50 +36,73 @@ __device__ __forceinline__ void mext_rows(int i, int rows, int layout, int& base
 }
 
 // ---------------------------------------------------------------------------------------------
-// MEXT: x[M,K] -> base and residue codes + scales.  One thread per 16-element block.
+// MEXT: x[M,K] -> base and residue codes + scales.  A thread owns BPT consecutive 16-element blocks of
+// one row: BPT = 1 for decode-sized inputs (as many threads as there are blocks, spread over several
+// CTAs), BPT = 2 for large inputs (two 256-bit loads in flight per thread, 128-bit code stores, 16-bit
+// scale stores).  The grid is (block columns of a row, rows): no index divisions in the kernel.
 // ---------------------------------------------------------------------------------------------
-template <typename T>
+template <typename T, int BPT>
 __global__ void __launch_bounds__(256) nvfp4_mext_kernel(const T* __restrict__ x, int64_t row_stride,
                                                          int in_rows, int out_rows, int k,
                                                          const float* __restrict__ gs_inv, int n_gs,
                                                          uint8_t* __restrict__ codes,
                                                          uint8_t* __restrict__ sf, int layout) {
   const int blocks_per_row = k / 16;
-  const int64_t total = int64_t(out_rows) * blocks_per_row;
+  const int blk = (blockIdx.x * blockDim.x + threadIdx.x) * BPT;      // first block of this thread
   // let the dependent kernel (the GEMM) be scheduled now: it prefetches weights while this grid runs and
   // waits for this grid (griddepcontrol.wait) before it reads the codes
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");   // inputs may come from a kernel still running
+  if (blk >= blocks_per_row) return;
   const float gs = gs_inv ? __ldg(gs_inv) : 1.0f;
   const float gs_res = (gs_inv && n_gs > 1) ? __ldg(gs_inv + 1) : gs;
-  for (int64_t t = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
-       t += int64_t(gridDim.x) * blockDim.x) {
-    const int row = int(t / blocks_per_row);
-    const int blk = int(t % blocks_per_row);
-    float v[16];
-    if (row < in_rows) {
-      load16(x + int64_t(row) * row_stride + blk * 16, v);
-    } else {
+  for (int row = blockIdx.y; row < out_rows; row += gridDim.y) {
+    float v[BPT][16];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) v[i] = 0.f;
+    for (int j = 0; j < BPT; ++j) {
+      if (row < in_rows) {
+        load16(x + int64_t(row) * row_stride + (blk + j) * 16, v[j]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[j][i] = 0.f;
+      }
     }
-    BlockQ q = quant_mext16(v, gs, gs_res);
-    if (layout == 5) {   // base codes only (plain NVFP4 activation quantisation)
-      *reinterpret_cast<uint2*>(codes + int64_t(row) * (k / 2) + blk * 8) = q.base;
-      sf[sf_offset<16>(row, blk, k)] = q.sf;
+    BlockQ q[BPT];
+#pragma unroll
+    for (int j = 0; j < BPT; ++j) q[j] = quant_mext16(v[j], gs, gs_res);
+    // destinations of the base and residue halves: code rows (bytes) and scale (row, first k-group)
+    uint8_t* base_codes;
+    uint8_t* res_codes = nullptr;
+    int sb, sr = 0, kg_res = blk, k_sf = k;
+    if (layout == 5) {          // base codes only (plain NVFP4 activation quantisation)
+      base_codes = codes + int64_t(row) * (k / 2);
+      sb = row;
     } else if (layout == 3) {   // concat_k: [M, 2K] elements, scales over Ktot = 2K
-      uint8_t* rowp = codes + int64_t(row) * k;
-      *reinterpret_cast<uint2*>(rowp + blk * 8) = q.base;
-      *reinterpret_cast<uint2*>(rowp + k / 2 + blk * 8) = q.res;
-      sf[sf_offset<16>(row, blk, 2 * k)] = q.sf;
-      sf[sf_offset<16>(row, blocks_per_row + blk, 2 * k)] = q.sf_res;
+      base_codes = codes + int64_t(row) * k;
+      res_codes = base_codes + k / 2;
+      sb = sr = row;
+      kg_res = blocks_per_row + blk;
+      k_sf = 2 * k;
     } else {
-      int br, rr, sb, sr;
+      int br, rr;
       mext_rows(row, out_rows, layout, br, rr, sb, sr);
-      *reinterpret_cast<uint2*>(codes + int64_t(br) * (k / 2) + blk * 8) = q.base;
-      *reinterpret_cast<uint2*>(codes + int64_t(rr) * (k / 2) + blk * 8) = q.res;
-      sf[sf_offset<16>(sb, blk, k)] = q.sf;
-      sf[sf_offset<16>(sr, blk, k)] = q.sf_res;
+      base_codes = codes + int64_t(br) * (k / 2);
+      res_codes = codes + int64_t(rr) * (k / 2);
+    }
+    if constexpr (BPT == 1) {
+      *reinterpret_cast<uint2*>(base_codes + blk * 8) = q[0].base;
+      sf[sf_offset<16>(sb, blk, k_sf)] = q[0].sf;
+      if (res_codes) {
+        *reinterpret_cast<uint2*>(res_codes + blk * 8) = q[0].res;
+        sf[sf_offset<16>(sr, kg_res, k_sf)] = q[0].sf_res;
+      }
+    } else {                    // two adjacent blocks: one 128-bit code store, one 16-bit scale store (blk is even)
+      *reinterpret_cast<uint4*>(base_codes + blk * 8) = make_uint4(q[0].base.x, q[0].base.y, q[1].base.x, q[1].base.y);
+      *reinterpret_cast<uint16_t*>(sf + sf_offset<16>(sb, blk, k_sf)) = uint16_t(q[0].sf | (uint32_t(q[1].sf) << 8));
+      if (res_codes) {
+        *reinterpret_cast<uint4*>(res_codes + blk * 8) = make_uint4(q[0].res.x, q[0].res.y, q[1].res.x, q[1].res.y);
+        *reinterpret_cast<uint16_t*>(sf + sf_offset<16>(sr, kg_res, k_sf)) = uint16_t(q[0].sf_res | (uint32_t(q[1].sf_res) << 8));
+      }
     }
   }
 }
@@ -267,13 +290,43 @@ extern "C" int ri_nvfp4_quant_mext(const void* x, int dtype, int m, int k, int64
                layout, (long long)(m_tiles * k_tiles * 512), (long long)sf_bytes);
   RI_CHECK_ARG((reinterpret_cast<uintptr_t>(codes) & 7) == 0, "codes buffer must be 8-byte aligned");
   if (m == 0) return RI_OK;
-  const int64_t work = out_m * (k / 16);
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (dtype == RI_DTYPE_BF16)
-    return launch(nvfp4_mext_kernel<__nv_bfloat16>, work, 256, enable_pdl, st,
-                  static_cast<const __nv_bfloat16*>(x), row_stride, m, int(out_m), k, gs_inv, n_gs, codes, sf, layout);
-  return launch(nvfp4_mext_kernel<__half>, work, 256, enable_pdl, st, static_cast<const __half*>(x),
-                row_stride, m, int(out_m), k, gs_inv, n_gs, codes, sf, layout);
+  // Geometry: a thread per 16-element block for small inputs; two blocks per thread once the input fills
+  // the machine anyway (needs an even block count per row, 16-byte aligned code rows and even scale groups).
+  DeviceInfo di;
+  int s = device_info(&di);
+  if (s) return s;
+  const int blocks_per_row = k / 16;
+  const bool wide = blocks_per_row % 2 == 0 && out_m * blocks_per_row >= int64_t(di.sm_count) * 2048 &&
+                    (reinterpret_cast<uintptr_t>(codes) & 15) == 0 && (k / 2) % 16 == 0 &&
+                    (reinterpret_cast<uintptr_t>(sf) & 1) == 0;
+  const int units = wide ? blocks_per_row / 2 : blocks_per_row;          // threads per row
+  const int col_blocks = (units + 255) / 256;
+  const int threads = ((units + col_blocks - 1) / col_blocks + 31) / 32 * 32;
+  int64_t rows_y = out_m;
+  const int64_t cap = int64_t(di.sm_count) * (2048 / threads) * 4 / col_blocks;   // a few waves, then rows are looped
+  if (rows_y > cap) rows_y = cap < 1 ? 1 : cap;
+  if (rows_y > 65535) rows_y = 65535;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)col_blocks, (unsigned)rows_y);
+  cfg.blockDim = dim3(threads);
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr{};
+  if (enable_pdl) {
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+  }
+  auto go = [&](auto kernel, auto* xp) {
+    return cuda_status(cudaLaunchKernelEx(&cfg, kernel, xp, row_stride, m, int(out_m), k, gs_inv, n_gs, codes, sf, layout),
+                       "quantiser launch");
+  };
+  if (dtype == RI_DTYPE_BF16) {
+    const auto* xp = static_cast<const __nv_bfloat16*>(x);
+    return wide ? go(nvfp4_mext_kernel<__nv_bfloat16, 2>, xp) : go(nvfp4_mext_kernel<__nv_bfloat16, 1>, xp);
+  }
+  const auto* xp = static_cast<const __half*>(x);
+  return wide ? go(nvfp4_mext_kernel<__half, 2>, xp) : go(nvfp4_mext_kernel<__half, 1>, xp);
 }
 
 template <typename T>

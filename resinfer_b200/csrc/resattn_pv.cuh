@@ -39,44 +39,21 @@ constexpr int kPvPLbo = 144;
 constexpr int kPvPGroup = 16 * kPvPLbo;           // 2304 bytes: one 8-row group over 128 tokens
 constexpr int kPvOffP = 4096;
 constexpr int kPvOffV = 11264;                    // [D/64 d-blocks][128 tokens][64 d] FP16, 128B swizzle, M-major
-#ifndef RI_PV_VBUFS
-#define RI_PV_VBUFS 2
-#define RI_PV_STAGES 2
-#define RI_PV_CTAS 2
-#endif
-#ifndef RI_PV256_VBUFS
-#define RI_PV256_VBUFS 2
-#define RI_PV256_STAGES 2
-#endif
-#ifndef RI_PV256_SOFT
-#define RI_PV256_SOFT 8
-#endif
-#ifndef RI_PV_SOFT
-#define RI_PV_SOFT 8
-#endif
-#ifndef RI_PV_PROD
-#define RI_PV_PROD 4
-#endif
-// head_dim 128: two CTAs of 17 warps per SM; head_dim 256: one CTA of 25 warps (the FP16 V tile is 64 KB)
+// head_dim 128: two CTAs of 21 warps per SM; head_dim 256: one CTA of 29 warps (the FP16 V tile is 64 KB)
 template <int D>
 struct PvCfg {
-  static constexpr int kSoft = D == 128 ? RI_PV_SOFT : RI_PV256_SOFT;          // softmax warps: 4 (8 heads per thread) or 8 (4 heads)
+  static constexpr int kSoft = 8;                                     // softmax warps (4 heads per thread)
   static constexpr int kHpt = 32 / kSoft;                             // heads a softmax thread handles
-  static constexpr int kProd = D == 128 ? RI_PV_PROD : 4;             // copy producer warps, 128 / kProd rows of a tile each
+  static constexpr int kProd = 4;                                     // copy producer warps, 128 / kProd rows of a tile each
   static constexpr int kConv = D == 128 ? 8 : 16;                     // conversion warps
-  static constexpr int kVBufs = D == 128 ? RI_PV_VBUFS : RI_PV256_VBUFS;        // FP16 V tiles in flight
-  static constexpr int kStages = D == 128 ? RI_PV_STAGES : RI_PV256_STAGES;     // cp.async pipeline stages
-  static constexpr int kCtasPerSm = D == 128 ? RI_PV_CTAS : 1;
+  static constexpr int kVBufs = 2;                                    // FP16 V tiles in flight
+  static constexpr int kStages = 2;                                   // cp.async pipeline stages
+  static constexpr int kCtasPerSm = D == 128 ? 2 : 1;
   static constexpr int kDBlocks = D / 64;                             // 64-wide blocks of the head dimension
   static constexpr int kHalves = D / 128;                             // 128-row halves of O^T (M of one MMA)
   static constexpr int kVBytes = 128 * D * 2;
-#ifdef RI_PV_ALIAS_V   // timing experiment only (wrong results): both V buffers share memory
-  static constexpr int kVStride = 0;
-  static constexpr int kHeaderBytes = kPvOffV + kVBytes;
-#else
   static constexpr int kVStride = kVBytes;
   static constexpr int kHeaderBytes = kPvOffV + kVBufs * kVBytes;      // a multiple of 1024
-#endif
   static constexpr int kThreads = (kSoft + 1 + kProd + kConv) * 32;
   static constexpr int kTmemCols = D == 128 ? 256 : 512;
   static constexpr int kSmemBytes = kHeaderBytes + kStages * TCfg<D>::kStageBytes + 1024;
@@ -110,6 +87,84 @@ __device__ __forceinline__ void tmem_st16f(uint32_t taddr, const float (&v)[16])
         "r"(__float_as_uint(v[15])) : "memory");
 }
 
+// Split-KV merge, fused into the decode kernel.  Every CTA of a (sequence, KV head) publishes its partial
+// (o, l, m) and takes a ticket; the CTA that draws the last ticket (nobody waits for anybody) combines the
+// partials of all splits in split order, so the result does not depend on which CTA arrives last:
+//   out = sum_s 2^(m_s - m) o_s / sum_s 2^(m_s - m) l_s * out_scale
+// `scratch` is shared memory of this CTA: [0, 8 D) floats for the NVFP4 output staging, then the weights.
+// Returns true in the CTA that merged (the caller then packs the NVFP4 output if that is asked for).
+template <int D>
+__device__ __forceinline__ bool merge_splits_last_cta(const AttnParams& p, int b, int hkv, float* scratch, int* flag_sh) {
+  const int G = p.group;
+  // every thread's partial stores are ordered before its arrival at the barrier; the ticket holder's fence
+  // publishes them device-wide before the ticket and orders the merging CTA's reads after it
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* counter = p.split_counter + b * p.hkv + hkv;
+    const int ticket = atomicAdd(counter, 1);
+    const int last = ticket == p.splits - 1;
+    if (last) *counter = 0;                                  // ready for the next call
+    __threadfence();
+    *flag_sh = last;
+  }
+  __syncthreads();
+  if (!*flag_sh) return false;
+  float* w_sh = scratch + 8 * D;                             // [splits][8] weights 2^(m_s - m), then [8] 1 / l
+  float* r_sh = w_sh + p.splits * 8;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (warp < G) {                                            // one warp per head: maximum, weights, row sum
+    const int head = hkv * G + warp;
+    float mm = -INFINITY;
+    for (int s = lane; s < p.splits; s += 32) mm = fmaxf(mm, __ldcg(p.m_part + (int64_t(s) * p.batch + b) * p.hq + head));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
+    for (int s = lane; s < p.splits; s += 32) {
+      const int64_t slot = (int64_t(s) * p.batch + b) * p.hq + head;
+      const float ms = __ldcg(p.m_part + slot);
+      w_sh[s * 8 + warp] = ms == -INFINITY ? 0.f : fast_exp2(ms - mm);
+    }
+    __syncwarp();
+    if (lane == 0) {                                         // the row sum in split order, like the outputs
+      float l = 0.f;
+      for (int s = 0; s < p.splits; ++s) l += w_sh[s * 8 + warp] * __ldcg(p.l_part + (int64_t(s) * p.batch + b) * p.hq + head);
+      r_sh[warp] = l > 0.f ? p.out_scale / l : 0.f;
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+    const int g = idx / D, c = idx - g * D;
+    const int head = hkv * G + g;
+    float o = 0.f;
+    for (int s = 0; s < p.splits; ++s) {
+      const float w = w_sh[s * 8 + g];
+      if (w != 0.f) o += w * __ldcg(p.o_part + ((int64_t(s) * p.batch + b) * p.hq + head) * D + c);   // empty partials hold no data
+    }
+    const float v = o * r_sh[g];
+    const int64_t oi = (int64_t(b) * p.hq + head) * D + c;
+    if (p.out_nvfp4) scratch[g * D + c] = v;
+    else if (p.out_f32) static_cast<float*>(p.out)[oi] = v;
+    else static_cast<__nv_bfloat16*>(p.out)[oi] = __float2bfloat16_rn(v);
+  }
+  __syncthreads();
+  return true;
+}
+
+// 16-value blocks of the [heads][D] staging tile -> packed NVFP4 codes + block scales of sequence b
+template <int D>
+__device__ __forceinline__ void pack_nvfp4_output(const AttnParams& p, int b, int hkv, const float* stage_out) {
+  const int G = p.group;
+  if (threadIdx.x < G * (D / 16)) {
+    const int g = threadIdx.x / (D / 16), blk = threadIdx.x % (D / 16);
+    float v[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = stage_out[g * D + blk * 16 + i];
+    const int head = hkv * G + g, hidden = p.hq * D;
+    store_nvfp4_out16(v, __ldg(p.out_gs), static_cast<uint8_t*>(p.out) + int64_t(b) * (hidden / 2), p.out_sf, b,
+                      head * (D / 16) + blk, hidden);
+  }
+}
+
 template <int D>
 __global__ void __launch_bounds__(PvCfg<D>::kThreads, PvCfg<D>::kCtasPerSm) resattn_pv_kernel(const AttnParams p) {
   using C = TCfg<D>;
@@ -124,6 +179,7 @@ __global__ void __launch_bounds__(PvCfg<D>::kThreads, PvCfg<D>::kCtasPerSm) resa
   __shared__ __align__(8) uint64_t bar_sfull[2], bar_vpready[2], bar_pvdone[2];
   __shared__ uint32_t tmem_slot;
   __shared__ volatile int abort_flag;
+  __shared__ int merge_flag;
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint8_t* q_op = smem;                                        // [16][64 B] swizzled FP4 codes
   uint8_t* qsf_s = smem + 2048;                                // [16][8] E4M3 scales
@@ -150,11 +206,15 @@ __global__ void __launch_bounds__(PvCfg<D>::kThreads, PvCfg<D>::kCtasPerSm) resa
   const int t_end = min(t_begin + p.tiles_per_split, n_tiles);
   const int my_tiles = t_end - t_begin;
   if (my_tiles == 0 && p.splits > 1 && !(p.q_pack && split == 0)) {
+    // nothing to read for this split: publish an empty partial and, if this CTA happens to draw the last
+    // ticket, merge the others' (the whole CTA takes this branch together)
     if (threadIdx.x < G) {
       const int64_t slot = (int64_t(split) * p.batch + b) * p.hq + hkv * G + threadIdx.x;
       p.l_part[slot] = 0.f;
       p.m_part[slot] = -INFINITY;
     }
+    float* scratch = reinterpret_cast<float*>(smem + kPvOffV);
+    if (merge_splits_last_cta<D>(p, b, hkv, scratch, &merge_flag) && p.out_nvfp4) pack_nvfp4_output<D>(p, b, hkv, scratch);
     return;
   }
   const int32_t* bt = p.block_tables + int64_t(b) * p.bt_stride;
@@ -185,7 +245,7 @@ __global__ void __launch_bounds__(PvCfg<D>::kThreads, PvCfg<D>::kCtasPerSm) resa
   const uint32_t tmem_base = tmem_slot;
   if (threadIdx.x < 8) m_sh[threadIdx.x] = -INFINITY;
 
-  // ---------------------------------------------------------------- query prologue (as in resattn_tc_kernel)
+  // ---------------------------------------------------------------- query prologue
   if (threadIdx.x < G * C::kSfPerRow) {
     const int g = threadIdx.x / C::kSfPerRow, blk = threadIdx.x % C::kSfPerRow;
     float v[16];
@@ -238,9 +298,7 @@ __global__ void __launch_bounds__(PvCfg<D>::kThreads, PvCfg<D>::kCtasPerSm) resa
       const int sb = i & 1;
       const int tile = t_begin + i;
       if (threadIdx.x == 0) {
-        attn_event(p, 0, i);
         soft_go[sb] = mbar_wait(smem_u32(&bar_sfull[sb]), (i >> 1) & 1, &abort_flag, 5) ? 1 : 0;
-        attn_event(p, 1, i);
       }
       asm volatile("bar.sync 1, %0;" ::"n"(kPvSoft * 32) : "memory");
       if (!soft_go[sb]) break;                                  // the same decision in all softmax warps
@@ -342,7 +400,6 @@ __global__ void __launch_bounds__(PvCfg<D>::kThreads, PvCfg<D>::kCtasPerSm) resa
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_vpready[sb]));
-      if (threadIdx.x == 0) attn_event(p, 2, i);
     }
   } else if (warp == kPvMmaWarp) {
     // ============================================================ MMA issuer
@@ -361,7 +418,6 @@ __global__ void __launch_bounds__(PvCfg<D>::kThreads, PvCfg<D>::kCtasPerSm) resa
       bool got = true;
       if (lane == 0) got = mbar_wait(smem_u32(&bar_full[stg]), (i / S) & 1, &abort_flag, 3);
       if (!__all_sync(0xffffffffu, got)) { alive = false; return; }
-      if (lane == 0) attn_event(p, 3, i);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // cp.async data -> tensor-core reads
       tc_fence_after();
       if (elect_one()) {
@@ -380,14 +436,12 @@ __global__ void __launch_bounds__(PvCfg<D>::kThreads, PvCfg<D>::kCtasPerSm) resa
         mma_commit(smem_u32(&bar_empty[stg]));                 // the K codes of the stage have been read
       }
       __syncwarp();
-      if (lane == 0) attn_event(p, 6, i);
     };
     auto issue_pv = [&](int i) -> bool {
       const int vb = i & 1;
       bool got = true;
       if (lane == 0) got = mbar_wait(smem_u32(&bar_vpready[vb]), (i >> 1) & 1, &abort_flag, 9);
       if (!__all_sync(0xffffffffu, got)) return false;
-      if (lane == 0) attn_event(p, 7, i);
       tc_fence_after();
       if (elect_one()) {
         // A = V^T: M-major, 128-byte swizzle: 64-d blocks 16 KB apart (leading offset), 8-token groups 1 KB apart
@@ -405,7 +459,6 @@ __global__ void __launch_bounds__(PvCfg<D>::kThreads, PvCfg<D>::kCtasPerSm) resa
         mma_commit(smem_u32(&bar_pvdone[vb]));
       }
       __syncwarp();
-      if (lane == 0) attn_event(p, 8, i);
       return true;
     };
     if (my_tiles > 0) issue_qk(0);
@@ -414,7 +467,7 @@ __global__ void __launch_bounds__(PvCfg<D>::kThreads, PvCfg<D>::kCtasPerSm) resa
       if (!alive || !issue_pv(i)) break;
     }
   } else if (warp < kPvFirstConv) {
-    // ============================================================ copy producers (as in resattn_tc_kernel)
+    // ============================================================ copy producers
     constexpr int kCpr = C::kRowBytes / 16;
     constexpr int kRowsPerIt = 32 / kCpr;
     constexpr int kRowsW = kTile / kPvProd;                    // rows of a tile per producer warp (32 or 16)
@@ -494,7 +547,6 @@ __global__ void __launch_bounds__(PvCfg<D>::kThreads, PvCfg<D>::kCtasPerSm) resa
       asm volatile("bar.sync 3, %0;" ::"n"(kPvConv * 32) : "memory");
       if (!conv_go[vb]) break;
       const uint8_t* st = stage0 + stg * C::kStageBytes;
-      if (cv == 0 && lane == 0) attn_event(p, 4, i);
       const bool valid = (t_begin + i) * kTile + tok < L;
       uint4 c0 = make_uint4(0, 0, 0, 0), c1 = c0;
       uint32_t sfw = 0;
@@ -541,7 +593,6 @@ __global__ void __launch_bounds__(PvCfg<D>::kThreads, PvCfg<D>::kCtasPerSm) resa
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(smem_u32(&bar_vpready[vb]));
-        if (cv == 0) attn_event(p, 5, i);
       }
     }
   }
@@ -618,15 +669,11 @@ __global__ void __launch_bounds__(PvCfg<D>::kThreads, PvCfg<D>::kCtasPerSm) resa
   }
   if (failed && threadIdx.x == 0 && p.status) atomicExch(p.status, 1 + int(blockIdx.z) + (abort_flag << 16));
   __syncthreads();
-  if (p.out_nvfp4 && p.splits == 1 && threadIdx.x < G * (D / 16)) {
-    const int g = threadIdx.x / (D / 16), blk = threadIdx.x % (D / 16);
-    float v[16];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = stage_out[g * D + blk * 16 + i];
-    const int head = hkv * G + g, hidden = p.hq * D;
-    store_nvfp4_out16(v, __ldg(p.out_gs), static_cast<uint8_t*>(p.out) + int64_t(b) * (hidden / 2), p.out_sf, b,
-                      head * (D / 16) + blk, hidden);
-  }
+  // every CTA takes its ticket, also one whose waits expired (the status word flags that call), so that
+  // the counters are back at zero when the grid has finished
+  bool pack = p.out_nvfp4 && p.splits == 1;
+  if (p.splits > 1) pack = merge_splits_last_cta<D>(p, b, hkv, stage_out, &merge_flag) && p.out_nvfp4;
+  if (pack) pack_nvfp4_output<D>(p, b, hkv, stage_out);
   if (warp == kPvMmaWarp) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kPvTmemCols) : "memory");

@@ -7,8 +7,9 @@ follow from this library's kernel:
   * any page size that is a multiple of 16 is accepted (``pool.page_size``), not only 128;
   * the query quantisation (NVFP4 + NVFP4 residue) is fused into the decode kernel, so there is no
     separate quantiser launch and no cached Q scratch;
-  * there is one reducer, the deterministic merge kernel; a caller-supplied reduction workspace is
-    validated like the reference does and then used as the partial (o, l, m) buffers.
+  * there is one reducer, fused into the decode launch (the CTA that finishes last merges the partials in
+    split order); a caller-supplied reduction workspace is validated like the reference does, the
+    partial (o, l, m) buffers themselves live in this library's cached workspace.
 """
 from __future__ import annotations
 
@@ -125,7 +126,7 @@ def run_paged_fp4_decode_qmul4_tmem(q: torch.Tensor, pool: NvFp4PagedKVPool, v_d
     else:
         validate_decode_plan(plan, head_dim=d)
         splits, reduction = plan
-    del reduction                                    # one reducer: the merge kernel
+    del reduction                                    # one reducer: the merge fused into the decode launch
     lib = _cabi.load()
     ws_ptr, ws_bytes = None, 0
     if splits > 1:
@@ -141,7 +142,7 @@ def run_paged_fp4_decode_qmul4_tmem(q: torch.Tensor, pool: NvFp4PagedKVPool, v_d
                     raise ValueError(f"{name} must be contiguous with dtype in ({torch.float32},), shape "
                                      f"{shapes[0]}, on {q.device}, got shape={tuple(t.shape)} dtype={t.dtype} "
                                      f"device={t.device}")
-        ws = ops._workspace(q.device, need, "attn")
+        ws = ops._workspace(q.device, need, "attn", zero_prefix=lib.ri_resattn_counter_bytes(b, hq))
         ws_ptr, ws_bytes = ws.data_ptr(), need
     with torch.cuda.device(q.device):
         st = lib.ri_resattn_decode(
@@ -223,7 +224,7 @@ def run_paged_fp4_decode_qmul4_tmem_nvfp4(q: torch.Tensor, pool: NvFp4PagedKVPoo
     else:
         validate_decode_plan(plan, output_nvfp4=True, head_dim=d)
         splits, reduction = plan
-    del reduction, reduction_workspace                # one reducer (the merge kernel) with its own cached workspace
+    del reduction, reduction_workspace                # one reducer (fused into the decode launch) with its own cached workspace
     ops.resattn_decode(q, pool.k_data, pool.k_sf, v_data_hnd, v_sf_bthd, block_tables, seq_lens, float(sm_scale),
                        float(value_scale), out, splits=splits, max_kv_len=int(max_seq_len or 0),
                        out_global_scale=gsi, out_block_scale=output_block_scale)

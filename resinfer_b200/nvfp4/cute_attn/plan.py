@@ -2,10 +2,13 @@
 
 Keeps the reference's selection interface and policy names (csrc/resattn/plan.py:21-93):
 ``(splits, reducer)`` with reducer in {"none", "kernel", "cga_sharded", "gmem_fused"} and the
-RESIDUE_ATTN_REDUCTION policy {"legacy", "auto", "deterministic"}.  This library has one reducer -- the
-deterministic two-pass merge kernel -- so every plan whose split count is above one resolves to
-"kernel"; the cluster / fused reducers of the reference are accepted by ``validate_decode_plan`` for
-compatibility and executed as "kernel".  The split count itself is chosen for this library's kernel
+RESIDUE_ATTN_REDUCTION policy {"legacy", "auto", "deterministic"}.  This library has one reducer, fused
+into the decode launch: every CTA of a (sequence, KV head) takes a ticket and the one that draws the last
+ticket sums the split partials in split order (deterministic; the counterpart of the reference's
+"gmem_fused" reducer, csrc/resattn/kernel_paged_decode.py:2365-2431, without its spin wait).  Plans whose
+split count is above one are reported as "kernel" -- the name the reference gives its deterministic
+reducer -- and the other reducer names are accepted by ``validate_decode_plan`` for compatibility and run
+the same way.  The split count itself is chosen for this library's kernel
 (one CTA per SM at a time, 128-token tiles): enough CTAs to cover the SMs several times over while
 leaving every split at least a few tiles.
 """

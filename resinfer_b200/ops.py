@@ -5,6 +5,10 @@ These are the functions the reference-named modules (``nvfp4.cute_fold.host``,
 (device, size) like the reference caches its reduction workspaces
 (ShawRong/ResInfer quant/vllm_integration/attn/decode.py:23-53); nothing is allocated once a
 shape has been seen, so the calls stay CUDA-graph capturable after a warm-up.
+
+One rule follows from the sharing: calls that use the same cached workspace (same device, same kind,
+same size) must not overlap on the GPU -- issue them on one stream, or order the streams with events.
+The split tickets in a workspace are left at zero by every launch that completes.
 """
 from __future__ import annotations
 
@@ -13,6 +17,7 @@ import torch
 from . import _cabi
 
 _WORKSPACES: dict[tuple, torch.Tensor] = {}
+_TICKET_BYTES: dict[tuple, int] = {}
 _STATUS: dict[torch.device, torch.Tensor] = {}
 _GEMM_PLANS: dict[tuple, tuple] = {}
 
@@ -43,6 +48,7 @@ def _workspace(device, nbytes: int, tag: str, zero_prefix: int = 0) -> torch.Ten
         if zero_prefix:
             ws[:zero_prefix].zero_()
         _WORKSPACES[key] = ws
+        _TICKET_BYTES[key] = int(zero_prefix)
     return ws
 
 
@@ -57,11 +63,17 @@ def status_word(device) -> torch.Tensor:
 
 
 def check_status(device) -> None:
-    """Synchronising check of the status word (tests and debugging only)."""
+    """Synchronising check of the status word.  A non-zero word means that a bounded device-side wait
+    expired in some launch since the last check: that launch's output is invalid and it may have left
+    split tickets behind, so the ticket areas of the cached workspaces of the device are cleared before
+    the error is raised."""
     st = status_word(device)
     v = int(st.item())
     if v:
         st.zero_()
+        for key, ws in _WORKSPACES.items():
+            if key[0] == str(torch.device(device)) and _TICKET_BYTES.get(key):
+                ws[:_TICKET_BYTES[key]].zero_()
         raise RuntimeError(f"a device-side wait expired (status {v})")
 
 
@@ -154,7 +166,7 @@ def resattn_decode(q: torch.Tensor, k_data: torch.Tensor, k_sf: torch.Tensor, v_
         ws_bytes = 0
         if splits > 1:
             ws_bytes = lib.ri_resattn_workspace_bytes(b, hq, d, splits)
-            ws = _workspace(dev, ws_bytes, "attn")
+            ws = _workspace(dev, ws_bytes, "attn", zero_prefix=lib.ri_resattn_counter_bytes(b, hq))
         st = lib.ri_resattn_decode(
             q.data_ptr(), k_data.data_ptr(), k_sf.data_ptr(), v_data.data_ptr(), v_sf.data_ptr(), pages,
             block_tables.data_ptr(), block_tables.stride(0), seq_lens.data_ptr(), b, hq, hkv, d, page,

@@ -79,7 +79,7 @@ class PeerAllReduce:
     All ranks must call ``partial`` / ``reduce`` in the same order.  Raises RuntimeError if peer mapping is
     not possible (ranks on different nodes, IPC disabled); callers then stay with NCCL."""
 
-    def __init__(self, max_numel: int, group=None, slots: int = 2, device=None):
+    def __init__(self, max_numel: int, group=None, slots: int = 2, device=None, enable_pdl: bool = True):
         from .. import _cabi
         if not (dist.is_available() and dist.is_initialized()):
             raise RuntimeError("PeerAllReduce needs an initialised process group")
@@ -93,20 +93,32 @@ class PeerAllReduce:
         self.lib = _cabi.load()
         self.max_numel = (int(max_numel) + 7) // 8 * 8
         self.slots = slots
+        self.enable_pdl = enable_pdl
         self.slot_bytes = (2 * self.max_numel + 255) // 256 * 256
         flag_bytes = int(self.lib.ri_peer_allreduce_flag_bytes())
         self.flag_off = self.slots * self.slot_bytes
         total = self.flag_off + (flag_bytes + 255) // 256 * 256
-        # a private allocation (not a slice of a cached block that other tensors share)
-        self.local = torch.zeros(total, dtype=torch.uint8, device=self.device)
-        self.state = torch.zeros(int(self.lib.ri_peer_allreduce_state_bytes()), dtype=torch.uint8, device=self.device)
-        torch.cuda.synchronize(self.device)
-        handle = self.local.untyped_storage()._share_cuda_()
+        # Every step that can fail on one rank only is followed by an exchange of the outcome, so that all
+        # ranks raise together and none is left waiting in a collective the others never enter.
+        handle, err = None, None
+        try:
+            # a private allocation (not a slice of a cached block that other tensors share)
+            self.local = torch.zeros(total, dtype=torch.uint8, device=self.device)
+            self.state = torch.zeros(int(self.lib.ri_peer_allreduce_state_bytes()), dtype=torch.uint8, device=self.device)
+            self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+            torch.cuda.synchronize(self.device)
+            handle = self.local.untyped_storage()._share_cuda_()
+        except Exception as e:                                # IPC disabled, out of memory
+            err = f"rank {self.rank} cannot export its buffer: {type(e).__name__}: {e}"
         handles = [None] * self.world
-        dist.all_gather_object(handles, handle, group=group)
+        dist.all_gather_object(handles, (handle, err), group=group)
+        errs = [e for _, e in handles if e]
+        if errs:
+            raise RuntimeError("; ".join(errs))
         self._peer_storages = []
         self.bases = []
-        for r, h in enumerate(handles):
+        err = None
+        for r, (h, _) in enumerate(handles):
             if r == self.rank:
                 self.bases.append(self.local.data_ptr())
                 continue
@@ -114,16 +126,21 @@ class PeerAllReduce:
                 with torch.cuda.device(self.device):
                     st = torch.UntypedStorage._new_shared_cuda(self.device.index, *h[1:])
             except Exception as e:                            # not on this node, no peer access, IPC refused
-                raise RuntimeError(f"cannot map the buffer of rank {r}: {type(e).__name__}: {e}") from e
+                err = f"rank {self.rank} cannot map the buffer of rank {r}: {type(e).__name__}: {e}"
+                break
             self._peer_storages.append(st)
             self.bases.append(st.data_ptr())
+        outcomes = [None] * self.world
+        dist.all_gather_object(outcomes, err, group=group)   # also: every rank has mapped every buffer
+        errs = [e for e in outcomes if e]
+        if errs:
+            raise RuntimeError("; ".join(errs))
         import ctypes
         self._ct = ctypes
         self._flag_ptrs = (ctypes.c_void_p * self.world)(*[b + self.flag_off for b in self.bases])
         self._data_ptrs = [(ctypes.c_void_p * self.world)(*[b + s * self.slot_bytes for b in self.bases])
                            for s in range(self.slots)]
         self._next = 0
-        dist.barrier(group=group)                              # every rank has mapped every buffer
 
     def partial(self, shape, dtype=torch.bfloat16) -> torch.Tensor:
         """The next partial buffer of this rank as a tensor of ``shape`` (row-major, BF16)."""
@@ -142,7 +159,13 @@ class PeerAllReduce:
         return t
 
     def reduce(self, partial: torch.Tensor, out: torch.Tensor | None = None, status: torch.Tensor | None = None) -> torch.Tensor:
-        """Sum ``partial`` (a tensor from ``partial()``) over the ranks into ``out`` (local BF16, same shape)."""
+        """Sum ``partial`` (a tensor from ``partial()``) over the ranks into ``out`` (local BF16, same shape).
+
+        The kernel waits for the peers for about ten seconds at most.  If a peer never announces its partial
+        the kernel writes THIS rank's partial to ``out`` (a defined value, not the sum) and stores
+        ``0x40000000 | missing_rank << 8 | rank`` in the status word: ``status`` if given, else this object's
+        own word, which ``check()`` reads.  Callers that cannot tolerate a silent local-only result call
+        ``check()`` at a point where a device synchronisation is acceptable (end of a step)."""
         from .. import _cabi
         slot = getattr(partial, "_ri_slot", None)
         if slot is None:
@@ -151,9 +174,19 @@ class PeerAllReduce:
             out = torch.empty(partial.shape, dtype=torch.bfloat16, device=self.device)
         if out.dtype != torch.bfloat16 or out.numel() != partial.numel() or not out.is_contiguous():
             raise ValueError("out must be a contiguous BF16 tensor of the partial's size")
+        word = self.status if status is None else status
         st = self.lib.ri_peer_allreduce_bf16(self._data_ptrs[slot], self._flag_ptrs, self.rank, self.world,
                                              partial.numel(), out.data_ptr(), self.state.data_ptr(),
-                                             0 if status is None else status.data_ptr(),
-                                             _cabi.current_stream(self.device))
+                                             word.data_ptr(), _cabi.current_stream(self.device),
+                                             int(self.enable_pdl))
         _cabi.check(st, "peer all-reduce")
         return out
+
+    def check(self) -> None:
+        """Synchronising read of this object's status word; raises RuntimeError (and clears the word) when a
+        reduce gave up waiting for a peer since the last check."""
+        v = int(self.status.item())
+        if v:
+            self.status.zero_()
+            raise RuntimeError(f"peer all-reduce: rank {v & 0xFF} gave up waiting for rank {(v >> 8) & 0xFF} "
+                               f"(status 0x{v & 0xFFFFFFFF:08x}); the output of that call is the local partial")

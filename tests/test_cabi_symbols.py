@@ -48,12 +48,13 @@ def test_argument_validation_needs_no_gpu(lib):
     assert st == _cabi.RI_ERR_ARG and b"GQA4/6/8" in lib.ri_last_error()
     st = lib.ri_fp4_gemm(None, 0, None, 0, None, 0, None, 0, None, 0, None, 0, 0, 4, 128, 100, 0, 0, 1, None, 0, None, 0, None)
     assert st == _cabi.RI_ERR_ARG and b"multiple of 64" in lib.ri_last_error()
-    assert lib.ri_resattn_workspace_bytes(2, 64, 128, 4) == 4 * 2 * 64 * (128 + 2) * 4
+    assert lib.ri_resattn_counter_bytes(2, 64) == 512
+    assert lib.ri_resattn_workspace_bytes(2, 64, 128, 4) == 512 + 4 * 2 * 64 * (128 + 2) * 4
     assert lib.ri_fp4_gemm_workspace_bytes(16, 5120, 8192, 0, 1, 1) == 0
     assert lib.ri_fp4_gemm_workspace_bytes(16, 5120, 8192, 0, 1, 4) > 4 * 40 * 128 * 32 * 4
-    st = lib.ri_peer_allreduce_bf16(None, None, 0, 1, 64, None, None, None, None)
+    st = lib.ri_peer_allreduce_bf16(None, None, 0, 1, 64, None, None, None, None, 0)
     assert st == _cabi.RI_ERR_ARG and b"2..8 ranks" in lib.ri_last_error()
-    st = lib.ri_peer_allreduce_bf16(None, None, 1, 2, 12, None, None, None, None)
+    st = lib.ri_peer_allreduce_bf16(None, None, 1, 2, 12, None, None, None, None, 0)
     assert st == _cabi.RI_ERR_ARG and b"multiple of 8" in lib.ri_last_error()
     assert lib.ri_peer_allreduce_flag_bytes() == 32 and lib.ri_peer_allreduce_state_bytes() == 8
 

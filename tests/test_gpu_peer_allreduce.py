@@ -1,5 +1,10 @@
-"""One-shot peer-memory all-reduce (ri_peer_allreduce_bf16) on two GPUs of one node: bit-exact against the
-rank-ordered FP32 sum, eager and under CUDA-graph replay.  Needs two GPUs; skipped otherwise."""
+"""One-shot peer-memory all-reduce (ri_peer_allreduce_bf16).
+
+Two GPUs of one node: bit-exact against the rank-ordered FP32 sum, eager and under CUDA-graph replay (skipped
+with fewer than two GPUs).  One GPU: the bounded wait.  Rank 0 of a two-rank group is launched alone, with both
+ranks' buffers in this process's memory; nothing ever sets rank 1's flag, so the wait runs out after the
+(shortened) limit, the status word names the missing rank, the output holds rank 0's own partial, and the next
+call works normally once the missing announcement is written by hand -- the context stays usable."""
 import os
 import subprocess
 import sys
@@ -20,3 +25,47 @@ def test_peer_allreduce_two_ranks():
                         os.path.join(here, "peer_allreduce_worker.py")],
                        capture_output=True, text=True, timeout=300, env=env)
     assert r.returncode == 0 and "PEER_ALLREDUCE_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
+
+
+def test_wait_for_a_missing_peer_runs_out_and_reports(cuda_device):
+    import ctypes
+
+    from resinfer_b200 import _cabi
+    lib = _cabi.load()
+    dev = cuda_device
+    n = 4096
+    parts = [torch.randn(n, device=dev).to(torch.bfloat16) for _ in range(2)]
+    flags = [torch.zeros(lib.ri_peer_allreduce_flag_bytes() // 4, dtype=torch.int32, device=dev) for _ in range(2)]
+    state = torch.zeros(lib.ri_peer_allreduce_state_bytes(), dtype=torch.uint8, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    out = torch.zeros(n, dtype=torch.bfloat16, device=dev)
+    data_ptrs = (ctypes.c_void_p * 2)(*[p.data_ptr() for p in parts])
+    flag_ptrs = (ctypes.c_void_p * 2)(*[f.data_ptr() for f in flags])
+    call = lambda: lib.ri_peer_allreduce_bf16(data_ptrs, flag_ptrs, 0, 2, n, out.data_ptr(), state.data_ptr(),   # noqa: E731
+                                              status.data_ptr(), _cabi.current_stream(dev), 0)
+    lib.ri_peer_allreduce_set_wait_ms(200)
+    try:
+        assert call() == 0
+        torch.cuda.synchronize()
+        assert int(status.item()) == (0x40000000 | (1 << 8) | 0)
+        assert torch.equal(out, parts[0])                     # a defined value: the local partial
+        # rank 0 announced call 1 to both flag arrays
+        assert int(flags[0][0].item()) == 1 and int(flags[1][0].item()) == 1
+        # the second call: write rank 1's announcement of call 2 by hand; the sum now comes out
+        status.zero_()
+        flags[0][1] = 2
+        assert call() == 0
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        assert torch.equal(out, (parts[0].float() + parts[1].float()).to(torch.bfloat16))
+    finally:
+        lib.ri_peer_allreduce_set_wait_ms(10000)
+
+
+def test_status_check_raises_and_clears(cuda_device):
+    from resinfer_b200 import ops
+    st = ops.status_word(cuda_device)
+    st.fill_(7)
+    with pytest.raises(RuntimeError, match="status 7"):
+        ops.check_status(cuda_device)
+    ops.check_status(cuda_device)                            # cleared by the failed check

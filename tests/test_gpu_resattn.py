@@ -236,3 +236,54 @@ def test_decode_late_maxima_rescale_accumulators(cuda_device, device_rcp, d, spl
     got = out32.cpu().numpy()
     assert np.isfinite(got).all()
     assert rel_fro(got, ref) < TOL_BF16
+
+
+@pytest.mark.parametrize("d,page", [(128, 16), (256, 16), (128, 128)])
+def test_decode_batch32_matches_oracle(cuda_device, device_rcp, d, page):
+    """Batch 32 with short, ragged contexts (including an empty sequence and exact tile / page multiples):
+    batch indexing, block-table row strides and per-sequence lengths beyond a handful of sequences."""
+    hkv, g = 2, 8
+    rng = np.random.default_rng(32)
+    lens = [int(v) for v in rng.integers(1, 700, size=32)]
+    lens[3], lens[7], lens[11], lens[30] = 0, 128, 256, 129
+    kv = O.make_paged_kv(lens, hkv, d, page, seed=77)
+    b, hq = len(lens), hkv * g
+    q_np = O.bf16_round(rng.standard_normal((b, hq, d)).astype(np.float32))
+    sm = d ** -0.5
+    ref = O.resattn_decode_reference(q_np, kv, sm, rcp=O.RecordingRcp(device_rcp))
+    for splits in (1, 3):
+        out32, _, _ = _run(cuda_device, kv, q_np, sm, splits)
+        got = out32.cpu().numpy()
+        assert np.isfinite(got).all()
+        assert rel_fro(got, ref) < TOL_BF16
+        # per sequence as well: one wrong row of the block table must not hide among 31 right ones
+        for i, L in enumerate(lens):
+            if L == 0:
+                assert not got[i].any()
+            else:
+                assert rel_fro(got[i], ref[i]) < 2 * TOL_BF16, (i, L)
+
+
+def test_distance_from_exact_and_from_reference_rounding(cuda_device, device_rcp):
+    """Where the kernel's numerics sit.  The reference kernel rounds P and the dequantised V to E4M3 before
+    its FP8 P.V product (csrc/resattn/kernel_paged_decode.py:1958-1963, qmul4.py:45); this kernel keeps V
+    exact (FP4 code x E4M3 scale fits FP16) and P in FP16.  Against the exact attention over the
+    dequantised cache the kernel must therefore be much closer than the oracle run with the reference's
+    E4M3 rounding is, and its distance from that E4M3-mode oracle must equal the rounding's own distance
+    from exact (the kernel adds nothing measurable on top).  The three numbers are printed (-s)."""
+    d, page, hkv, g = 128, 16, 2, 8
+    lens = [3000, 1200, 257]
+    # FP8-range cache (global scale amax/448): the E4M3 expansion of V then never saturates
+    kv = O.make_paged_kv(lens, hkv, d, page, seed=9, scale_range=448.0)
+    q_np = O.bf16_round(np.random.default_rng(6).standard_normal((len(lens), hkv * g, d)).astype(np.float32))
+    sm = d ** -0.5
+    rcp = O.RecordingRcp(device_rcp)
+    exact = O.resattn_decode_reference(q_np, kv, sm, rcp=rcp)
+    e4m3 = O.resattn_decode_reference(q_np, kv, sm, rcp=rcp, p_e4m3=True, v_e4m3=True)
+    out32, _, _ = _run(cuda_device, kv, q_np, sm, 2)
+    got = out32.cpu().numpy()
+    d_exact, d_e4m3, d_round = rel_fro(got, exact), rel_fro(got, e4m3), rel_fro(e4m3, exact)
+    print(f"kernel vs exact {d_exact:.3e}; kernel vs E4M3-mode oracle {d_e4m3:.3e}; E4M3-mode vs exact {d_round:.3e}")
+    assert d_exact < TOL_BF16
+    assert d_exact < 0.5 * d_round
+    assert abs(d_e4m3 - d_round) < 0.25 * d_round + TOL_BF16
