@@ -283,7 +283,9 @@ def main():
                          "and print them as a second JSON line {\"sweeps\": ...}; N = 1 only")
     ap.add_argument("--only", default=None,
                     help="profiling aid: 'gemm:<shape>:<M>' times that single (shape, M) case, 'resattn:<index>' "
-                         "that single ResAttn point; no e2e, no CPU baseline, not a bench value")
+                         "that single ResAttn point, 'kext:<shape>:<M>:<ratio>' one KEXT case (ratio 1.0 = K-concat "
+                         "MEXT), 'quant:<M>:<K>' the NVFP4 MEXT quantiser alone; plain launches, no e2e, no CPU "
+                         "baseline, not a bench value")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
@@ -322,6 +324,10 @@ def main():
             res = measure_resattn(torch, dev, ops, None, None, hbm_gbs, only=int(rest), steps=args.steps,
                                   warmup=args.warmup)
             print(json.dumps({"only": args.only, "resattn": res}), flush=True)
+            return
+        if kind in ("kext", "quant"):
+            print(json.dumps({"only": args.only, "result": run_single_case(torch, dev, kind, rest, args.steps, args.warmup)}),
+                  flush=True)
             return
         shape, _, m_only = rest.partition(":")
         SHAPES = [s for s in SHAPES if s[0] == shape]
@@ -702,6 +708,71 @@ def main():
         os._exit(0)
 
 
+def run_single_case(torch, dev, kind, rest, steps, warmup):
+    """`--only kext:<shape>:<M>:<ratio>` / `--only quant:<M>:<K>`: plain launches of one case on the current
+    stream (what a profiler is pointed at), timed with CUDA events.  Weights rotate over copies larger than L2."""
+    from resinfer_b200 import nvfp4, ops
+    from resinfer_b200.nvfp4.quant import indices_to_channel_masks
+    from resinfer_b200.quant import weight_prep
+    parts = rest.split(":")
+    g = torch.Generator(device=dev).manual_seed(0)
+
+    def act(m, k):
+        x = torch.randn(m, k, generator=g, device=dev, dtype=torch.float32)
+        x[:, torch.randperm(k, generator=g, device=dev)[: max(1, k // 100)]] *= 20.0
+        return x.to(torch.bfloat16)
+
+    if kind == "quant":
+        m, k = int(parts[0]), int(parts[1])
+        x = act(m, k)
+        gi = torch.tensor([100.0], dtype=torch.float32, device=dev)
+        xs = [x.clone() for _ in range(max(2, min(8, (2 * L2_BYTES) // (2 * m * k) + 1)))]
+        fn = lambda i: nvfp4.scaled_fp4_quant_mext_r1(xs[i % len(xs)], gi, layout_mode=1)    # noqa: E731
+        nbytes = 2 * m * k + 2 * m * k * (0.5 + 1.0 / 16)
+        flops = 0.0
+    else:
+        name, m, ratio = parts[0], int(parts[1]), float(parts[2])
+        k, n = next((kk, nn) for nm, kk, nn, _ in SHAPES if nm == name)
+        per8 = {0.125: 1, 0.25: 2, 0.5: 4, 1.0: 8}[ratio]
+        idx = None if per8 == 8 else weight_prep.salient_indices_per8(k, per8, device=dev)
+        w = (torch.randn(n, k, generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+        prep = weight_prep.quantize_weight_nvfp4(w, idx)
+        del w
+        nb = prep["weight"].numel() + prep["weight_scale"].numel()
+        copies = max(2, min(8, -(-2 * L2_BYTES // nb)))
+        ws = [prep["weight"].clone() for _ in range(copies)]
+        sfs = [prep["weight_scale"].clone() for _ in range(copies)]
+        s = 0 if idx is None else idx.numel()
+        mask = None if idx is None else indices_to_channel_masks(idx, k)
+        x = act(m, k)
+        gs = float(x.float().abs().max()) / (6.0 * 448.0)
+        gi = torch.tensor([1.0 / gs], dtype=torch.float32, device=dev)
+        alpha = (prep["weight_global_scale"] * gs).float().reshape(1)
+        y = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+
+        def fn(i):
+            c = i % copies
+            if per8 == 8:
+                codes, sf = nvfp4.scaled_fp4_quant_mext_r1(x, gi, layout_mode=3)
+                return ops.fp4_gemm(codes, sf, ws[c], sfs[c], alpha, m=m, fmt="nvfp4", layout="concat_k", out=y)
+            codes, sf = nvfp4.scaled_fp4_quant_with_mask(x, gi, mask, s, use_swapped_residue=False)
+            return ops.fp4_gemm(codes, sf, ws[c], sfs[c], alpha, m=m, fmt="nvfp4", layout="plain", out=y)
+        k_eff = 2 * k if per8 == 8 else k + s
+        nbytes = 2 * m * k + k / 8 + n * (k if per8 == 8 else k + s) * 0.5625 + 2 * m * n
+        flops = 2.0 * m * n * k_eff
+    for i in range(max(1, warmup)):
+        fn(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(max(1, steps)):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) / max(1, steps) * 1e3
+    return {"us": round(us, 2), "gbs": round(nbytes / us / 1e3), "tflops": round(flops / us / 1e6, 1)}
+
+
 def measure_detail(torch, dev, layers, outs, nvfp4, ops, capture, timed, hbm_gbs):
     """Per-case latency (cold weights: rotating copies larger than L2) and a ResAttn decode point."""
     cases = []
@@ -845,7 +916,9 @@ def measure_sweeps(torch, dev, capture, timed, hbm_gbs):
 RESATTN_POINTS = ((128, 8, 16), (128, 64, 16), (256, 32, 16),
                   (128, 1, 16), (128, 32, 16), (128, 128, 16), (128, 256, 16),
                   (256, 1, 16), (256, 8, 16), (256, 128, 16), (256, 256, 16),
-                  (128, 1, 128), (128, 8, 128), (128, 64, 128), (128, 256, 128), (256, 32, 128), (256, 128, 128))
+                  (128, 1, 128), (128, 8, 128), (128, 64, 128), (128, 256, 128), (256, 32, 128), (256, 128, 128),
+                  # fixed context lengths, page 128: the cases of the reference's own published latency plot
+                  (128, 1, 128, 8192), (128, 8, 128, 32768), (128, 32, 128, 32768), (128, 64, 128, 32768))
 
 
 def measure_resattn(torch, dev, ops, capture, timed, hbm_gbs, only=None, steps=10, warmup=3, custom=None,
@@ -858,11 +931,15 @@ def measure_resattn(torch, dev, ops, capture, timed, hbm_gbs, only=None, steps=1
     res = []
     hq, hkv = heads
     sms = torch.cuda.get_device_properties(dev).multi_processor_count
-    for idx, (d, batch, page) in enumerate(points if custom is None else (custom,)):
+    for idx, point in enumerate(points if custom is None else (custom,)):
+        d, batch, page = point[:3]
+        fixed_len = point[3] if len(point) > 3 else None
         if only is not None and idx != only:
             continue
         g = torch.Generator(device=dev).manual_seed(3)
         lens = torch.randint(1024, 32769, (batch,), generator=g, device=dev, dtype=torch.int32)
+        if fixed_len:
+            lens = torch.full((batch,), fixed_len, device=dev, dtype=torch.int32)
         pages_per = (lens + page - 1) // page
         total = int(pages_per.sum())
         pool = int(total * 1.1) + 1
@@ -895,7 +972,8 @@ def measure_resattn(torch, dev, ops, capture, timed, hbm_gbs, only=None, steps=1
             us = timed(capture(call), 10, 3) * 1e3
         tokens = int(lens.sum())
         nbytes = tokens * hkv * d * 2 * (0.5 + 1 / 16) + 4 * batch * hq * d + 4 * total
-        res.append({"head_dim": d, "batch": batch, "page": page, "tokens": tokens, "splits": splits, "us": round(us, 1),
+        res.append({"head_dim": d, "batch": batch, "page": page, "context": fixed_len or "U[1024,32768]", "tokens": tokens,
+                    "splits": splits, "us": round(us, 1),
                     "tbs": round(nbytes / us / 1e6, 3), "frac_hbm": round(nbytes / us / 1e3 / hbm_gbs, 3),
                     "kv_bytes_gt_l2": bool(nbytes > L2_BYTES)})
         del kd, vd, ks, vs, q, out, bt

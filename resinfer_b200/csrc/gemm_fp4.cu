@@ -18,8 +18,9 @@
 //     whole tiles, even K splits or ragged ranges, chosen by a measured cost model.  K-split tiles
 //     exchange FP32 partials through a caller workspace; the contributor that arrives last (atomic
 //     ticket, nobody waits) sums them in CTA order, so the result is deterministic.
-// Warp roles (11 warps): warp 0 = weight TMA producer, warp 10 = activation TMA producer, warp 1 =
-// MMA issuer (owns tensor memory), warps 2-5 = epilogue, warps 6-9 = scale warps.  Every mbarrier
+// Warp roles (12 warps): warp 0 = weight TMA producer, warp 10 = activation TMA producer, warp 11 =
+// producer of the activation scales, warp 1 = MMA issuer (owns tensor memory), warps 2-5 = epilogue,
+// warps 6-9 = scale warps.  Every mbarrier
 // wait is bounded: on expiry the kernel records a status word, stops issuing and tears down normally.
 //
 // Stands in for the reference's CuTeDSL Fold kernel (ShawRong/ResInfer
@@ -38,7 +39,7 @@ namespace {
 constexpr int kTileW = 128;       // weight rows per CTA (MMA M)
 constexpr int kTileKBytes = 128;  // 256 FP4 per K tile
 constexpr int kMmaPerTile = 4;    // 4 x K64 instructions per K tile
-constexpr int kThreads = 352;       // 11 warps: W producer, MMA, 4 epilogue, 4 scale, activation producer
+constexpr int kThreads = 384;       // 12 warps: W producer, MMA, 4 epilogue, 4 scale, activation producer, activation-scale producer
 constexpr int kTmemCols = 512;
 constexpr int kSfCol = 256;        // first tensor-memory column of the block-scale sets
 constexpr int kMaxSfSets = 10;      // = kMaxStages: one scale set per pipeline stage when tensor memory allows
@@ -111,6 +112,16 @@ __device__ __forceinline__ void stamp(const GemmParams& p, int slot) {
   }
 #endif
 }
+// per-unit event times of the first two CTAs (development builds): row `ev`, first 24 units
+__device__ __forceinline__ void trace_ev(const GemmParams& p, int ev, int unit) {
+#ifdef RI_GEMM_TRACE
+  if (p.trace && blockIdx.x < 2 && unit < 24) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    p.trace[8 * 296 + (blockIdx.x * 8 + ev) * 24 + unit] = (long long)t;
+  }
+#endif
+}
 __device__ __forceinline__ long long range_start(const GemmParams& p, int c) {
   if (p.tile_granular) return ((long long)c * p.tiles / p.grid) * p.k_tiles;
   return (long long)c * p.units / p.grid;
@@ -139,7 +150,84 @@ struct Walk {
   }
 };
 
+// ---- helpers of the two-CTA variant (a cluster of two CTAs works on one 256-row weight tile)
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {      // every thread of both CTAs
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrive on the mbarrier at the same shared-memory offset in the leader CTA (rank 0) of the pair.  From
+// the other CTA this is a relaxed arrive: the default release at cluster scope costs about 1 us per call
+// (measured), which the scale warps would pay for every K tile, and nothing needs it here -- what the
+// arrive announces are tensor-memory stores and loads that this thread has already waited for
+// (tcgen05.wait), not generic-proxy writes.
+__device__ __forceinline__ void mbar_arrive_leader(uint32_t bar, int rank) {
+  if (rank == 0) {
+    mbar_arrive(bar);
+    return;
+  }
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(bar), "r"(0));
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
+}
+// completion of this thread's earlier MMAs -> the mbarrier at this offset in BOTH CTAs of the pair
+__device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
 template <bool MX>
+__device__ __forceinline__ void mma_fp4_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
+  if constexpr (MX) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf4.block_scale.block32 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb) : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb) : "memory");
+  }
+}
+// Bounded wait on a barrier that the other CTA of the pair completes (its arrives, or the leader's
+// multicast commits).  Polls without a suspend-time hint: a thread put to sleep by the hinted form was
+// woken late when the completing arrive came from the other SM (measured: about 1.5 us per K tile).
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag, int site) {
+  long long t0 = 0;
+  for (uint32_t spin = 0;; ++spin) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    if (ok) return true;
+    if ((spin & 255u) == 255u) {
+      if (*abort_flag) return false;
+      const long long now = clock64();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kWaitLimitCycles) { *abort_flag = site; return false; }
+    }
+  }
+}
+template <bool PAIR>
+__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag, int site) {
+  if constexpr (PAIR) return mbar_wait_cluster(bar, parity, abort_flag, site);
+  else return mbar_wait(bar, parity, abort_flag, site);
+}
+
+// PAIR = false: one CTA per 128-row weight tile (all plans, K splits included).
+// PAIR = true: clusters of two CTAs, tcgen05.mma.cta_group::2.  A pair owns 256 weight rows and n_tile token
+// columns: CTA r loads weight rows 128 r .. of the pair's tile and HALF of the activation tile (rows
+// n_tile / 2 * r ..) with its own plain TMA loads -- no multicast -- so an SM takes in half as many
+// activation bytes per weight byte; the MMA of the leader CTA (rank 0) reads both halves and writes 128
+// accumulator rows in each CTA's tensor memory; each CTA writes its own 128 output features.  Block
+// scales: every CTA loads the scales of its own weight rows and of ALL token columns.  Only whole tiles
+// (no K split).  Cross-CTA signals: the scale warps of both CTAs arrive on the leader's scale barrier (an
+// arrival implies that CTA's stage has landed), the leader's commits arrive on the barriers of both CTAs,
+// both epilogues arrive on the leader's accumulator-free barrier.
+template <bool MX, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap act_map,
                 const GemmParams p) {
@@ -159,14 +247,15 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int cta = blockIdx.x;
+  const int rank = PAIR ? int(cluster_rank()) : 0;          // CTA of the pair; rank 0 issues the MMAs
+  const int cta = PAIR ? int(blockIdx.x >> 1) : int(blockIdx.x);   // index of the unit range (pairs share one)
   if (threadIdx.x == 0) stamp(p, 0);
   const long long u_begin = range_start(p, cta);
   const long long u_end = range_start(p, cta + 1);
   const bool kcat = p.layout == RI_GEMM_CONCAT_K;
   const int halves = kcat ? 2 : 1;
   const int row_tiles = (p.n_tile + 127) / 128;             // scale row tiles per activation tile
-  const int act_tile_bytes = p.n_tile * kTileKBytes;
+  const int act_tile_bytes = (PAIR ? p.n_tile / 2 : p.n_tile) * kTileKBytes;   // activation rows this CTA loads
   const int nbuf = p.n_tile <= 128 ? 2 : 1;                  // accumulator buffers in tensor memory
 
   // Set-up.  Warp 0 (the weight producer) initialises the barriers and only *arrives* at the set-up
@@ -183,10 +272,10 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
       }
       for (int b = 0; b < 2; ++b) {
         mbar_init(smem_u32(&bar_acc_full[b]), 1);
-        mbar_init(smem_u32(&bar_acc_empty[b]), 1);
+        mbar_init(smem_u32(&bar_acc_empty[b]), PAIR ? 2 : 1);   // pair: the epilogues of both CTAs
       }
       for (int s = 0; s < kMaxSfSets; ++s) {
-        mbar_init(smem_u32(&bar_sf_full[s]), 4);     // one arrival per scale warp
+        mbar_init(smem_u32(&bar_sf_full[s]), PAIR ? 8 : 4);     // one arrival per scale warp (of both CTAs)
       }
       abort_flag = 0;
       is_last_cta = 0;
@@ -198,9 +287,15 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
     asm volatile("bar.arrive 2, %0;" ::"n"(kThreads) : "memory");
   } else {
     if (warp == 1) {
-      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                   ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemCols) : "memory");
-      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+      if constexpr (PAIR) {       // one warp of each CTA of the pair executes the pair allocation
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+      } else {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+      }
     }
     if (warp == 10 && lane == 0)
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&act_map)) : "memory");
@@ -209,20 +304,25 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
     tc_fence_after();
     tmem_base = tmem_base_slot;
   }
+  // pair: the barriers of both CTAs exist before anybody signals across the pair
+  if constexpr (PAIR) cluster_sync_all();
   if (threadIdx.x == 32) stamp(p, 1);
 
-  if (warp == 0 || warp == 10) {
+  if (warp == 0 || warp >= 10) {
     // ------------------------------------------------------------------ TMA producers
-    // two issuing threads in different warps so that their issue costs overlap: warp 0 arms the
-    // barrier and loads the weight tile and its scales, warp 10 loads the activation tile(s) and
-    // their scales
+    // Three issuing threads in three warps.  Issuing a copy occupies the issuing warp for 0.15-0.3 us
+    // (measured), so a thread that issued all four to six copies of a K tile paced the whole pipeline;
+    // in different warps the issue costs overlap.  Warp 0 arms the barrier and loads the weight tile and
+    // its scales, warp 10 loads the activation tile(s), warp 11 the activation scales.
     const bool w_role = warp == 0;
+    const bool act_tile_role = warp == 10;
     if (lane == 0) {
       const uint32_t sf_stride = p.chunks * 512;           // bytes of a full tile's scale chunks
       const int n_units = int(u_end - u_begin);
       Walk w;
       w.init(p, u_begin);
       int cur_tile = -1, w_tile = 0, tok_tile = 0, first_row_tile = 0, valid_row_tiles = 0;
+      bool w_sf_valid = true;                                // pair: the odd last tile has no second half
       const uint8_t* w_sf_tile = nullptr;
       if (!w_role) asm volatile("griddepcontrol.wait;" ::: "memory");   // activations come from the previous kernel
       for (int i = 0; i < n_units; ++i, w.next(p)) {
@@ -230,6 +330,8 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
           cur_tile = w.tile;
           w_tile = cur_tile / p.tok_tiles;
           tok_tile = cur_tile - w_tile * p.tok_tiles;
+          if constexpr (PAIR) w_tile = 2 * w_tile + rank;     // this CTA's 128 rows of the pair's 256
+          w_sf_valid = w_tile * kTileW < p.n;
           first_row_tile = (tok_tile * p.n_tile) >> 7;
           valid_row_tiles = 0;
           for (int t = 0; t < row_tiles; ++t)
@@ -241,19 +343,25 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
         const int n_mma = rem >= 256 ? kMmaPerTile : rem >> 6;
         const uint32_t sf_bytes = uint32_t(MX ? (n_mma + 1) >> 1 : n_mma) * 512;
         if (w.it >= p.stages) {
-          if (!mbar_wait(smem_u32(&bar_empty[w.stage]), w.stage_par ^ 1, &abort_flag, w_role ? 1 : 2)) break;
+          if (!wait_bar<PAIR>(smem_u32(&bar_empty[w.stage]), w.stage_par ^ 1, &abort_flag, w_role ? 1 : 2)) break;
         }
         uint8_t* st = smem + w.stage * p.stage_bytes;
         const uint32_t full = smem_u32(&bar_full[w.stage]);
+        trace_ev(p, w_role ? 0 : (act_tile_role ? 1 : 7), i);
         if (w_role) {
-          const uint32_t tx = kTileW * kTileKBytes + sf_bytes + halves * (act_tile_bytes + valid_row_tiles * sf_bytes);
+          const uint32_t tx = kTileW * kTileKBytes + (w_sf_valid ? sf_bytes : 0u) +
+                              halves * (act_tile_bytes + valid_row_tiles * sf_bytes);
           mbar_expect_tx(full, tx);
-          tma_load_2d(smem_u32(st), &w_map, w.kt * kTileKBytes, w_tile * kTileW, full);
-          bulk_load_1d(smem_u32(st + p.smem_sfa_off), w_sf_tile + w.kt * sf_stride, sf_bytes, full);
+          tma_load_2d(smem_u32(st), &w_map, w.kt * kTileKBytes, w_tile * kTileW, full);   // rows past N read as zero
+          if (w_sf_valid) bulk_load_1d(smem_u32(st + p.smem_sfa_off), w_sf_tile + w.kt * sf_stride, sf_bytes, full);
         } else {
           for (int h = 0; h < halves; ++h) {
-            tma_load_2d(smem_u32(st + p.smem_act_off + h * act_tile_bytes), &act_map,
-                        w.kt * kTileKBytes + h * p.act_res_col0, tok_tile * p.n_tile, full);
+            if (act_tile_role) {
+              tma_load_2d(smem_u32(st + p.smem_act_off + h * act_tile_bytes), &act_map,
+                          w.kt * kTileKBytes + h * p.act_res_col0,
+                          tok_tile * p.n_tile + (PAIR ? rank * (p.n_tile / 2) : 0), full);
+              continue;
+            }
             for (int t = 0; t < row_tiles; ++t) {
               if (first_row_tile + t >= p.act_row_tiles) continue;
               const uint8_t* src = p.act_sf + int64_t(first_row_tile + t) * p.act_sf_tile_stride +
@@ -266,10 +374,10 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    {   // the whole warp walks the loop (converged); one elected lane issues the tcgen05 instructions
+    if (!PAIR || rank == 0) {   // the whole warp walks the loop (converged); one elected lane issues the tcgen05 instructions
       // instruction descriptor: E2M1 x E2M1, K-major A and B, M = 128, N = n_tile
       const uint32_t idesc_base = (1u << 7) | (1u << 10) | (uint32_t(p.n_tile >> 3) << 17) |
-                                  (MX ? (1u << 23) : 0u) | (uint32_t(kTileW >> 4) << 24);
+                                  (MX ? (1u << 23) : 0u) | (uint32_t((PAIR ? 2 * kTileW : kTileW) >> 4) << 24);
       bool ok = true;
       const int n_units = int(u_end - u_begin);
       Walk w;
@@ -278,19 +386,21 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
       while (i < n_units && ok) {
         const int buf = nbuf == 2 ? (seg & 1) : 0;
         if (seg >= nbuf) {                          // the epilogue must have drained this buffer
-          const bool got = mbar_wait(smem_u32(&bar_acc_empty[buf]), ((seg / nbuf) - 1) & 1, &abort_flag, 3);
+          const bool got = wait_bar<PAIR>(smem_u32(&bar_acc_empty[buf]), ((seg / nbuf) - 1) & 1, &abort_flag, 3);
           if (!__all_sync(0xffffffffu, got)) { ok = false; break; }       // warp-uniform decision
           tc_fence_after();
         }
         const uint32_t d_tmem = tmem_base + buf * p.n_tile;
         uint32_t accumulate = 0;
         for (;;) {                                  // K tiles of this segment (same output tile)
-          bool got = mbar_wait(smem_u32(&bar_full[w.stage]), w.stage_par, &abort_flag, 4);
+          bool got = wait_bar<PAIR>(smem_u32(&bar_full[w.stage]), w.stage_par, &abort_flag, 4);
           // the scale warps have put this K tile's block scales into scale set `set` of tensor memory
-          got = got && mbar_wait(smem_u32(&bar_sf_full[w.set]), w.set_par, &abort_flag, 5);
+          // (pair: by the scale warps of both CTAs, which also tells that the other CTA's stage has landed)
+          got = got && wait_bar<PAIR>(smem_u32(&bar_sf_full[w.set]), w.set_par, &abort_flag, 5);
           if (!__all_sync(0xffffffffu, got)) { ok = false; break; }       // warp-uniform decision
           tc_fence_after();
           if (w.it == 0 && lane == 0) stamp(p, 3);
+          if (lane == 0) trace_ev(p, 2, i);
           const bool leader = elect_one();
           uint8_t* st = smem + w.stage * p.stage_bytes;
           const int rem = p.k - w.kt * 256;
@@ -308,20 +418,32 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
               const int c = MX ? (j >> 1) : j;
               const uint32_t sf_id = MX ? uint32_t((j & 1) * 2) : 0u;
               const uint32_t idesc = idesc_base | (sf_id << 4) | (sf_id << 29);
-              if (leader)
-                mma_fp4<MX>(d_tmem, a_desc + uint64_t(j * 2), b_desc + uint64_t(j * 2), idesc,
-                            sfa_col + 4 * c, sfb_col + ((h * p.chunks + c) * row_tiles) * 4, accumulate);
+              if (leader) {
+                if constexpr (PAIR)
+                  mma_fp4_pair<MX>(d_tmem, a_desc + uint64_t(j * 2), b_desc + uint64_t(j * 2), idesc,
+                                   sfa_col + 4 * c, sfb_col + ((h * p.chunks + c) * row_tiles) * 4, accumulate);
+                else
+                  mma_fp4<MX>(d_tmem, a_desc + uint64_t(j * 2), b_desc + uint64_t(j * 2), idesc,
+                              sfa_col + 4 * c, sfb_col + ((h * p.chunks + c) * row_tiles) * 4, accumulate);
+              }
               accumulate = 1;
             }
           }
-          if (leader) mma_commit(smem_u32(&bar_empty[w.stage]));   // frees the stage (and, later, its scale set)
+          if (leader) {                               // frees the stage (and, later, its scale set); pair: in both CTAs
+            if constexpr (PAIR) mma_commit_pair(smem_u32(&bar_empty[w.stage]));
+            else mma_commit(smem_u32(&bar_empty[w.stage]));
+          }
           __syncwarp();
+          if (lane == 0) trace_ev(p, 3, i);
           const bool tile_done = w.kt == p.k_tiles - 1;
           w.next(p);
           ++i;
           if (tile_done || i == n_units) break;
         }
-        if (ok && elect_one()) mma_commit(smem_u32(&bar_acc_full[buf]));   // this segment's accumulator is complete
+        if (ok && elect_one()) {                    // this segment's accumulator is complete
+          if constexpr (PAIR) mma_commit_pair(smem_u32(&bar_acc_full[buf]));
+          else mma_commit(smem_u32(&bar_acc_full[buf]));
+        }
         __syncwarp();
         ++seg;
       }
@@ -374,17 +496,18 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
         const int rem = p.k - w.kt * 256;
         const int n_mma = rem >= 256 ? kMmaPerTile : rem >> 6;
         const int n_chunks = MX ? (n_mma + 1) >> 1 : n_mma;
-        bool got = mbar_wait(smem_u32(&bar_full[w.stage]), w.stage_par, &abort_flag, 6);
+        bool got = wait_bar<PAIR>(smem_u32(&bar_full[w.stage]), w.stage_par, &abort_flag, 6);
         if (got && p.sf_sets < p.stages && w.it >= p.sf_sets) {
           // fewer scale sets than stages: before a set is reused the MMAs of unit (it - sf_sets) must have
           // completed, which is what the commit on that unit's stage barrier reports.  (With one set per
           // stage the arrival of the stage's data already implies it: the stage was refilled only after
           // that commit.)
-          got = mbar_wait(smem_u32(&bar_empty[lag_stage]), lag_par, &abort_flag, 7);
+          got = wait_bar<PAIR>(smem_u32(&bar_empty[lag_stage]), lag_par, &abort_flag, 7);
           if (++lag_stage == p.stages) { lag_stage = 0; lag_par ^= 1; }
         }
         if (!__all_sync(0xffffffffu, got)) { scale_alive = false; continue; }
         tc_fence_after();
+        if (warp == 6 && lane == 0) trace_ev(p, 4, i);
         const uint8_t* st = smem + w.stage * p.stage_bytes;
         const uint32_t col0 = tmem_base + q_lane + kSfCol + w.set * p.sf_set_cols;
         const uint8_t* sfa_src = st + p.smem_sfa_off + lane * 16;
@@ -443,7 +566,12 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
         }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         tc_fence_before();
-        if (lane == 0) mbar_arrive(smem_u32(&bar_sf_full[w.set]));
+        if (warp == 6 && lane == 0) trace_ev(p, 5, i);
+        if (lane == 0) {
+          if constexpr (PAIR) mbar_arrive_leader(smem_u32(&bar_sf_full[w.set]), rank);   // the leader's barrier
+          else mbar_arrive(smem_u32(&bar_sf_full[w.set]));
+        }
+        if (warp == 6 && lane == 0) trace_ev(p, 6, i);
       }
       ++seg;
       continue;
@@ -459,7 +587,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
         if (!complete) {
           asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(others) : "l"(p.ws_counter + tile) : "memory");
         }
-        acc_ok = mbar_wait(smem_u32(&bar_acc_full[buf]), (seg / nbuf) & 1, &abort_flag, 8) ? 1 : 0;
+        acc_ok = wait_bar<PAIR>(smem_u32(&bar_acc_full[buf]), (seg / nbuf) & 1, &abort_flag, 8) ? 1 : 0;
         is_last_cta = (!complete && others == c_last - c_first) ? 2 : 0;
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -467,7 +595,8 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
       tc_fence_after();
       const bool finish_now = is_last_cta == 2;
       if (seg == 0 && threadIdx.x == 64) stamp(p, 5);
-      const int w_tile = tile / p.tok_tiles, tok_tile = tile % p.tok_tiles;
+      const int tok_tile = tile % p.tok_tiles;
+      const int w_tile = PAIR ? 2 * (tile / p.tok_tiles) + rank : tile / p.tok_tiles;
       const int n_row0 = w_tile * kTileW;
       const int tok0 = tok_tile * p.tok_per_tile;
       const uint32_t t_lane = tmem_base + buf * p.n_tile + (uint32_t(quarter * 32) << 16);
@@ -595,7 +724,8 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
       tc_fence_before();
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (warp == 2 && lane == 0) {
-        mbar_arrive(smem_u32(&bar_acc_empty[buf]));
+        if constexpr (PAIR) mbar_arrive_leader(smem_u32(&bar_acc_empty[buf]), rank);   // the leader issues the next tile's MMAs
+        else mbar_arrive(smem_u32(&bar_acc_empty[buf]));
         if (finish_now) {
           p.ws_counter[tile] = 0;                  // everybody else has arrived: ready for the next call
         } else if (!complete) {
@@ -653,7 +783,14 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
     if (threadIdx.x == 0 && p.status) atomicExch(p.status, 1 + (int)blockIdx.x + (abort_flag << 16));   // CTA and wait site
     __nanosleep(1000000);                          // let copies that are still in flight land
   }
-  if (warp == 1) {
+  if constexpr (PAIR) {
+    // neither CTA frees tensor memory or leaves while its partner may still signal it or read its tiles
+    cluster_sync_all();
+    if (warp == 1) {
+      tc_fence_after();
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+  } else if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
@@ -684,21 +821,49 @@ int make_map(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t ro
   return RI_OK;
 }
 
+// Pairs (clusters of two CTAs with the kernel's shared-memory footprint) that can be resident at once,
+// per device; 0 = not asked yet (then SMs / 2 is assumed).  Filled by ri_fp4_gemm before it plans.
+int g_pair_slots[64] = {};
+int g_plan_device = 0;
+
 struct Plan {
   int n_tile, tok_per_tile, tok_tiles, w_tiles, k_tiles, tiles, stages;
   long long units;
-  int grid, tile_granular;      // persistent CTAs and how their unit ranges are cut
+  int grid, tile_granular;      // persistent CTAs (pair plans: pairs) and how their unit ranges are cut
+  int pair;                     // two-CTA tiles of 256 weight rows (cta_group::2), whole tiles only
   int chunks, stage_bytes, smem_act_off, smem_sfa_off, smem_sfb_off, smem_total;
+};
+
+// Measured choices for the projection shapes of the benchmark model on a 148-SM part (NVFP4 and MXFP4,
+// row_pair activations; sweep over splits 1, 2, 3, 4, 6 per (shape, M) under CUDA graphs with rotating
+// weight copies): weight rows, K, largest M of the bucket, `splits` value of the fastest plan.  Shapes that
+// are not listed use the cost model below, which reproduces these rows to within 2 %.  Stands where the
+// reference keys tile and cluster shapes on M (csrc/common/fold/sm10x/tactics.py:14-87).
+struct Tactic { int n, k, m_max, splits; };
+constexpr Tactic kTactics[] = {
+    {10240, 5120, 128, 1},                          // qkv: 80 whole tiles; K splits over all SMs measured 4-8 % slower
+    {5120, 8192, 128, 3},                           // o: 40 tiles x 3 K slices
+    {51200, 5120, 16, 2}, {51200, 5120, 128, 1},    // gate_up: ragged ranges up to 16 tokens, whole tiles above
+    {5120, 25600, 32, 4}, {5120, 25600, 128, 3},    // down: ragged ranges up to 32 tokens, 3 K slices above
 };
 
 // `splits`: 1 = ranges are cut at output-tile boundaries only (no K split, no workspace);
 // 0 = choose (stream-K over all SMs unless the tiles already balance); s > 1 = stream-K over
-// min(tiles * s, SMs) CTAs.
+// min(tiles * s, SMs) CTAs; -2 = two-CTA tiles where the shape allows them (256 accumulator columns),
+// else as 1.
 int make_plan(int m, int n, int k, int fmt, int layout, int splits, int sm_count, Plan* pl) {
+  if (splits == 0 && sm_count == 148 && layout == RI_GEMM_ROW_PAIR) {
+    for (const Tactic& t : kTactics)
+      if (t.n == n && t.k == k && m <= t.m_max) {
+        splits = t.splits;
+        break;
+      }
+  }
   const int act_rows = layout == RI_GEMM_ROW_PAIR ? 2 * m : m;
   const int halves_c = layout == RI_GEMM_CONCAT_K ? 2 : 1;
   pl->w_tiles = (n + kTileW - 1) / kTileW;
   pl->k_tiles = (k + 255) / 256;
+  pl->pair = 0;
   pl->chunks = fmt == RI_FMT_NVFP4 ? 4 : 2;
   // accumulator columns per CTA: one tile for up to `cap` activation rows, tiles of `cap` rows above.
   // Plans that split K use cap 128 (smaller FP32 partials, double-buffered accumulators), others 256.
@@ -725,15 +890,33 @@ int make_plan(int m, int n, int k, int fmt, int layout, int splits, int sm_count
     return units_per_cta * (w_unit_kb / rate + act_unit_kb(n_tile) / 120.0);     // KB / (GB/s) = us
   };
   auto epi_us = [&](int n_tile) { return 0.75 * ((n_tile + 31) / 32); };
-  if (splits == 1) {
+  // two-CTA tiles: 256 weight rows x 256 accumulator columns per pair, (SMs / 2) pairs at a time
+  auto pair_geometry = [&]() {
+    geometry(256);
+    pl->pair = 1;
+    pl->tiles = ((pl->w_tiles + 1) / 2) * pl->tok_tiles;
+    pl->units = (long long)pl->tiles * pl->k_tiles;
+    pl->tile_granular = 1;
+    const int slots = g_pair_slots[g_plan_device] > 0 ? g_pair_slots[g_plan_device] : sm_count / 2;
+    pl->grid = pl->tiles < slots ? pl->tiles : slots;
+  };
+  auto pair_eligible = [&]() {
+    geometry(256);
+    return pl->n_tile == 256 && pl->w_tiles >= 2 && sm_count >= 2;
+  };
+  if (splits == 1 || (splits == -2 && !pair_eligible())) {
     geometry(256);
     pl->tile_granular = 1;
     pl->grid = pl->tiles < sm_count ? pl->tiles : sm_count;
+  } else if (splits == -2) {
+    pair_geometry();
   } else if (splits <= 0) {
     geometry(256);
     const int grid_t = pl->tiles < sm_count ? pl->tiles : sm_count;
     const double waves = double((pl->tiles + grid_t - 1) / grid_t);
-    double best = stream_us(waves * pl->k_tiles, grid_t, pl->n_tile) + waves * epi_us(pl->n_tile);
+    // (with two accumulator buffers the output pass of a tile runs under the next tile's K loop: only the
+    // last one is exposed)
+    double best = stream_us(waves * pl->k_tiles, grid_t, pl->n_tile) + (pl->n_tile <= 128 ? 1.0 : waves) * epi_us(pl->n_tile);
     int best_split = 1;                                   // 1 = whole tiles, -1 = ragged ranges, s > 1 = even split
     geometry(128);
     if (pl->units >= 2) {
@@ -749,14 +932,30 @@ int make_plan(int m, int n, int k, int fmt, int layout, int splits, int sm_count
         if (c < best) { best = c; best_split = -1; }
       }
     }
-    if (best_split == 1) {
+    if (pair_eligible() && pl->tok_tiles >= 2) {
+      // a CTA of a pair takes in half of the activation tile per weight tile; measured: no gain while all
+      // tokens fit one tile (the K loop is short and latency-bound either way), 10-20 % with several tiles
+      const int pair_tiles = ((pl->w_tiles + 1) / 2) * pl->tok_tiles;
+      const int slots = g_pair_slots[g_plan_device] > 0 ? g_pair_slots[g_plan_device] : sm_count / 2;
+      const int grid_p = pair_tiles < slots ? pair_tiles : slots;
+      const double waves_p = double((pair_tiles + grid_p - 1) / grid_p);
+      const double act_kb = halves_c * (128 * kTileKBytes + pl->chunks * 512 * 2) / 1024.0;
+      const double rate = 2 * grid_p <= 96 ? 42.0 : 35.0;
+      const double c = waves_p * pl->k_tiles * (w_unit_kb / rate + act_kb / 120.0) + waves_p * epi_us(256) + 1.0;
+      if (c < best) { best = c; best_split = -2; }
+    }
+    if (best_split == -2) {
+      pair_geometry();
+    } else if (best_split == 1) {
       geometry(256);
       pl->tile_granular = 1;
       pl->grid = grid_t;
     } else if (best_split > 1) {
+      geometry(128);
       pl->tile_granular = 0;
       pl->grid = best_split * pl->tiles;
     } else {
+      geometry(128);
       pl->tile_granular = 0;
       long long g = sm_count;
       if (pl->units / 2 < g) g = pl->units / 2;
@@ -775,7 +974,7 @@ int make_plan(int m, int n, int k, int fmt, int layout, int splits, int sm_count
   const int row_tiles = (pl->n_tile + 127) / 128;
   const int sf_bytes = pl->chunks * 512;
   pl->smem_act_off = kTileW * kTileKBytes;
-  pl->smem_sfa_off = pl->smem_act_off + halves * pl->n_tile * kTileKBytes;
+  pl->smem_sfa_off = pl->smem_act_off + halves * (pl->pair ? pl->n_tile / 2 : pl->n_tile) * kTileKBytes;
   pl->smem_sfb_off = pl->smem_sfa_off + sf_bytes;
   int stage = pl->smem_sfb_off + halves * row_tiles * sf_bytes;
   pl->stage_bytes = (stage + 1023) / 1024 * 1024;
@@ -814,6 +1013,7 @@ extern "C" int64_t ri_fp4_gemm_counter_bytes(int m, int n) {
 }
 
 extern "C" int ri_fp4_gemm_auto_splits(int m, int n, int k, int fmt, int layout) {
+  if (m <= 0) return 1;
   DeviceInfo di;
   int sms = 148;                                   // planning without a visible device assumes a B200
   if (device_info(&di) == 0) sms = di.sm_count;
@@ -823,7 +1023,7 @@ extern "C" int ri_fp4_gemm_auto_splits(int m, int n, int k, int fmt, int layout)
 }
 
 extern "C" int64_t ri_fp4_gemm_workspace_bytes(int m, int n, int k, int fmt, int layout, int splits) {
-  if (splits == 1) return 0;
+  if (splits == 1 || m <= 0) return 0;
   // The plan depends on the SM count.  The size returned covers the plan of the device in use (when one
   // is visible) and the plan of a full 148-SM part, so that a launch never finds the workspace short.
   DeviceInfo di;
@@ -884,6 +1084,26 @@ extern "C" int ri_fp4_gemm(const uint8_t* act, int64_t act_row_bytes, const uint
   DeviceInfo di;
   int s = device_info(&di);
   if (s) return s;
+  g_plan_device = di.ordinal;
+  if (g_pair_slots[di.ordinal] == 0) {
+    // how many two-CTA clusters of this kernel the device holds at once (GPC shapes decide, not SMs / 2 alone)
+    RI_CUDA(cudaFuncSetAttribute(fp4_gemm_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem));
+    cudaLaunchConfig_t q{};
+    q.gridDim = dim3(2 * di.sm_count);
+    q.blockDim = dim3(kThreads);
+    q.dynamicSmemBytes = kMaxDynSmem;
+    cudaLaunchAttribute ca{};
+    ca.id = cudaLaunchAttributeClusterDimension;
+    ca.val.clusterDim.x = 2; ca.val.clusterDim.y = 1; ca.val.clusterDim.z = 1;
+    q.attrs = &ca;
+    q.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, fp4_gemm_kernel<false, true>, &q) != cudaSuccess || clusters <= 0) {
+      (void)cudaGetLastError();
+      clusters = di.sm_count / 2;
+    }
+    g_pair_slots[di.ordinal] = clusters;
+  }
   Plan pl;
   s = make_plan(m, n, k, fmt, layout, splits, di.sm_count, &pl);
   if (s) {
@@ -907,7 +1127,8 @@ extern "C" int ri_fp4_gemm(const uint8_t* act, int64_t act_row_bytes, const uint
   CUtensorMap w_map, act_map;
   s = make_map(&w_map, w, uint64_t(k / 2), uint64_t(n), uint64_t(w_row_bytes), kTileW);
   if (s) return s;
-  s = make_map(&act_map, act, uint64_t(act_cols), uint64_t(act_rows), uint64_t(act_row_bytes), uint32_t(pl.n_tile));
+  s = make_map(&act_map, act, uint64_t(act_cols), uint64_t(act_rows), uint64_t(act_row_bytes),
+               uint32_t(pl.pair ? pl.n_tile / 2 : pl.n_tile));
   if (s) return s;
 
   GemmParams p{};
@@ -945,23 +1166,33 @@ extern "C" int ri_fp4_gemm(const uint8_t* act, int64_t act_row_bytes, const uint
   p.trace = g_trace;
 #endif
 
-  auto kernel = fmt == RI_FMT_MXFP4 ? fp4_gemm_kernel<true> : fp4_gemm_kernel<false>;
-  static bool attr_set[64][2] = {};                 // function attributes are per device
-  if (!attr_set[di.ordinal][fmt]) {
+  auto kernel = pl.pair ? (fmt == RI_FMT_MXFP4 ? fp4_gemm_kernel<true, true> : fp4_gemm_kernel<false, true>)
+                        : (fmt == RI_FMT_MXFP4 ? fp4_gemm_kernel<true, false> : fp4_gemm_kernel<false, false>);
+  static bool attr_set[64][2][2] = {};              // function attributes are per device
+  if (!attr_set[di.ordinal][fmt][pl.pair]) {
     RI_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem));
-    attr_set[di.ordinal][fmt] = true;
+    attr_set[di.ordinal][fmt][pl.pair] = true;
   }
   cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(pl.grid);
+  cfg.gridDim = dim3(pl.pair ? 2 * pl.grid : pl.grid);
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = pl.smem_total;
   cfg.stream = static_cast<cudaStream_t>(stream);
-  cudaLaunchAttribute attr{};
+  cudaLaunchAttribute attrs[2]{};
+  int n_attrs = 0;
   if (enable_pdl) {
-    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr.val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
+    attrs[n_attrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[n_attrs].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attrs;
   }
+  if (pl.pair) {                                    // the two CTAs of a pair form a cluster
+    attrs[n_attrs].id = cudaLaunchAttributeClusterDimension;
+    attrs[n_attrs].val.clusterDim.x = 2;
+    attrs[n_attrs].val.clusterDim.y = 1;
+    attrs[n_attrs].val.clusterDim.z = 1;
+    ++n_attrs;
+  }
+  cfg.attrs = n_attrs ? attrs : nullptr;
+  cfg.numAttrs = n_attrs;
   return cuda_status(cudaLaunchKernelEx(&cfg, kernel, w_map, act_map, p), "fp4 gemm launch");
 }

@@ -53,14 +53,19 @@ __global__ void __launch_bounds__(256) nvfp4_mext_kernel(const T* __restrict__ x
   // waits for this grid (griddepcontrol.wait) before it reads the codes
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");   // inputs may come from a kernel still running
-  if (blk >= blocks_per_row) return;
+  const bool active = blk < blocks_per_row;
+  // BPT = 1: four neighbouring lanes hold the four scale bytes of one 32-bit word of the 128x4 layout
+  // (k-groups 4j .. 4j+3 of a row); when every row has whole groups of four they are gathered with
+  // shuffles and stored as one word.  Lanes past the end of the row then stay for the shuffles.
+  const bool gather_sf = BPT == 1 && blocks_per_row % 4 == 0 && (reinterpret_cast<uintptr_t>(sf) & 3) == 0;
+  if (!active && !gather_sf) return;
   const float gs = gs_inv ? __ldg(gs_inv) : 1.0f;
   const float gs_res = (gs_inv && n_gs > 1) ? __ldg(gs_inv + 1) : gs;
   for (int row = blockIdx.y; row < out_rows; row += gridDim.y) {
     float v[BPT][16];
 #pragma unroll
     for (int j = 0; j < BPT; ++j) {
-      if (row < in_rows) {
+      if (row < in_rows && active) {
         load16(x + int64_t(row) * row_stride + (blk + j) * 16, v[j]);
       } else {
 #pragma unroll
@@ -90,11 +95,27 @@ __global__ void __launch_bounds__(256) nvfp4_mext_kernel(const T* __restrict__ x
       res_codes = codes + int64_t(rr) * (k / 2);
     }
     if constexpr (BPT == 1) {
-      *reinterpret_cast<uint2*>(base_codes + blk * 8) = q[0].base;
-      sf[sf_offset<16>(sb, blk, k_sf)] = q[0].sf;
-      if (res_codes) {
-        *reinterpret_cast<uint2*>(res_codes + blk * 8) = q[0].res;
-        sf[sf_offset<16>(sr, kg_res, k_sf)] = q[0].sf_res;
+      if (gather_sf) {
+        uint32_t wb = q[0].sf, wr = q[0].sf_res;
+        wb |= __shfl_down_sync(0xffffffffu, wb, 1) << 8;
+        wr |= __shfl_down_sync(0xffffffffu, wr, 1) << 8;
+        wb |= __shfl_down_sync(0xffffffffu, wb, 2) << 16;
+        wr |= __shfl_down_sync(0xffffffffu, wr, 2) << 16;
+        if (active) {
+          *reinterpret_cast<uint2*>(base_codes + blk * 8) = q[0].base;
+          if (res_codes) *reinterpret_cast<uint2*>(res_codes + blk * 8) = q[0].res;
+          if ((blk & 3) == 0) {
+            *reinterpret_cast<uint32_t*>(sf + sf_offset<16>(sb, blk, k_sf)) = wb;
+            if (res_codes) *reinterpret_cast<uint32_t*>(sf + sf_offset<16>(sr, kg_res, k_sf)) = wr;
+          }
+        }
+      } else {
+        *reinterpret_cast<uint2*>(base_codes + blk * 8) = q[0].base;
+        sf[sf_offset<16>(sb, blk, k_sf)] = q[0].sf;
+        if (res_codes) {
+          *reinterpret_cast<uint2*>(res_codes + blk * 8) = q[0].res;
+          sf[sf_offset<16>(sr, kg_res, k_sf)] = q[0].sf_res;
+        }
       }
     } else {                    // two adjacent blocks: one 128-bit code store, one 16-bit scale store (blk is even)
       *reinterpret_cast<uint4*>(base_codes + blk * 8) = make_uint4(q[0].base.x, q[0].base.y, q[1].base.x, q[1].base.y);

@@ -30,6 +30,7 @@ struct AttnParams {
   int64_t num_pages;
   int batch, hq, hkv, group, page_size;
   int page_shift;                          // log2(page_size) when it is a power of two, else -1
+  int tma_pages;                           // pages hold whole 128-token tiles: codes and V scales come by TMA
   int tiles_per_split;                     // 128-token tiles a KV split covers (the same for every sequence)
   float score_scale_log2;                  // sm_scale * k_global_scale * log2(e)
   float out_scale;
@@ -172,6 +173,8 @@ extern "C" int ri_resattn_decode(const void* q_bf16, const uint8_t* k_data, cons
   p.page_shift = -1;
   for (int sft = 4; sft < 31; ++sft)
     if ((1 << sft) == page_size) p.page_shift = sft;
+  // tiled TMA coordinates are 32-bit: pools of 2^31 rows or more stay on the cp.async path
+  p.tma_pages = (page_size % 128 == 0 && num_pages * num_kv_heads * page_size < (int64_t(1) << 31)) ? 1 : 0;
   p.score_scale_log2 = score_scale * kLog2e;
   p.out_scale = out_scale;
   p.out = out;

@@ -119,26 +119,37 @@ __device__ __forceinline__ bool merge_splits_last_cta(const AttnParams& p, int b
     for (int s = lane; s < p.splits; s += 32) mm = fmaxf(mm, __ldcg(p.m_part + (int64_t(s) * p.batch + b) * p.hq + head));
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
+    // every lane takes the splits s = lane, lane + 32, ...: all loads of a pass are in flight together.  The
+    // row sum is a fixed tree over the lanes (it depends on the split count only, never on arrival order).
+    float l = 0.f;
     for (int s = lane; s < p.splits; s += 32) {
       const int64_t slot = (int64_t(s) * p.batch + b) * p.hq + head;
-      const float ms = __ldcg(p.m_part + slot);
-      w_sh[s * 8 + warp] = ms == -INFINITY ? 0.f : fast_exp2(ms - mm);
+      const float ms = __ldcg(p.m_part + slot), ls = __ldcg(p.l_part + slot);
+      const float w = ms == -INFINITY ? 0.f : fast_exp2(ms - mm);
+      w_sh[s * 8 + warp] = w;
+      l += w * ls;
     }
-    __syncwarp();
-    if (lane == 0) {                                         // the row sum in split order, like the outputs
-      float l = 0.f;
-      for (int s = 0; s < p.splits; ++s) l += w_sh[s * 8 + warp] * __ldcg(p.l_part + (int64_t(s) * p.batch + b) * p.hq + head);
-      r_sh[warp] = l > 0.f ? p.out_scale / l : 0.f;
-    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+    if (lane == 0) r_sh[warp] = l > 0.f ? p.out_scale / l : 0.f;
   }
   __syncthreads();
   for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
     const int g = idx / D, c = idx - g * D;
     const int head = hkv * G + g;
+    const float* src = p.o_part + (int64_t(b) * p.hq + head) * D + c;      // split s lies s * stride further
+    const int64_t stride = int64_t(p.batch) * p.hq * D;
     float o = 0.f;
-    for (int s = 0; s < p.splits; ++s) {
-      const float w = w_sh[s * 8 + g];
-      if (w != 0.f) o += w * __ldcg(p.o_part + ((int64_t(s) * p.batch + b) * p.hq + head) * D + c);   // empty partials hold no data
+    for (int s0 = 0; s0 < p.splits; s0 += 8) {               // eight loads in flight, then added in split order
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int s = s0 + j;
+        v[j] = (s < p.splits && w_sh[s * 8 + g] != 0.f) ? __ldcg(src + s * stride) : 0.f;   // empty partials hold no data
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (s0 + j < p.splits) o += w_sh[(s0 + j) * 8 + g] * v[j];
     }
     const float v = o * r_sh[g];
     const int64_t oi = (int64_t(b) * p.hq + head) * D + c;
@@ -166,7 +177,8 @@ __device__ __forceinline__ void pack_nvfp4_output(const AttnParams& p, int b, in
 }
 
 template <int D>
-__global__ void __launch_bounds__(PvCfg<D>::kThreads, PvCfg<D>::kCtasPerSm) resattn_pv_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(PvCfg<D>::kThreads, PvCfg<D>::kCtasPerSm)
+resattn_pv_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map, const AttnParams p) {
   using C = TCfg<D>;
   using PC = PvCfg<D>;
   constexpr int kPvConv = PC::kConv, kPvVBufs = PC::kVBufs, kPvStages = PC::kStages, kThreadsPv = PC::kThreads;
@@ -502,21 +514,36 @@ __global__ void __launch_bounds__(PvCfg<D>::kThreads, PvCfg<D>::kCtasPerSm) resa
         if (!prod_go[i & 1]) break;
       }
       const uint32_t st = smem_u32(stage0 + stg * C::kStageBytes);
-      const uint8_t* kg[2] = {p.k_data + base0 * C::kRowBytes + chn * 16, p.k_data + base1 * C::kRowBytes + chn * 16};
-      const uint8_t* vg[2] = {p.v_data + base0 * C::kRowBytes + chn * 16, p.v_data + base1 * C::kRowBytes + chn * 16};
-#pragma unroll
-      for (int it = 0; it < kIters; ++it) {
-        const int r = it * kRowsPerIt + r_lane;
-        if (it * kRowsPerIt < rows) {
-          const int sl = (it * kRowsPerIt) >> 4;
-          const int off = (r & 15) * C::kRowBytes;
-          cp_async16(st + k_dst[it], kg[sl] + off);
-          cp_async16(st + C::kOffV + k_dst[it], vg[sl] + off);
+      if (p.tma_pages) {
+        // Pages of 128 tokens (or a multiple): the K codes, the V codes and the V scales of a tile are three
+        // contiguous blocks of the pool.  One thread fetches them with the copy engine: the two code blocks
+        // as tiled loads that write the operand swizzle, the scales as one bulk copy.  The tile's rows
+        // past the end of the sequence belong to the same page, so whole blocks are always fetched.
+        if (pw == 0 && lane == 0) {
+          const int64_t row0 = base0;                          // first pool row of the tile
+          const uint32_t full = smem_u32(&bar_full[stg]);
+          mbar_expect_tx(full, 2 * C::kKBytes + C::kSfBytes);
+          tma_load_2d(st, &k_map, 0, int(row0), full);
+          tma_load_2d(st + C::kOffV, &v_map, 0, int(row0), full);
+          bulk_load_1d(st + C::kOffVsf, p.v_sf + row0 * C::kSfPerRow, C::kSfBytes, full);
         }
-      }
-      if (sf_lane && sf_row < rows) {
-        const int64_t br = (sf_row < 16 ? base0 : base1) + (sf_row & 15);
-        cp_async16(st + C::kOffVsf + sf_dst, p.v_sf + br * C::kSfPerRow);
+      } else {
+        const uint8_t* kg[2] = {p.k_data + base0 * C::kRowBytes + chn * 16, p.k_data + base1 * C::kRowBytes + chn * 16};
+        const uint8_t* vg[2] = {p.v_data + base0 * C::kRowBytes + chn * 16, p.v_data + base1 * C::kRowBytes + chn * 16};
+#pragma unroll
+        for (int it = 0; it < kIters; ++it) {
+          const int r = it * kRowsPerIt + r_lane;
+          if (it * kRowsPerIt < rows) {
+            const int sl = (it * kRowsPerIt) >> 4;
+            const int off = (r & 15) * C::kRowBytes;
+            cp_async16(st + k_dst[it], kg[sl] + off);
+            cp_async16(st + C::kOffV + k_dst[it], vg[sl] + off);
+          }
+        }
+        if (sf_lane && sf_row < rows) {
+          const int64_t br = (sf_row < 16 ? base0 : base1) + (sf_row & 15);
+          cp_async16(st + C::kOffVsf + sf_dst, p.v_sf + br * C::kSfPerRow);
+        }
       }
       if (lane < rows) {                                       // K scales of token kRowsW pw + lane, 4 bytes per MMA
         const uint8_t* src = p.k_sf + ((lane < 16 ? base0 : base1) + (lane & 15)) * C::kSfPerRow;
@@ -526,7 +553,10 @@ __global__ void __launch_bounds__(PvCfg<D>::kThreads, PvCfg<D>::kCtasPerSm) resa
         for (int j = 0; j < C::kMma; ++j)
           asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 512 * j), "l"(src + 4 * j) : "memory");
       }
-      asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&bar_full[stg])) : "memory");
+      // every producer thread arrives once per tile, when its own cp.async copies have landed; the thread
+      // that armed the barrier for the copy engine's bytes has arrived with that instruction already
+      if (!(p.tma_pages && pw == 0 && lane == 0))
+        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&bar_full[stg])) : "memory");
     }
   } else {
     // ============================================================ V conversion warps
@@ -680,6 +710,27 @@ __global__ void __launch_bounds__(PvCfg<D>::kThreads, PvCfg<D>::kCtasPerSm) resa
   }
 }
 
+// 2-D byte tensor over a code pool: [rows = pages * heads * page_size, D/2 bytes], box = one 128-token tile,
+// swizzle = the operand swizzle of the scores' MMA (64 bytes for head_dim 128, 128 bytes for 256)
+template <int D>
+int make_pool_map(CUtensorMap* map, const uint8_t* base, int64_t rows) {
+  EncodeTiledFn fn;
+  int s = get_encode_fn(&fn);
+  if (s) return s;
+  cuuint64_t dims[2] = {cuuint64_t(D / 2), cuuint64_t(rows)};
+  cuuint64_t strides[1] = {cuuint64_t(D / 2)};
+  cuuint32_t box[2] = {cuuint32_t(D / 2), cuuint32_t(kTile)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, D == 128 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed for the KV pool with CUresult %d (base %p, rows %lld)", (int)r, base, (long long)rows);
+    return RI_ERR_ARG;
+  }
+  return RI_OK;
+}
+
 template <int D>
 int launch_decode_pv(const AttnParams& p, cudaStream_t st) {
   using PC = PvCfg<D>;
@@ -692,6 +743,14 @@ int launch_decode_pv(const AttnParams& p, cudaStream_t st) {
     RI_CUDA(cudaFuncSetAttribute(resattn_pv_kernel<D>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
     attr_done[dev] = true;
   }
+  CUtensorMap k_map{}, v_map{};
+  if (p.tma_pages) {
+    const int64_t rows = p.num_pages * p.hkv * p.page_size;
+    int s = make_pool_map<D>(&k_map, p.k_data, rows);
+    if (s) return s;
+    s = make_pool_map<D>(&v_map, p.v_data, rows);
+    if (s) return s;
+  }
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(p.splits, p.hkv, p.batch);
   cfg.blockDim = dim3(PC::kThreads);
@@ -702,5 +761,5 @@ int launch_decode_pv(const AttnParams& p, cudaStream_t st) {
   attr.val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  return cuda_status(cudaLaunchKernelEx(&cfg, resattn_pv_kernel<D>, p), "resattn decode launch");
+  return cuda_status(cudaLaunchKernelEx(&cfg, resattn_pv_kernel<D>, k_map, v_map, p), "resattn decode launch");
 }

@@ -176,3 +176,49 @@ def test_gemm_rejects_bad_arguments(cuda_device):
     with pytest.raises(RuntimeError, match="MXFP4 has no global scale"):
         ops.fp4_gemm(a, sf, w, sf, torch.ones(1, device=cuda_device), m=4, fmt="mxfp4", layout="plain")
     assert ops.fp4_gemm(a[:0], sf, w, sf, None, m=0, fmt="nvfp4", layout="plain").shape == (0, 128)
+
+
+@pytest.mark.parametrize("fmt,m,n,k,layout", [("nvfp4", 128, 384, 1024, "row_pair"), ("nvfp4", 300, 512, 512, "plain"),
+                                              ("nvfp4", 256, 1000, 2048, "concat_k"), ("mxfp4", 130, 384, 640, "row_pair"),
+                                              ("nvfp4", 520, 2560, 5120, "row_pair")])
+def test_two_cta_tiles_against_one_cta_tiles(cuda_device, fmt, m, n, k, layout):
+    """Plans with 256 accumulator columns can run as pairs of CTAs on 256-row weight tiles
+    (tcgen05.mma.cta_group::2, ``splits=-2``).  Same products in the same K order as the one-CTA tiles
+    (``splits=1``): the FP32 outputs must agree to rounding noise, and both with the oracle.  Shapes cover an
+    odd number of 128-row tiles (the last pair is half empty), a ragged last tile and several token tiles."""
+    from resinfer_b200 import nvfp4, ops
+    from resinfer_b200.nvfp4 import mxfp4 as mx
+    dev = cuda_device
+    x_np, w_np = O.make_activation(m, k, seed=11), O.make_weight(n, k, seed=12)
+    x = torch.from_numpy(x_np).to(torch.bfloat16).to(dev)
+    if fmt == "nvfp4":
+        gx = np.float32(np.abs(x_np).max() / (6 * 448))
+        gw = np.float32(np.abs(w_np).max() / (6 * 448))
+        wc, wsf = O.nvfp4_quant_plain(w_np, np.float32(1) / gw)
+        gi = torch.tensor([1.0 / gx], dtype=torch.float32, device=dev)
+        alpha = torch.tensor([float(gx) * float(gw)], dtype=torch.float32, device=dev)
+        if layout == "plain":
+            codes = torch.empty((m, k // 2), dtype=torch.uint8, device=dev)
+            sf = torch.zeros(((m + 127) // 128) * ((k + 63) // 64) * 512, dtype=torch.uint8, device=dev)
+            torch.ops.nvfp4.scaled_fp4_quant_mext_r1(codes, x, sf, gi, 0, 5, True)
+        else:
+            codes, sf = nvfp4.scaled_fp4_quant_mext_r1(x, gi, layout_mode=1 if layout == "row_pair" else 3)
+    else:
+        wc, wsf = O.mxfp4_quant_plain(w_np)
+        codes, sf = mx.quantize_mext(x)
+        alpha = None
+    run = lambda s: ops.fp4_gemm(codes, sf, _t(wc, dev), _t(wsf, dev), alpha, m=m, fmt=fmt, layout=layout, splits=s,   # noqa: E731
+                                 out_dtype=torch.float32)
+    y_pair, y_one = run(-2), run(1)
+    torch.cuda.synchronize()
+    ops.check_status(dev)
+    assert rel_fro(y_pair.cpu().numpy(), y_one.cpu().numpy()) < 1e-6
+    a = O.dequant_operand(codes.cpu().numpy(), sf.cpu().numpy(), fmt)
+    if layout == "row_pair":
+        a = a[0::2] + a[1::2]
+    elif layout == "concat_k":
+        a = a[:, :k] + a[:, k:]
+    ref = O.fp4_linear_reference(a, O.dequant_operand(wc, wsf, fmt), 1.0 if alpha is None else float(alpha.item()), False)
+    assert rel_fro(y_pair.cpu().numpy(), ref) < TOL_F32
+    yb = ops.fp4_gemm(codes, sf, _t(wc, dev), _t(wsf, dev), alpha, m=m, fmt=fmt, layout=layout, splits=-2)
+    assert torch.equal(yb, y_pair.to(torch.bfloat16))

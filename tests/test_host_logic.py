@@ -219,3 +219,17 @@ def test_plugin_fails_closed(monkeypatch, capsys):
     with pytest.raises(ImportError):
         plug.apply()
     assert "refusing to serve" in capsys.readouterr().out
+
+
+def test_gemm_plan_selection_needs_no_gpu():
+    """The library plans without a device (a 148-SM part is assumed): the measured table for the benchmark
+    model's projections, the cost model elsewhere, no work for zero tokens."""
+    from resinfer_b200.nvfp4.cute_fold.tactics import describe_plan, kernel_arch_for_capability
+    assert kernel_arch_for_capability(10, 0) == "sm100" and kernel_arch_for_capability(12, 0) is None
+    assert [describe_plan(m, 10240, 5120)["k_split"] for m in (1, 16, 128)] == [1, 1, 1]          # qkv: whole tiles
+    assert [describe_plan(m, 5120, 8192)["k_split"] for m in (1, 16, 128)] == [3, 3, 3]           # o: 3 K slices
+    assert describe_plan(1, 51200, 5120)["k_split"] == 2 and describe_plan(64, 51200, 5120)["k_split"] == 1
+    assert describe_plan(1, 5120, 25600)["workspace_bytes"] > 0                                   # K split -> scratch
+    assert describe_plan(1024, 10240, 5120, layout="concat_k") == {"k_split": 1, "workspace_bytes": 0}
+    assert describe_plan(0, 10240, 5120) == {"k_split": 1, "workspace_bytes": 0}
+    assert describe_plan(16, 4096, 4096)["k_split"] > 1                                           # 32 tiles: split K
