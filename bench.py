@@ -275,9 +275,10 @@ def main():
     ap.add_argument("--format", default="nvfp4", choices=["nvfp4", "mxfp4"],
                     help="number format of the headline sweep (NVFP4 MEXT is the headline configuration, MXFP4 MEXT "
                          "the second one)")
-    ap.add_argument("--allreduce", choices=("peer", "nccl"), default="peer",
-                    help="N > 1: how the row-parallel partials are summed (this library's one-shot all-reduce over "
-                         "peer memory, or NCCL)")
+    ap.add_argument("--allreduce", choices=("fused", "peer", "nccl"), default="fused",
+                    help="N > 1: how the row-parallel partials are summed: in the GEMM's epilogue over peer memory "
+                         "(ri_fp4_gemm_allreduce), by this library's stand-alone one-shot kernel over peer memory, "
+                         "or by NCCL")
     ap.add_argument("--sweeps", action="store_true",
                     help="measure the other sweeps of the three hot paths (MXFP4 MEXT, KEXT, ResAttn batch sizes) "
                          "and print them as a second JSON line {\"sweeps\": ...}; N = 1 only")
@@ -345,7 +346,7 @@ def main():
     # over peer memory (a kernel per rank, plain NVLink loads); NCCL if the peers cannot be mapped or
     # --allreduce nccl is given.  The GEMM writes its partial straight into the exported buffer.
     peer_ar = None
-    if tp > 1 and args.allreduce == "peer":
+    if tp > 1 and args.allreduce in ("fused", "peer"):
         # the constructor exchanges its outcome among the ranks: it raises on all of them or on none
         try:
             from resinfer_b200.quant.tp import PeerAllReduce
@@ -354,13 +355,16 @@ def main():
             note(f"peer all-reduce unavailable ({type(e).__name__}: {e}); using NCCL")
     ar_status = torch.zeros(1, dtype=torch.int32, device=dev)
 
+    def fused_for(L, reduce):
+        return peer_ar if (peer_ar is not None and args.allreduce == "fused" and L.par == "row" and reduce) else None
+
     def gemm_out(L, m, reduce):
-        if peer_ar is not None and L.par == "row" and reduce:
+        if peer_ar is not None and L.par == "row" and reduce and fused_for(L, reduce) is None:
             return peer_ar.partial((m, L.n))
         return outs[(L.name, m)]
 
     def finish(L, m, y, reduce):
-        if tp > 1 and L.par == "row" and reduce:
+        if tp > 1 and L.par == "row" and reduce and fused_for(L, reduce) is None:
             if peer_ar is not None:
                 launches["n"] += 1
                 return peer_ar.reduce(y, outs[(L.name, m)], status=ar_status)
@@ -378,7 +382,7 @@ def main():
         else:
             codes, sf = pre
         y = ops.fp4_gemm(codes, sf, L.w[c], L.w_sf[c], None if mx else L.alpha[m], m=m, fmt=args.format,
-                         layout="row_pair", out=gemm_out(L, m, reduce))
+                         layout="row_pair", out=gemm_out(L, m, reduce), allreduce=fused_for(L, reduce))
         launches["n"] += 1
         return finish(L, m, y, reduce)
 
@@ -407,15 +411,19 @@ def main():
             for q in parts:                                  # rank order, FP32: the kernel's own order
                 want += q.float()
             want = want.to(torch.bfloat16)
-            pbuf = peer_ar.partial((m, L.n))
-            pbuf.copy_(part)
-            got = peer_ar.reduce(pbuf, status=ar_status)
-            pbuf2 = peer_ar.partial((m, L.n))                # keep the buffers alternating in pairs
-            pbuf2.copy_(part)
-            peer_ar.reduce(pbuf2, status=ar_status)
+            if args.allreduce == "fused":
+                got = run_case(L, m).clone()
+                run_case(L, m)                               # keep the buffers alternating in pairs
+            else:
+                pbuf = peer_ar.partial((m, L.n))
+                pbuf.copy_(part)
+                got = peer_ar.reduce(pbuf, status=ar_status)
+                pbuf2 = peer_ar.partial((m, L.n))
+                pbuf2.copy_(part)
+                peer_ar.reduce(pbuf2, status=ar_status)
             torch.cuda.synchronize()
             bad = bad or not torch.equal(got, want)
-        bad = bad or int(ar_status.item()) != 0
+        bad = bad or int(ar_status.item()) != 0 or int(peer_ar.status.item()) != 0
         flag = torch.tensor([1 if bad else 0], device=dev)
         dist.all_reduce(flag, op=dist.ReduceOp.MAX)
         if int(flag.item()):
@@ -529,13 +537,14 @@ def main():
                 for L in layers:
                     c = L.next_copy()
                     xd = hx[(L.name, m)].to(dev, non_blocking=True)
-                    if mx:
-                        y = torch.ops.residue.mxfp4_linear(xd, L.w[c], L.w_sf[c], zero_mask, zero_mask, "mext_r1",
-                                                           torch.bfloat16, None)
-                    else:
-                        y = torch.ops.residue.nvfp4_linear(xd, L.w[c], L.gs_inv[m], L.w_sf[c], L.w_sf[c], zero_mask,
-                                                           L.alpha[m], L.k, 0, 0, L.n, True, False, True)
-                    if tp > 1 and L.par == "row":
+                    with ops.row_parallel_reduction(fused_for(L, True)):    # row-parallel layers: sum in the epilogue
+                        if mx:
+                            y = torch.ops.residue.mxfp4_linear(xd, L.w[c], L.w_sf[c], zero_mask, zero_mask, "mext_r1",
+                                                               torch.bfloat16, None)
+                        else:
+                            y = torch.ops.residue.nvfp4_linear(xd, L.w[c], L.gs_inv[m], L.w_sf[c], L.w_sf[c], zero_mask,
+                                                               L.alpha[m], L.k, 0, 0, L.n, True, False, True)
+                    if tp > 1 and L.par == "row" and fused_for(L, True) is None:
                         if peer_ar is not None:             # the op's output is copied into the exported buffer first
                             pbuf = peer_ar.partial(tuple(y.shape))
                             pbuf.copy_(y)
@@ -592,13 +601,14 @@ def main():
                         c = L.next_copy()
                         xd = xs[(L.name, m)]
                         cur.wait_event(arrived[(L.name, m)])
-                        if mx:
-                            y = torch.ops.residue.mxfp4_linear(xd, L.w[c], L.w_sf[c], zero_mask, zero_mask, "mext_r1",
-                                                               torch.bfloat16, None)
-                        else:
-                            y = torch.ops.residue.nvfp4_linear(xd, L.w[c], L.gs_inv[m], L.w_sf[c], L.w_sf[c], zero_mask,
-                                                               L.alpha[m], L.k, 0, 0, L.n, True, False, True)
-                        if tp > 1 and L.par == "row":
+                        with ops.row_parallel_reduction(fused_for(L, True)):
+                            if mx:
+                                y = torch.ops.residue.mxfp4_linear(xd, L.w[c], L.w_sf[c], zero_mask, zero_mask, "mext_r1",
+                                                                   torch.bfloat16, None)
+                            else:
+                                y = torch.ops.residue.nvfp4_linear(xd, L.w[c], L.gs_inv[m], L.w_sf[c], L.w_sf[c],
+                                                                   zero_mask, L.alpha[m], L.k, 0, 0, L.n, True, False, True)
+                        if tp > 1 and L.par == "row" and fused_for(L, True) is None:
                             pbuf = peer_ar.partial(tuple(y.shape))
                             pbuf.copy_(y)
                             y = peer_ar.reduce(pbuf, status=ar_status)
@@ -679,10 +689,13 @@ def main():
             "dtype": ("mxfp4 (E2M1 x E8M0 block scales)" if mx else "nvfp4 (E2M1 x E4M3 block scales)") + ", fp32 accumulate",
             "data": "synthetic",
             "config": dict(workload_config(world, args.format),
-                           **({"allreduce": "one-shot over peer memory (ri_peer_allreduce_bf16)" if peer_ar is not None
+                           **({"allreduce": ("in the GEMM's epilogue over peer memory (ri_fp4_gemm_allreduce)"
+                                             if args.allreduce == "fused" else
+                                             "one-shot over peer memory (ri_peer_allreduce_bf16)") if peer_ar is not None
                                else "NCCL"} if tp > 1 else {})),
             "clocks": clk.summary(),
-            **({"allreduce_status": int(ar_status.item()), "allreduce_us": allreduce_us} if tp > 1 else {}),
+            **({"allreduce_status": int(ar_status.item()) | (int(peer_ar.status.item()) if peer_ar is not None else 0),
+                "allreduce_us": allreduce_us} if tp > 1 else {}),
             "gpu_launches": per_sweep_launches * inner * args.steps,
             "tflops": flops * inner / (ms_step * 1e-3) / 1e12, "fp4_peak_frac": flops * inner / (ms_step * 1e-3) / 9.0e15,
             "hbm_gbs_algorithmic": sum(mext_bytes(m, L.k_full, L.n_full) for L in layers for m in MS) * inner / (ms_step * 1e-3) / 1e9,

@@ -179,6 +179,44 @@ int ri_peer_allreduce_bf16(const void* const* rank_data, void* const* rank_flags
                            int64_t numel, void* out, void* state, int32_t* status, void* stream,
                            int enable_pdl);
 
+/* ri_fp4_gemm of a row-parallel linear with the all-reduce of the BF16 partial outputs done by the same kernel
+ * over peer memory.  The reference returns the rank-local partial from its linear methods and leaves the sum to
+ * vLLM's RowParallelLinear (quant/vllm_integration/linear_method_v2.py, linear_method_mxfp4.py; the partition rule
+ * is quant/vllm_integration/residue_tp.py); this entry point is that pair of steps in one launch.
+ *   rank_inboxes[r]   this process's mapping of rank r's inbox: `world` areas of `inbox_area` BF16 elements, area s
+ *                     receiving rank s's partial as [M, partial_row_stride]; 16-byte aligned; for r == rank the
+ *                     local inbox
+ *   rank_flags[r]     this process's mapping of rank r's flag array, ri_fp4_gemm_allreduce_flag_bytes(max_tiles)
+ *                     bytes, zeroed once before the first call and owned by the library afterwards
+ *   tile_calls        local device memory, ri_fp4_gemm_allreduce_call_bytes(max_tiles) bytes, zeroed once
+ *   max_tiles         flag entries the arrays hold; a call needs at most ri_fp4_gemm_allreduce_tiles(M, N)
+ *   reduced_out       local result [M, reduced_row_stride] BF16, not part of an inbox
+ * The CTA that completes a 128-column output tile goes over the tile twice.  First pass: the BF16 tile is stored
+ * into this rank's area of every PEER's inbox (plain 16-byte stores that cross NVLink without waiting for
+ * anything) and the tile's call number is published to every peer with a system-scope release.  After the wait for
+ * the peers' announcements of the same tile, second pass: the tile is formed again from tensor memory (or the
+ * K-split partials), the peers' tiles are read from the local inbox, everything is added in rank order in FP32
+ * and written as BF16.  Every rank holds the same bits, and they equal ri_fp4_gemm followed by
+ * ri_peer_allreduce_bf16.  No multicast, no NCCL, no load from a peer; this rank's own tile never travels through
+ * memory (its area of the local inbox stays unused).
+ * Every rank must make the same sequence of calls with the same shapes and `splits`; an inbox may be written
+ * again after the rank's NEXT fused call has completed (alternate between two inboxes).  The wait is bounded as
+ * for ri_peer_allreduce_bf16 (ri_peer_allreduce_set_wait_ms); on expiry `status` receives
+ * 0x40000000 | missing_rank << 8 | rank, the tile of reduced_out receives this rank's own partial, and the flag
+ * arrays and call counters of all ranks must be zeroed together before the next call.  The other arguments are
+ * ri_fp4_gemm's; N, both row strides and inbox_area must be multiples of 8. */
+int64_t ri_fp4_gemm_allreduce_tiles(int m, int n);
+int64_t ri_fp4_gemm_allreduce_flag_bytes(int64_t max_tiles);
+int64_t ri_fp4_gemm_allreduce_call_bytes(int64_t max_tiles);
+int ri_fp4_gemm_allreduce(const uint8_t* act, int64_t act_row_bytes, const uint8_t* act_sf,
+                          int64_t act_sf_bytes, const uint8_t* w, int64_t w_row_bytes, const uint8_t* w_sf,
+                          int64_t w_sf_bytes, const float* alpha, int n_alpha, int64_t partial_row_stride,
+                          int m, int n, int k, int fmt, int layout, int splits, void* workspace,
+                          int64_t workspace_bytes, int32_t* status, int enable_pdl, void* stream,
+                          void* const* rank_inboxes, int64_t inbox_area, void* const* rank_flags,
+                          void* tile_calls, int64_t max_tiles, int rank, int world, void* reduced_out,
+                          int64_t reduced_row_stride);
+
 /* ResAttn: residue-compensated paged NVFP4-KV decode attention, one query token per sequence.
  * q [B,Hq,D] bf16; k_data/v_data [pages,Hkv,page_size,D/2]; k_sf/v_sf [pages,Hkv,page_size,D/16]
  * E4M3 bytes (linear); block_tables int32 [B, bt_stride]; seq_lens int32 [B]; out [B,Hq,D] bf16

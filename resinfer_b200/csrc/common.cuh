@@ -61,6 +61,8 @@ struct DeviceInfo {
 };
 // Cached per device ordinal (the reference caches the first device's value only).
 int device_info(DeviceInfo* out);
+// how long a kernel waits for another rank before it gives up (ri_peer_allreduce_set_wait_ms)
+long long peer_wait_ns();
 
 // ------------------------------------------------------------------------------------------
 // device arithmetic that must match the reference build (-O3 --use_fast_math): flush-to-zero

@@ -45,6 +45,7 @@ constexpr int kSfCol = 256;        // first tensor-memory column of the block-sc
 constexpr int kMaxSfSets = 10;      // = kMaxStages: one scale set per pipeline stage when tensor memory allows
 constexpr int kMaxStages = 10;
 constexpr int kMaxDynSmem = 227 * 1024 - 2048;    // 227 KB per CTA minus the static barriers / flags
+constexpr int kArMaxRanks = 8;                    // ranks of the fused all-reduce
 constexpr int kEpiStageBytes = 8 * 1024;          // epilogue staging: 16 token pairs x 128 outputs x 4 bytes
 
 struct GemmParams {
@@ -78,18 +79,24 @@ struct GemmParams {
   // shared memory carve-up
   int smem_act_off, smem_sfa_off, smem_sfb_off, stage_bytes;
   long long* trace;             // development builds: [grid][8] nanosecond stamps
+  // Fused all-reduce over peer memory (ri_fp4_gemm_allreduce).  Every rank owns an "inbox" with one area per
+  // source rank.  The CTA that completes an output tile goes over the tile twice.  First pass: the BF16 tile is
+  // stored into this rank's area of every PEER's inbox (plain stores that cross NVLink without waiting for
+  // anything) and the tile is announced to the peers.  After the (bounded) wait for their announcements of the
+  // same tile, second pass: the tile is formed again from tensor memory / the K-split partials, the peers'
+  // tiles are read from the local inbox, everything is added in rank order in FP32 and written to ar_out.
+  // This rank's own tile never travels through memory.
+  uint16_t* ar_push[kArMaxRanks];      // where this rank's partial goes in rank r's inbox ([ar_rank] is unused)
+  const uint4* ar_pull[kArMaxRanks];   // rank r's area of this rank's inbox (local memory)
+  uint32_t* ar_flags[kArMaxRanks];     // rank r's flag array, [tile][kArMaxRanks] call numbers
+  uint32_t* ar_epoch;                  // local: fused calls completed so far, per tile
+  void* ar_out;
+  int64_t ar_out_stride;
+  long long ar_wait_ns;
+  int ar_rank, ar_world;
 };
 
 using namespace tc;
-
-__device__ __forceinline__ void store_out(const GemmParams& p, int tok, int n, float v) {
-  if (p.out_fp16 == 2)
-    static_cast<float*>(p.out)[int64_t(tok) * p.out_stride + n] = v;
-  else if (p.out_fp16)
-    static_cast<__half*>(p.out)[int64_t(tok) * p.out_stride + n] = __float2half_rn(v);
-  else
-    static_cast<__nv_bfloat16*>(p.out)[int64_t(tok) * p.out_stride + n] = __float2bfloat16_rn(v);
-}
 
 // ---------------------------------------------------------------------------------------------
 // kernel
@@ -149,6 +156,120 @@ struct Walk {
     ++it;
   }
 };
+
+// Fused all-reduce, the hand-shake for one output tile, run by the four epilogue warps (threads 64..191) once
+// this rank's tile has been stored into every peer's inbox.  Thread r of the first warp handles rank r: one
+// system-scope release store of this tile's call number into that rank's flag array (the release covers the
+// whole CTA's tile stores, which the barrier before it ordered ahead of this thread), then a wait, for at most
+// ar_wait_ns, until that rank has announced the same call number here.  A CTA meets its tiles in increasing
+// order and announces each before it waits, so the ranks cannot block each other in a cycle.  If a peer never
+// arrives, *ar_ok is cleared and the status word says which one.
+// A function of its own, not inlined: its registers are allocated apart from the kernel's main loops.
+__device__ __noinline__ void ar_exchange_tile(const GemmParams& p, int* ar_ok, uint32_t ar_call, int flag_tile) {
+  const int et = int(threadIdx.x) - 64;
+  if (et == 0) *ar_ok = 1;
+  asm volatile("bar.sync 1, 128;" ::: "memory");        // every thread's stores of the tile are behind it
+  if (et < p.ar_world && et != p.ar_rank) {
+    // (selected with compile-time indices: a run-time index would move the kernel arguments to local memory)
+    uint32_t* flags_peer = p.ar_flags[0];
+    uint32_t* flags_here = p.ar_flags[0];
+#pragma unroll
+    for (int r = 1; r < kArMaxRanks; ++r) {
+      if (r == et) flags_peer = p.ar_flags[r];
+      if (r == p.ar_rank) flags_here = p.ar_flags[r];
+    }
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags_peer + flag_tile * kArMaxRanks + p.ar_rank),
+                 "r"(ar_call) : "memory");
+    const uint32_t* theirs = flags_here + flag_tile * kArMaxRanks + et;
+    unsigned long long t0;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+    for (uint32_t spin = 0;; ++spin) {
+      uint32_t seen;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(theirs) : "memory");
+      if (int32_t(seen - ar_call) >= 0) break;
+      if ((spin & 63u) == 63u) {
+        unsigned long long t1;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
+        if ((long long)(t1 - t0) > p.ar_wait_ns) {
+          *ar_ok = 0;
+          if (p.status) atomicExch(p.status, 0x40000000 | (et << 8) | p.ar_rank);
+          break;
+        }
+      }
+    }
+  }
+  if (et == 0) p.ar_epoch[flag_tile] = ar_call;
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+}
+
+// Fused all-reduce, the two vectors (tokens tok and tok + 1, eight outputs each) that one thread of the copy-out
+// holds.  First pass (phase 1): store them into this rank's area of every peer's inbox.  Second pass (phase 2):
+// read the peers' vectors from the local inbox (four ranks' loads in flight), add all ranks in rank order in FP32
+// with this rank's BF16 values in its place, write BF16 to ar_out; a missing peer (ok == 0) leaves this rank's
+// own values.  Not inlined, for the same reason as ar_exchange_tile.
+__device__ __noinline__ void ar_tile_vectors(const GemmParams& p, int phase, int ok, uint4 t0, uint4 t1, int64_t eoff,
+                                             int64_t out_off, bool second) {
+  if (phase == 1) {
+#pragma unroll
+    for (int r = 0; r < kArMaxRanks; ++r) {
+      if (r < p.ar_world && r != p.ar_rank) {
+        *reinterpret_cast<uint4*>(p.ar_push[r] + eoff) = t0;
+        if (second) *reinterpret_cast<uint4*>(p.ar_push[r] + eoff + p.out_stride) = t1;
+      }
+    }
+    return;
+  }
+  float a0s[8], a1s[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) { a0s[e] = 0.f; a1s[e] = 0.f; }
+#pragma unroll
+  for (int r0 = 0; r0 < kArMaxRanks; r0 += 4) {
+    if (r0 < p.ar_world) {
+      uint4 la[4], lb[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        la[q] = make_uint4(0u, 0u, 0u, 0u);
+        lb[q] = make_uint4(0u, 0u, 0u, 0u);
+        if (ok && r0 + q < p.ar_world && r0 + q != p.ar_rank) {
+          const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.ar_pull[r0 + q]) + eoff);
+          asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(la[q].x), "=r"(la[q].y), "=r"(la[q].z), "=r"(la[q].w) : "l"(src));
+          if (second)
+            asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(lb[q].x), "=r"(lb[q].y), "=r"(lb[q].z), "=r"(lb[q].w) : "l"(src + (p.out_stride >> 3)));
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if (r0 + q < p.ar_world) {
+          const bool mine_r = r0 + q == p.ar_rank;
+          const uint32_t wa[4] = {mine_r ? t0.x : la[q].x, mine_r ? t0.y : la[q].y, mine_r ? t0.z : la[q].z, mine_r ? t0.w : la[q].w};
+          const uint32_t wb[4] = {mine_r ? t1.x : lb[q].x, mine_r ? t1.y : lb[q].y, mine_r ? t1.z : lb[q].z, mine_r ? t1.w : lb[q].w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            a0s[2 * e] += __uint_as_float(wa[e] << 16);
+            a0s[2 * e + 1] += __uint_as_float(wa[e] & 0xFFFF0000u);
+            a1s[2 * e] += __uint_as_float(wb[e] << 16);
+            a1s[2 * e + 1] += __uint_as_float(wb[e] & 0xFFFF0000u);
+          }
+        }
+      }
+    }
+  }
+  uint4 o0, o1;
+  uint32_t* w0 = &o0.x;
+  uint32_t* w1 = &o1.x;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const __nv_bfloat162 h0 = __floats2bfloat162_rn(a0s[2 * e], a0s[2 * e + 1]);
+    const __nv_bfloat162 h1 = __floats2bfloat162_rn(a1s[2 * e], a1s[2 * e + 1]);
+    w0[e] = *reinterpret_cast<const uint32_t*>(&h0);
+    w1[e] = *reinterpret_cast<const uint32_t*>(&h1);
+  }
+  uint16_t* fin = static_cast<uint16_t*>(p.ar_out) + out_off;
+  *reinterpret_cast<uint4*>(fin) = o0;
+  if (second) *reinterpret_cast<uint4*>(fin + p.ar_out_stride) = o1;
+}
 
 // ---- helpers of the two-CTA variant (a cluster of two CTAs works on one 256-row weight tile)
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -227,10 +348,10 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
 // (no K split).  Cross-CTA signals: the scale warps of both CTAs arrive on the leader's scale barrier (an
 // arrival implies that CTA's stage has landed), the leader's commits arrive on the barriers of both CTAs,
 // both epilogues arrive on the leader's accumulator-free barrier.
-template <bool MX, bool PAIR>
+template <bool MX, bool PAIR, bool AR = false>
 __global__ void __launch_bounds__(kThreads, 1)
 fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap act_map,
-                const GemmParams p) {
+                const __grid_constant__ GemmParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[kMaxStages];
   __shared__ __align__(8) uint64_t bar_empty[kMaxStages];
@@ -241,6 +362,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
   __shared__ volatile int abort_flag;
   __shared__ int is_last_cta;
   __shared__ int acc_ok;
+  __shared__ int ar_ok;
 
   // dynamic shared memory is only guaranteed 16-byte aligned: round up to the 1024-byte swizzle atom
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // stays a shared-space pointer
@@ -453,129 +575,127 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
     }
   } else {
     // ------------------------------------------------------ epilogue (warps 2..5), scales (warps 6..9)
-    // both roles walk the same list of segments; a warp touches tensor-memory lanes 32*(warp%4)..+31
+    // a warp touches tensor-memory lanes 32*(warp%4)..+31; each role walks the list of segments in a loop of its own (separate loops keep the registers of one role
+    // out of the other's way: values that are live in a shared loop get spilled into the per-K-tile path)
     const bool scale_role = warp >= 6;
     const int quarter = warp & 3;
-    const int row_in_tile = quarter * 32 + lane;
-    const bool pair = p.layout == RI_GEMM_ROW_PAIR;
-    const int64_t tile_elems = int64_t(kTileW) * p.n_tile;
-    float a0 = 1.f, a1 = 1.f;
-    bool scale_alive = true;
-    const uint32_t sf_stride = p.chunks * 512;
-    const uint32_t q_lane = uint32_t(quarter * 32) << 16;
     const int n_units = int(u_end - u_begin);
     Walk w;
     w.init(p, u_begin);
-    int seg = 0, i = 0;
-    int lag_stage = 0;
-    uint32_t lag_par = 0;
+    int i = 0;
+    if (scale_role) {
+      // ---- scale duty: copy the block scales of every K tile from shared memory into a scale set of
+      // tensor memory.  The 512-byte chunk of (128 rows x 4 k-groups) is laid out so that lane l reads
+      // 16 bytes = the 4 columns of rows l, l+32, l+64, l+96; every warp writes the same 32 x 4 columns
+      // into its own quarter (the MMA expects them replicated).
+      bool scale_alive = true;
+      const uint32_t sf_stride = p.chunks * 512;
+      const uint32_t q_lane = uint32_t(quarter * 32) << 16;
+      int lag_stage = 0;
+      uint32_t lag_par = 0;
+      {
+        for (; i < n_units; ++i, w.next(p)) {
+          if (!scale_alive) continue;
+          const int rem = p.k - w.kt * 256;
+          const int n_mma = rem >= 256 ? kMmaPerTile : rem >> 6;
+          const int n_chunks = MX ? (n_mma + 1) >> 1 : n_mma;
+          bool got = wait_bar<PAIR>(smem_u32(&bar_full[w.stage]), w.stage_par, &abort_flag, 6);
+          if (got && p.sf_sets < p.stages && w.it >= p.sf_sets) {
+            // fewer scale sets than stages: before a set is reused the MMAs of unit (it - sf_sets) must have
+            // completed, which is what the commit on that unit's stage barrier reports.  (With one set per
+            // stage the arrival of the stage's data already implies it: the stage was refilled only after
+            // that commit.)
+            got = wait_bar<PAIR>(smem_u32(&bar_empty[lag_stage]), lag_par, &abort_flag, 7);
+            if (++lag_stage == p.stages) { lag_stage = 0; lag_par ^= 1; }
+          }
+          if (!__all_sync(0xffffffffu, got)) { scale_alive = false; continue; }
+          tc_fence_after();
+          if (warp == 6 && lane == 0) trace_ev(p, 4, i);
+          const uint8_t* st = smem + w.stage * p.stage_bytes;
+          const uint32_t col0 = tmem_base + q_lane + kSfCol + w.set * p.sf_set_cols;
+          const uint8_t* sfa_src = st + p.smem_sfa_off + lane * 16;
+          const uint8_t* sfb_src = st + p.smem_sfb_off + lane * 16;
+          if (n_chunks == p.chunks) {
+            // full K tile: 16-byte chunk slices are fetched first, then written with wide stores
+            // (4 chunks = 16 columns per instruction; MXFP4 has 2 chunks = 8 columns)
+            if constexpr (MX) {
+              uint4 a[2] = {*reinterpret_cast<const uint4*>(sfa_src), *reinterpret_cast<const uint4*>(sfa_src + 512)};
+              tmem_st8(col0, a);
+              for (int g8 = 0; g8 < halves * row_tiles; ++g8) {       // column order (h, c, t): pairs of chunks
+                const int h = g8 / row_tiles, tt = g8 % row_tiles;
+                // with two row tiles the column order interleaves them: c0t0 c0t1 c1t0 c1t1
+                if (row_tiles == 1) {
+                  const uint8_t* s0 = sfb_src + h * sf_stride;
+                  uint4 b[2] = {*reinterpret_cast<const uint4*>(s0), *reinterpret_cast<const uint4*>(s0 + 512)};
+                  tmem_st8(col0 + 16 + h * 8, b);
+                } else {
+                  const int c = tt;                                    // one chunk, both row tiles
+                  const uint8_t* s0 = sfb_src + (h * 2) * sf_stride + c * 512;
+                  uint4 b[2] = {*reinterpret_cast<const uint4*>(s0), *reinterpret_cast<const uint4*>(s0 + sf_stride)};
+                  tmem_st8(col0 + 16 + (h * 2 + c) * 8, b);
+                }
+              }
+            } else {
+              uint4 a[4];
+#pragma unroll
+              for (int c = 0; c < 4; ++c) a[c] = *reinterpret_cast<const uint4*>(sfa_src + c * 512);
+              tmem_st16(col0, a);
+              if (row_tiles == 1) {
+                for (int h = 0; h < halves; ++h) {
+                  uint4 b[4];
+#pragma unroll
+                  for (int c = 0; c < 4; ++c) b[c] = *reinterpret_cast<const uint4*>(sfb_src + h * sf_stride + c * 512);
+                  tmem_st16(col0 + 16 + h * 16, b);
+                }
+              } else {
+                for (int h = 0; h < halves; ++h)
+                  for (int cp = 0; cp < 2; ++cp) {                     // chunk pair: c, t order = c0t0 c0t1 c1t0 c1t1
+                    uint4 b[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                      b[q] = *reinterpret_cast<const uint4*>(sfb_src + (h * 2 + (q & 1)) * sf_stride + (cp * 2 + (q >> 1)) * 512);
+                    tmem_st16(col0 + 16 + (h * 4 + cp * 2) * 8, b);
+                  }
+              }
+            }
+          } else {
+            for (int c = 0; c < n_chunks; ++c) {
+              tmem_st4(col0 + 4 * c, *reinterpret_cast<const uint4*>(sfa_src + c * 512));
+              for (int h = 0; h < halves; ++h)
+                for (int t = 0; t < row_tiles; ++t)
+                  tmem_st4(col0 + 16 + ((h * p.chunks + c) * row_tiles + t) * 4,
+                           *reinterpret_cast<const uint4*>(sfb_src + (h * row_tiles + t) * sf_stride + c * 512));
+            }
+          }
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+          tc_fence_before();
+          if (warp == 6 && lane == 0) trace_ev(p, 5, i);
+          if (lane == 0) {
+            if constexpr (PAIR) mbar_arrive_leader(smem_u32(&bar_sf_full[w.set]), rank);   // the leader's barrier
+            else mbar_arrive(smem_u32(&bar_sf_full[w.set]));
+          }
+          if (warp == 6 && lane == 0) trace_ev(p, 6, i);
+        }
+      }
+    } else {
+    const int row_in_tile = quarter * 32 + lane;
+    const bool pair = p.layout == RI_GEMM_ROW_PAIR;
+    const int64_t tile_elems = int64_t(kTileW) * p.n_tile;
+    int seg = 0;
     const int esz = p.out_fp16 == 2 ? 4 : 2;                  // output element size
     const bool out_vec = ((reinterpret_cast<uintptr_t>(p.out) | uintptr_t(p.out_stride * esz)) & 15) == 0;
     uint8_t* epi_stage = smem + p.stages * p.stage_bytes;     // kEpiStageBytes behind the pipeline stages
-    if (!scale_role) {
-      // global scales may come from the kernel before this one; fetch them while the main loop runs
-      asm volatile("griddepcontrol.wait;" ::: "memory");
-      a0 = p.alpha ? __ldg(p.alpha) : 1.0f;
-      a1 = (p.alpha && p.n_alpha > 1) ? __ldg(p.alpha + 1) : a0;
-    }
+    // global scales may come from the kernel before this one; fetch them while the main loop runs
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const float a0 = p.alpha ? __ldg(p.alpha) : 1.0f;
+    const float a1 = (p.alpha && p.n_alpha > 1) ? __ldg(p.alpha + 1) : a0;
     while (i < n_units) {
       const int tile = w.tile;
       const long long tile_begin = (long long)tile * p.k_tiles, tile_end = tile_begin + p.k_tiles;
       const int seg_units = min(p.k_tiles - w.kt, n_units - i);          // K tiles of this segment
       const bool complete = seg_units == p.k_tiles;
       const int buf = nbuf == 2 ? (seg & 1) : 0;
-      // ---- scale duty: copy the block scales of every K tile of this segment from shared memory
-      // into a scale set of tensor memory.  The 512-byte chunk of (128 rows x 4 k-groups) is laid
-      // out so that lane l reads 16 bytes = the 4 columns of rows l, l+32, l+64, l+96; every warp
-      // writes the same 32 x 4 columns into its own quarter (the MMA expects them replicated).
-      if (!scale_role) {
-        for (int j = 0; j < seg_units; ++j, ++i) w.next(p);
-      } else {
-      for (int j = 0; j < seg_units; ++j, ++i, w.next(p)) {
-        if (!scale_alive) continue;
-        const int rem = p.k - w.kt * 256;
-        const int n_mma = rem >= 256 ? kMmaPerTile : rem >> 6;
-        const int n_chunks = MX ? (n_mma + 1) >> 1 : n_mma;
-        bool got = wait_bar<PAIR>(smem_u32(&bar_full[w.stage]), w.stage_par, &abort_flag, 6);
-        if (got && p.sf_sets < p.stages && w.it >= p.sf_sets) {
-          // fewer scale sets than stages: before a set is reused the MMAs of unit (it - sf_sets) must have
-          // completed, which is what the commit on that unit's stage barrier reports.  (With one set per
-          // stage the arrival of the stage's data already implies it: the stage was refilled only after
-          // that commit.)
-          got = wait_bar<PAIR>(smem_u32(&bar_empty[lag_stage]), lag_par, &abort_flag, 7);
-          if (++lag_stage == p.stages) { lag_stage = 0; lag_par ^= 1; }
-        }
-        if (!__all_sync(0xffffffffu, got)) { scale_alive = false; continue; }
-        tc_fence_after();
-        if (warp == 6 && lane == 0) trace_ev(p, 4, i);
-        const uint8_t* st = smem + w.stage * p.stage_bytes;
-        const uint32_t col0 = tmem_base + q_lane + kSfCol + w.set * p.sf_set_cols;
-        const uint8_t* sfa_src = st + p.smem_sfa_off + lane * 16;
-        const uint8_t* sfb_src = st + p.smem_sfb_off + lane * 16;
-        if (n_chunks == p.chunks) {
-          // full K tile: 16-byte chunk slices are fetched first, then written with wide stores
-          // (4 chunks = 16 columns per instruction; MXFP4 has 2 chunks = 8 columns)
-          if constexpr (MX) {
-            uint4 a[2] = {*reinterpret_cast<const uint4*>(sfa_src), *reinterpret_cast<const uint4*>(sfa_src + 512)};
-            tmem_st8(col0, a);
-            for (int g8 = 0; g8 < halves * row_tiles; ++g8) {       // column order (h, c, t): pairs of chunks
-              const int h = g8 / row_tiles, tt = g8 % row_tiles;
-              // with two row tiles the column order interleaves them: c0t0 c0t1 c1t0 c1t1
-              if (row_tiles == 1) {
-                const uint8_t* s0 = sfb_src + h * sf_stride;
-                uint4 b[2] = {*reinterpret_cast<const uint4*>(s0), *reinterpret_cast<const uint4*>(s0 + 512)};
-                tmem_st8(col0 + 16 + h * 8, b);
-              } else {
-                const int c = tt;                                    // one chunk, both row tiles
-                const uint8_t* s0 = sfb_src + (h * 2) * sf_stride + c * 512;
-                uint4 b[2] = {*reinterpret_cast<const uint4*>(s0), *reinterpret_cast<const uint4*>(s0 + sf_stride)};
-                tmem_st8(col0 + 16 + (h * 2 + c) * 8, b);
-              }
-            }
-          } else {
-            uint4 a[4];
-#pragma unroll
-            for (int c = 0; c < 4; ++c) a[c] = *reinterpret_cast<const uint4*>(sfa_src + c * 512);
-            tmem_st16(col0, a);
-            if (row_tiles == 1) {
-              for (int h = 0; h < halves; ++h) {
-                uint4 b[4];
-#pragma unroll
-                for (int c = 0; c < 4; ++c) b[c] = *reinterpret_cast<const uint4*>(sfb_src + h * sf_stride + c * 512);
-                tmem_st16(col0 + 16 + h * 16, b);
-              }
-            } else {
-              for (int h = 0; h < halves; ++h)
-                for (int cp = 0; cp < 2; ++cp) {                     // chunk pair: c, t order = c0t0 c0t1 c1t0 c1t1
-                  uint4 b[4];
-#pragma unroll
-                  for (int q = 0; q < 4; ++q)
-                    b[q] = *reinterpret_cast<const uint4*>(sfb_src + (h * 2 + (q & 1)) * sf_stride + (cp * 2 + (q >> 1)) * 512);
-                  tmem_st16(col0 + 16 + (h * 4 + cp * 2) * 8, b);
-                }
-            }
-          }
-        } else {
-          for (int c = 0; c < n_chunks; ++c) {
-            tmem_st4(col0 + 4 * c, *reinterpret_cast<const uint4*>(sfa_src + c * 512));
-            for (int h = 0; h < halves; ++h)
-              for (int t = 0; t < row_tiles; ++t)
-                tmem_st4(col0 + 16 + ((h * p.chunks + c) * row_tiles + t) * 4,
-                         *reinterpret_cast<const uint4*>(sfb_src + (h * row_tiles + t) * sf_stride + c * 512));
-          }
-        }
-        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-        tc_fence_before();
-        if (warp == 6 && lane == 0) trace_ev(p, 5, i);
-        if (lane == 0) {
-          if constexpr (PAIR) mbar_arrive_leader(smem_u32(&bar_sf_full[w.set]), rank);   // the leader's barrier
-          else mbar_arrive(smem_u32(&bar_sf_full[w.set]));
-        }
-        if (warp == 6 && lane == 0) trace_ev(p, 6, i);
-      }
-      ++seg;
-      continue;
-      }
+      for (int j = 0; j < seg_units; ++j, ++i) w.next(p);
       // ---- epilogue duty for the segment
       // one thread waits for the accumulator so that all four warps take the same decision
       const int c_first = cta_of_unit(p, tile_begin), c_last = cta_of_unit(p, tile_end - 1);
@@ -601,6 +721,10 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
       const int tok0 = tok_tile * p.tok_per_tile;
       const uint32_t t_lane = tmem_base + buf * p.n_tile + (uint32_t(quarter * 32) << 16);
       float* mine = p.ws_partial + (int64_t(cta) * 2 + (cta == c_first ? 1 : 0)) * tile_elems;
+      uint32_t ar_call = 0;                                      // this tile's call number (fused all-reduce)
+      if constexpr (AR) {
+        if (n_row0 < p.n) ar_call = p.ar_epoch[w_tile * p.tok_tiles + tok_tile] + 1;
+      }
 
       // Output of one chunk of 32 accumulator columns (16 tokens with the row_pair layout, 32
       // otherwise).  A thread owns one output column n (its weight row) and `ntok` token values.
@@ -608,7 +732,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
       // n: two tokens are packed into one 32-bit word, word [token pair][n]; a thread of the
       // copy-out reads 8 words of a pair row and writes one vector for each of the two tokens.
       // FP32 output (a debugging format) is stored element by element.
-      auto emit_chunk = [&](const float (&v)[32], int c0, int cols) {
+      auto emit_chunk = [&](const float (&v)[32], int c0, int cols, int phase) {
         const int ntok = pair ? cols >> 1 : cols;
         const int tokc0 = tok0 + (pair ? c0 >> 1 : c0);
         float o[32];
@@ -662,6 +786,13 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
           t1.z = __byte_perm(hi4.x, hi4.y, 0x7632); t1.w = __byte_perm(hi4.z, hi4.w, 0x7632);
           uint16_t* dst = static_cast<uint16_t*>(p.out) + int64_t(tok) * p.out_stride + n0;
           const bool second = tok + 1 < p.m && 2 * pr + 1 < ntok;
+          if constexpr (AR) {
+            if (phase) {                                           // (the host checked the vector alignment)
+              ar_tile_vectors(p, phase, ar_ok, t0, t1, int64_t(tok) * p.out_stride + n0,
+                              int64_t(tok) * p.ar_out_stride + n0, second);
+              continue;
+            }
+          }
           if (out_vec && n0 + 8 <= p.n) {
             *reinterpret_cast<uint4*>(dst) = t0;
             if (second) *reinterpret_cast<uint4*>(dst + p.out_stride) = t1;
@@ -677,6 +808,10 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
         asm volatile("bar.sync 1, 128;" ::: "memory");      // the stage is reused by the next chunk
       };
 
+      // A tile that is finished here goes through its chunks once -- or, with the fused all-reduce, twice
+      // (store to the peers, hand-shake, form again and add the peers' tiles).
+      const bool ar_tile = AR && n_row0 < p.n;
+      for (int phase = (ar_tile && (complete || finish_now)) ? 1 : 0;;) {
       for (int c0 = 0; c0 < p.n_tile; c0 += 32) {
         const int cols = min(32, p.n_tile - c0);               // 32, or 16 for the last chunk
         float v[32];
@@ -708,17 +843,19 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
               for (int q = 0; q < 32; ++q) s[q] += fa[q];
             }
           }
-          emit_chunk(s, c0, cols);
+          emit_chunk(s, c0, cols, phase);
         } else if (!complete) {
           // partial tile, column-major [n_tile][128]: a warp writes one full 128-byte line per column
           float* dst = mine + int64_t(c0) * kTileW + row_in_tile;
 #pragma unroll
           for (int j = 0; j < 32; ++j) if (j < cols) __stcg(dst + j * kTileW, v[j]);
         } else {
-          emit_chunk(v, c0, cols);
+          emit_chunk(v, c0, cols, phase);
         }
       }
-      if (threadIdx.x == 64 && seg == 0) {
+      if (phase != 1) break;
+      if constexpr (AR) ar_exchange_tile(p, &ar_ok, ar_call, w_tile * p.tok_tiles + tok_tile);
+      phase = 2;
       }
       // the accumulator buffer has been read: hand it back to the MMA warp
       tc_fence_before();
@@ -745,6 +882,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
         if (is_last_cta) {
           // add the parts in CTA order (deterministic), 32 columns at a time with the loads of two
           // contributors in flight together, then write the chunk like a complete tile's
+          for (int phase = ar_tile ? 1 : 0;;) {
           for (int c0 = 0; c0 < p.n_tile; c0 += 32) {
             const int cols = min(32, p.n_tile - c0);
             float s[32];
@@ -765,7 +903,11 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
 #pragma unroll
               for (int q = 0; q < 32; ++q) s[q] += fb[q];
             }
-            emit_chunk(s, c0, cols);
+            emit_chunk(s, c0, cols, phase);
+          }
+          if (phase != 1) break;
+          if constexpr (AR) ar_exchange_tile(p, &ar_ok, ar_call, w_tile * p.tok_tiles + tok_tile);
+          phase = 2;
           }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");    // is_last_cta is reused by the next segment
@@ -773,6 +915,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
       ++seg;
     }
     if (threadIdx.x == 64) stamp(p, 6);
+    }
   }
 
   // ------------------------------------------------------------------ teardown
@@ -1041,12 +1184,26 @@ extern "C" int64_t ri_fp4_gemm_workspace_bytes(int m, int n, int k, int fmt, int
   return partial ? ri_fp4_gemm_counter_bytes(m, n) + partial : 0;
 }
 
-extern "C" int ri_fp4_gemm(const uint8_t* act, int64_t act_row_bytes, const uint8_t* act_sf,
-                           int64_t act_sf_bytes, const uint8_t* w, int64_t w_row_bytes,
-                           const uint8_t* w_sf, int64_t w_sf_bytes, const float* alpha, int n_alpha,
-                           void* out, int out_dtype, int64_t out_row_stride, int m, int n, int k,
-                           int fmt, int layout, int splits, void* workspace, int64_t workspace_bytes,
-                           int32_t* status, int enable_pdl, void* stream) {
+namespace ri {
+namespace {
+// the ranks of a fused all-reduce (ri_fp4_gemm_allreduce); null for a plain launch
+struct ArArgs {
+  void* const* rank_inboxes;
+  int64_t inbox_area;                  // BF16 elements between the areas of consecutive source ranks
+  void* const* rank_flags;
+  void* tile_calls;
+  int64_t max_tiles;
+  int rank, world;
+  void* reduced_out;
+  int64_t reduced_row_stride;
+};
+
+int gemm_launch(const uint8_t* act, int64_t act_row_bytes, const uint8_t* act_sf,
+                int64_t act_sf_bytes, const uint8_t* w, int64_t w_row_bytes,
+                const uint8_t* w_sf, int64_t w_sf_bytes, const float* alpha, int n_alpha,
+                void* out, int out_dtype, int64_t out_row_stride, int m, int n, int k,
+                int fmt, int layout, int splits, void* workspace, int64_t workspace_bytes,
+                int32_t* status, int enable_pdl, void* stream, const ArArgs* ar) {
   RI_CHECK_ARG(fmt == RI_FMT_NVFP4 || fmt == RI_FMT_MXFP4, "unknown FP4 format: %d", fmt);
   RI_CHECK_ARG(layout >= RI_GEMM_PLAIN && layout <= RI_GEMM_CONCAT_K, "unknown activation layout %d", layout);
   RI_CHECK_ARG(m >= 0 && n > 0 && k > 0, "positive dimensions required");
@@ -1165,13 +1322,35 @@ extern "C" int ri_fp4_gemm(const uint8_t* act, int64_t act_row_bytes, const uint
 #ifdef RI_GEMM_TRACE
   p.trace = g_trace;
 #endif
+  if (ar) {
+    // flag entries are indexed by (128-row weight tile, token tile); a two-CTA plan rounds the weight tiles up to pairs
+    const int64_t w_tiles_flag = pl.pair ? 2 * ((int64_t(n) + 2 * kTileW - 1) / (2 * kTileW)) : (int64_t(n) + kTileW - 1) / kTileW;
+    RI_CHECK_ARG(w_tiles_flag * pl.tok_tiles <= ar->max_tiles,
+                 "the fused all-reduce needs %lld tile flags, the flag arrays hold %lld",
+                 (long long)(w_tiles_flag * pl.tok_tiles), (long long)ar->max_tiles);
+    for (int r = 0; r < ar->world; ++r) {
+      p.ar_push[r] = static_cast<uint16_t*>(ar->rank_inboxes[r]) + int64_t(ar->rank) * ar->inbox_area;
+      p.ar_pull[r] = reinterpret_cast<const uint4*>(static_cast<uint16_t*>(ar->rank_inboxes[ar->rank]) + int64_t(r) * ar->inbox_area);
+      p.ar_flags[r] = static_cast<uint32_t*>(ar->rank_flags[r]);
+    }
+    p.ar_epoch = static_cast<uint32_t*>(ar->tile_calls);
+    p.ar_out = ar->reduced_out;
+    p.ar_out_stride = ar->reduced_row_stride;
+    p.ar_wait_ns = peer_wait_ns();
+    p.ar_rank = ar->rank;
+    p.ar_world = ar->world;
+  }
 
-  auto kernel = pl.pair ? (fmt == RI_FMT_MXFP4 ? fp4_gemm_kernel<true, true> : fp4_gemm_kernel<false, true>)
-                        : (fmt == RI_FMT_MXFP4 ? fp4_gemm_kernel<true, false> : fp4_gemm_kernel<false, false>);
-  static bool attr_set[64][2][2] = {};              // function attributes are per device
-  if (!attr_set[di.ordinal][fmt][pl.pair]) {
+  const bool mxk = fmt == RI_FMT_MXFP4;
+  auto kernel = pl.pair ? (mxk ? fp4_gemm_kernel<true, true> : fp4_gemm_kernel<false, true>)
+                        : (mxk ? fp4_gemm_kernel<true, false> : fp4_gemm_kernel<false, false>);
+  if (ar)                                           // the variant whose epilogue sums over the ranks
+    kernel = pl.pair ? (mxk ? fp4_gemm_kernel<true, true, true> : fp4_gemm_kernel<false, true, true>)
+                     : (mxk ? fp4_gemm_kernel<true, false, true> : fp4_gemm_kernel<false, false, true>);
+  static bool attr_set[64][2][2][2] = {};           // function attributes are per device
+  if (!attr_set[di.ordinal][fmt][pl.pair][ar ? 1 : 0]) {
     RI_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem));
-    attr_set[di.ordinal][fmt][pl.pair] = true;
+    attr_set[di.ordinal][fmt][pl.pair][ar ? 1 : 0] = true;
   }
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(pl.pair ? 2 * pl.grid : pl.grid);
@@ -1195,4 +1374,53 @@ extern "C" int ri_fp4_gemm(const uint8_t* act, int64_t act_row_bytes, const uint
   cfg.attrs = n_attrs ? attrs : nullptr;
   cfg.numAttrs = n_attrs;
   return cuda_status(cudaLaunchKernelEx(&cfg, kernel, w_map, act_map, p), "fp4 gemm launch");
+}
+}  // namespace
+}  // namespace ri
+
+extern "C" int ri_fp4_gemm(const uint8_t* act, int64_t act_row_bytes, const uint8_t* act_sf,
+                           int64_t act_sf_bytes, const uint8_t* w, int64_t w_row_bytes,
+                           const uint8_t* w_sf, int64_t w_sf_bytes, const float* alpha, int n_alpha,
+                           void* out, int out_dtype, int64_t out_row_stride, int m, int n, int k,
+                           int fmt, int layout, int splits, void* workspace, int64_t workspace_bytes,
+                           int32_t* status, int enable_pdl, void* stream) {
+  return ri::gemm_launch(act, act_row_bytes, act_sf, act_sf_bytes, w, w_row_bytes, w_sf, w_sf_bytes, alpha, n_alpha, out,
+                         out_dtype, out_row_stride, m, n, k, fmt, layout, splits, workspace, workspace_bytes, status,
+                         enable_pdl, stream, nullptr);
+}
+
+extern "C" int64_t ri_fp4_gemm_allreduce_tiles(int m, int n) {
+  // an upper bound of the (weight tile, token tile) pairs of any plan for the shape, weight tiles rounded to pairs
+  const int64_t w_tiles = 2 * ((int64_t(n) + 2 * ri::kTileW - 1) / (2 * ri::kTileW));
+  const int64_t tok_tiles = (2 * int64_t(m < 1 ? 1 : m) + 15) / 16;
+  return w_tiles * tok_tiles;
+}
+extern "C" int64_t ri_fp4_gemm_allreduce_flag_bytes(int64_t max_tiles) { return max_tiles * ri::kArMaxRanks * 4; }
+extern "C" int64_t ri_fp4_gemm_allreduce_call_bytes(int64_t max_tiles) { return max_tiles * 4; }
+
+extern "C" int ri_fp4_gemm_allreduce(const uint8_t* act, int64_t act_row_bytes, const uint8_t* act_sf,
+                                     int64_t act_sf_bytes, const uint8_t* w, int64_t w_row_bytes,
+                                     const uint8_t* w_sf, int64_t w_sf_bytes, const float* alpha, int n_alpha,
+                                     int64_t partial_row_stride, int m, int n, int k, int fmt, int layout, int splits,
+                                     void* workspace, int64_t workspace_bytes, int32_t* status, int enable_pdl,
+                                     void* stream, void* const* rank_inboxes, int64_t inbox_area,
+                                     void* const* rank_flags, void* tile_calls, int64_t max_tiles, int rank, int world,
+                                     void* reduced_out, int64_t reduced_row_stride) {
+  using namespace ri;
+  RI_CHECK_ARG(world >= 2 && world <= kArMaxRanks && rank >= 0 && rank < world, "bad rank %d / world %d (2..%d ranks)",
+               rank, world, kArMaxRanks);
+  RI_CHECK_ARG(rank_inboxes && rank_flags && tile_calls && reduced_out && max_tiles > 0, "null argument");
+  for (int r = 0; r < world; ++r)
+    RI_CHECK_ARG(rank_inboxes[r] && rank_flags[r] && (reinterpret_cast<uintptr_t>(rank_inboxes[r]) & 15) == 0,
+                 "rank %d: buffers must be mapped and 16-byte aligned", r);
+  RI_CHECK_ARG(n % 8 == 0 && partial_row_stride % 8 == 0 && partial_row_stride >= n && reduced_row_stride % 8 == 0 &&
+                   reduced_row_stride >= n && inbox_area % 8 == 0 && (reinterpret_cast<uintptr_t>(reduced_out) & 15) == 0,
+               "the fused all-reduce moves 16-byte vectors: N, the row strides and the inbox areas must be multiples of 8");
+  RI_CHECK_ARG(inbox_area >= int64_t(m) * partial_row_stride, "an inbox area of %lld elements is too small for [%d, %lld]",
+               (long long)inbox_area, m, (long long)partial_row_stride);
+  ArArgs ar{rank_inboxes, inbox_area, rank_flags, tile_calls, max_tiles, rank, world, reduced_out, reduced_row_stride};
+  void* own_area = static_cast<uint16_t*>(rank_inboxes[rank]) + int64_t(rank) * inbox_area;
+  return gemm_launch(act, act_row_bytes, act_sf, act_sf_bytes, w, w_row_bytes, w_sf, w_sf_bytes, alpha, n_alpha, own_area,
+                     RI_DTYPE_BF16, partial_row_stride, m, n, k, fmt, layout, splits, workspace, workspace_bytes, status,
+                     enable_pdl, stream, &ar);
 }

@@ -120,6 +120,7 @@ namespace ri {
 namespace {
 long long g_wait_ns = 10ll * 1000 * 1000 * 1000;       // ten seconds: rank skew from a first-call module load or a host stall
 }
+long long peer_wait_ns() { return g_wait_ns; }
 }  // namespace ri
 
 extern "C" void ri_peer_allreduce_set_wait_ms(int milliseconds) {

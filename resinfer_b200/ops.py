@@ -12,6 +12,8 @@ The split tickets in a workspace are left at zero by every launch that completes
 """
 from __future__ import annotations
 
+import contextlib
+
 import torch
 
 from . import _cabi
@@ -77,16 +79,42 @@ def check_status(device) -> None:
         raise RuntimeError(f"a device-side wait expired (status {v})")
 
 
+_ACTIVE_REDUCER = None
+
+
+@contextlib.contextmanager
+def row_parallel_reduction(reducer):
+    """Inside the block every ``fp4_gemm`` call without an explicit ``allreduce`` argument -- in particular the
+    ones made by ``residue::nvfp4_linear`` and ``residue::mxfp4_linear``, whose schemas have no room for it --
+    sums its output over the ranks of ``reducer`` (a ``resinfer_b200.quant.tp.PeerAllReduce``) in the GEMM's
+    epilogue.  This is where a tensor-parallel model wraps the linear of a row-parallel layer; ``None`` switches
+    it off again for a nested block.  Process-wide, not per thread."""
+    global _ACTIVE_REDUCER
+    prev = _ACTIVE_REDUCER
+    _ACTIVE_REDUCER = reducer
+    try:
+        yield reducer
+    finally:
+        _ACTIVE_REDUCER = prev
+
+
 def fp4_gemm(act: torch.Tensor, act_sf: torch.Tensor, weight: torch.Tensor, weight_sf: torch.Tensor,
              alpha: torch.Tensor | None, *, m: int, fmt: str = "nvfp4", layout: str = "plain",
              out_dtype: torch.dtype = torch.bfloat16, out: torch.Tensor | None = None,
-             splits: int = 0, enable_pdl: bool = True) -> torch.Tensor:
+             splits: int = 0, enable_pdl: bool = True, allreduce=None) -> torch.Tensor:
     """out[m, N] = alpha * act . weight^T with block-scaled FP4 operands.
 
     act: uint8 codes, [M, K/2] (plain), [2M, K/2] (row_pair) or [M, K] (concat_k); weight uint8
     [N, K/2] (row stride may exceed K/2); scale buffers 128x4-swizzled uint8 (E4M3 for nvfp4, E8M0
-    for mxfp4); alpha float32 device tensor with 1 (or, row_pair, 2) elements or None."""
+    for mxfp4); alpha float32 device tensor with 1 (or, row_pair, 2) elements or None.
+
+    ``allreduce``: a ``resinfer_b200.quant.tp.PeerAllReduce`` makes this the GEMM of a row-parallel
+    linear: the kernel stores this rank's BF16 partial into every rank's inbox and sums the partials of
+    all ranks itself (``ri_fp4_gemm_allreduce``); ``out`` (BF16) receives the sum.  Every
+    rank of the group must make the same calls in the same order."""
     lib = _cabi.load()
+    if allreduce is None:
+        allreduce = _ACTIVE_REDUCER
     fmt_c = {"nvfp4": _cabi.FMT_NVFP4, "mxfp4": _cabi.FMT_MXFP4}[fmt]
     lay_c = {"plain": _cabi.GEMM_PLAIN, "row_pair": _cabi.GEMM_ROW_PAIR, "concat_k": _cabi.GEMM_CONCAT_K}[layout]
     n, kp = weight.shape
@@ -110,6 +138,20 @@ def fp4_gemm(act: torch.Tensor, act_sf: torch.Tensor, weight: torch.Tensor, weig
             _cabi.check(_cabi.RI_ERR_ARG, "fp4_gemm plan")
         if ws_bytes > 0:
             ws = _workspace(dev, ws_bytes, "gemm", zero_prefix=plan[1])
+        if allreduce is not None:
+            if out.dtype != torch.bfloat16 or out.stride(1) != 1:
+                raise ValueError("the fused all-reduce writes a BF16 result with contiguous rows")
+            inboxes, area = allreduce.next_inbox(m * n)
+            st = lib.ri_fp4_gemm_allreduce(
+                act.data_ptr(), act.stride(0), act_sf.data_ptr(), act_sf.numel(),
+                weight.data_ptr(), weight.stride(0), weight_sf.data_ptr(), weight_sf.numel(),
+                _cabi.ptr(alpha), 0 if alpha is None else alpha.numel(), n, m, n, k, fmt_c, lay_c,
+                splits, _cabi.ptr(ws), ws_bytes, allreduce.status.data_ptr(), int(enable_pdl),
+                _cabi.current_stream(dev), inboxes, area, allreduce.tile_flag_ptrs,
+                allreduce.tile_calls.data_ptr(), allreduce.max_tiles, allreduce.rank, allreduce.world,
+                out.data_ptr(), out.stride(0))
+            _cabi.check(st, "fp4_gemm_allreduce")
+            return out
         st = lib.ri_fp4_gemm(
             act.data_ptr(), act.stride(0), act_sf.data_ptr(), act_sf.numel(),
             weight.data_ptr(), weight.stride(0), weight_sf.data_ptr(), weight_sf.numel(),

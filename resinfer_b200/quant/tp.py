@@ -76,10 +76,15 @@ class PeerAllReduce:
     ``out``.  Buffers are used round-robin; with two or more slots a buffer is only written again after
     this rank's next reduce has completed, which is what the kernel's contract asks for.
 
-    All ranks must call ``partial`` / ``reduce`` in the same order.  Raises RuntimeError if peer mapping is
+    ``ops.fp4_gemm(..., allreduce=self)`` is the GEMM whose epilogue does the reduction itself: it stores its
+    tiles into every rank's inbox (``slots`` inboxes with one area per source rank, in the same exported
+    allocation) and uses per-tile flags (``max_tiles`` of them; a call needs ``ri_fp4_gemm_allreduce_tiles(M, N)``).
+
+    All ranks must call ``partial`` / ``reduce`` (or the fused GEMM) in the same order.  Raises RuntimeError if peer mapping is
     not possible (ranks on different nodes, IPC disabled); callers then stay with NCCL."""
 
-    def __init__(self, max_numel: int, group=None, slots: int = 2, device=None, enable_pdl: bool = True):
+    def __init__(self, max_numel: int, group=None, slots: int = 2, device=None, enable_pdl: bool = True,
+                 max_tiles: int = 4096):
         from .. import _cabi
         if not (dist.is_available() and dist.is_initialized()):
             raise RuntimeError("PeerAllReduce needs an initialised process group")
@@ -97,7 +102,12 @@ class PeerAllReduce:
         self.slot_bytes = (2 * self.max_numel + 255) // 256 * 256
         flag_bytes = int(self.lib.ri_peer_allreduce_flag_bytes())
         self.flag_off = self.slots * self.slot_bytes
-        total = self.flag_off + (flag_bytes + 255) // 256 * 256
+        # behind the flags of the stand-alone kernel: the per-tile flags of the GEMM with the fused reduction
+        self.max_tiles = int(max_tiles)
+        self.tile_flag_off = self.flag_off + (flag_bytes + 255) // 256 * 256
+        # ... and its inboxes: per slot one area of max_numel values for every source rank
+        self.inbox_off = self.tile_flag_off + (int(self.lib.ri_fp4_gemm_allreduce_flag_bytes(self.max_tiles)) + 255) // 256 * 256
+        total = self.inbox_off + self.slots * self.world * self.slot_bytes
         # Every step that can fail on one rank only is followed by an exchange of the outcome, so that all
         # ranks raise together and none is left waiting in a collective the others never enter.
         handle, err = None, None
@@ -106,6 +116,8 @@ class PeerAllReduce:
             self.local = torch.zeros(total, dtype=torch.uint8, device=self.device)
             self.state = torch.zeros(int(self.lib.ri_peer_allreduce_state_bytes()), dtype=torch.uint8, device=self.device)
             self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+            self.tile_calls = torch.zeros(int(self.lib.ri_fp4_gemm_allreduce_call_bytes(self.max_tiles)),
+                                          dtype=torch.uint8, device=self.device)
             torch.cuda.synchronize(self.device)
             handle = self.local.untyped_storage()._share_cuda_()
         except Exception as e:                                # IPC disabled, out of memory
@@ -140,7 +152,11 @@ class PeerAllReduce:
         self._flag_ptrs = (ctypes.c_void_p * self.world)(*[b + self.flag_off for b in self.bases])
         self._data_ptrs = [(ctypes.c_void_p * self.world)(*[b + s * self.slot_bytes for b in self.bases])
                            for s in range(self.slots)]
+        self.tile_flag_ptrs = (ctypes.c_void_p * self.world)(*[b + self.tile_flag_off for b in self.bases])
+        self._inbox_ptrs = [(ctypes.c_void_p * self.world)(*[b + self.inbox_off + s * self.world * self.slot_bytes
+                                                             for b in self.bases]) for s in range(self.slots)]
         self._next = 0
+        self._next_inbox = 0
 
     def partial(self, shape, dtype=torch.bfloat16) -> torch.Tensor:
         """The next partial buffer of this rank as a tensor of ``shape`` (row-major, BF16)."""
@@ -157,6 +173,15 @@ class PeerAllReduce:
         t = self.local[off:off + 2 * n].view(torch.bfloat16).view(*shape)
         t._ri_slot = slot
         return t
+
+    def next_inbox(self, numel: int):
+        """The next inbox for a GEMM with the reduction in its epilogue: (C array of every rank's mapping of
+        it, BF16 elements between the areas of consecutive source ranks).  Inboxes alternate like partials."""
+        if numel > self.max_numel:
+            raise ValueError(f"{numel} elements: at most {self.max_numel}")
+        slot = self._next_inbox
+        self._next_inbox = (self._next_inbox + 1) % self.slots
+        return self._inbox_ptrs[slot], self.slot_bytes // 2
 
     def reduce(self, partial: torch.Tensor, out: torch.Tensor | None = None, status: torch.Tensor | None = None) -> torch.Tensor:
         """Sum ``partial`` (a tensor from ``partial()``) over the ranks into ``out`` (local BF16, same shape).
