@@ -275,10 +275,12 @@ def main():
     ap.add_argument("--format", default="nvfp4", choices=["nvfp4", "mxfp4"],
                     help="number format of the headline sweep (NVFP4 MEXT is the headline configuration, MXFP4 MEXT "
                          "the second one)")
-    ap.add_argument("--allreduce", choices=("fused", "peer", "nccl"), default="fused",
-                    help="N > 1: how the row-parallel partials are summed: in the GEMM's epilogue over peer memory "
-                         "(ri_fp4_gemm_allreduce), by this library's stand-alone one-shot kernel over peer memory, "
-                         "or by NCCL")
+    ap.add_argument("--allreduce", choices=("peer", "fused", "auto", "nccl"), default="peer",
+                    help="N > 1: how the row-parallel partials are summed: by this library's stand-alone one-shot "
+                         "kernel over peer memory (the default: fastest inside the sweep, 10.7 us per reduction on two "
+                         "GPUs against 20.1 for the epilogue), in the GEMM's epilogue over peer memory "
+                         "(ri_fp4_gemm_allreduce), auto = the epilogue up to 16 tokens and the stand-alone kernel "
+                         "above, or NCCL")
     ap.add_argument("--sweeps", action="store_true",
                     help="measure the other sweeps of the three hot paths (MXFP4 MEXT, KEXT, ResAttn batch sizes) "
                          "and print them as a second JSON line {\"sweeps\": ...}; N = 1 only")
@@ -346,7 +348,7 @@ def main():
     # over peer memory (a kernel per rank, plain NVLink loads); NCCL if the peers cannot be mapped or
     # --allreduce nccl is given.  The GEMM writes its partial straight into the exported buffer.
     peer_ar = None
-    if tp > 1 and args.allreduce in ("fused", "peer"):
+    if tp > 1 and args.allreduce in ("auto", "fused", "peer"):
         # the constructor exchanges its outcome among the ranks: it raises on all of them or on none
         try:
             from resinfer_b200.quant.tp import PeerAllReduce
@@ -355,16 +357,22 @@ def main():
             note(f"peer all-reduce unavailable ({type(e).__name__}: {e}); using NCCL")
     ar_status = torch.zeros(1, dtype=torch.int32, device=dev)
 
-    def fused_for(L, reduce):
-        return peer_ar if (peer_ar is not None and args.allreduce == "fused" and L.par == "row" and reduce) else None
+    FUSED_MAX_M = 16                                         # --allreduce auto: the epilogue reduction up to here
+
+    def fused_for(L, reduce, m=None):
+        if peer_ar is None or L.par != "row" or not reduce:
+            return None
+        if args.allreduce == "fused" or (args.allreduce == "auto" and m is not None and m <= FUSED_MAX_M):
+            return peer_ar
+        return None
 
     def gemm_out(L, m, reduce):
-        if peer_ar is not None and L.par == "row" and reduce and fused_for(L, reduce) is None:
+        if peer_ar is not None and L.par == "row" and reduce and fused_for(L, reduce, m) is None:
             return peer_ar.partial((m, L.n))
         return outs[(L.name, m)]
 
     def finish(L, m, y, reduce):
-        if tp > 1 and L.par == "row" and reduce and fused_for(L, reduce) is None:
+        if tp > 1 and L.par == "row" and reduce and fused_for(L, reduce, m) is None:
             if peer_ar is not None:
                 launches["n"] += 1
                 return peer_ar.reduce(y, outs[(L.name, m)], status=ar_status)
@@ -382,7 +390,7 @@ def main():
         else:
             codes, sf = pre
         y = ops.fp4_gemm(codes, sf, L.w[c], L.w_sf[c], None if mx else L.alpha[m], m=m, fmt=args.format,
-                         layout="row_pair", out=gemm_out(L, m, reduce), allreduce=fused_for(L, reduce))
+                         layout="row_pair", out=gemm_out(L, m, reduce), allreduce=fused_for(L, reduce, m))
         launches["n"] += 1
         return finish(L, m, y, reduce)
 
@@ -411,9 +419,20 @@ def main():
             for q in parts:                                  # rank order, FP32: the kernel's own order
                 want += q.float()
             want = want.to(torch.bfloat16)
+            if args.allreduce in ("auto", "fused"):
+                # (auto: the largest M goes through the stand-alone kernel below, the smallest through the epilogue)
+                ms = MS[0] if args.allreduce == "auto" else m
+                ps = [torch.empty(ms, L.n, dtype=torch.bfloat16, device=dev) for _ in range(tp)]
+                dist.all_gather(ps, run_case(L, ms, reduce=False).clone())
+                ws_ = torch.zeros(ms, L.n, dtype=torch.float32, device=dev)
+                for q in ps:
+                    ws_ += q.float()
+                got_s = run_case(L, ms).clone()
+                run_case(L, ms)                              # keep the inboxes alternating in pairs
+                torch.cuda.synchronize()
+                bad = bad or not torch.equal(got_s, ws_.to(torch.bfloat16))
             if args.allreduce == "fused":
-                got = run_case(L, m).clone()
-                run_case(L, m)                               # keep the buffers alternating in pairs
+                got = want
             else:
                 pbuf = peer_ar.partial((m, L.n))
                 pbuf.copy_(part)
@@ -537,14 +556,14 @@ def main():
                 for L in layers:
                     c = L.next_copy()
                     xd = hx[(L.name, m)].to(dev, non_blocking=True)
-                    with ops.row_parallel_reduction(fused_for(L, True)):    # row-parallel layers: sum in the epilogue
+                    with ops.row_parallel_reduction(fused_for(L, True, m)):    # row-parallel layers: sum in the epilogue
                         if mx:
                             y = torch.ops.residue.mxfp4_linear(xd, L.w[c], L.w_sf[c], zero_mask, zero_mask, "mext_r1",
                                                                torch.bfloat16, None)
                         else:
                             y = torch.ops.residue.nvfp4_linear(xd, L.w[c], L.gs_inv[m], L.w_sf[c], L.w_sf[c], zero_mask,
                                                                L.alpha[m], L.k, 0, 0, L.n, True, False, True)
-                    if tp > 1 and L.par == "row" and fused_for(L, True) is None:
+                    if tp > 1 and L.par == "row" and fused_for(L, True, m) is None:
                         if peer_ar is not None:             # the op's output is copied into the exported buffer first
                             pbuf = peer_ar.partial(tuple(y.shape))
                             pbuf.copy_(y)
@@ -601,14 +620,14 @@ def main():
                         c = L.next_copy()
                         xd = xs[(L.name, m)]
                         cur.wait_event(arrived[(L.name, m)])
-                        with ops.row_parallel_reduction(fused_for(L, True)):
+                        with ops.row_parallel_reduction(fused_for(L, True, m)):
                             if mx:
                                 y = torch.ops.residue.mxfp4_linear(xd, L.w[c], L.w_sf[c], zero_mask, zero_mask, "mext_r1",
                                                                    torch.bfloat16, None)
                             else:
                                 y = torch.ops.residue.nvfp4_linear(xd, L.w[c], L.gs_inv[m], L.w_sf[c], L.w_sf[c],
                                                                    zero_mask, L.alpha[m], L.k, 0, 0, L.n, True, False, True)
-                        if tp > 1 and L.par == "row" and fused_for(L, True) is None:
+                        if tp > 1 and L.par == "row" and fused_for(L, True, m) is None:
                             pbuf = peer_ar.partial(tuple(y.shape))
                             pbuf.copy_(y)
                             y = peer_ar.reduce(pbuf, status=ar_status)
@@ -689,9 +708,12 @@ def main():
             "dtype": ("mxfp4 (E2M1 x E8M0 block scales)" if mx else "nvfp4 (E2M1 x E4M3 block scales)") + ", fp32 accumulate",
             "data": "synthetic",
             "config": dict(workload_config(world, args.format),
-                           **({"allreduce": ("in the GEMM's epilogue over peer memory (ri_fp4_gemm_allreduce)"
-                                             if args.allreduce == "fused" else
-                                             "one-shot over peer memory (ri_peer_allreduce_bf16)") if peer_ar is not None
+                           **({"allreduce": {"fused": "in the GEMM's epilogue over peer memory (ri_fp4_gemm_allreduce)",
+                                             "auto": "M <= 16: in the GEMM's epilogue over peer memory "
+                                                     "(ri_fp4_gemm_allreduce); above: one-shot kernel over peer memory "
+                                                     "(ri_peer_allreduce_bf16)"}.get(
+                                                 args.allreduce, "one-shot over peer memory (ri_peer_allreduce_bf16)")
+                               if peer_ar is not None
                                else "NCCL"} if tp > 1 else {})),
             "clocks": clk.summary(),
             **({"allreduce_status": int(ar_status.item()) | (int(peer_ar.status.item()) if peer_ar is not None else 0),

@@ -183,9 +183,9 @@ int ri_peer_allreduce_bf16(const void* const* rank_data, void* const* rank_flags
  * over peer memory.  The reference returns the rank-local partial from its linear methods and leaves the sum to
  * vLLM's RowParallelLinear (quant/vllm_integration/linear_method_v2.py, linear_method_mxfp4.py; the partition rule
  * is quant/vllm_integration/residue_tp.py); this entry point is that pair of steps in one launch.
- *   rank_inboxes[r]   this process's mapping of rank r's inbox: `world` areas of `inbox_area` BF16 elements, area s
- *                     receiving rank s's partial as [M, partial_row_stride]; 16-byte aligned; for r == rank the
- *                     local inbox
+ *   rank_inboxes[r]   this process's mapping of rank r's inbox: `world` areas of 4 * inbox_area bytes, area s
+ *                     receiving rank s's partial ([M, partial_row_stride] BF16 in the first half of the area, or
+ *                     the pair format below in all of it); 16-byte aligned; for r == rank the local inbox
  *   rank_flags[r]     this process's mapping of rank r's flag array, ri_fp4_gemm_allreduce_flag_bytes(max_tiles)
  *                     bytes, zeroed once before the first call and owned by the library afterwards
  *   tile_calls        local device memory, ri_fp4_gemm_allreduce_call_bytes(max_tiles) bytes, zeroed once
@@ -199,6 +199,10 @@ int ri_peer_allreduce_bf16(const void* const* rank_data, void* const* rank_flags
  * and written as BF16.  Every rank holds the same bits, and they equal ri_fp4_gemm followed by
  * ri_peer_allreduce_bf16.  No multicast, no NCCL, no load from a peer; this rank's own tile never travels through
  * memory (its area of the local inbox stays unused).
+ * Small partials (ri_fp4_gemm_allreduce_uses_pairs(M, N, world): at most 2 MiB leave a rank per call) use neither
+ * the flag arrays nor any fence: every 32-bit word travels as an aligned 8-byte pair (word, call number), the
+ * reader polls the pairs of the vector it needs until all carry this call's number.  The call number counts the
+ * launches on these inboxes (two words behind the per-tile counts in tile_calls; the last CTA of a launch adds one).
  * Every rank must make the same sequence of calls with the same shapes and `splits`; an inbox may be written
  * again after the rank's NEXT fused call has completed (alternate between two inboxes).  The wait is bounded as
  * for ri_peer_allreduce_bf16 (ri_peer_allreduce_set_wait_ms); on expiry `status` receives
@@ -206,6 +210,7 @@ int ri_peer_allreduce_bf16(const void* const* rank_data, void* const* rank_flags
  * arrays and call counters of all ranks must be zeroed together before the next call.  The other arguments are
  * ri_fp4_gemm's; N, both row strides and inbox_area must be multiples of 8. */
 int64_t ri_fp4_gemm_allreduce_tiles(int m, int n);
+int ri_fp4_gemm_allreduce_uses_pairs(int m, int n, int world);
 int64_t ri_fp4_gemm_allreduce_flag_bytes(int64_t max_tiles);
 int64_t ri_fp4_gemm_allreduce_call_bytes(int64_t max_tiles);
 int ri_fp4_gemm_allreduce(const uint8_t* act, int64_t act_row_bytes, const uint8_t* act_sf,

@@ -39,6 +39,7 @@ SIGNATURES = {
     "ri_fp4_gemm_counter_bytes": (_i64, [_i, _i]),
     "ri_fp4_gemm_auto_splits": (_i, [_i, _i, _i, _i, _i]),
     "ri_fp4_gemm_allreduce_tiles": (_i64, [_i, _i]),
+    "ri_fp4_gemm_allreduce_uses_pairs": (_i, [_i, _i, _i]),
     "ri_fp4_gemm_allreduce_flag_bytes": (_i64, [_i64]),
     "ri_fp4_gemm_allreduce_call_bytes": (_i64, [_i64]),
     "ri_fp4_gemm_allreduce": (_i, [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i, _i64, _i, _i, _i, _i, _i, _i,

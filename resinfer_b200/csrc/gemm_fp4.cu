@@ -46,6 +46,7 @@ constexpr int kMaxSfSets = 10;      // = kMaxStages: one scale set per pipeline 
 constexpr int kMaxStages = 10;
 constexpr int kMaxDynSmem = 227 * 1024 - 2048;    // 227 KB per CTA minus the static barriers / flags
 constexpr int kArMaxRanks = 8;                    // ranks of the fused all-reduce
+constexpr int64_t kArPairBytesMax = 2 << 20;      // fused all-reduce: up to this many bytes per rank go out as (value, call) pairs
 constexpr int kEpiStageBytes = 8 * 1024;          // epilogue staging: 16 token pairs x 128 outputs x 4 bytes
 
 struct GemmParams {
@@ -90,9 +91,11 @@ struct GemmParams {
   const uint4* ar_pull[kArMaxRanks];   // rank r's area of this rank's inbox (local memory)
   uint32_t* ar_flags[kArMaxRanks];     // rank r's flag array, [tile][kArMaxRanks] call numbers
   uint32_t* ar_epoch;                  // local: fused calls completed so far, per tile
+  uint32_t* ar_state;                  // local: [0] launches completed so far, [1] CTA ticket of the running launch
   void* ar_out;
   int64_t ar_out_stride;
   long long ar_wait_ns;
+  int ar_ll;                           // 1: small tiles travel as (value, call number) pairs and nobody fences (see ar_tile_vectors)
   int ar_rank, ar_world;
 };
 
@@ -206,15 +209,50 @@ __device__ __noinline__ void ar_exchange_tile(const GemmParams& p, int* ar_ok, u
 // holds.  First pass (phase 1): store them into this rank's area of every peer's inbox.  Second pass (phase 2):
 // read the peers' vectors from the local inbox (four ranks' loads in flight), add all ranks in rank order in FP32
 // with this rank's BF16 values in its place, write BF16 to ar_out; a missing peer (ok == 0) leaves this rank's
-// own values.  Not inlined, for the same reason as ar_exchange_tile.
-__device__ __noinline__ void ar_tile_vectors(const GemmParams& p, int phase, int ok, uint4 t0, uint4 t1, int64_t eoff,
-                                             int64_t out_off, bool second) {
+// own values.
+// Small tiles (p.ar_ll) use a protocol without fences or flag arrays: every 32-bit word of a vector travels as
+// an 8-byte pair (word, call number) -- an aligned 8-byte store arrives whole -- so the reader simply polls the
+// pairs of its own vector until all four carry this call's number (bounded like every other wait).  Twice the
+// bytes, one NVLink crossing of latency.  The call number counts the launches on this set of inboxes, so data
+// left over from earlier calls (at least two calls old: the inboxes alternate) never matches.
+// Not inlined, for the same reason as ar_exchange_tile.
+__device__ __forceinline__ void ll_store(uint8_t* dst, uint4 t, uint32_t call) {
+  asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(t.x), "r"(call), "r"(t.y), "r"(call) : "memory");
+  asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 16), "r"(t.z), "r"(call), "r"(t.w), "r"(call) : "memory");
+}
+// polls one vector's four pairs; false if they did not all arrive in time
+__device__ __forceinline__ bool ll_load(const uint8_t* src, uint32_t call, long long wait_ns, uint4* out) {
+  uint4 a, b;
+  unsigned long long t0 = 0;
+  for (uint32_t spin = 0;; ++spin) {
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(src) : "memory");
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(src + 16) : "memory");
+    if (a.y == call && a.w == call && b.y == call && b.w == call) break;
+    if ((spin & 63u) == 0u) {
+      unsigned long long t1;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
+      if (spin == 0) t0 = t1;
+      else if ((long long)(t1 - t0) > wait_ns) return false;
+    }
+  }
+  *out = make_uint4(a.x, a.z, b.x, b.z);
+  return true;
+}
+__device__ __noinline__ void ar_tile_vectors(const GemmParams& p, int phase, int ok, uint32_t call, uint4 t0, uint4 t1,
+                                             int64_t eoff, int64_t out_off, bool second) {
+  const bool ll = p.ar_ll != 0;
   if (phase == 1) {
 #pragma unroll
     for (int r = 0; r < kArMaxRanks; ++r) {
       if (r < p.ar_world && r != p.ar_rank) {
-        *reinterpret_cast<uint4*>(p.ar_push[r] + eoff) = t0;
-        if (second) *reinterpret_cast<uint4*>(p.ar_push[r] + eoff + p.out_stride) = t1;
+        if (ll) {
+          uint8_t* dst = reinterpret_cast<uint8_t*>(p.ar_push[r]) + 4 * eoff;
+          ll_store(dst, t0, call);
+          if (second) ll_store(dst + 4 * p.out_stride, t1, call);
+        } else {
+          *reinterpret_cast<uint4*>(p.ar_push[r] + eoff) = t0;
+          if (second) *reinterpret_cast<uint4*>(p.ar_push[r] + eoff + p.out_stride) = t1;
+        }
       }
     }
     return;
@@ -231,12 +269,22 @@ __device__ __noinline__ void ar_tile_vectors(const GemmParams& p, int phase, int
         la[q] = make_uint4(0u, 0u, 0u, 0u);
         lb[q] = make_uint4(0u, 0u, 0u, 0u);
         if (ok && r0 + q < p.ar_world && r0 + q != p.ar_rank) {
-          const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.ar_pull[r0 + q]) + eoff);
-          asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                       : "=r"(la[q].x), "=r"(la[q].y), "=r"(la[q].z), "=r"(la[q].w) : "l"(src));
-          if (second)
+          if (ll) {
+            const uint8_t* src = reinterpret_cast<const uint8_t*>(p.ar_pull[r0 + q]) + 4 * eoff;
+            bool got = ll_load(src, call, p.ar_wait_ns, &la[q]);
+            if (got && second) got = ll_load(src + 4 * p.out_stride, call, p.ar_wait_ns, &lb[q]);
+            if (!got) {
+              ok = 0;                                        // the rest of this thread's vector: own values only
+              if (p.status) atomicExch(p.status, 0x40000000 | ((r0 + q) << 8) | p.ar_rank);
+            }
+          } else {
+            const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.ar_pull[r0 + q]) + eoff);
             asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(lb[q].x), "=r"(lb[q].y), "=r"(lb[q].z), "=r"(lb[q].w) : "l"(src + (p.out_stride >> 3)));
+                         : "=r"(la[q].x), "=r"(la[q].y), "=r"(la[q].z), "=r"(la[q].w) : "l"(src));
+            if (second)
+              asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(lb[q].x), "=r"(lb[q].y), "=r"(lb[q].z), "=r"(lb[q].w) : "l"(src + (p.out_stride >> 3)));
+          }
         }
       }
 #pragma unroll
@@ -256,15 +304,17 @@ __device__ __noinline__ void ar_tile_vectors(const GemmParams& p, int phase, int
       }
     }
   }
-  uint4 o0, o1;
-  uint32_t* w0 = &o0.x;
-  uint32_t* w1 = &o1.x;
+  uint4 o0 = t0, o1 = t1;                                    // a peer is missing: this rank's own values
+  if (ok) {
+    uint32_t* w0 = &o0.x;
+    uint32_t* w1 = &o1.x;
 #pragma unroll
-  for (int e = 0; e < 4; ++e) {
-    const __nv_bfloat162 h0 = __floats2bfloat162_rn(a0s[2 * e], a0s[2 * e + 1]);
-    const __nv_bfloat162 h1 = __floats2bfloat162_rn(a1s[2 * e], a1s[2 * e + 1]);
-    w0[e] = *reinterpret_cast<const uint32_t*>(&h0);
-    w1[e] = *reinterpret_cast<const uint32_t*>(&h1);
+    for (int e = 0; e < 4; ++e) {
+      const __nv_bfloat162 h0 = __floats2bfloat162_rn(a0s[2 * e], a0s[2 * e + 1]);
+      const __nv_bfloat162 h1 = __floats2bfloat162_rn(a1s[2 * e], a1s[2 * e + 1]);
+      w0[e] = *reinterpret_cast<const uint32_t*>(&h0);
+      w1[e] = *reinterpret_cast<const uint32_t*>(&h1);
+    }
   }
   uint16_t* fin = static_cast<uint16_t*>(p.ar_out) + out_off;
   *reinterpret_cast<uint4*>(fin) = o0;
@@ -689,6 +739,10 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const float a0 = p.alpha ? __ldg(p.alpha) : 1.0f;
     const float a1 = (p.alpha && p.n_alpha > 1) ? __ldg(p.alpha + 1) : a0;
+    uint32_t ar_launch_call = 0;                               // launches on these inboxes so far, plus one
+    if constexpr (AR) {
+      if (p.ar_ll) ar_launch_call = p.ar_state[0] + 1;        // (the launch before this one has completed: see the wait above)
+    }
     while (i < n_units) {
       const int tile = w.tile;
       const long long tile_begin = (long long)tile * p.k_tiles, tile_end = tile_begin + p.k_tiles;
@@ -721,9 +775,11 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
       const int tok0 = tok_tile * p.tok_per_tile;
       const uint32_t t_lane = tmem_base + buf * p.n_tile + (uint32_t(quarter * 32) << 16);
       float* mine = p.ws_partial + (int64_t(cta) * 2 + (cta == c_first ? 1 : 0)) * tile_elems;
-      uint32_t ar_call = 0;                                      // this tile's call number (fused all-reduce)
+      // fused all-reduce: this tile's call number (per tile with the flag protocol, per launch with the pairs)
+      uint32_t ar_call = 0;
       if constexpr (AR) {
-        if (n_row0 < p.n) ar_call = p.ar_epoch[w_tile * p.tok_tiles + tok_tile] + 1;
+        if (p.ar_ll) ar_call = ar_launch_call;
+        else if (n_row0 < p.n) ar_call = p.ar_epoch[w_tile * p.tok_tiles + tok_tile] + 1;
       }
 
       // Output of one chunk of 32 accumulator columns (16 tokens with the row_pair layout, 32
@@ -788,7 +844,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
           const bool second = tok + 1 < p.m && 2 * pr + 1 < ntok;
           if constexpr (AR) {
             if (phase) {                                           // (the host checked the vector alignment)
-              ar_tile_vectors(p, phase, ar_ok, t0, t1, int64_t(tok) * p.out_stride + n0,
+              ar_tile_vectors(p, phase, p.ar_ll ? 1 : ar_ok, ar_call, t0, t1, int64_t(tok) * p.out_stride + n0,
                               int64_t(tok) * p.ar_out_stride + n0, second);
               continue;
             }
@@ -854,7 +910,9 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
         }
       }
       if (phase != 1) break;
-      if constexpr (AR) ar_exchange_tile(p, &ar_ok, ar_call, w_tile * p.tok_tiles + tok_tile);
+      if constexpr (AR) {
+        if (!p.ar_ll) ar_exchange_tile(p, &ar_ok, ar_call, w_tile * p.tok_tiles + tok_tile);
+      }
       phase = 2;
       }
       // the accumulator buffer has been read: hand it back to the MMA warp
@@ -906,7 +964,9 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
             emit_chunk(s, c0, cols, phase);
           }
           if (phase != 1) break;
-          if constexpr (AR) ar_exchange_tile(p, &ar_ok, ar_call, w_tile * p.tok_tiles + tok_tile);
+          if constexpr (AR) {
+            if (!p.ar_ll) ar_exchange_tile(p, &ar_ok, ar_call, w_tile * p.tok_tiles + tok_tile);
+          }
           phase = 2;
           }
         }
@@ -922,6 +982,17 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
   tc_fence_before();
   __syncthreads();
   if (threadIdx.x == 0) stamp(p, 7);
+  if constexpr (AR) {
+    // the last CTA to get here closes the call: the next launch on these inboxes reads the new count
+    if (p.ar_ll && threadIdx.x == 0) {
+      const uint32_t t = atomicAdd(p.ar_state + 1, 1u);
+      if (t == gridDim.x - 1) {
+        p.ar_state[1] = 0;
+        __threadfence();
+        *reinterpret_cast<volatile uint32_t*>(p.ar_state) = *reinterpret_cast<volatile uint32_t*>(p.ar_state) + 1;
+      }
+    }
+  }
   if (abort_flag) {
     if (threadIdx.x == 0 && p.status) atomicExch(p.status, 1 + (int)blockIdx.x + (abort_flag << 16));   // CTA and wait site
     __nanosleep(1000000);                          // let copies that are still in flight land
@@ -1184,6 +1255,8 @@ extern "C" int64_t ri_fp4_gemm_workspace_bytes(int m, int n, int k, int fmt, int
   return partial ? ri_fp4_gemm_counter_bytes(m, n) + partial : 0;
 }
 
+extern "C" int ri_fp4_gemm_allreduce_uses_pairs(int m, int n, int world);
+
 namespace ri {
 namespace {
 // the ranks of a fused all-reduce (ri_fp4_gemm_allreduce); null for a plain launch
@@ -1329,11 +1402,15 @@ int gemm_launch(const uint8_t* act, int64_t act_row_bytes, const uint8_t* act_sf
                  "the fused all-reduce needs %lld tile flags, the flag arrays hold %lld",
                  (long long)(w_tiles_flag * pl.tok_tiles), (long long)ar->max_tiles);
     for (int r = 0; r < ar->world; ++r) {
-      p.ar_push[r] = static_cast<uint16_t*>(ar->rank_inboxes[r]) + int64_t(ar->rank) * ar->inbox_area;
-      p.ar_pull[r] = reinterpret_cast<const uint4*>(static_cast<uint16_t*>(ar->rank_inboxes[ar->rank]) + int64_t(r) * ar->inbox_area);
+      // an area holds inbox_area elements of 4 bytes (room for the pairs); plain BF16 tiles use its first half
+      p.ar_push[r] = reinterpret_cast<uint16_t*>(static_cast<uint8_t*>(ar->rank_inboxes[r]) + int64_t(ar->rank) * ar->inbox_area * 4);
+      p.ar_pull[r] = reinterpret_cast<const uint4*>(static_cast<uint8_t*>(ar->rank_inboxes[ar->rank]) + int64_t(r) * ar->inbox_area * 4);
       p.ar_flags[r] = static_cast<uint32_t*>(ar->rank_flags[r]);
     }
     p.ar_epoch = static_cast<uint32_t*>(ar->tile_calls);
+    p.ar_state = p.ar_epoch + ar->max_tiles;            // two words behind the per-tile counts
+    // small partials travel as (value, call number) pairs: twice the bytes, no fences
+    p.ar_ll = ri_fp4_gemm_allreduce_uses_pairs(m, n, ar->world);
     p.ar_out = ar->reduced_out;
     p.ar_out_stride = ar->reduced_row_stride;
     p.ar_wait_ns = peer_wait_ns();
@@ -1395,8 +1472,11 @@ extern "C" int64_t ri_fp4_gemm_allreduce_tiles(int m, int n) {
   const int64_t tok_tiles = (2 * int64_t(m < 1 ? 1 : m) + 15) / 16;
   return w_tiles * tok_tiles;
 }
+extern "C" int ri_fp4_gemm_allreduce_uses_pairs(int m, int n, int world) {
+  return int64_t(world - 1) * m * n * 4 <= ri::kArPairBytesMax ? 1 : 0;
+}
 extern "C" int64_t ri_fp4_gemm_allreduce_flag_bytes(int64_t max_tiles) { return max_tiles * ri::kArMaxRanks * 4; }
-extern "C" int64_t ri_fp4_gemm_allreduce_call_bytes(int64_t max_tiles) { return max_tiles * 4; }
+extern "C" int64_t ri_fp4_gemm_allreduce_call_bytes(int64_t max_tiles) { return (max_tiles + 2) * 4; }
 
 extern "C" int ri_fp4_gemm_allreduce(const uint8_t* act, int64_t act_row_bytes, const uint8_t* act_sf,
                                      int64_t act_sf_bytes, const uint8_t* w, int64_t w_row_bytes,
@@ -1419,7 +1499,7 @@ extern "C" int ri_fp4_gemm_allreduce(const uint8_t* act, int64_t act_row_bytes, 
   RI_CHECK_ARG(inbox_area >= int64_t(m) * partial_row_stride, "an inbox area of %lld elements is too small for [%d, %lld]",
                (long long)inbox_area, m, (long long)partial_row_stride);
   ArArgs ar{rank_inboxes, inbox_area, rank_flags, tile_calls, max_tiles, rank, world, reduced_out, reduced_row_stride};
-  void* own_area = static_cast<uint16_t*>(rank_inboxes[rank]) + int64_t(rank) * inbox_area;
+  void* own_area = static_cast<uint8_t*>(rank_inboxes[rank]) + int64_t(rank) * inbox_area * 4;
   return gemm_launch(act, act_row_bytes, act_sf, act_sf_bytes, w, w_row_bytes, w_sf, w_sf_bytes, alpha, n_alpha, own_area,
                      RI_DTYPE_BF16, partial_row_stride, m, n, k, fmt, layout, splits, workspace, workspace_bytes, status,
                      enable_pdl, stream, &ar);

@@ -107,7 +107,7 @@ class PeerAllReduce:
         self.tile_flag_off = self.flag_off + (flag_bytes + 255) // 256 * 256
         # ... and its inboxes: per slot one area of max_numel values for every source rank
         self.inbox_off = self.tile_flag_off + (int(self.lib.ri_fp4_gemm_allreduce_flag_bytes(self.max_tiles)) + 255) // 256 * 256
-        total = self.inbox_off + self.slots * self.world * self.slot_bytes
+        total = self.inbox_off + self.slots * self.world * 2 * self.slot_bytes       # 4 bytes per element (pair format)
         # Every step that can fail on one rank only is followed by an exchange of the outcome, so that all
         # ranks raise together and none is left waiting in a collective the others never enter.
         handle, err = None, None
@@ -153,7 +153,7 @@ class PeerAllReduce:
         self._data_ptrs = [(ctypes.c_void_p * self.world)(*[b + s * self.slot_bytes for b in self.bases])
                            for s in range(self.slots)]
         self.tile_flag_ptrs = (ctypes.c_void_p * self.world)(*[b + self.tile_flag_off for b in self.bases])
-        self._inbox_ptrs = [(ctypes.c_void_p * self.world)(*[b + self.inbox_off + s * self.world * self.slot_bytes
+        self._inbox_ptrs = [(ctypes.c_void_p * self.world)(*[b + self.inbox_off + s * self.world * 2 * self.slot_bytes
                                                              for b in self.bases]) for s in range(self.slots)]
         self._next = 0
         self._next_inbox = 0
@@ -176,7 +176,7 @@ class PeerAllReduce:
 
     def next_inbox(self, numel: int):
         """The next inbox for a GEMM with the reduction in its epilogue: (C array of every rank's mapping of
-        it, BF16 elements between the areas of consecutive source ranks).  Inboxes alternate like partials."""
+        it, elements per source rank's area -- an area is four bytes per element).  Inboxes alternate like partials."""
         if numel > self.max_numel:
             raise ValueError(f"{numel} elements: at most {self.max_numel}")
         slot = self._next_inbox
