@@ -47,7 +47,7 @@ L2_BYTES = 126 * 1024 * 1024
 SWEEPS_PER_STEP = 40                 # replays of the 32-case sweep graph per step
 CPU_MS = (1, 16, 128)                # token counts the CPU arm runs (4 shapes each)
 # DRAM traffic of the GEMM kernel / its algorithmic bytes, from one ncu capture per shape (see roofline.traffic_source)
-NCU_TRAFFIC_RATIO = 289.49 / 277.36
+NCU_TRAFFIC_RATIO = 286.68 / 277.36
 
 
 def load_peaks():
@@ -281,6 +281,8 @@ def main():
                          "GPUs against 20.1 for the epilogue), in the GEMM's epilogue over peer memory "
                          "(ri_fp4_gemm_allreduce), auto = the epilogue up to 16 tokens and the stand-alone kernel "
                          "above, or NCCL")
+    ap.add_argument("--attn-format", default="fp16", choices=["fp16", "e4m3"],
+                    help="number format of V and P in the ResAttn measurements (ops.resattn_pv_format)")
     ap.add_argument("--sweeps", action="store_true",
                     help="measure the other sweeps of the three hot paths (MXFP4 MEXT, KEXT, ResAttn batch sizes) "
                          "and print them as a second JSON line {\"sweeps\": ...}; N = 1 only")
@@ -317,8 +319,9 @@ def main():
     from resinfer_b200.quant.vllm_integration import residue_linear_op  # noqa: F401
     nvfp4.ensure_loaded()
 
-    global SHAPES, MS, SCALE_BLOCK, FORMAT
+    global SHAPES, MS, SCALE_BLOCK, FORMAT, ATTN_FORMAT
     FORMAT = args.format
+    ATTN_FORMAT = args.attn_format
     SCALE_BLOCK = 32 if args.format == "mxfp4" else 16
     if args.only:
         kind, _, rest = args.only.partition(":")
@@ -948,6 +951,7 @@ def measure_sweeps(torch, dev, capture, timed, hbm_gbs):
 
 # ResAttn decode points of the driver-run line: (head_dim, batch, page size).  The first three are the ones
 # `--only resattn:<index>` addresses.
+ATTN_FORMAT = "fp16"
 RESATTN_POINTS = ((128, 8, 16), (128, 64, 16), (256, 32, 16),
                   (128, 1, 16), (128, 32, 16), (128, 128, 16), (128, 256, 16),
                   (256, 1, 16), (256, 8, 16), (256, 128, 16), (256, 256, 16),
@@ -992,7 +996,9 @@ def measure_resattn(torch, dev, ops, capture, timed, hbm_gbs, only=None, steps=1
         q = torch.randn(batch, hq, d, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
         out = torch.empty(batch, hq, d, dtype=torch.bfloat16, device=dev)
         splits, _ = select_decode_plan(batch, hkv, int(lens.max()), sms, head_dim=d)
-        call = lambda: ops.resattn_decode(q, kd, ks, vd, vs, bt, lens, d ** -0.5, 1.0, out, splits=splits)  # noqa: E731
+        def call():                                         # the format switch is a host-side setting: it is
+            with ops.resattn_pv_format(ATTN_FORMAT):        # captured with the launch
+                ops.resattn_decode(q, kd, ks, vd, vs, bt, lens, d ** -0.5, 1.0, out, splits=splits)
         if capture is None:                                 # single-case mode: plain launches, CUDA events
             for _ in range(warmup):
                 call()
@@ -1008,7 +1014,7 @@ def measure_resattn(torch, dev, ops, capture, timed, hbm_gbs, only=None, steps=1
         tokens = int(lens.sum())
         nbytes = tokens * hkv * d * 2 * (0.5 + 1 / 16) + 4 * batch * hq * d + 4 * total
         res.append({"head_dim": d, "batch": batch, "page": page, "context": fixed_len or "U[1024,32768]", "tokens": tokens,
-                    "splits": splits, "us": round(us, 1),
+                    "splits": splits, "pv_format": ATTN_FORMAT, "us": round(us, 1),
                     "tbs": round(nbytes / us / 1e6, 3), "frac_hbm": round(nbytes / us / 1e3 / hbm_gbs, 3),
                     "kv_bytes_gt_l2": bool(nbytes > L2_BYTES)})
         del kd, vd, ks, vs, q, out, bt

@@ -255,6 +255,13 @@ int ri_resattn_decode(const void* q_bf16, const uint8_t* k_data, const uint8_t* 
                       const float* out_global_scale, uint8_t* out_block_scale, int64_t out_block_scale_bytes,
                       int splits, void* workspace, int64_t workspace_bytes, int q_residue, int32_t* status,
                       void* stream);
+/* Number format of V and P in the second product of ri_resattn_decode, process-wide: 0 (default) = FP16 -- code x
+ * block scale is exact in FP16 and P keeps 11 bits, 3e-3 from exact attention; 1 = E4M3 for both, the reference's
+ * choice (csrc/resattn/kernel_paged_decode.py:1958-1963, csrc/resattn/qmul4.py:45): tcgen05.mma kind::f8f6f4,
+ * half the shared-memory bytes per tile and a third copy stage, about 3e-2 from exact attention, and V saturates
+ * at 448 (caches whose code x block scale products stay in the FP8 range). */
+void ri_resattn_set_pv_format(int e4m3);
+int ri_resattn_get_pv_format(void);
 int64_t ri_resattn_workspace_bytes(int batch, int num_q_heads, int head_dim, int splits);
 int64_t ri_resattn_counter_bytes(int batch, int num_q_heads);
 

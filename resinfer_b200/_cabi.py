@@ -48,6 +48,8 @@ SIGNATURES = {
                                _vp, _i, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i, _vp, _i64, _i, _vp, _vp]),
     "ri_resattn_workspace_bytes": (_i64, [_i, _i, _i, _i]),
     "ri_resattn_counter_bytes": (_i64, [_i, _i]),
+    "ri_resattn_set_pv_format": (None, [_i]),
+    "ri_resattn_get_pv_format": (_i, []),
     "ri_peer_allreduce_flag_bytes": (_i64, []),
     "ri_peer_allreduce_state_bytes": (_i64, []),
     "ri_peer_allreduce_set_wait_ms": (None, [_i]),

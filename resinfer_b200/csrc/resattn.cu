@@ -110,6 +110,12 @@ __device__ __forceinline__ void store_nvfp4_out16(const float (&v)[16], float gs
 
 using namespace ri;
 
+namespace {
+int g_pv_e4m3 = 0;        // number format of V and P in the second product: 0 = FP16, 1 = E4M3
+}
+extern "C" void ri_resattn_set_pv_format(int e4m3) { g_pv_e4m3 = e4m3 ? 1 : 0; }
+extern "C" int ri_resattn_get_pv_format(void) { return g_pv_e4m3; }
+
 extern "C" int64_t ri_resattn_counter_bytes(int batch, int num_q_heads) {
   // one ticket per (sequence, KV head); sized by the query heads, which bound the KV heads
   return (int64_t(batch) * num_q_heads * 4 + 255) / 256 * 256;
@@ -203,6 +209,9 @@ extern "C" int ri_resattn_decode(const void* q_bf16, const uint8_t* k_data, cons
     p.m_part = p.l_part + rows;
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  s = head_dim == 128 ? tcattn::launch_decode_pv<128>(p, st) : tcattn::launch_decode_pv<256>(p, st);
+  if (g_pv_e4m3)
+    s = head_dim == 128 ? tcattn::launch_decode_pv<128, true>(p, st) : tcattn::launch_decode_pv<256, true>(p, st);
+  else
+    s = head_dim == 128 ? tcattn::launch_decode_pv<128, false>(p, st) : tcattn::launch_decode_pv<256, false>(p, st);
   return s;
 }

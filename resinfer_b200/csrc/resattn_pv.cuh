@@ -29,7 +29,6 @@
 // O^T accumulators: the eight P.V MMAs of a tile (16 tokens each) add into eight different accumulators,
 // 16 columns apart, which are summed at the end (head_dim 256: two sets, one per 128 output rows)
 constexpr int kPvColO = 128;
-constexpr int kPvAccs = 8;
 constexpr int kPvOffMisc = 3072;                  // running maxima, rescale factors, flags
 // P: K-major B operand without swizzle.  A core matrix is 8 rows (heads) x 16 bytes (8 tokens); the
 // core matrices of consecutive 8-token groups are 144 bytes apart (not 128: the softmax warps then
@@ -40,18 +39,19 @@ constexpr int kPvPGroup = 16 * kPvPLbo;           // 2304 bytes: one 8-row group
 constexpr int kPvOffP = 4096;
 constexpr int kPvOffV = 11264;                    // [D/64 d-blocks][128 tokens][64 d] FP16, 128B swizzle, M-major
 // head_dim 128: two CTAs of 21 warps per SM; head_dim 256: one CTA of 29 warps (the FP16 V tile is 64 KB)
-template <int D>
+template <int D, bool F8 = false>
 struct PvCfg {
   static constexpr int kSoft = 8;                                     // softmax warps (4 heads per thread)
   static constexpr int kHpt = 32 / kSoft;                             // heads a softmax thread handles
   static constexpr int kProd = 4;                                     // copy producer warps, 128 / kProd rows of a tile each
   static constexpr int kConv = D == 128 ? 8 : 16;                     // conversion warps
-  static constexpr int kVBufs = 2;                                    // FP16 V tiles in flight
-  static constexpr int kStages = 2;                                   // cp.async pipeline stages
+  static constexpr int kVBufs = 2;                                    // expanded V tiles in flight
+  static constexpr int kStages = F8 ? 3 : 2;                          // copy pipeline stages (the one-byte V tile leaves room for a third)
   static constexpr int kCtasPerSm = D == 128 ? 2 : 1;
   static constexpr int kDBlocks = D / 64;                             // 64-wide blocks of the head dimension
   static constexpr int kHalves = D / 128;                             // 128-row halves of O^T (M of one MMA)
-  static constexpr int kVBytes = 128 * D * 2;
+  static constexpr int kAccs = F8 ? 4 : 8;                            // P.V MMAs (and accumulators) per tile and half: K = 32 / 16 tokens
+  static constexpr int kVBytes = 128 * D * (F8 ? 1 : 2);
   static constexpr int kVStride = kVBytes;
   static constexpr int kHeaderBytes = kPvOffV + kVBufs * kVBytes;      // a multiple of 1024
   static constexpr int kThreads = (kSoft + 1 + kProd + kConv) * 32;
@@ -64,6 +64,13 @@ __device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uin
   asm volatile(
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void mma_f8_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 // shared-memory matrix descriptor with explicit leading / stride byte offsets (sm_100 encoding)
@@ -176,11 +183,12 @@ __device__ __forceinline__ void pack_nvfp4_output(const AttnParams& p, int b, in
   }
 }
 
-template <int D>
-__global__ void __launch_bounds__(PvCfg<D>::kThreads, PvCfg<D>::kCtasPerSm)
+template <int D, bool F8>
+__global__ void __launch_bounds__(PvCfg<D, F8>::kThreads, PvCfg<D, F8>::kCtasPerSm)
 resattn_pv_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map, const AttnParams p) {
   using C = TCfg<D>;
-  using PC = PvCfg<D>;
+  using PC = PvCfg<D, F8>;
+  constexpr int kPvAccs = PC::kAccs;
   constexpr int kPvConv = PC::kConv, kPvVBufs = PC::kVBufs, kPvStages = PC::kStages, kThreadsPv = PC::kThreads;
   constexpr int kPvTmemCols = PC::kTmemCols, kPvVStride = PC::kVStride, kPvHeaderBytes = PC::kHeaderBytes;
   constexpr int kPvSoft = PC::kSoft, kHpt = PC::kHpt, kPvProd = PC::kProd;
@@ -401,12 +409,32 @@ resattn_pv_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
       // MMAs of tile i-2, so having seen it means those have read the buffer.)
       {
         const int t = 32 * q + lane;
+        if constexpr (F8) {
+          // E4M3 probabilities (the reference's choice, csrc/resattn/kernel_paged_decode.py:1958-1963); the row
+          // sums keep the unrounded values, as there.  A core matrix of the 8-bit K-major operand is 8 heads x
+          // 16 tokens; the core matrices of consecutive 16-token groups are kPvPLbo bytes apart.
+          uint8_t* pb = smem + kPvOffP + sb * kPvPGroup + (t >> 4) * kPvPLbo + (t & 15) + g0 * 16;
+          float pv[kHpt];
+#pragma unroll
+          for (int h = 0; h < kHpt; ++h) {
+            pv[h] = fast_exp2(s[h] - m_sh[g0 + h]);            // 0 for tokens past the end (s = -inf)
+            l_thr[h] += pv[h];
+          }
+#pragma unroll
+          for (int h = 0; h < kHpt; h += 2) {
+            uint16_t two;                                      // low byte: first operand of the pair
+            asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(two) : "f"(pv[h + 1]), "f"(pv[h]));
+            pb[h * 16] = uint8_t(two & 0xFF);
+            pb[(h + 1) * 16] = uint8_t(two >> 8);
+          }
+        } else {
         __half* pb = reinterpret_cast<__half*>(smem + kPvOffP + sb * kPvPGroup + (t >> 3) * kPvPLbo) + (t & 7) + g0 * 8;
 #pragma unroll
         for (int h = 0; h < kHpt; ++h) {
           const float pv = fast_exp2(s[h] - m_sh[g0 + h]);     // 0 for tokens past the end (s = -inf)
           l_thr[h] += pv;
           pb[h * 8] = __float2half_rn(pv);
+        }
         }
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -461,6 +489,18 @@ resattn_pv_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
         // B = P: K-major, no swizzle: 8-token core matrices kPvPLbo apart along K; rows 8-15 are the zero group
         const uint32_t pa = smem_u32(smem + kPvOffP + vb * kPvPGroup);
         const uint32_t p_sbo = (2 - vb) * kPvPGroup;
+        if constexpr (F8) {
+          // kind::f8f6f4, E4M3 x E4M3, K = 32 tokens per instruction: A = one 128-byte row per token (128 d),
+          // 8-token groups 1 KB apart; B = two 16-token core matrices per instruction
+          const uint32_t idesc_pv8 = (1u << 4) | (1u << 15) | (uint32_t(16 >> 3) << 17) | (uint32_t(128 >> 4) << 24);
+#pragma unroll
+          for (int hf = 0; hf < PC::kHalves; ++hf)
+#pragma unroll
+            for (int k32 = 0; k32 < kTile / 32; ++k32)
+              mma_f8_ss(tmem_base + kPvColO + 16 * (hf * kPvAccs + k32),
+                        desc_full(va + hf * 16384 + k32 * 4096, 16384, 1024, 2),
+                        desc_full(pa + k32 * 2 * kPvPLbo, kPvPLbo, p_sbo, 0), idesc_pv8, i > 0 ? 1u : 0u);
+        } else {
 #pragma unroll
         for (int hf = 0; hf < PC::kHalves; ++hf)
 #pragma unroll
@@ -468,6 +508,7 @@ resattn_pv_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
             mma_f16_ss(tmem_base + kPvColO + 16 * (hf * kPvAccs + k16),
                        desc_full(va + hf * 2 * 16384 + k16 * 2048, 16384, 1024, 2),
                        desc_full(pa + k16 * 2 * kPvPLbo, kPvPLbo, p_sbo, 0), idesc_pv, i > 0 ? 1u : 0u);
+        }
         mma_commit(smem_u32(&bar_pvdone[vb]));
       }
       __syncwarp();
@@ -603,6 +644,35 @@ resattn_pv_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
         sc2[0] = __byte_perm(lo, 0, 0x1010); sc2[1] = __byte_perm(lo, 0, 0x3232);
         sc2[2] = __byte_perm(hi, 0, 0x1010); sc2[3] = __byte_perm(hi, 0, 0x3232);
       }
+      if constexpr (F8) {
+        // E4M3 V (the reference's choice, csrc/resattn/qmul4.py:45): code x block scale is exact in FP16 and is
+        // rounded to E4M3 (nearest even, saturating).  One 128-byte row per token holds 128 head-dim values; this
+        // thread's 64 values are the four 16-byte chunks (dblk & 1) * 4 .. + 3, one per scale block.
+        const uint32_t row0 = smem_u32(smem + kPvOffV + (kPvVBufs == 2 ? vb * kPvVStride : 0) + (dblk >> 1) * 16384 +
+                                       (tok >> 3) * 1024 + (tok & 7) * 128);
+#pragma unroll
+        for (int blk = 0; blk < 4; ++blk) {
+          const __half2 s2 = bits_h2(sc2[blk]);
+          uint32_t o[4];
+#pragma unroll
+          for (int hw = 0; hw < 2; ++hw) {
+            uint32_t h0, h1, h2, h3;
+            asm("{\n\t.reg .b8 a, b, c, d;\n\tmov.b32 {a, b, c, d}, %4;\n\t"
+                "cvt.rn.f16x2.e2m1x2 %0, a;\n\tcvt.rn.f16x2.e2m1x2 %1, b;\n\t"
+                "cvt.rn.f16x2.e2m1x2 %2, c;\n\tcvt.rn.f16x2.e2m1x2 %3, d;\n\t}"
+                : "=r"(h0), "=r"(h1), "=r"(h2), "=r"(h3) : "r"(words[2 * blk + hw]));
+            const uint32_t p0 = h2_bits(__hmul2(bits_h2(h0), s2)), p1 = h2_bits(__hmul2(bits_h2(h1), s2));
+            const uint32_t p2 = h2_bits(__hmul2(bits_h2(h2), s2)), p3 = h2_bits(__hmul2(bits_h2(h3), s2));
+            asm("{\n\t.reg .b16 a, b, c, d;\n\t"
+                "cvt.rn.satfinite.e4m3x2.f16x2 a, %2;\n\tcvt.rn.satfinite.e4m3x2.f16x2 b, %3;\n\t"
+                "cvt.rn.satfinite.e4m3x2.f16x2 c, %4;\n\tcvt.rn.satfinite.e4m3x2.f16x2 d, %5;\n\t"
+                "mov.b32 %0, {a, b};\n\tmov.b32 %1, {c, d};\n\t}"
+                : "=r"(o[2 * hw]), "=r"(o[2 * hw + 1]) : "r"(p0), "r"(p1), "r"(p2), "r"(p3));
+          }
+          const uint32_t chunk = uint32_t(((dblk & 1) * 4 + blk) ^ (tok & 7));
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row0 + (chunk << 4)), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+        }
+      } else {
       // destination row of this token in the swizzled M-major tile; chunk w goes to (w ^ (tok & 7)) << 4,
       // which is an XOR on the address because the row is 128-byte aligned
       const uint32_t dst0 = smem_u32(smem + kPvOffV + (kPvVBufs == 2 ? vb * kPvVStride : 0) + dblk * 16384 +
@@ -618,6 +688,7 @@ resattn_pv_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
         const uint32_t o0 = h2_bits(__hmul2(bits_h2(h0), s2)), o1 = h2_bits(__hmul2(bits_h2(h1), s2));
         const uint32_t o2 = h2_bits(__hmul2(bits_h2(h2), s2)), o3 = h2_bits(__hmul2(bits_h2(h3), s2));
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst0 ^ (w8 << 4)), "r"(o0), "r"(o1), "r"(o2), "r"(o3) : "memory");
+      }
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
@@ -731,16 +802,16 @@ int make_pool_map(CUtensorMap* map, const uint8_t* base, int64_t rows) {
   return RI_OK;
 }
 
-template <int D>
+template <int D, bool F8>
 int launch_decode_pv(const AttnParams& p, cudaStream_t st) {
-  using PC = PvCfg<D>;
+  using PC = PvCfg<D, F8>;
   static bool attr_done[64] = {};
   int dev = 0;
   RI_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) dev = 0;
   if (!attr_done[dev]) {
-    RI_CUDA(cudaFuncSetAttribute(resattn_pv_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, PC::kSmemBytes));
-    RI_CUDA(cudaFuncSetAttribute(resattn_pv_kernel<D>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
+    RI_CUDA(cudaFuncSetAttribute(resattn_pv_kernel<D, F8>, cudaFuncAttributeMaxDynamicSharedMemorySize, PC::kSmemBytes));
+    RI_CUDA(cudaFuncSetAttribute(resattn_pv_kernel<D, F8>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
     attr_done[dev] = true;
   }
   CUtensorMap k_map{}, v_map{};
@@ -761,5 +832,5 @@ int launch_decode_pv(const AttnParams& p, cudaStream_t st) {
   attr.val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  return cuda_status(cudaLaunchKernelEx(&cfg, resattn_pv_kernel<D>, k_map, v_map, p), "resattn decode launch");
+  return cuda_status(cudaLaunchKernelEx(&cfg, resattn_pv_kernel<D, F8>, k_map, v_map, p), "resattn decode launch");
 }

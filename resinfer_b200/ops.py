@@ -188,6 +188,21 @@ def fp4_gemm_static_scratch(act: torch.Tensor, act_sf: torch.Tensor, weight: tor
     return out
 
 
+@contextlib.contextmanager
+def resattn_pv_format(fmt: str):
+    """Inside the block ``resattn_decode`` runs its second product in ``fmt``: "fp16" (the default: V exact,
+    P with 11 bits) or "e4m3" (V and P rounded to E4M3 like the reference's kernel: faster, about ten times
+    further from exact attention).  Process-wide (``ri_resattn_set_pv_format``)."""
+    lib = _cabi.load()
+    code = {"fp16": 0, "e4m3": 1}[fmt]
+    prev = int(lib.ri_resattn_get_pv_format())
+    lib.ri_resattn_set_pv_format(code)
+    try:
+        yield
+    finally:
+        lib.ri_resattn_set_pv_format(prev)
+
+
 def resattn_decode(q: torch.Tensor, k_data: torch.Tensor, k_sf: torch.Tensor, v_data: torch.Tensor,
                    v_sf: torch.Tensor, block_tables: torch.Tensor, seq_lens: torch.Tensor,
                    score_scale: float, out_scale: float, out: torch.Tensor, *, splits: int = 1,
