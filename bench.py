@@ -382,18 +382,25 @@ def main():
             dist.all_reduce(y)
         return y
 
+    def mext_layout(L, m):
+        # the operand layout the public op picks for the fold route (same arithmetic either way)
+        from resinfer_b200.quant.vllm_integration.residue_linear_op import fold_prefers_concat_k
+        return "concat_k" if (not mx and fold_prefers_concat_k(m, L.k)) else "row_pair"
+
     def run_case(L, m, quant=True, pre=None, reduce=True):
         c = L.next_copy()
+        lay = mext_layout(L, m)
         if quant:
             if mx:
                 codes, sf = mxfp4.quantize_mext(L.x[m], pdl_mode="early")
             else:
-                codes, sf = nvfp4.scaled_fp4_quant_mext_r1(L.x[m], L.gs_inv[m], layout_mode=1, enable_pdl=True)
+                codes, sf = nvfp4.scaled_fp4_quant_mext_r1(L.x[m], L.gs_inv[m], layout_mode=3 if lay == "concat_k" else 1,
+                                                           enable_pdl=True)
             launches["n"] += 1
         else:
             codes, sf = pre
         y = ops.fp4_gemm(codes, sf, L.w[c], L.w_sf[c], None if mx else L.alpha[m], m=m, fmt=args.format,
-                         layout="row_pair", out=gemm_out(L, m, reduce), allreduce=fused_for(L, reduce, m))
+                         layout=lay, out=gemm_out(L, m, reduce), allreduce=fused_for(L, reduce, m))
         launches["n"] += 1
         return finish(L, m, y, reduce)
 
@@ -525,7 +532,9 @@ def main():
 
     # ---- GEMM kernel alone (pre-quantised activations) for the roofline of the dominant kernel
     pre = {(L.name, m): (mxfp4.quantize_mext(L.x[m]) if mx else
-                         nvfp4.scaled_fp4_quant_mext_r1(L.x[m], L.gs_inv[m], layout_mode=1)) for L in layers for m in MS}
+                         nvfp4.scaled_fp4_quant_mext_r1(L.x[m], L.gs_inv[m],
+                                                        layout_mode=3 if mext_layout(L, m) == "concat_k" else 1))
+           for L in layers for m in MS}
     replay_g = capture(lambda: sweep(False, pre, reduce=False))
     hbm_gbs, peak_kind = load_peaks()
     roofline = None
@@ -813,14 +822,17 @@ def run_single_case(torch, dev, kind, rest, steps, warmup):
 
 def measure_detail(torch, dev, layers, outs, nvfp4, ops, capture, timed, hbm_gbs):
     """Per-case latency (cold weights: rotating copies larger than L2) and a ResAttn decode point."""
+    from resinfer_b200.quant.vllm_integration.residue_linear_op import fold_prefers_concat_k
     cases = []
     for L in layers:
         for m in MS:
             def one(L=L, m=m):
                 for _ in range(L.copies):
                     c = L.next_copy()
-                    codes, sf = nvfp4.scaled_fp4_quant_mext_r1(L.x[m], L.gs_inv[m], layout_mode=1, enable_pdl=True)
-                    ops.fp4_gemm(codes, sf, L.w[c], L.w_sf[c], L.alpha[m], m=m, fmt="nvfp4", layout="row_pair",
+                    lay = "concat_k" if fold_prefers_concat_k(m, L.k) else "row_pair"     # as the public op picks it
+                    codes, sf = nvfp4.scaled_fp4_quant_mext_r1(L.x[m], L.gs_inv[m], layout_mode=3 if lay == "concat_k" else 1,
+                                                               enable_pdl=True)
+                    ops.fp4_gemm(codes, sf, L.w[c], L.w_sf[c], L.alpha[m], m=m, fmt="nvfp4", layout=lay,
                                  out=outs[(L.name, m)])
             rp = capture(one)
             us = timed(rp, 10, 3) * 1e3 / L.copies

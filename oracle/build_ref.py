@@ -33,7 +33,9 @@ REF_SOURCES = [
 
 
 def default_reference() -> Path:
-    return Path(os.environ.get("RESINFER_REFERENCE", "/root/reference"))
+    """The reference checkout: ``$RESINFER_REFERENCE``, else a directory ``reference`` beside this repository."""
+    env = os.environ.get("RESINFER_REFERENCE")
+    return Path(env) if env else Path(__file__).resolve().parents[2] / "reference"
 
 
 def build(reference: Path | None = None, jobs: int = 0, verbose: bool = True) -> Path | None:

@@ -12,8 +12,7 @@ import os
 from pathlib import Path
 
 _PKG = Path(__file__).resolve().parent
-# RESINFER_B200_LIB selects another build of the library (development: A/B comparisons of kernels)
-LIB_PATH = Path(os.environ.get("RESINFER_B200_LIB") or _PKG / "_lib" / "libresinfer_b200.so")
+LIB_PATH = _PKG / "_lib" / "libresinfer_b200.so"
 
 RI_ERR_ARG, RI_ERR_UNSUPPORTED, RI_ERR_DEVICE, RI_ERR_TIMEOUT = -1, -2, -3, -4
 DTYPE_BF16, DTYPE_FP16, DTYPE_F32, DTYPE_NVFP4 = 0, 1, 2, 3

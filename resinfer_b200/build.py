@@ -31,8 +31,6 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC",
     "--expt-relaxed-constexpr", "-diag-suppress", "177",
 ]
-# development switch: RESINFER_B200_DEFINES="RI_GEMM_PROFILE" adds -D flags (cycle accounting in the GEMM)
-NVCC_FLAGS += [f"-D{d}" for d in os.environ.get("RESINFER_B200_DEFINES", "").split(",") if d]
 
 
 def _nvcc() -> str:

@@ -131,7 +131,7 @@ def test_fold_host_api_dual_alpha_and_strided_weight(cuda_device):
 
 
 def test_gemm_properties_at_baseline_size(cuda_device):
-    """Size-independent properties on a BASELINE shape (qkv 5120 -> 10240, M = 128): split-K invariance,
+    """Size-independent properties on a benchmarked shape (qkv 5120 -> 10240, M = 128): split-K invariance,
     row independence (a token's output does not depend on the other tokens) and scaling in alpha."""
     from resinfer_b200 import nvfp4, ops
     from resinfer_b200.quant import weight_prep

@@ -217,7 +217,7 @@ def test_kernels_reproduce_golden_fixtures(cuda_device, path):
 
 
 def test_quantiser_roundtrip_property_at_full_size(cuda_device):
-    """Size-independent property on a BASELINE-sized input (down projection, M=128): dequantised base +
+    """Size-independent property on a benchmark-sized input (down projection, M=128): dequantised base +
     dequantised residue reconstructs x far better than the base alone, for every row."""
     from resinfer_b200 import nvfp4
     m, k = 128, 25600

@@ -5,7 +5,7 @@ launches, CUDA events around 5 replays after 3 warm-up replays.
 
 Covers the NVFP4 MEXT quantiser (row_pair), the NVFP4 KEXT quantiser at residue ratios 0.125 / 0.25 / 0.5 and
 the MXFP4 MEXT quantiser, at decode and prefill token counts for K = 5120, 8192, 25600.  The table is printed
-(run with ``-s``) and, when a ``gpurun_out`` directory exists at the repository root, written there as
+(run with ``-s``) and, when the environment variable ``RESINFER_B200_REPORT_DIR`` names a directory, written there as
 ``quantisers_vs_reference.json``.  The assertion is deliberately loose (a launch must not take more than
 1.6 x the reference kernel's time, plus 0.3 us): it guards against regressions, the numbers are the product.
 
@@ -98,8 +98,8 @@ def test_quantisers_beside_the_reference_kernels(cuda_device, ref_ops):
         plain = f"  {r['ours_plain_us']:.2f} / {r['ref_plain_us']:.2f}" if "ours_plain_us" in r else ""
         print(f"{r['kernel']:18s} {r['k']:6d} {r['m']:5d} {r['ours_us']:9.2f} {r['ref_us']:9.2f} "
               f"{r['ours_us'] / r['ref_us']:6.2f} {r['ours_gbs']:10d}{plain}")
-    out_dir = os.path.join(ROOT, "gpurun_out")
-    if os.path.isdir(out_dir):
+    out_dir = os.environ.get("RESINFER_B200_REPORT_DIR", "")
+    if out_dir and os.path.isdir(out_dir):
         with open(os.path.join(out_dir, "quantisers_vs_reference.json"), "w") as f:
             json.dump(rows, f, indent=1)
     slow = [r for r in rows if r["ours_us"] > 1.6 * r["ref_us"] + 0.3]

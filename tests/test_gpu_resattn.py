@@ -129,7 +129,7 @@ def test_reference_named_host_entry(cuda_device):
 
 
 def test_decode_at_baseline_shape(cuda_device):
-    """BASELINE shape (64 query heads, 8 KV heads, page 16, contexts up to 32768) with random KV bytes:
+    """The benchmarked shape (64 query heads, 8 KV heads, page 16, contexts up to 32768) with random KV bytes:
     properties only -- finite output, split invariance, and permuting the page pool together with the
     block table leaves the result unchanged."""
     from resinfer_b200 import ops

@@ -115,7 +115,7 @@ def test_mxfp4_blocks_power_of_two_scale():
 
 
 def test_config0_mext_linear_on_cpu():
-    """BASELINE config 0 (reduced N for speed): the folded contraction equals the two-term sum and
+    """The reference's CPU-runnable configuration (x [16, 5120], reduced N for speed): the folded contraction equals the two-term sum and
     tracks the torch-eager reference path."""
     import torch
     m, k, n = 16, 5120, 512
