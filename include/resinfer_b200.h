@@ -169,7 +169,11 @@ int ri_fp4_gemm_static_scratch(const uint8_t* act, int64_t act_row_bytes, const 
  * says otherwise; measured on the GPU's nanosecond timer); on expiry `status` (optional) receives
  * 0x40000000 | missing_rank << 8 | rank and `out` receives this rank's own partial -- a defined value,
  * not the sum -- so callers must look at the status word where that matters.  The sum is taken in
- * rank order with FP32 accumulation, so every rank holds the same bits.  enable_pdl != 0 launches
+ * rank order with FP32 accumulation, so every rank holds the same bits.  When more than 4 MB would have to be
+ * read from the peers (more than two ranks), each rank sums only its own slice of the vectors, writes the sums back
+ * into its own partial buffer and fetches the other slices from their owners after a second hand-shake -- same bits,
+ * 2 (world - 1) / world instead of (world - 1) times the bytes; the partial buffer then holds those sums in this
+ * rank's slice afterwards.  enable_pdl != 0 launches
  * with programmatic stream serialisation: the kernel's launch overlaps the tail of the kernel that
  * wrote the partial and its first instruction waits for that kernel's completion. */
 int64_t ri_peer_allreduce_flag_bytes(void);

@@ -56,7 +56,7 @@ def test_argument_validation_needs_no_gpu(lib):
     assert st == _cabi.RI_ERR_ARG and b"2..8 ranks" in lib.ri_last_error()
     st = lib.ri_peer_allreduce_bf16(None, None, 1, 2, 12, None, None, None, None, 0)
     assert st == _cabi.RI_ERR_ARG and b"multiple of 8" in lib.ri_last_error()
-    assert lib.ri_peer_allreduce_flag_bytes() == 32 and lib.ri_peer_allreduce_state_bytes() == 8
+    assert lib.ri_peer_allreduce_flag_bytes() == 64 and lib.ri_peer_allreduce_state_bytes() == 16
 
 
 def test_missing_library_is_loud(monkeypatch, tmp_path):
