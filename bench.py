@@ -369,6 +369,12 @@ def main():
             return peer_ar
         return None
 
+    def red_ctx(L, m):
+        # how the public op of a row-parallel layer gets its sum: in the epilogue or by the stand-alone kernel
+        if peer_ar is None or L.par != "row":
+            return ops.row_parallel_reduction(None)
+        return ops.row_parallel_reduction(peer_ar, epilogue=fused_for(L, True, m) is not None)
+
     def gemm_out(L, m, reduce):
         if peer_ar is not None and L.par == "row" and reduce and fused_for(L, reduce, m) is None:
             return peer_ar.partial((m, L.n))
@@ -568,20 +574,15 @@ def main():
                 for L in layers:
                     c = L.next_copy()
                     xd = hx[(L.name, m)].to(dev, non_blocking=True)
-                    with ops.row_parallel_reduction(fused_for(L, True, m)):    # row-parallel layers: sum in the epilogue
+                    with red_ctx(L, m):                         # row-parallel layers: the sum over the ranks
                         if mx:
                             y = torch.ops.residue.mxfp4_linear(xd, L.w[c], L.w_sf[c], zero_mask, zero_mask, "mext_r1",
                                                                torch.bfloat16, None)
                         else:
                             y = torch.ops.residue.nvfp4_linear(xd, L.w[c], L.gs_inv[m], L.w_sf[c], L.w_sf[c], zero_mask,
                                                                L.alpha[m], L.k, 0, 0, L.n, True, False, True)
-                    if tp > 1 and L.par == "row" and fused_for(L, True, m) is None:
-                        if peer_ar is not None:             # the op's output is copied into the exported buffer first
-                            pbuf = peer_ar.partial(tuple(y.shape))
-                            pbuf.copy_(y)
-                            y = peer_ar.reduce(pbuf, status=ar_status)
-                        else:
-                            dist.all_reduce(y)
+                    if tp > 1 and L.par == "row" and peer_ar is None:
+                        dist.all_reduce(y)
                     done[i].record()
                     out_stream.wait_event(done[i])
                     with torch.cuda.stream(out_stream):
@@ -632,17 +633,13 @@ def main():
                         c = L.next_copy()
                         xd = xs[(L.name, m)]
                         cur.wait_event(arrived[(L.name, m)])
-                        with ops.row_parallel_reduction(fused_for(L, True, m)):
+                        with red_ctx(L, m):
                             if mx:
                                 y = torch.ops.residue.mxfp4_linear(xd, L.w[c], L.w_sf[c], zero_mask, zero_mask, "mext_r1",
                                                                    torch.bfloat16, None)
                             else:
                                 y = torch.ops.residue.nvfp4_linear(xd, L.w[c], L.gs_inv[m], L.w_sf[c], L.w_sf[c],
                                                                    zero_mask, L.alpha[m], L.k, 0, 0, L.n, True, False, True)
-                        if tp > 1 and L.par == "row" and fused_for(L, True, m) is None:
-                            pbuf = peer_ar.partial(tuple(y.shape))
-                            pbuf.copy_(y)
-                            y = peer_ar.reduce(pbuf, status=ar_status)
                         side.wait_stream(cur)
                         with torch.cuda.stream(side):
                             hy[(L.name, m)].copy_(y, non_blocking=True)

@@ -90,7 +90,7 @@ __device__ __forceinline__ void wait_for_peers(const PeerArParams& p, uint32_t e
   }
 }
 
-__global__ void __launch_bounds__(kArThreads) peer_allreduce_kernel(const PeerArParams p) {
+__global__ void __launch_bounds__(kArThreads, 2) peer_allreduce_kernel(const PeerArParams p) {
   __shared__ int ok;
   __shared__ int last_block;
   // launched with programmatic stream serialisation: the partial is the previous kernel's output
@@ -143,14 +143,17 @@ __global__ void __launch_bounds__(kArThreads) peer_allreduce_kernel(const PeerAr
     wait_for_peers(p, epoch, 1, &ok);
     __syncthreads();
     if (ok) {
-      for (int q = 0; q < p.world; ++q) {
-        if (q == p.rank) continue;
-        const int64_t qlo = int64_t(q) * len, qhi = qlo + len < p.n16 ? qlo + len : p.n16;
-        for (int64_t i = qlo + first; i < qhi; i += stride) {
-          uint4 v;
-          asm volatile("ld.global.cv.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p.data[q] + i));
-          p.out[i] = v;
-        }
+      // every vector outside this rank's slice from its owner; one load per thread and pass, all of them in flight
+      for (int64_t i = first; i < p.n16; i += stride) {
+        if (i >= lo && i < hi) continue;
+        const int q = int(i / len);
+        const uint4* src = p.data[0];                      // (selected with compile-time indices)
+#pragma unroll
+        for (int r = 1; r < kMaxRanks; ++r)
+          if (r == q) src = p.data[r];
+        uint4 v;
+        asm volatile("ld.global.cv.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src + i));
+        p.out[i] = v;
       }
     } else {
       for (int64_t i = first; i < p.n16; i += stride)
@@ -215,7 +218,17 @@ extern "C" int ri_peer_allreduce_bf16(const void* const* rank_data, void* const*
   int s = device_info(&di);
   if (s) return s;
   const int64_t want = (p.n16 + kArThreads - 1) / kArThreads;
-  const int64_t cap = 2 * int64_t(di.sm_count);         // two blocks of this size are resident per SM
+  // every block must be resident at once (blocks wait for announcements that the last block of a pass makes)
+  static int blocks_per_sm = 0;
+  if (blocks_per_sm == 0) {
+    int b = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&b, peer_allreduce_kernel, kArThreads, 0) != cudaSuccess || b < 1) {
+      (void)cudaGetLastError();
+      b = 1;
+    }
+    blocks_per_sm = b > 2 ? 2 : b;
+  }
+  const int64_t cap = int64_t(blocks_per_sm) * di.sm_count;
   const int grid = int(want < 1 ? 1 : (want > cap ? cap : want));
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(grid);

@@ -80,22 +80,26 @@ def check_status(device) -> None:
 
 
 _ACTIVE_REDUCER = None
+_ACTIVE_REDUCER_EPILOGUE = True
+_NO_REDUCER = object()                   # "no reduction for this call" inside a row_parallel_reduction block
 
 
 @contextlib.contextmanager
-def row_parallel_reduction(reducer):
+def row_parallel_reduction(reducer, epilogue: bool = True):
     """Inside the block every ``fp4_gemm`` call without an explicit ``allreduce`` argument -- in particular the
     ones made by ``residue::nvfp4_linear`` and ``residue::mxfp4_linear``, whose schemas have no room for it --
-    sums its output over the ranks of ``reducer`` (a ``resinfer_b200.quant.tp.PeerAllReduce``) in the GEMM's
-    epilogue.  This is where a tensor-parallel model wraps the linear of a row-parallel layer; ``None`` switches
-    it off again for a nested block.  Process-wide, not per thread."""
-    global _ACTIVE_REDUCER
-    prev = _ACTIVE_REDUCER
-    _ACTIVE_REDUCER = reducer
+    returns its output summed over the ranks of ``reducer`` (a ``resinfer_b200.quant.tp.PeerAllReduce``):
+    in the GEMM's epilogue (``epilogue=True``), or by the stand-alone kernel with the GEMM writing its partial
+    straight into the exported buffer (``epilogue=False``: two launches, no copy in between).  This is where a
+    tensor-parallel model wraps the linear of a row-parallel layer; ``None`` switches it off again for a nested
+    block.  Process-wide, not per thread."""
+    global _ACTIVE_REDUCER, _ACTIVE_REDUCER_EPILOGUE
+    prev = (_ACTIVE_REDUCER, _ACTIVE_REDUCER_EPILOGUE)
+    _ACTIVE_REDUCER, _ACTIVE_REDUCER_EPILOGUE = reducer, bool(epilogue)
     try:
         yield reducer
     finally:
-        _ACTIVE_REDUCER = prev
+        _ACTIVE_REDUCER, _ACTIVE_REDUCER_EPILOGUE = prev
 
 
 def fp4_gemm(act: torch.Tensor, act_sf: torch.Tensor, weight: torch.Tensor, weight_sf: torch.Tensor,
@@ -113,8 +117,19 @@ def fp4_gemm(act: torch.Tensor, act_sf: torch.Tensor, weight: torch.Tensor, weig
     all ranks itself (``ri_fp4_gemm_allreduce``); ``out`` (BF16) receives the sum.  Every
     rank of the group must make the same calls in the same order."""
     lib = _cabi.load()
-    if allreduce is None:
-        allreduce = _ACTIVE_REDUCER
+    if allreduce is None and _ACTIVE_REDUCER is not None:
+        if _ACTIVE_REDUCER_EPILOGUE:
+            allreduce = _ACTIVE_REDUCER
+        else:
+            # the GEMM writes this rank's partial into the exported buffer, the stand-alone kernel sums the ranks
+            red, n_out = _ACTIVE_REDUCER, weight.shape[0]
+            if out_dtype != torch.bfloat16 or (out is not None and out.dtype != torch.bfloat16):
+                raise ValueError("the all-reduce sums BF16 partials")
+            part = fp4_gemm(act, act_sf, weight, weight_sf, alpha, m=m, fmt=fmt, layout=layout, out_dtype=out_dtype,
+                            out=red.partial((m, n_out)), splits=splits, enable_pdl=enable_pdl, allreduce=_NO_REDUCER)
+            return red.reduce(part, out)
+    if allreduce is _NO_REDUCER:
+        allreduce = None
     fmt_c = {"nvfp4": _cabi.FMT_NVFP4, "mxfp4": _cabi.FMT_MXFP4}[fmt]
     lay_c = {"plain": _cabi.GEMM_PLAIN, "row_pair": _cabi.GEMM_ROW_PAIR, "concat_k": _cabi.GEMM_CONCAT_K}[layout]
     n, kp = weight.shape

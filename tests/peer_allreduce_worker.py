@@ -44,6 +44,13 @@ def fused_gemm(rank, world, dev, ar):
         ops.check_status(dev)
         assert torch.equal(outs[0], want) and torch.equal(outs[1], want), (rank, m, n, k)
 
+        # the same sum through the two-kernel form that the context manager selects for the registered ops
+        with ops.row_parallel_reduction(ar, epilogue=False):
+            two = [ops.fp4_gemm(c, s, w, ws, alpha, m=m, layout="row_pair", splits=splits) for _ in range(2)]
+        torch.cuda.synchronize()
+        ar.check()
+        assert torch.equal(two[0], want) and torch.equal(two[1], want), (rank, m, n, k, "two kernels")
+
         def body():
             for o in outs:
                 ops.fp4_gemm(c, s, w, ws, alpha, m=m, layout="row_pair", splits=splits, out=o, allreduce=ar)
