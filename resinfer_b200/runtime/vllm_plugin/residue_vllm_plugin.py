@@ -6,10 +6,12 @@ or RESIDUE_ATTN is "1"; when a gate is set and anything fails, the exception is 
 worker refuses to serve without the residue kernels.
 
 What is installed: the native library is loaded and the ``nvfp4::*`` / ``residue::*`` ops are
-registered, and this package is aliased under the reference's module names.  The vLLM-side adapter
-classes (linear methods, attention backend) are not part of this library; when they are importable
-from the reference checkout (``quant.vllm_integration.*`` on sys.path) they are installed on top of
-these ops exactly as the reference plugin does.
+registered, this package is aliased under the reference's module names, and -- for RESIDUE_NVFP4 --
+this library's NVFP4 linear method is patched into vLLM's ModelOpt loader
+(``quant/vllm_integration/patch.py``).  The MXFP4 linear method and the attention backend class are not
+part of this library; when they are importable from the reference checkout
+(``quant.vllm_integration.*`` on sys.path) they are installed on top of these ops as the reference
+plugin does.
 """
 from __future__ import annotations
 
@@ -43,9 +45,9 @@ def initialize() -> None:
         if nvfp4:
             from resinfer_b200.quant.vllm_integration import env_contract, residue_linear_op  # noqa: F401
             env_contract.settings()
-            patch = _optional("quant.vllm_integration.patch")
-            if patch is not None and hasattr(patch, "patch_vllm_modelopt"):
-                patch.patch_vllm_modelopt(model_dir=os.environ.get("RESIDUE_VLLM_MODEL_DIR"))
+            # this library's own linear method (resinfer_b200/quant/vllm_integration/linear_method_v2.py)
+            from resinfer_b200.quant.vllm_integration import patch
+            patch.patch_vllm_modelopt(model_dir=os.environ.get("RESIDUE_VLLM_MODEL_DIR"))
         if resattn:
             from resinfer_b200.nvfp4.cute_attn import host  # noqa: F401
             register = _optional("quant.vllm_integration.attn.register")
