@@ -202,6 +202,32 @@ def validate_layer(spec: dict) -> None:
                          "per group of 8")
 
 
+def residue_spec(metadata: dict | None, input_size: int, output_size: int) -> dict:
+    """A sidecar layer record -> the MXFP4 execution contract of ``validate_layer`` (reference:
+    quant/kernel_metadata.py:79-100).  ``mext_r1`` records must list every input channel in order and carry
+    no indices in the spec; ``extended_k`` records become ``selective``; records without indices are ``standard``."""
+    metadata = metadata or {}
+    indices = list(metadata.get("salient_indices", []))
+    if metadata.get("num_salient", len(indices)) != len(indices):
+        raise ValueError("num_salient disagrees with salient_indices")
+    runtime_mode = metadata.get("runtime_mode", "extended_k" if indices else "standard")
+    if runtime_mode == "mext_r1":
+        if indices != list(range(input_size)):
+            raise ValueError("mext_r1 requires every input channel in order")
+        mode, indices = "mext_r1", []
+    elif runtime_mode == "extended_k" and indices:
+        mode = "selective"
+    elif runtime_mode == "standard" and not indices:
+        mode = "standard"
+    else:
+        raise ValueError(f"invalid residue runtime mode: {runtime_mode}")
+    spec = {"mode": mode, "input_size": input_size, "output_size": output_size}
+    if indices:
+        spec["indices"] = indices
+    validate_layer(spec)
+    return spec
+
+
 def fuse_projection_specs(layers: dict) -> dict:
     """Merge the checkpoint constituents of fused projections; they must agree on everything but N."""
     out = dict(layers)

@@ -69,6 +69,7 @@ def quantize_weight_nvfp4(w: torch.Tensor, salient_indices: torch.Tensor | None 
     base_sf = sf[:, :k // 16].contiguous()
     return dict(weight=pack_codes(codes), weight_scale=swizzle_scales_any(sf),
                 weight_scale_base=swizzle_scales_any(base_sf), weight_global_scale=gs.reshape(1).float(),
+                weight_scale_raw=sf,                       # E4M3 bytes [N, (K+S)/16] as a checkpoint stores them
                 k_base=k, num_salient=0 if salient_indices is None else int(salient_indices.numel()))
 
 
@@ -90,6 +91,7 @@ def quantize_weight_mxfp4(w: torch.Tensor, salient_indices: torch.Tensor | None 
     q = torch.where(amax[..., None] > 0, wb / scale[..., None], torch.zeros_like(wb))
     codes = e2m1_codes(q).reshape(n, kp)
     return dict(weight=pack_codes(codes), weight_scale=swizzle_scales_any(e.to(torch.uint8)), k_base=k,
+                weight_scale_raw=e.to(torch.uint8),        # E8M0 bytes [N, Kp/32] as a checkpoint stores them
                 k_padded=kp, num_salient=0 if salient_indices is None else int(salient_indices.numel()))
 
 

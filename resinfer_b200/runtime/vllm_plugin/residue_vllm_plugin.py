@@ -8,10 +8,11 @@ worker refuses to serve without the residue kernels.
 What is installed: the native library is loaded and the ``nvfp4::*`` / ``residue::*`` ops are
 registered, this package is aliased under the reference's module names, and -- for RESIDUE_NVFP4 --
 this library's NVFP4 linear method is patched into vLLM's ModelOpt loader
-(``quant/vllm_integration/patch.py``).  The MXFP4 linear method and the attention backend class are not
-part of this library; when they are importable from the reference checkout
-(``quant.vllm_integration.*`` on sys.path) they are installed on top of these ops as the reference
-plugin does.
+(``quant/vllm_integration/patch.py``); for RESIDUE_MXFP4 the ``modelopt_mxfp4`` quantisation config and
+its linear method are registered (``quant/vllm_integration/linear_method_mxfp4.py``).  The attention
+backend class is not part of this library; when it is importable from the reference checkout
+(``quant.vllm_integration.attn.register`` on sys.path) it is installed on top of these ops as the
+reference plugin does.
 """
 from __future__ import annotations
 
@@ -41,7 +42,8 @@ def initialize() -> None:
         resinfer_b200.install_aliases()
         if mxfp4:
             from resinfer_b200.quant import mxfp4_linear  # noqa: F401
-            _optional("quant.vllm_integration.linear_method_mxfp4")
+            # registers the "modelopt_mxfp4" quantisation config with vLLM
+            from resinfer_b200.quant.vllm_integration import linear_method_mxfp4  # noqa: F401
         if nvfp4:
             from resinfer_b200.quant.vllm_integration import env_contract, residue_linear_op  # noqa: F401
             env_contract.settings()

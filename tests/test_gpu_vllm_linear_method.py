@@ -40,10 +40,8 @@ def _build(name, mode, k, n, dev, monkeypatch):
     w = torch.from_numpy(w_np)
     ext = sel if mode == "extended_k" else None
     packed = weight_prep.quantize_weight_nvfp4(w, ext)
-    wx = weight_prep.extend_weight(w, ext)
-    _, sf_raw = weight_prep._nvfp4_blocks(wx, packed["weight_global_scale"].float())
     layer.weight.weight_loader(layer.weight, packed["weight"].to(dev))
-    layer.weight_scale.weight_loader(layer.weight_scale, sf_raw.view(torch.float8_e4m3fn).reshape(n, -1).to(dev))
+    layer.weight_scale.weight_loader(layer.weight_scale, packed["weight_scale_raw"].view(torch.float8_e4m3fn).to(dev))
     layer.weight_scale_2.weight_loader(layer.weight_scale_2, packed["weight_global_scale"].reshape(1).to(dev))
     return method, layer, w_np, ext
 
@@ -84,3 +82,58 @@ def test_linear_method_against_the_oracle(cuda_device, monkeypatch, mode, m):
     assert rel_fro(got, ref) < 6e-3                               # BF16 output (+ BF16 bias add), approximate reciprocals
     assert rel_fro(got, x_np.astype(np.float64) @ w_np.astype(np.float64).T) < 0.15
     env_contract.settings.cache_clear()
+
+
+@pytest.mark.parametrize("mode,m", [("selective", 40), ("mext_r1", 8), ("standard", 130)])
+def test_mxfp4_linear_method_against_the_oracle(cuda_device, mode, m):
+    from resinfer_b200.quant.vllm_integration.linear_method_mxfp4 import ResidueMxfp4LinearMethod
+    dev = cuda_device
+    k, n = 1024, 384
+    sel = {"selective": weight_prep.salient_indices_per8(k, 2), "mext_r1": torch.arange(k), "standard": None}[mode]
+    rec = {} if sel is None else {"runtime_mode": "mext_r1" if mode == "mext_r1" else "extended_k",
+                                  "num_salient": sel.numel(), "salient_indices": sel.tolist()}
+    method = ResidueMxfp4LinearMethod(rec)
+    layer = torch.nn.Module()
+    method.create_weights(layer, k, [n], k, n, torch.bfloat16)
+    layer.to(dev)
+    w_np = O.make_weight(n, k, seed=41)
+    packed = weight_prep.quantize_weight_mxfp4(torch.from_numpy(w_np), sel if mode == "selective" else None)
+    assert layer.weight.shape == packed["weight"].shape
+    layer.weight.weight_loader(layer.weight, packed["weight"].to(dev))
+    layer.weight_scale.weight_loader(layer.weight_scale, packed["weight_scale_raw"].to(dev))
+    method.process_weights_after_loading(layer)
+    assert layer._mxfp4_prepared and not isinstance(layer.weight_scale, torch.nn.Parameter)
+    assert torch.equal(layer.weight_scale.cpu(), packed["weight_scale"])                    # swizzled after loading
+    x_np = O.make_activation(m, k, seed=8)
+    x = torch.from_numpy(x_np).to(torch.bfloat16).to(dev)
+    y = method.apply(layer, x.view(1, m, k), None)
+    torch.cuda.synchronize()
+    from resinfer_b200 import ops
+    ops.check_status(dev)
+    assert y.shape == (1, m, n) and y.dtype == torch.bfloat16
+    got = y.float().view(m, n).cpu().numpy()
+    wd = O.dequant_operand(packed["weight"].numpy(), packed["weight_scale"].numpy(), "mxfp4")
+    if mode == "mext_r1":
+        codes, sf = O.mxfp4_quant_mext(x_np)[:2]
+        a = O.dequant_operand(codes, sf, "mxfp4")
+        ref = O.fp4_linear_reference(a[0::2] + a[1::2], wd, 1.0, False)
+    elif mode == "selective":
+        codes, sf = O.mxfp4_quant_selective(x_np, layer.salient_masks.cpu().numpy(), 2, kp=wd.shape[1])[:2]
+        ref = O.fp4_linear_reference(O.dequant_operand(codes, sf, "mxfp4"), wd, 1.0, False)
+    else:
+        codes, sf = O.mxfp4_quant_plain(x_np)[:2]
+        ref = O.fp4_linear_reference(O.dequant_operand(codes, sf, "mxfp4"), wd, 1.0, False)
+    assert rel_fro(got, ref) < 5e-3
+    # quantisation error against the dense product: plain W4A4 MXFP4 (no residue) is the coarsest of the three
+    assert rel_fro(got, x_np.astype(np.float64) @ w_np.astype(np.float64).T) < (0.25 if mode == "standard" else 0.2)
+    # NaN scale codes are refused
+    bad = torch.nn.Module()
+    m2 = ResidueMxfp4LinearMethod(rec)
+    m2.create_weights(bad, k, [n], k, n, torch.bfloat16)
+    bad.to(dev)
+    with pytest.raises(ValueError, match="incomplete packed MXFP4"):                        # nothing loaded yet
+        m2.process_weights_after_loading(bad)
+    bad.weight.weight_loader(bad.weight, packed["weight"].to(dev))
+    bad.weight_scale.weight_loader(bad.weight_scale, torch.full_like(packed["weight_scale_raw"], 255).to(dev))
+    with pytest.raises(ValueError, match="NaN E8M0"):
+        m2.process_weights_after_loading(bad)

@@ -47,11 +47,7 @@ def _pack(n, k, sel):
     g = torch.Generator().manual_seed(n + k)
     w = (torch.randn(n, k, generator=g) * 0.02).to(torch.bfloat16)
     p = weight_prep.quantize_weight_nvfp4(w, sel)
-    kx = k + (0 if sel is None else sel.numel())
-    # the raw (unswizzled) E4M3 scales as a checkpoint stores them
-    wx = weight_prep.extend_weight(w, sel)
-    _, sf = weight_prep._nvfp4_blocks(wx, p["weight_global_scale"].float())
-    p["weight_scale_raw"] = sf.view(torch.float8_e4m3fn).reshape(n, kx // 16)
+    p["weight_scale_raw"] = p["weight_scale_raw"].view(torch.float8_e4m3fn)     # as a checkpoint stores them
     return p
 
 
