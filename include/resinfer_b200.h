@@ -259,6 +259,26 @@ int ri_resattn_decode(const void* q_bf16, const uint8_t* k_data, const uint8_t* 
                       const float* out_global_scale, uint8_t* out_block_scale, int64_t out_block_scale_bytes,
                       int splits, void* workspace, int64_t workspace_bytes, int q_residue, int32_t* status,
                       void* stream);
+/* ri_resattn_decode over a pool whose pages are not packed back to back: `code_page_stride` / `sf_page_stride` are
+ * the bytes from one page's [Hkv, page_size] rows of codes / block scales to the next page's (multiples of 16;
+ * 0 = dense), the same for K and V.  This is the form vLLM's NVFP4 cache has -- every page keeps K codes | K scales
+ * | V codes | V scales together, and the reference hands its kernel strided views of it
+ * (quant/vllm_integration/attn/backend.py:125-144) -- so the cache is read in place, no repacking. */
+int ri_resattn_decode_strided(const void* q_bf16, const uint8_t* k_data, const uint8_t* k_sf,
+                              const uint8_t* v_data, const uint8_t* v_sf, int64_t num_pages,
+                              int64_t code_page_stride, int64_t sf_page_stride,
+                              const int32_t* block_tables, int64_t bt_stride, const int32_t* seq_lens,
+                              int batch, int num_q_heads, int num_kv_heads, int head_dim, int page_size,
+                              int max_kv_len, float score_scale, float out_scale, void* out, int out_dtype, uint8_t* q_pack,
+                              int64_t q_pack_bytes, uint8_t* q_sf, int64_t q_sf_bytes,
+                              const float* out_global_scale, uint8_t* out_block_scale, int64_t out_block_scale_bytes,
+                              int splits, void* workspace, int64_t workspace_bytes, int q_residue, int32_t* status,
+                              void* stream);
+/* Sets the launch attributes of the decode kernel's instantiations for `head_dim` on the current device, which the
+ * first ri_resattn_decode would otherwise do.  The reference compiles its kernel variants at run time and lists the
+ * compilations for vLLM's warm-up (quant/vllm_integration/attn/warmup.py:21-44); this is what is left of that step
+ * when the kernels are built ahead of time. */
+int ri_resattn_prepare(int head_dim);
 /* Number format of V and P in the second product of ri_resattn_decode, process-wide: 0 (default) = FP16 -- code x
  * block scale is exact in FP16 and P keeps 11 bits, 3e-3 from exact attention; 1 = E4M3 for both, the reference's
  * choice (csrc/resattn/kernel_paged_decode.py:1958-1963, csrc/resattn/qmul4.py:45): tcgen05.mma kind::f8f6f4,

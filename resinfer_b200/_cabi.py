@@ -45,6 +45,9 @@ SIGNATURES = {
                                    _vp, _i64, _vp, _i, _vp, _vp, _i64, _vp, _vp, _i64, _i, _i, _vp, _i64]),
     "ri_resattn_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _vp, _i, _i, _i, _i, _i, _i, _f, _f,
                                _vp, _i, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i, _vp, _i64, _i, _vp, _vp]),
+    "ri_resattn_decode_strided": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp, _i, _i, _i, _i, _i, _i,
+                                       _f, _f, _vp, _i, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i, _vp, _i64, _i, _vp, _vp]),
+    "ri_resattn_prepare": (_i, [_i]),
     "ri_resattn_workspace_bytes": (_i64, [_i, _i, _i, _i]),
     "ri_resattn_counter_bytes": (_i64, [_i, _i]),
     "ri_resattn_set_pv_format": (None, [_i]),

@@ -28,6 +28,7 @@ struct AttnParams {
   const int32_t* block_tables; int64_t bt_stride;
   const int32_t* seq_lens;
   int64_t num_pages;
+  int64_t code_page_stride, sf_page_stride; // bytes from one page's [Hkv, page_size] rows of codes (scales) to the next page's
   int batch, hq, hkv, group, page_size;
   int page_shift;                          // log2(page_size) when it is a power of two, else -1
   int tma_pages;                           // pages hold whole 128-token tiles: codes and V scales come by TMA
@@ -127,8 +128,9 @@ extern "C" int64_t ri_resattn_workspace_bytes(int batch, int num_q_heads, int he
   return ri_resattn_counter_bytes(batch, num_q_heads) + rows * head_dim * 4 + 2 * rows * 4;
 }
 
-extern "C" int ri_resattn_decode(const void* q_bf16, const uint8_t* k_data, const uint8_t* k_sf,
+extern "C" int ri_resattn_decode_strided(const void* q_bf16, const uint8_t* k_data, const uint8_t* k_sf,
                                  const uint8_t* v_data, const uint8_t* v_sf, int64_t num_pages,
+                                 int64_t code_page_stride, int64_t sf_page_stride,
                                  const int32_t* block_tables, int64_t bt_stride, const int32_t* seq_lens,
                                  int batch, int num_q_heads, int num_kv_heads, int head_dim, int page_size,
                                  int max_kv_len, float score_scale, float out_scale, void* out, int out_dtype, uint8_t* q_pack,
@@ -155,6 +157,15 @@ extern "C" int ri_resattn_decode(const void* q_bf16, const uint8_t* k_data, cons
                "decode residue Q8/Q16 supports logical GQA ratios (4, 6, 8), got %d", group);
   RI_CHECK_ARG(page_size >= 16 && page_size % 16 == 0, "page size must be a multiple of 16, got %d", page_size);
   RI_CHECK_ARG(batch >= 0 && num_pages > 0 && bt_stride >= 1, "bad batch / page pool / block table");
+  {
+    const int64_t page_rows = int64_t(num_kv_heads) * page_size;
+    if (code_page_stride == 0) code_page_stride = page_rows * (head_dim / 2);
+    if (sf_page_stride == 0) sf_page_stride = page_rows * (head_dim / 16);
+    RI_CHECK_ARG(code_page_stride >= page_rows * (head_dim / 2) && sf_page_stride >= page_rows * (head_dim / 16) &&
+                     code_page_stride % 16 == 0 && sf_page_stride % 16 == 0,
+                 "page strides (%lld, %lld bytes) must be multiples of 16 and hold a page's %lld rows",
+                 (long long)code_page_stride, (long long)sf_page_stride, (long long)page_rows);
+  }
   RI_CHECK_ARG(splits >= 1 && splits <= 256, "splits must be in [1, 256]");
   RI_CHECK_ARG(max_kv_len >= 0, "max_kv_len must be non-negative");
   RI_CHECK_ARG((reinterpret_cast<uintptr_t>(k_data) & 15) == 0 && (reinterpret_cast<uintptr_t>(v_data) & 15) == 0 &&
@@ -175,12 +186,13 @@ extern "C" int ri_resattn_decode(const void* q_bf16, const uint8_t* k_data, cons
   p.q = static_cast<const __nv_bfloat16*>(q_bf16);
   p.k_data = k_data; p.k_sf = k_sf; p.v_data = v_data; p.v_sf = v_sf;
   p.block_tables = block_tables; p.bt_stride = bt_stride; p.seq_lens = seq_lens; p.num_pages = num_pages;
+  p.code_page_stride = code_page_stride; p.sf_page_stride = sf_page_stride;
   p.batch = batch; p.hq = num_q_heads; p.hkv = num_kv_heads; p.group = group; p.page_size = page_size;
   p.page_shift = -1;
   for (int sft = 4; sft < 31; ++sft)
     if ((1 << sft) == page_size) p.page_shift = sft;
-  // tiled TMA coordinates are 32-bit: pools of 2^31 rows or more stay on the cp.async path
-  p.tma_pages = (page_size % 128 == 0 && num_pages * num_kv_heads * page_size < (int64_t(1) << 31)) ? 1 : 0;
+  // tiled TMA coordinates are 32-bit (row within the page, page): always in range for a page pool
+  p.tma_pages = (page_size % 128 == 0 && num_pages < (int64_t(1) << 31)) ? 1 : 0;
   p.score_scale_log2 = score_scale * kLog2e;
   p.out_scale = out_scale;
   p.out = out;
@@ -214,4 +226,28 @@ extern "C" int ri_resattn_decode(const void* q_bf16, const uint8_t* k_data, cons
   else
     s = head_dim == 128 ? tcattn::launch_decode_pv<128, false>(p, st) : tcattn::launch_decode_pv<256, false>(p, st);
   return s;
+}
+
+extern "C" int ri_resattn_prepare(int head_dim) {
+  RI_CHECK_ARG(head_dim == 128 || head_dim == 256, "ResAttn supports head_dim=128 or 256");
+  int s = head_dim == 128 ? tcattn::prepare_decode_pv<128, false>() : tcattn::prepare_decode_pv<256, false>();
+  if (s) return s;
+  return head_dim == 128 ? tcattn::prepare_decode_pv<128, true>() : tcattn::prepare_decode_pv<256, true>();
+}
+
+extern "C" int ri_resattn_decode(const void* q_bf16, const uint8_t* k_data, const uint8_t* k_sf,
+                                 const uint8_t* v_data, const uint8_t* v_sf, int64_t num_pages,
+                                 const int32_t* block_tables, int64_t bt_stride, const int32_t* seq_lens,
+                                 int batch, int num_q_heads, int num_kv_heads, int head_dim, int page_size,
+                                 int max_kv_len, float score_scale, float out_scale, void* out, int out_dtype, uint8_t* q_pack,
+                                 int64_t q_pack_bytes, uint8_t* q_sf, int64_t q_sf_bytes,
+                                 const float* out_global_scale, uint8_t* out_block_scale,
+                                 int64_t out_block_scale_bytes, int splits,
+                                 void* workspace, int64_t workspace_bytes, int q_residue, int32_t* status,
+                                 void* stream) {
+  return ri_resattn_decode_strided(q_bf16, k_data, k_sf, v_data, v_sf, num_pages, 0, 0, block_tables, bt_stride, seq_lens,
+                                   batch, num_q_heads, num_kv_heads, head_dim, page_size, max_kv_len, score_scale,
+                                   out_scale, out, out_dtype, q_pack, q_pack_bytes, q_sf, q_sf_bytes, out_global_scale,
+                                   out_block_scale, out_block_scale_bytes, splits, workspace, workspace_bytes, q_residue,
+                                   status, stream);
 }

@@ -547,8 +547,16 @@ resattn_pv_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
       page = page < 0 ? 0 : (page >= p.num_pages ? p.num_pages - 1 : page);
       const int t0 = tok0 + lane * 16;
       const int in_page = p.page_shift >= 0 ? (t0 & (p.page_size - 1)) : t0 % p.page_size;
-      const int64_t base_row = (page * p.hkv + hkv) * p.page_size + in_page;
-      const int64_t base0 = __shfl_sync(0xffffffffu, base_row, 0), base1 = __shfl_sync(0xffffffffu, base_row, 1);
+      // a page holds [Hkv, page_size] rows of codes (and of scales); pages lie code_page_stride (sf_page_stride)
+      // bytes apart, which is the dense distance for a pool of its own and the whole interleaved page for a
+      // cache that keeps K codes | K scales | V codes | V scales together
+      const int in_row = hkv * p.page_size + in_page;
+      const int pg0 = __shfl_sync(0xffffffffu, int(page), 0), pg1 = __shfl_sync(0xffffffffu, int(page), 1);
+      const int in0 = __shfl_sync(0xffffffffu, in_row, 0), in1 = __shfl_sync(0xffffffffu, in_row, 1);
+      const int64_t code0 = pg0 * p.code_page_stride + int64_t(in0) * C::kRowBytes;
+      const int64_t code1 = pg1 * p.code_page_stride + int64_t(in1) * C::kRowBytes;
+      const int64_t sf0 = pg0 * p.sf_page_stride + int64_t(in0) * C::kSfPerRow;
+      const int64_t sf1 = pg1 * p.sf_page_stride + int64_t(in1) * C::kSfPerRow;
       if (i >= S) {                                            // one lane polls, the four warps meet on a named barrier
         if (pw == 0 && lane == 0) prod_go[i & 1] = mbar_wait(smem_u32(&bar_empty[stg]), ph ^ 1, &abort_flag, 4) ? 1 : 0;
         asm volatile("bar.sync 4, %0;" ::"n"(kPvProd * 32) : "memory");
@@ -561,16 +569,15 @@ resattn_pv_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
         // as tiled loads that write the operand swizzle, the scales as one bulk copy.  The tile's rows
         // past the end of the sequence belong to the same page, so whole blocks are always fetched.
         if (pw == 0 && lane == 0) {
-          const int64_t row0 = base0;                          // first pool row of the tile
           const uint32_t full = smem_u32(&bar_full[stg]);
           mbar_expect_tx(full, 2 * C::kKBytes + C::kSfBytes);
-          tma_load_2d(st, &k_map, 0, int(row0), full);
-          tma_load_2d(st + C::kOffV, &v_map, 0, int(row0), full);
-          bulk_load_1d(st + C::kOffVsf, p.v_sf + row0 * C::kSfPerRow, C::kSfBytes, full);
+          tma_load_3d(st, &k_map, 0, in0, pg0, full);
+          tma_load_3d(st + C::kOffV, &v_map, 0, in0, pg0, full);
+          bulk_load_1d(st + C::kOffVsf, p.v_sf + sf0, C::kSfBytes, full);
         }
       } else {
-        const uint8_t* kg[2] = {p.k_data + base0 * C::kRowBytes + chn * 16, p.k_data + base1 * C::kRowBytes + chn * 16};
-        const uint8_t* vg[2] = {p.v_data + base0 * C::kRowBytes + chn * 16, p.v_data + base1 * C::kRowBytes + chn * 16};
+        const uint8_t* kg[2] = {p.k_data + code0 + chn * 16, p.k_data + code1 + chn * 16};
+        const uint8_t* vg[2] = {p.v_data + code0 + chn * 16, p.v_data + code1 + chn * 16};
 #pragma unroll
         for (int it = 0; it < kIters; ++it) {
           const int r = it * kRowsPerIt + r_lane;
@@ -582,12 +589,11 @@ resattn_pv_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
           }
         }
         if (sf_lane && sf_row < rows) {
-          const int64_t br = (sf_row < 16 ? base0 : base1) + (sf_row & 15);
-          cp_async16(st + C::kOffVsf + sf_dst, p.v_sf + br * C::kSfPerRow);
+          cp_async16(st + C::kOffVsf + sf_dst, p.v_sf + (sf_row < 16 ? sf0 : sf1) + (sf_row & 15) * C::kSfPerRow);
         }
       }
       if (lane < rows) {                                       // K scales of token kRowsW pw + lane, 4 bytes per MMA
-        const uint8_t* src = p.k_sf + ((lane < 16 ? base0 : base1) + (lane & 15)) * C::kSfPerRow;
+        const uint8_t* src = p.k_sf + (lane < 16 ? sf0 : sf1) + (lane & 15) * C::kSfPerRow;
         const int tk = kRowsW * pw + lane;
         const uint32_t dst = st + C::kOffKsf + (tk & 31) * 16 + (tk >> 5) * 4;
 #pragma unroll
@@ -781,29 +787,33 @@ resattn_pv_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
   }
 }
 
-// 2-D byte tensor over a code pool: [rows = pages * heads * page_size, D/2 bytes], box = one 128-token tile,
-// swizzle = the operand swizzle of the scores' MMA (64 bytes for head_dim 128, 128 bytes for 256)
+// 3-D byte tensor over a code pool: [pages, rows of a page = heads * page_size, D/2 bytes], pages `page_stride`
+// bytes apart; box = one 128-token tile; swizzle = the operand swizzle of the scores' MMA (64 bytes for head_dim
+// 128, 128 bytes for 256)
 template <int D>
-int make_pool_map(CUtensorMap* map, const uint8_t* base, int64_t rows) {
+int make_pool_map(CUtensorMap* map, const uint8_t* base, int64_t pages, int64_t page_rows, int64_t page_stride) {
   EncodeTiledFn fn;
   int s = get_encode_fn(&fn);
   if (s) return s;
-  cuuint64_t dims[2] = {cuuint64_t(D / 2), cuuint64_t(rows)};
-  cuuint64_t strides[1] = {cuuint64_t(D / 2)};
-  cuuint32_t box[2] = {cuuint32_t(D / 2), cuuint32_t(kTile)};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(base), dims, strides, box, estr,
+  cuuint64_t dims[3] = {cuuint64_t(D / 2), cuuint64_t(page_rows), cuuint64_t(pages)};
+  cuuint64_t strides[2] = {cuuint64_t(D / 2), cuuint64_t(page_stride)};
+  cuuint32_t box[3] = {cuuint32_t(D / 2), cuuint32_t(kTile), 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<uint8_t*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, D == 128 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
-    set_error("cuTensorMapEncodeTiled failed for the KV pool with CUresult %d (base %p, rows %lld)", (int)r, base, (long long)rows);
+    set_error("cuTensorMapEncodeTiled failed for the KV pool with CUresult %d (base %p, %lld pages of %lld rows, "
+              "%lld bytes apart)", (int)r, base, (long long)pages, (long long)page_rows, (long long)page_stride);
     return RI_ERR_ARG;
   }
   return RI_OK;
 }
 
+// Launch attributes of one instantiation on the current device, set once per device (also callable ahead of the
+// first launch: ri_resattn_prepare).
 template <int D, bool F8>
-int launch_decode_pv(const AttnParams& p, cudaStream_t st) {
+int prepare_decode_pv() {
   using PC = PvCfg<D, F8>;
   static bool attr_done[64] = {};
   int dev = 0;
@@ -814,12 +824,22 @@ int launch_decode_pv(const AttnParams& p, cudaStream_t st) {
     RI_CUDA(cudaFuncSetAttribute(resattn_pv_kernel<D, F8>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
     attr_done[dev] = true;
   }
+  return RI_OK;
+}
+
+template <int D, bool F8>
+int launch_decode_pv(const AttnParams& p, cudaStream_t st) {
+  using PC = PvCfg<D, F8>;
+  {
+    int s = prepare_decode_pv<D, F8>();
+    if (s) return s;
+  }
   CUtensorMap k_map{}, v_map{};
   if (p.tma_pages) {
-    const int64_t rows = p.num_pages * p.hkv * p.page_size;
-    int s = make_pool_map<D>(&k_map, p.k_data, rows);
+    const int64_t page_rows = int64_t(p.hkv) * p.page_size;
+    int s = make_pool_map<D>(&k_map, p.k_data, p.num_pages, page_rows, p.code_page_stride);
     if (s) return s;
-    s = make_pool_map<D>(&v_map, p.v_data, rows);
+    s = make_pool_map<D>(&v_map, p.v_data, p.num_pages, page_rows, p.code_page_stride);
     if (s) return s;
   }
   cudaLaunchConfig_t cfg{};

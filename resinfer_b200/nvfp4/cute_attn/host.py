@@ -144,16 +144,38 @@ def run_paged_fp4_decode_qmul4_tmem(q: torch.Tensor, pool: NvFp4PagedKVPool, v_d
                                      f"device={t.device}")
         ws = ops._workspace(q.device, need, "attn", zero_prefix=lib.ri_resattn_counter_bytes(b, hq))
         ws_ptr, ws_bytes = ws.data_ptr(), need
+    code_stride, sf_stride = ops.kv_page_strides(pool.k_data, pool.k_sf, v_data_hnd, v_sf_bthd)
     with torch.cuda.device(q.device):
-        st = lib.ri_resattn_decode(
+        st = lib.ri_resattn_decode_strided(
             q.data_ptr(), pool.k_data.data_ptr(), pool.k_sf.data_ptr(), v_data_hnd.data_ptr(),
-            v_sf_bthd.data_ptr(), pool.k_data.shape[0], block_tables.data_ptr(), block_tables.stride(0),
+            v_sf_bthd.data_ptr(), pool.k_data.shape[0], code_stride, sf_stride, block_tables.data_ptr(), block_tables.stride(0),
             seq_lens.data_ptr(), b, hq, h, d, page, int(max_seq_len or 0), float(sm_scale), float(value_scale),
             out.data_ptr(),
             _cabi.DTYPE_BF16, None, 0, None, 0, None, None, 0, splits, ws_ptr, ws_bytes, 1,
             ops.status_word(q.device).data_ptr(), _cabi.current_stream(q.device))
     _cabi.check(st, "run_paged_fp4_decode_qmul4_tmem")
     return out
+
+
+def decode_compile_variants(num_qo_heads, num_kv_heads, head_dim, *, residue_fold, output_nvfp4):
+    """The kernel specialisations a (geometry, output format) can launch, as dicts with ``args``, ``kwargs`` and
+    ``label`` like the reference's list (csrc/resattn/host.py:635-652).  The reference has one per static plan;
+    here the split count, the reducer and the output format are launch arguments of one instantiation per
+    head_dim, so the list has one entry."""
+    if not residue_fold:
+        raise NotImplementedError("ordinary QK is not supported")
+    check_shape_supported(num_qo_heads, num_kv_heads, head_dim)
+    static_compile_plans(output_nvfp4=output_nvfp4, residue_fold=residue_fold, head_dim=head_dim,
+                         grouped_head_tile=_residue_padded_group_size(num_qo_heads, num_kv_heads))
+    return [dict(args=(int(head_dim),), kwargs={}, label=f"D{head_dim}")]
+
+
+def compile_decode_variant(plan: dict):
+    """Make one entry of ``decode_compile_variants`` ready to launch on the current device (nothing is compiled:
+    the shared library holds the kernel; its launch attributes are set)."""
+    lib = _cabi.load()
+    _cabi.check(lib.ri_resattn_prepare(*plan["args"]), "compile_decode_variant")
+    return plan["args"]
 
 
 def plan_qmul4_decode_nvfp4(batch, num_qo_heads, num_kv_heads, max_kv_len, device, *, residue_fold=True):

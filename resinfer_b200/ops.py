@@ -218,6 +218,26 @@ def resattn_pv_format(fmt: str):
         lib.ri_resattn_set_pv_format(prev)
 
 
+def kv_page_strides(k_data: torch.Tensor, k_sf: torch.Tensor, v_data: torch.Tensor, v_sf: torch.Tensor):
+    """(code bytes, scale bytes) between consecutive pages of a paged NVFP4 KV pool.
+
+    Each of the four tensors is [pages, Hkv, page, D/2 or D/16] with the three inner dimensions dense; the page
+    stride is free, so the views vLLM cuts out of its interleaved cache (every page = K codes | K scales |
+    V codes | V scales) are taken as they are.  K and V must share their strides."""
+    def one(t, name):
+        _, h, page, w = t.shape
+        want = (page * w, w, 1)
+        if t.element_size() != 1 or tuple(t.stride()[1:]) != want or (t.shape[0] > 1 and t.stride(0) < h * page * w):
+            raise ValueError(f"{name} must be a byte tensor [pages, Hkv, page, {w}] with dense inner dimensions, got "
+                             f"shape {tuple(t.shape)} strides {tuple(t.stride())}")
+        return int(t.stride(0)) if t.shape[0] > 1 else h * page * w
+    kc, vc = one(k_data, "k_data"), one(v_data, "v_data")
+    ks, vs = one(k_sf, "k_sf"), one(v_sf, "v_sf")
+    if kc != vc or ks != vs:
+        raise ValueError(f"K and V must have the same page strides, got codes {kc} / {vc}, scales {ks} / {vs}")
+    return kc, ks
+
+
 def resattn_decode(q: torch.Tensor, k_data: torch.Tensor, k_sf: torch.Tensor, v_data: torch.Tensor,
                    v_sf: torch.Tensor, block_tables: torch.Tensor, seq_lens: torch.Tensor,
                    score_scale: float, out_scale: float, out: torch.Tensor, *, splits: int = 1,
@@ -226,22 +246,23 @@ def resattn_decode(q: torch.Tensor, k_data: torch.Tensor, k_sf: torch.Tensor, v_
                    out_global_scale: torch.Tensor | None = None,
                    out_block_scale: torch.Tensor | None = None) -> torch.Tensor:
     """Paged NVFP4-KV decode attention.  q bf16 [B,Hq,D]; k_data/v_data uint8 [pages,Hkv,page,D/2];
-    k_sf/v_sf uint8 (or float8_e4m3fn) [pages,Hkv,page,D/16]; out bf16 [B,Hq,D] (written) -- or, with
+    k_sf/v_sf uint8 (or float8_e4m3fn) [pages,Hkv,page,D/16] (any page stride: ``kv_page_strides``); out bf16 [B,Hq,D] (written) -- or, with
     ``out_global_scale`` (float32[1]) and ``out_block_scale`` (128x4-swizzled E4M3 bytes), packed NVFP4:
     out uint8 [B, Hq*D/2]."""
     lib = _cabi.load()
     b, hq, d = q.shape
     pages, hkv, page, _ = k_data.shape
     dev = q.device
+    code_stride, sf_stride = kv_page_strides(k_data, k_sf, v_data, v_sf)
     with torch.cuda.device(dev):
         ws = None
         ws_bytes = 0
         if splits > 1:
             ws_bytes = lib.ri_resattn_workspace_bytes(b, hq, d, splits)
             ws = _workspace(dev, ws_bytes, "attn", zero_prefix=lib.ri_resattn_counter_bytes(b, hq))
-        st = lib.ri_resattn_decode(
+        st = lib.ri_resattn_decode_strided(
             q.data_ptr(), k_data.data_ptr(), k_sf.data_ptr(), v_data.data_ptr(), v_sf.data_ptr(), pages,
-            block_tables.data_ptr(), block_tables.stride(0), seq_lens.data_ptr(), b, hq, hkv, d, page,
+            code_stride, sf_stride, block_tables.data_ptr(), block_tables.stride(0), seq_lens.data_ptr(), b, hq, hkv, d, page,
             int(max_kv_len), float(score_scale), float(out_scale), out.data_ptr(),
             _cabi.DTYPE_NVFP4 if out_block_scale is not None else _cabi.torch_dtype_code(out.dtype, allow_f32=True),
             _cabi.ptr(q_pack), 0 if q_pack is None else q_pack.numel(),

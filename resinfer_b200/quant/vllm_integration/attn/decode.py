@@ -8,9 +8,8 @@ workspaces (:23-53).  The host class supplies ``num_heads``, ``num_kv_heads``, `
 and a dict ``_decode_reduction_workspaces``; the metadata object supplies ``num_decode_tokens`` and
 ``decode.block_tables / seq_lens / max_seq_len``; ``pool`` is an ``NvFp4PagedKVPool``.
 
-Nothing here imports vLLM, so the mixin can be exercised with plain objects.  The vLLM-facing backend
-class (metadata builder, prefill through the stock implementation) is not part of this package: it
-subclasses vLLM 0.26 interfaces.
+Nothing here imports vLLM, so the mixin can be exercised with plain objects; the vLLM-facing classes
+(metadata builder, prefill through the stock implementation) are in ``backend.py``.
 """
 from __future__ import annotations
 

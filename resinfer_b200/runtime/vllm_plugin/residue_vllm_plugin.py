@@ -9,22 +9,13 @@ What is installed: the native library is loaded and the ``nvfp4::*`` / ``residue
 registered, this package is aliased under the reference's module names, and -- for RESIDUE_NVFP4 --
 this library's NVFP4 linear method is patched into vLLM's ModelOpt loader
 (``quant/vllm_integration/patch.py``); for RESIDUE_MXFP4 the ``modelopt_mxfp4`` quantisation config and
-its linear method are registered (``quant/vllm_integration/linear_method_mxfp4.py``).  The attention
-backend class is not part of this library; when it is importable from the reference checkout
-(``quant.vllm_integration.attn.register`` on sys.path) it is installed on top of these ops as the
-reference plugin does.
+its linear method are registered (``quant/vllm_integration/linear_method_mxfp4.py``); for RESIDUE_ATTN this
+library's attention backend is registered as vLLM's CUSTOM backend
+(``quant/vllm_integration/attn/register.py``).
 """
 from __future__ import annotations
 
-import importlib
 import os
-
-
-def _optional(module: str):
-    try:
-        return importlib.import_module(module)
-    except ImportError:
-        return None
 
 
 def initialize() -> None:
@@ -51,9 +42,8 @@ def initialize() -> None:
             from resinfer_b200.quant.vllm_integration import patch
             patch.patch_vllm_modelopt(model_dir=os.environ.get("RESIDUE_VLLM_MODEL_DIR"))
         if resattn:
-            from resinfer_b200.nvfp4.cute_attn import host  # noqa: F401
-            register = _optional("quant.vllm_integration.attn.register")
-            if register is not None and hasattr(register, "install") and not register.install():
+            from resinfer_b200.quant.vllm_integration.attn.register import install
+            if not install():
                 raise RuntimeError("ResAttn backend registration was refused")
         print(f"[residue:plugin] applied in pid={pid}", flush=True)
     except Exception as exc:
