@@ -1004,10 +1004,13 @@ def measure_resattn(torch, dev, ops, capture, timed, hbm_gbs, only=None, steps=1
         vs = torch.randint(0x28, 0x48, (pool, hkv, page, d // 16), generator=g, device=dev, dtype=torch.uint8)
         q = torch.randn(batch, hq, d, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
         out = torch.empty(batch, hq, d, dtype=torch.bfloat16, device=dev)
-        splits, _ = select_decode_plan(batch, hkv, int(lens.max()), sms, head_dim=d)
+        splits, reducer = select_decode_plan(batch, hkv, int(lens.max()), sms, head_dim=d)
+        reducer = "cluster" if reducer == "cga_sharded" else "ticket"
+        max_len = int(lens.max())
         def call():                                         # the format switch is a host-side setting: it is
             with ops.resattn_pv_format(ATTN_FORMAT):        # captured with the launch
-                ops.resattn_decode(q, kd, ks, vd, vs, bt, lens, d ** -0.5, 1.0, out, splits=splits)
+                ops.resattn_decode(q, kd, ks, vd, vs, bt, lens, d ** -0.5, 1.0, out, splits=splits, reducer=reducer,
+                                   max_kv_len=max_len)
         if capture is None:                                 # single-case mode: plain launches, CUDA events
             for _ in range(warmup):
                 call()
@@ -1023,7 +1026,7 @@ def measure_resattn(torch, dev, ops, capture, timed, hbm_gbs, only=None, steps=1
         tokens = int(lens.sum())
         nbytes = tokens * hkv * d * 2 * (0.5 + 1 / 16) + 4 * batch * hq * d + 4 * total
         res.append({"head_dim": d, "batch": batch, "page": page, "context": fixed_len or "U[1024,32768]", "tokens": tokens,
-                    "splits": splits, "pv_format": ATTN_FORMAT, "us": round(us, 1),
+                    "splits": splits, "reducer": reducer, "pv_format": ATTN_FORMAT, "us": round(us, 1),
                     "tbs": round(nbytes / us / 1e6, 3), "frac_hbm": round(nbytes / us / 1e3 / hbm_gbs, 3),
                     "kv_bytes_gt_l2": bool(nbytes > L2_BYTES)})
         del kd, vd, ks, vs, q, out, bt

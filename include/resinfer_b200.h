@@ -259,7 +259,19 @@ int ri_resattn_decode(const void* q_bf16, const uint8_t* k_data, const uint8_t* 
                       const float* out_global_scale, uint8_t* out_block_scale, int64_t out_block_scale_bytes,
                       int splits, void* workspace, int64_t workspace_bytes, int q_residue, int32_t* status,
                       void* stream);
-/* ri_resattn_decode over a pool whose pages are not packed back to back: `code_page_stride` / `sf_page_stride` are
+/* How the partial results of the KV splits of one (sequence, KV head) are combined -- in both cases inside the
+ * decode launch, in split order, with identical results (the reference's reducers: csrc/resattn/plan.py:36-92,
+ * kernel_paged_decode.py:80-104).
+ * TICKET:  partials go through the workspace; the CTA that draws the last ticket combines them ("kernel" /
+ *          "gmem_fused" of the reference).  Any split count, any output type.
+ * CLUSTER: the splits are one thread-block cluster and combine through distributed shared memory, each CTA a share
+ *          of the output ("cga_sharded" of the reference).  2 to 8 or 16 splits, BF16 / FP32 output, no workspace;
+ *          meant for grids of a few clusters (one sequence, or a tensor-parallel shard's few KV heads): measured on
+ *          B200 it is a fifth faster than TICKET there and slower from about sixteen clusters up. */
+#define RI_ATTN_REDUCER_TICKET 0
+#define RI_ATTN_REDUCER_CLUSTER 1
+
+/* ri_resattn_decode with the reducer as an argument, over a pool whose pages need not be packed back to back: `code_page_stride` / `sf_page_stride` are
  * the bytes from one page's [Hkv, page_size] rows of codes / block scales to the next page's (multiples of 16;
  * 0 = dense), the same for K and V.  This is the form vLLM's NVFP4 cache has -- every page keeps K codes | K scales
  * | V codes | V scales together, and the reference hands its kernel strided views of it
@@ -272,8 +284,8 @@ int ri_resattn_decode_strided(const void* q_bf16, const uint8_t* k_data, const u
                               int max_kv_len, float score_scale, float out_scale, void* out, int out_dtype, uint8_t* q_pack,
                               int64_t q_pack_bytes, uint8_t* q_sf, int64_t q_sf_bytes,
                               const float* out_global_scale, uint8_t* out_block_scale, int64_t out_block_scale_bytes,
-                              int splits, void* workspace, int64_t workspace_bytes, int q_residue, int32_t* status,
-                              void* stream);
+                              int splits, int reducer, void* workspace, int64_t workspace_bytes, int q_residue,
+                              int32_t* status, void* stream);
 /* Sets the launch attributes of the decode kernel's instantiations for `head_dim` on the current device, which the
  * first ri_resattn_decode would otherwise do.  The reference compiles its kernel variants at run time and lists the
  * compilations for vLLM's warm-up (quant/vllm_integration/attn/warmup.py:21-44); this is what is left of that step

@@ -16,6 +16,7 @@ LIB_PATH = _PKG / "_lib" / "libresinfer_b200.so"
 
 RI_ERR_ARG, RI_ERR_UNSUPPORTED, RI_ERR_DEVICE, RI_ERR_TIMEOUT = -1, -2, -3, -4
 DTYPE_BF16, DTYPE_FP16, DTYPE_F32, DTYPE_NVFP4 = 0, 1, 2, 3
+ATTN_REDUCER_TICKET, ATTN_REDUCER_CLUSTER = 0, 1
 FMT_NVFP4, FMT_MXFP4 = 0, 1
 GEMM_PLAIN, GEMM_ROW_PAIR, GEMM_CONCAT_K = 0, 1, 2
 
@@ -46,7 +47,7 @@ SIGNATURES = {
     "ri_resattn_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _vp, _i, _i, _i, _i, _i, _i, _f, _f,
                                _vp, _i, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i, _vp, _i64, _i, _vp, _vp]),
     "ri_resattn_decode_strided": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp, _i, _i, _i, _i, _i, _i,
-                                       _f, _f, _vp, _i, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i, _vp, _i64, _i, _vp, _vp]),
+                                       _f, _f, _vp, _i, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i, _i, _vp, _i64, _i, _vp, _vp]),
     "ri_resattn_prepare": (_i, [_i]),
     "ri_resattn_workspace_bytes": (_i64, [_i, _i, _i, _i]),
     "ri_resattn_counter_bytes": (_i64, [_i, _i]),

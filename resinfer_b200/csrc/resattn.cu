@@ -44,6 +44,8 @@ struct AttnParams {
   int* split_counter;                      // [B, Hkv] tickets of the fused split merge (zero between calls)
   uint8_t* q_pack; uint8_t* q_sf;          // optional copies of the quantised query
   int splits, q_residue;
+  int sm_count;                            // host side only: SMs of the device
+  int cluster_merge;                       // the splits of a (sequence, KV head) are one cluster and merge through its shared memory
   int32_t* status;
 };
 
@@ -136,10 +138,15 @@ extern "C" int ri_resattn_decode_strided(const void* q_bf16, const uint8_t* k_da
                                  int max_kv_len, float score_scale, float out_scale, void* out, int out_dtype, uint8_t* q_pack,
                                  int64_t q_pack_bytes, uint8_t* q_sf, int64_t q_sf_bytes,
                                  const float* out_global_scale, uint8_t* out_block_scale,
-                                 int64_t out_block_scale_bytes, int splits,
+                                 int64_t out_block_scale_bytes, int splits, int reducer,
                                  void* workspace, int64_t workspace_bytes, int q_residue, int32_t* status,
                                  void* stream) {
   RI_CHECK_ARG(head_dim == 128 || head_dim == 256, "ResAttn supports head_dim=128 or 256");
+  RI_CHECK_ARG(reducer == RI_ATTN_REDUCER_TICKET || reducer == RI_ATTN_REDUCER_CLUSTER, "unknown split reducer %d", reducer);
+  RI_CHECK_ARG(reducer != RI_ATTN_REDUCER_CLUSTER ||
+                   (((splits >= 2 && splits <= 8) || splits == 16) && out_dtype != RI_DTYPE_NVFP4),
+               "the cluster reducer takes 2 to 8 or 16 splits and BF16 / FP32 output, got %d splits, output type %d",
+               splits, out_dtype);
   RI_CHECK_ARG(out_dtype == RI_DTYPE_BF16 || out_dtype == RI_DTYPE_F32 || out_dtype == RI_DTYPE_NVFP4,
                "output must be bf16 (or packed NVFP4)");
   if (out_dtype == RI_DTYPE_NVFP4) {
@@ -209,7 +216,9 @@ extern "C" int ri_resattn_decode_strided(const void* q_bf16, const uint8_t* k_da
     p.tiles_per_split = int((tiles + splits - 1) / splits);
     if (p.tiles_per_split < 1) p.tiles_per_split = 1;
   }
-  if (splits > 1) {
+  p.cluster_merge = reducer == RI_ATTN_REDUCER_CLUSTER;
+  p.sm_count = di.sm_count;
+  if (splits > 1 && !p.cluster_merge) {
     const int64_t need = ri_resattn_workspace_bytes(batch, num_q_heads, head_dim, splits);
     RI_CHECK_ARG(workspace != nullptr && workspace_bytes >= need && (reinterpret_cast<uintptr_t>(workspace) & 15) == 0,
                  "split-KV with %d splits needs a 16-byte aligned workspace of %lld bytes, got %lld", splits,
@@ -248,6 +257,6 @@ extern "C" int ri_resattn_decode(const void* q_bf16, const uint8_t* k_data, cons
   return ri_resattn_decode_strided(q_bf16, k_data, k_sf, v_data, v_sf, num_pages, 0, 0, block_tables, bt_stride, seq_lens,
                                    batch, num_q_heads, num_kv_heads, head_dim, page_size, max_kv_len, score_scale,
                                    out_scale, out, out_dtype, q_pack, q_pack_bytes, q_sf, q_sf_bytes, out_global_scale,
-                                   out_block_scale, out_block_scale_bytes, splits, workspace, workspace_bytes, q_residue,
-                                   status, stream);
+                                   out_block_scale, out_block_scale_bytes, splits, RI_ATTN_REDUCER_TICKET, workspace,
+                                   workspace_bytes, q_residue, status, stream);
 }

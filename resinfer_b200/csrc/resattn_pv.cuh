@@ -94,12 +94,75 @@ __device__ __forceinline__ void tmem_st16f(uint32_t taddr, const float (&v)[16])
         "r"(__float_as_uint(v[15])) : "memory");
 }
 
-// Split-KV merge, fused into the decode kernel.  Every CTA of a (sequence, KV head) publishes its partial
-// (o, l, m) and takes a ticket; the CTA that draws the last ticket (nobody waits for anybody) combines the
-// partials of all splits in split order, so the result does not depend on which CTA arrives last:
+// Split-KV merge, fused into the decode kernel:
 //   out = sum_s 2^(m_s - m) o_s / sum_s 2^(m_s - m) l_s * out_scale
-// `scratch` is shared memory of this CTA: [0, 8 D) floats for the NVFP4 output staging, then the weights.
+// combined in split order, so the result does not depend on who merges or when.  Two carriers for the partials:
+// global memory with tickets (merge_splits_last_cta) and the shared memory of a thread-block cluster
+// (merge_splits_cluster).  Both do the same arithmetic in the same order, so they give the same bits; this is the
+// body of the cluster form, with the loads as parameters.
+// `scratch` is shared memory of this CTA: [0, 8 D) floats hold the output staging (or, in the cluster form, this
+// CTA's own partial o), then 16 floats (the cluster form's l and m), then the weights [splits][8] and [8] 1 / l.
+// The thread with index `first` (of `step` in all) handles the (head, column) pairs first, first + step, ...
+constexpr int kMergeWeightsOff = 16;                         // floats between the o staging and the weights
+template <int D, class LoadLM, class LoadO>
+__device__ __forceinline__ void merge_partials(const AttnParams& p, int b, int hkv, float* scratch, int first, int step,
+                                               LoadLM load_lm, LoadO load_o) {
+  const int G = p.group;
+  float* w_sh = scratch + 8 * D + kMergeWeightsOff;          // [splits][8] weights 2^(m_s - m), then [8] 1 / l
+  float* r_sh = w_sh + p.splits * 8;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (warp < G) {                                            // one warp per head: maximum, weights, row sum
+    // every lane takes the splits s = lane, lane + 32, ...: all loads of a pass are in flight together.  The
+    // row sum is a fixed tree over the lanes (it depends on the split count only, never on arrival order).
+    float mm = -INFINITY;
+    for (int s = lane; s < p.splits; s += 32) {
+      float ms, ls;
+      load_lm(s, warp, ms, ls);
+      mm = fmaxf(mm, ms);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
+    float l = 0.f;
+    for (int s = lane; s < p.splits; s += 32) {
+      float ms, ls;
+      load_lm(s, warp, ms, ls);
+      const float w = ms == -INFINITY ? 0.f : fast_exp2(ms - mm);
+      w_sh[s * 8 + warp] = w;
+      l += w * ls;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+    if (lane == 0) r_sh[warp] = l > 0.f ? p.out_scale / l : 0.f;
+  }
+  __syncthreads();
+  for (int idx = first; idx < G * D; idx += step) {
+    const int g = idx / D, c = idx - g * D;
+    const int head = hkv * G + g;
+    float o = 0.f;
+    for (int s0 = 0; s0 < p.splits; s0 += 8) {               // eight loads in flight, then added in split order
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int s = s0 + j;
+        v[j] = (s < p.splits && w_sh[s * 8 + g] != 0.f) ? load_o(s, g, c) : 0.f;   // empty partials hold no data
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (s0 + j < p.splits) o += w_sh[(s0 + j) * 8 + g] * v[j];
+    }
+    const float v = o * r_sh[g];
+    const int64_t oi = (int64_t(b) * p.hq + head) * D + c;
+    if (p.out_nvfp4) scratch[g * D + c] = v;
+    else if (p.out_f32) static_cast<float*>(p.out)[oi] = v;
+    else static_cast<__nv_bfloat16*>(p.out)[oi] = __float2bfloat16_rn(v);
+  }
+}
+
+// Global-memory carrier.  Every CTA of a (sequence, KV head) publishes its partial (o, l, m) and takes a ticket;
+// the CTA that draws the last ticket (nobody waits for anybody) combines the partials of all splits.
 // Returns true in the CTA that merged (the caller then packs the NVFP4 output if that is asked for).
+// The same arithmetic in the same order as merge_partials, written out: sharing that body cost this hot
+// instantiation register spills.
 template <int D>
 __device__ __forceinline__ bool merge_splits_last_cta(const AttnParams& p, int b, int hkv, float* scratch, int* flag_sh) {
   const int G = p.group;
@@ -168,6 +231,36 @@ __device__ __forceinline__ bool merge_splits_last_cta(const AttnParams& p, int b
   return true;
 }
 
+// Cluster carrier: the CTAs of a (sequence, KV head) form one thread-block cluster (cluster rank = split), every
+// CTA leaves its partial in its own shared memory -- o at scratch[0, 8 D), l at [8 D, 8 D + 8), m behind it -- and
+// after one cluster barrier each CTA combines a 1 / splits share of the (head, column) pairs, reading its peers'
+// partials through distributed shared memory; a second barrier keeps every CTA's memory alive until its peers
+// have read it.  No global round trip, no ticket, no workspace.  The barrier is the hardware's: every thread of
+// every CTA of the cluster must reach both calls, which the kernel's two exits do unconditionally (all other
+// waits of the kernel are bounded, so every CTA gets here).
+__device__ __forceinline__ void cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(const float* local, uint32_t rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+template <int D>
+__device__ __forceinline__ void merge_splits_cluster(const AttnParams& p, int b, int hkv, float* scratch, int split) {
+  cluster_barrier();                                         // everybody's partial is in place
+  const float* l_loc = scratch + 8 * D;
+  merge_partials<D>(p, b, hkv, scratch, split * int(blockDim.x) + int(threadIdx.x), p.splits * int(blockDim.x),
+      [=](int s, int g, float& ms, float& ls) {
+        ls = ld_cluster_f32(l_loc + g, uint32_t(s));
+        ms = ld_cluster_f32(l_loc + 8 + g, uint32_t(s));
+      },
+      [=](int s, int g, int c) { return ld_cluster_f32(scratch + g * D + c, uint32_t(s)); });
+  cluster_barrier();                                         // nobody reads this CTA's partial any more
+}
+
 // 16-value blocks of the [heads][D] staging tile -> packed NVFP4 codes + block scales of sequence b
 template <int D>
 __device__ __forceinline__ void pack_nvfp4_output(const AttnParams& p, int b, int hkv, const float* stage_out) {
@@ -183,9 +276,11 @@ __device__ __forceinline__ void pack_nvfp4_output(const AttnParams& p, int b, in
   }
 }
 
-template <int D, bool F8>
+// CL: the cluster reducer.  An instantiation of its own, so that the ticket form carries none of its code.
+template <int D, bool F8, bool CL>
 __global__ void __launch_bounds__(PvCfg<D, F8>::kThreads, PvCfg<D, F8>::kCtasPerSm)
-resattn_pv_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map, const AttnParams p) {
+resattn_pv_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+                  const __grid_constant__ AttnParams p) {
   using C = TCfg<D>;
   using PC = PvCfg<D, F8>;
   constexpr int kPvAccs = PC::kAccs;
@@ -228,13 +323,22 @@ resattn_pv_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
   if (my_tiles == 0 && p.splits > 1 && !(p.q_pack && split == 0)) {
     // nothing to read for this split: publish an empty partial and, if this CTA happens to draw the last
     // ticket, merge the others' (the whole CTA takes this branch together)
-    if (threadIdx.x < G) {
-      const int64_t slot = (int64_t(split) * p.batch + b) * p.hq + hkv * G + threadIdx.x;
-      p.l_part[slot] = 0.f;
-      p.m_part[slot] = -INFINITY;
-    }
     float* scratch = reinterpret_cast<float*>(smem + kPvOffV);
-    if (merge_splits_last_cta<D>(p, b, hkv, scratch, &merge_flag) && p.out_nvfp4) pack_nvfp4_output<D>(p, b, hkv, scratch);
+    if constexpr (CL) {
+      if (threadIdx.x < G) {
+        scratch[8 * D + threadIdx.x] = 0.f;
+        scratch[8 * D + 8 + threadIdx.x] = -INFINITY;
+      }
+      __syncthreads();
+      merge_splits_cluster<D>(p, b, hkv, scratch, split);
+    } else {
+      if (threadIdx.x < G) {
+        const int64_t slot = (int64_t(split) * p.batch + b) * p.hq + hkv * G + threadIdx.x;
+        p.l_part[slot] = 0.f;
+        p.m_part[slot] = -INFINITY;
+      }
+      if (merge_splits_last_cta<D>(p, b, hkv, scratch, &merge_flag) && p.out_nvfp4) pack_nvfp4_output<D>(p, b, hkv, scratch);
+    }
     return;
   }
   const int32_t* bt = p.block_tables + int64_t(b) * p.bt_stride;
@@ -763,6 +867,12 @@ resattn_pv_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
           if (p.out_nvfp4) stage_out[g * D + d] = o_acc[g] * rr;
           else if (p.out_f32) static_cast<float*>(p.out)[oi] = o_acc[g] * rr;
           else static_cast<__nv_bfloat16*>(p.out)[oi] = __float2bfloat16_rn(o_acc[g] * rr);
+        } else if constexpr (CL) {
+          stage_out[g * D + d] = o_acc[g];
+          if (d == 0) {
+            stage_out[8 * D + g] = l;
+            stage_out[8 * D + 8 + g] = my_tiles > 0 ? m_sh[g] : -INFINITY;
+          }
         } else {
           const int64_t slot = (int64_t(split) * p.batch + b) * p.hq + head;
           p.o_part[slot * D + d] = o_acc[g];
@@ -779,7 +889,10 @@ resattn_pv_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
   // every CTA takes its ticket, also one whose waits expired (the status word flags that call), so that
   // the counters are back at zero when the grid has finished
   bool pack = p.out_nvfp4 && p.splits == 1;
-  if (p.splits > 1) pack = merge_splits_last_cta<D>(p, b, hkv, stage_out, &merge_flag) && p.out_nvfp4;
+  if (p.splits > 1) {
+    if constexpr (CL) merge_splits_cluster<D>(p, b, hkv, stage_out, split);
+    else pack = merge_splits_last_cta<D>(p, b, hkv, stage_out, &merge_flag) && p.out_nvfp4;
+  }
   if (pack) pack_nvfp4_output<D>(p, b, hkv, stage_out);
   if (warp == kPvMmaWarp) {
     tc_fence_after();
@@ -810,8 +923,13 @@ int make_pool_map(CUtensorMap* map, const uint8_t* base, int64_t pages, int64_t 
   return RI_OK;
 }
 
-// Launch attributes of one instantiation on the current device, set once per device (also callable ahead of the
-// first launch: ri_resattn_prepare).
+// A cluster launch places the CTAs of a cluster on as few SMs as their resources allow, two per SM for head_dim
+// 128, where they then share the conversion pipes.  A grid that has an SM for every CTA asks for this much
+// shared memory instead, which makes every CTA take an SM of its own.
+constexpr int kSpreadSmemBytes = 120 * 1024;
+
+// Launch attributes of the instantiations of one (head_dim, format) on the current device, set once per device
+// (also callable ahead of the first launch: ri_resattn_prepare).
 template <int D, bool F8>
 int prepare_decode_pv() {
   using PC = PvCfg<D, F8>;
@@ -820,8 +938,12 @@ int prepare_decode_pv() {
   RI_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) dev = 0;
   if (!attr_done[dev]) {
-    RI_CUDA(cudaFuncSetAttribute(resattn_pv_kernel<D, F8>, cudaFuncAttributeMaxDynamicSharedMemorySize, PC::kSmemBytes));
-    RI_CUDA(cudaFuncSetAttribute(resattn_pv_kernel<D, F8>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
+    RI_CUDA(cudaFuncSetAttribute(resattn_pv_kernel<D, F8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PC::kSmemBytes));
+    RI_CUDA(cudaFuncSetAttribute(resattn_pv_kernel<D, F8, false>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
+    RI_CUDA(cudaFuncSetAttribute(resattn_pv_kernel<D, F8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 PC::kSmemBytes > kSpreadSmemBytes ? PC::kSmemBytes : kSpreadSmemBytes));
+    RI_CUDA(cudaFuncSetAttribute(resattn_pv_kernel<D, F8, true>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
+    RI_CUDA(cudaFuncSetAttribute(resattn_pv_kernel<D, F8, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));   // clusters of 16
     attr_done[dev] = true;
   }
   return RI_OK;
@@ -847,10 +969,35 @@ int launch_decode_pv(const AttnParams& p, cudaStream_t st) {
   cfg.blockDim = dim3(PC::kThreads);
   cfg.dynamicSmemBytes = PC::kSmemBytes;
   cfg.stream = st;
-  cudaLaunchAttribute attr{};
-  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr.val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = &attr;
+  cudaLaunchAttribute attr[2] = {};
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cuda_status(cudaLaunchKernelEx(&cfg, resattn_pv_kernel<D, F8>, k_map, v_map, p), "resattn decode launch");
+  if (p.cluster_merge) {                                     // the splits of a (sequence, KV head) form one cluster
+    if (int64_t(p.splits) * p.hkv * p.batch <= p.sm_count && PC::kSmemBytes < kSpreadSmemBytes)
+      cfg.dynamicSmemBytes = kSpreadSmemBytes;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = p.splits;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.numAttrs = 2;
+    static int fits[64][17] = {};                             // per device and cluster size: 0 unknown, 1 fits, -1 does not
+    int dev = 0;
+    RI_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) dev = 0;
+    int& fit = fits[dev][p.splits];
+    if (fit == 0) {
+      int clusters = 0;
+      RI_CUDA(cudaOccupancyMaxActiveClusters(&clusters, resattn_pv_kernel<D, F8, true>, &cfg));
+      fit = clusters >= 1 ? 1 : -1;
+    }
+    if (fit < 0) {
+      set_error("this device cannot co-schedule a cluster of %d decode CTAs: use the ticket reducer", p.splits);
+      return RI_ERR_ARG;
+    }
+  }
+  if (p.cluster_merge)
+    return cuda_status(cudaLaunchKernelEx(&cfg, resattn_pv_kernel<D, F8, true>, k_map, v_map, p), "resattn decode launch");
+  return cuda_status(cudaLaunchKernelEx(&cfg, resattn_pv_kernel<D, F8, false>, k_map, v_map, p), "resattn decode launch");
 }

@@ -126,10 +126,11 @@ def run_paged_fp4_decode_qmul4_tmem(q: torch.Tensor, pool: NvFp4PagedKVPool, v_d
     else:
         validate_decode_plan(plan, head_dim=d)
         splits, reduction = plan
-    del reduction                                    # one reducer: the merge fused into the decode launch
+    # "kernel" / "gmem_fused": the ticket merge through the workspace; "cga_sharded": the splits as one cluster
+    cluster = reduction == "cga_sharded" and splits > 1
     lib = _cabi.load()
     ws_ptr, ws_bytes = None, 0
-    if splits > 1:
+    if splits > 1 and not cluster:
         need = lib.ri_resattn_workspace_bytes(b, hq, d, splits)
         if reduction_workspace is not None:
             o_p, l_p, m_p = reduction_workspace
@@ -151,7 +152,8 @@ def run_paged_fp4_decode_qmul4_tmem(q: torch.Tensor, pool: NvFp4PagedKVPool, v_d
             v_sf_bthd.data_ptr(), pool.k_data.shape[0], code_stride, sf_stride, block_tables.data_ptr(), block_tables.stride(0),
             seq_lens.data_ptr(), b, hq, h, d, page, int(max_seq_len or 0), float(sm_scale), float(value_scale),
             out.data_ptr(),
-            _cabi.DTYPE_BF16, None, 0, None, 0, None, None, 0, splits, ws_ptr, ws_bytes, 1,
+            _cabi.DTYPE_BF16, None, 0, None, 0, None, None, 0, splits,
+            _cabi.ATTN_REDUCER_CLUSTER if cluster else _cabi.ATTN_REDUCER_TICKET, ws_ptr, ws_bytes, 1,
             ops.status_word(q.device).data_ptr(), _cabi.current_stream(q.device))
     _cabi.check(st, "run_paged_fp4_decode_qmul4_tmem")
     return out

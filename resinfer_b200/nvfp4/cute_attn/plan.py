@@ -2,14 +2,19 @@
 
 Keeps the reference's selection interface and policy names (csrc/resattn/plan.py:21-93):
 ``(splits, reducer)`` with reducer in {"none", "kernel", "cga_sharded", "gmem_fused"} and the
-RESIDUE_ATTN_REDUCTION policy {"legacy", "auto", "deterministic"}.  This library has one reducer, fused
-into the decode launch: every CTA of a (sequence, KV head) takes a ticket and the one that draws the last
-ticket sums the split partials in split order (deterministic; the counterpart of the reference's
-"gmem_fused" reducer, csrc/resattn/kernel_paged_decode.py:2365-2431, without its spin wait).  Plans whose
-split count is above one are reported as "kernel" -- the name the reference gives its deterministic
-reducer -- and the other reducer names are accepted by ``validate_decode_plan`` for compatibility and run
-the same way.  The split count itself is chosen for this library's kernel
-(one CTA per SM at a time, 128-token tiles): enough CTAs to cover the SMs several times over while
+RESIDUE_ATTN_REDUCTION policy {"legacy", "auto", "deterministic"}.  Both reducers of this library are fused
+into the decode launch and combine the partials in split order, so they give the same bits:
+
+* "kernel" (and "gmem_fused", which runs the same way): every CTA of a (sequence, KV head) takes a ticket and the
+  one that draws the last ticket sums the partials from a global workspace (the counterpart of the reference's
+  "gmem_fused" reducer, csrc/resattn/kernel_paged_decode.py:2365-2431, without its spin wait);
+* "cga_sharded": the splits of a (sequence, KV head) are one thread-block cluster and combine through distributed
+  shared memory, each CTA a share of the output.  Chosen for BF16 output when the whole grid is a handful of
+  clusters and the context is not very long (measured on B200, one sequence, 8 KV heads: 14.6 against 18.7 us
+  at 2.5 K tokens, 15.9 against 20.6 us at 4 K; with 16 clusters or more the cluster launch loses to the ticket
+  form, which spreads its CTAs over the SMs freely).  Unlike the reference, head_dim 256 takes it too.
+
+The split count itself is chosen for this library's kernel (128-token tiles): enough CTAs to cover the SMs while
 leaving every split at least a few tiles.
 """
 from __future__ import annotations
@@ -64,11 +69,35 @@ def select_decode_plan(batch, num_kv_heads, max_kv_len, sm_count, *, output_nvfp
                        grouped_head_tile=16, residue_fold=True, reduction_policy=None, head_dim=128):
     """Select the static split/reducer, then apply the caller's reduction policy."""
     _check_output_dimension(head_dim, output_nvfp4)
-    _reduction_policy(reduction_policy)
     if not residue_fold or grouped_head_tile not in (8, 16):
         raise NotImplementedError("production ResAttn requires residue Q8/Q16")
+    policy = _reduction_policy(reduction_policy)
+    if not output_nvfp4 and policy != "deterministic":
+        cga = _cluster_splits(batch, num_kv_heads, max_kv_len, sm_count)
+        if cga >= 2:
+            return cga, "cga_sharded"
     splits = _select_splits(batch, num_kv_heads, max_kv_len, sm_count, ctas_per_sm=2 if head_dim == 128 else 1)
     return (1, "none") if splits == 1 else (splits, "kernel")
+
+
+_MAX_CLUSTERS = 8            # (sequence, KV head) pairs up to which the cluster reducer wins
+_CLUSTER_MAX_TILES = 160     # ... and the context (128-token tiles) up to which: beyond it 16 ticket splits are faster
+CLUSTER_SIZES = (2, 3, 4, 5, 6, 7, 8, 16)
+
+
+def _cluster_splits(batch: int, heads: int, length: int, sms: int) -> int:
+    """Cluster size for the "cga_sharded" reducer, 0 when the ticket reducer is the better choice: at most
+    `_MAX_CLUSTERS` clusters of at most eight CTAs, one CTA per SM, one split per 128-token tile at most.  Measured
+    for one sequence and 8 KV heads: eight clustered CTAs beat every ticket plan up to 16 K tokens (29.9 against
+    31.7 us there) and lose to sixteen ticket splits from 24 K on (38.8 against 35.2 us); a cluster of sixteen, which
+    the kernel accepts, is slower than either (the device places few of them at a time)."""
+    clusters = max(1, batch * heads)
+    tiles = max(1, (length + 127) // 128)
+    if clusters > _MAX_CLUSTERS or tiles < 2:
+        return 0
+    if tiles > _CLUSTER_MAX_TILES:
+        return 0
+    return min(8, sms // clusters, tiles)
 
 
 def static_compile_plans(*, output_nvfp4=False, grouped_head_tile=16, residue_fold=True, head_dim=128):
@@ -77,7 +106,8 @@ def static_compile_plans(*, output_nvfp4=False, grouped_head_tile=16, residue_fo
     if not residue_fold or grouped_head_tile not in (8, 16):
         raise NotImplementedError("production ResAttn requires residue Q8/Q16")
     _check_output_dimension(head_dim, output_nvfp4)
-    return ((1, "none"), (2, "kernel"), (4, "kernel"))
+    plans = ((1, "none"), (2, "kernel"), (4, "kernel"))
+    return plans if output_nvfp4 else plans + ((4, "cga_sharded"),)
 
 
 def validate_decode_plan(plan, *, output_nvfp4=False, head_dim=128):
@@ -88,8 +118,12 @@ def validate_decode_plan(plan, *, output_nvfp4=False, head_dim=128):
         raise ValueError(f"decode plan splits must be a positive integer, got {splits!r}")
     if reducer not in _REDUCERS:
         raise ValueError(f"unsupported decode reducer: {reducer!r}")
-    if head_dim == 256 and reducer not in ("none", "kernel"):
-        raise NotImplementedError("D256 supports none/kernel reduction only")
+    if head_dim == 256 and reducer == "gmem_fused":
+        raise NotImplementedError("D256 supports none/kernel/cga_sharded reduction only")
+    if output_nvfp4 and reducer == "cga_sharded":
+        raise NotImplementedError("cga_sharded does not support output_nvfp4=True")
+    if reducer == "cga_sharded" and splits not in (1,) + CLUSTER_SIZES:
+        raise ValueError(f"cga_sharded requires splits in {(1,) + CLUSTER_SIZES}")
     if reducer == "none" and splits != 1:
         raise ValueError("none reduction requires splits=1")
     if splits > 256:

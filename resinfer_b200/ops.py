@@ -244,20 +244,22 @@ def resattn_decode(q: torch.Tensor, k_data: torch.Tensor, k_sf: torch.Tensor, v_
                    q_residue: bool = True, q_pack: torch.Tensor | None = None,
                    q_sf: torch.Tensor | None = None, max_kv_len: int = 0,
                    out_global_scale: torch.Tensor | None = None,
-                   out_block_scale: torch.Tensor | None = None) -> torch.Tensor:
+                   out_block_scale: torch.Tensor | None = None, reducer: str = "ticket") -> torch.Tensor:
     """Paged NVFP4-KV decode attention.  q bf16 [B,Hq,D]; k_data/v_data uint8 [pages,Hkv,page,D/2];
     k_sf/v_sf uint8 (or float8_e4m3fn) [pages,Hkv,page,D/16] (any page stride: ``kv_page_strides``); out bf16 [B,Hq,D] (written) -- or, with
     ``out_global_scale`` (float32[1]) and ``out_block_scale`` (128x4-swizzled E4M3 bytes), packed NVFP4:
-    out uint8 [B, Hq*D/2]."""
+    out uint8 [B, Hq*D/2].  ``reducer``: how the KV splits are combined, "ticket" (through a workspace, the CTA
+    that finishes last) or "cluster" (2 to 8 or 16 splits as one thread-block cluster, through shared memory); same bits."""
     lib = _cabi.load()
     b, hq, d = q.shape
     pages, hkv, page, _ = k_data.shape
     dev = q.device
     code_stride, sf_stride = kv_page_strides(k_data, k_sf, v_data, v_sf)
+    reducer_c = {"ticket": _cabi.ATTN_REDUCER_TICKET, "cluster": _cabi.ATTN_REDUCER_CLUSTER}[reducer]
     with torch.cuda.device(dev):
         ws = None
         ws_bytes = 0
-        if splits > 1:
+        if splits > 1 and reducer == "ticket":
             ws_bytes = lib.ri_resattn_workspace_bytes(b, hq, d, splits)
             ws = _workspace(dev, ws_bytes, "attn", zero_prefix=lib.ri_resattn_counter_bytes(b, hq))
         st = lib.ri_resattn_decode_strided(
@@ -269,7 +271,7 @@ def resattn_decode(q: torch.Tensor, k_data: torch.Tensor, k_sf: torch.Tensor, v_
             _cabi.ptr(q_sf), 0 if q_sf is None else q_sf.numel(),
             _cabi.ptr(out_global_scale), _cabi.ptr(out_block_scale),
             0 if out_block_scale is None else out_block_scale.numel() * out_block_scale.element_size(),
-            splits, _cabi.ptr(ws), ws_bytes, int(q_residue), status_word(dev).data_ptr(),
+            splits, reducer_c, _cabi.ptr(ws), ws_bytes, int(q_residue), status_word(dev).data_ptr(),
             _cabi.current_stream(dev))
     _cabi.check(st, "resattn_decode")
     return out

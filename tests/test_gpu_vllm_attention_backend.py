@@ -134,7 +134,7 @@ def test_strided_entry_rejects_bad_strides(cuda_device):
         return lib.ri_resattn_decode_strided(
             q.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), 1, code_stride, sf_stride, bt.data_ptr(), 1,
             sl.data_ptr(), 1, 8, 1, 128, 16, 0, 1.0, 1.0, out.data_ptr(), _cabi.DTYPE_BF16, None, 0, None, 0, None, None, 0,
-            1, None, 0, 1, ops.status_word(dev).data_ptr(), _cabi.current_stream(dev))
+            1, _cabi.ATTN_REDUCER_TICKET, None, 0, 1, ops.status_word(dev).data_ptr(), _cabi.current_stream(dev))
     assert call(16 * 64 - 16, 0) != 0 and b"page strides" in lib.ri_last_error()       # smaller than a page
     assert call(16 * 64 + 8, 0) != 0                                                   # not a multiple of 16
     assert call(0, 16 * 8 + 4) != 0

@@ -61,7 +61,18 @@ def test_env_contract():
 def test_decode_plan_selection_and_validation():
     from resinfer_b200.nvfp4.cute_attn.plan import select_decode_plan, validate_decode_plan, static_compile_plans
     assert select_decode_plan(256, 8, 32768, 148, head_dim=256) == (1, "none")
-    s, r = select_decode_plan(1, 8, 32768, 148)
+    # a handful of (sequence, KV head) pairs: the splits form a cluster, one CTA per SM
+    assert select_decode_plan(1, 8, 16384, 148) == (8, "cga_sharded")
+    s, r = select_decode_plan(1, 8, 32768, 148)                            # very long: more ticket splits win
+    assert r == "kernel" and 8 <= s <= 64
+    assert select_decode_plan(1, 8, 4096, 148) == (8, "cga_sharded")
+    assert select_decode_plan(1, 8, 4096, 148, head_dim=256) == (8, "cga_sharded")
+    assert select_decode_plan(1, 8, 600, 148) == (5, "cga_sharded")        # one split per tile at most
+    assert select_decode_plan(4, 2, 8192, 148) == (8, "cga_sharded")       # a tensor-parallel shard's heads
+    assert select_decode_plan(1, 32, 8192, 148)[1] == "kernel"             # too many clusters
+    s, r = select_decode_plan(1, 8, 32768, 148, reduction_policy="deterministic")
+    assert r == "kernel" and 8 <= s <= 64
+    s, r = select_decode_plan(1, 8, 32768, 148, output_nvfp4=True)         # packed output: ticket reducer
     assert r == "kernel" and 8 <= s <= 64
     # eight sequences of up to 32768 tokens: pieces sized so that the working CTAs fill the SMs once
     assert select_decode_plan(8, 8, 32768, 148, head_dim=256) == (4, "kernel")
@@ -75,8 +86,15 @@ def test_decode_plan_selection_and_validation():
             validate_decode_plan(bad)
     with pytest.raises(NotImplementedError):
         select_decode_plan(1, 8, 100, 148, head_dim=64)
+    validate_decode_plan((4, "cga_sharded"), head_dim=256)
+    validate_decode_plan((16, "cga_sharded"))
     with pytest.raises(NotImplementedError):
-        validate_decode_plan((4, "cga_sharded"), head_dim=256)
+        validate_decode_plan((4, "gmem_fused"), head_dim=256)
+    with pytest.raises(NotImplementedError):
+        validate_decode_plan((4, "cga_sharded"), output_nvfp4=True)
+    with pytest.raises(ValueError):
+        validate_decode_plan((12, "cga_sharded"))
+    assert (4, "cga_sharded") in static_compile_plans() and (4, "cga_sharded") not in static_compile_plans(output_nvfp4=True)
     with pytest.raises(ValueError):
         select_decode_plan(1, 8, 100, 148, reduction_policy="fastest")
 
