@@ -1004,7 +1004,8 @@ def measure_resattn(torch, dev, ops, capture, timed, hbm_gbs, only=None, steps=1
         vs = torch.randint(0x28, 0x48, (pool, hkv, page, d // 16), generator=g, device=dev, dtype=torch.uint8)
         q = torch.randn(batch, hq, d, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
         out = torch.empty(batch, hq, d, dtype=torch.bfloat16, device=dev)
-        splits, reducer = select_decode_plan(batch, hkv, int(lens.max()), sms, head_dim=d)
+        # the lengths are host knowledge in a serving stack (the scheduler's), so the plan may use them
+        splits, reducer = select_decode_plan(batch, hkv, int(lens.max()), sms, head_dim=d, seq_lens=lens.tolist())
         reducer = "cluster" if reducer == "cga_sharded" else "ticket"
         max_len = int(lens.max())
         def call():                                         # the format switch is a host-side setting: it is

@@ -56,12 +56,13 @@ def _sm_count(device_str: str) -> int:
 
 
 def plan_qmul4_decode(batch, num_kv_heads, max_kv_len, device, *, grouped_head_tile=16, residue_fold=True,
-                      head_dim=128):
-    """(splits, reducer) for a BF16-output decode launch."""
+                      head_dim=128, seq_lens=None):
+    """(splits, reducer) for a BF16-output decode launch; ``seq_lens``: host lengths, if the caller has them."""
     if not residue_fold:
         raise NotImplementedError("ordinary QK is not supported")
     return select_decode_plan(batch, num_kv_heads, max_kv_len, _sm_count(str(device)),
-                              grouped_head_tile=grouped_head_tile, residue_fold=residue_fold, head_dim=head_dim)
+                              grouped_head_tile=grouped_head_tile, residue_fold=residue_fold, head_dim=head_dim,
+                              seq_lens=seq_lens)
 
 
 def allocate_qmul4_reduction_workspace(splits: int, batch: int, num_qo_heads: int, head_dim: int, device, *,
@@ -180,14 +181,14 @@ def compile_decode_variant(plan: dict):
     return plan["args"]
 
 
-def plan_qmul4_decode_nvfp4(batch, num_qo_heads, num_kv_heads, max_kv_len, device, *, residue_fold=True):
+def plan_qmul4_decode_nvfp4(batch, num_qo_heads, num_kv_heads, max_kv_len, device, *, residue_fold=True, seq_lens=None):
     """(splits, reducer) for a packed-NVFP4-output decode launch (head_dim 128 only, as in the reference:
     csrc/resattn/host.py:94-106)."""
     if not residue_fold:
         raise NotImplementedError("ordinary QK is not supported")
     return select_decode_plan(batch, num_kv_heads, max_kv_len, _sm_count(str(device)), output_nvfp4=True,
                               grouped_head_tile=_residue_padded_group_size(num_qo_heads, num_kv_heads),
-                              residue_fold=residue_fold)
+                              residue_fold=residue_fold, seq_lens=seq_lens)
 
 
 def allocate_nvfp4_attention_output(batch: int, num_qo_heads: int, head_dim: int, device):

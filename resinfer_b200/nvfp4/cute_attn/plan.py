@@ -65,9 +65,31 @@ def _select_splits(batch: int, heads: int, length: int, sms: int, min_tiles_per_
     return max(1, min(splits, 64))
 
 
+def _working_ctas(seq_lens, heads: int, splits: int, tiles_max: int) -> int:
+    """CTAs of a ticket launch that have tiles to read: every sequence is cut into pieces of
+    ceil(tiles_max / splits) tiles, the CTAs of the splits beyond its end leave at once."""
+    piece = -(-tiles_max // splits)
+    return heads * sum(-(-((max(int(n), 0) + 127) // 128) // piece) for n in seq_lens)
+
+
+def _select_splits_exact(seq_lens, heads: int, tiles_max: int, slots: int) -> int:
+    """With the lengths known on the host and a grid well below the device: the largest split count whose working
+    CTAs still run in one wave.  Measured on B200 over batches of 2 to 16 sequences, equal and unequal lengths,
+    both head dimensions, that count is the fastest or within a few percent of it (equal lengths of 32 K tokens,
+    head_dim 128: 16 / 12 / 8 / 6 / 4 splits for 2 / 3 / 4 / 6 / 8 sequences); one more wave costs 15 to 40 %."""
+    best = 1
+    for s in range(2, min(64, tiles_max) + 1):
+        if _working_ctas(seq_lens, heads, s, tiles_max) <= slots:
+            best = s
+    piece = -(-tiles_max // best)
+    return -(-tiles_max // piece)                     # no CTAs beyond the last piece of the longest sequence
+
+
 def select_decode_plan(batch, num_kv_heads, max_kv_len, sm_count, *, output_nvfp4=False,
-                       grouped_head_tile=16, residue_fold=True, reduction_policy=None, head_dim=128):
-    """Select the static split/reducer, then apply the caller's reduction policy."""
+                       grouped_head_tile=16, residue_fold=True, reduction_policy=None, head_dim=128, seq_lens=None):
+    """Select the static split/reducer, then apply the caller's reduction policy.  ``seq_lens`` (optional; this
+    library's addition): the sequences' lengths as host integers, when the caller has them without a device
+    synchronisation -- small grids are then planned on the real tile counts instead of an assumed distribution."""
     _check_output_dimension(head_dim, output_nvfp4)
     if not residue_fold or grouped_head_tile not in (8, 16):
         raise NotImplementedError("production ResAttn requires residue Q8/Q16")
@@ -76,7 +98,12 @@ def select_decode_plan(batch, num_kv_heads, max_kv_len, sm_count, *, output_nvfp
         cga = _cluster_splits(batch, num_kv_heads, max_kv_len, sm_count)
         if cga >= 2:
             return cga, "cga_sharded"
-    splits = _select_splits(batch, num_kv_heads, max_kv_len, sm_count, ctas_per_sm=2 if head_dim == 128 else 1)
+    ctas_per_sm = 2 if head_dim == 128 else 1
+    slots = sm_count * ctas_per_sm
+    if seq_lens is not None and len(seq_lens) == batch and 2 * batch * num_kv_heads <= slots:
+        splits = _select_splits_exact(seq_lens, num_kv_heads, max(1, (max_kv_len + 127) // 128), slots)
+    else:
+        splits = _select_splits(batch, num_kv_heads, max_kv_len, sm_count, ctas_per_sm=ctas_per_sm)
     return (1, "none") if splits == 1 else (splits, "kernel")
 
 

@@ -105,14 +105,28 @@ class ResAttnFlashInferMetadataBuilder(FlashInferMetadataBuilder):
                 raise ValueError("Expected int32 block table with unit column stride")
         return stock
 
+    @staticmethod
+    def _host_seq_lens(common_attn_metadata, n):
+        """The decode requests' lengths as host integers when vLLM has them on the host already (no device
+        synchronisation is ever made for them), else None.  Decode requests come first in the batch."""
+        for name in ("seq_lens_cpu_upper_bound", "_seq_lens_cpu"):
+            t = getattr(common_attn_metadata, name, None)
+            if t is not None and t.shape[0] >= n:
+                return [int(v) for v in t[:n].tolist()]
+        return None
+
     def build(self, common_prefix_len, common_attn_metadata, fast_build=False) -> FlashInferMetadata:
-        return self._check(super().build(common_prefix_len, common_attn_metadata, fast_build))
+        md = self._check(super().build(common_prefix_len, common_attn_metadata, fast_build))
+        if md.num_decodes:                               # lets the split plan count the real tiles (plan.py)
+            md.decode.seq_lens_host = self._host_seq_lens(common_attn_metadata, md.num_decodes)
+        return md
 
     def build_for_cudagraph_capture(self, common_attn_metadata):
         md = self.build(0, common_attn_metadata)
         if md.num_decodes:                               # capture with the split plan of the longest sequence served
             decode = _require_trtllm_decode(md)
             decode.max_seq_len = max(decode.max_seq_len, self._cg_capture_seq_len)
+            decode.seq_lens_host = None                  # the captured plan must not depend on this batch's lengths
         return md
 
 

@@ -6,7 +6,8 @@ the decode tokens of a step (ShawRong/ResInfer quant/vllm_integration/attn/decod
 activation buffers of the following projection), plus the per-layer cache of split-KV reduction
 workspaces (:23-53).  The host class supplies ``num_heads``, ``num_kv_heads``, ``head_size``, ``scale``
 and a dict ``_decode_reduction_workspaces``; the metadata object supplies ``num_decode_tokens`` and
-``decode.block_tables / seq_lens / max_seq_len``; ``pool`` is an ``NvFp4PagedKVPool``.
+``decode.block_tables / seq_lens / max_seq_len`` (and, optionally, ``decode.seq_lens_host``: the lengths as host
+integers for the split plan, this library's addition); ``pool`` is an ``NvFp4PagedKVPool``.
 
 Nothing here imports vLLM, so the mixin can be exercised with plain objects; the vLLM-facing classes
 (metadata builder, prefill through the stock implementation) are in ``backend.py``.
@@ -55,7 +56,8 @@ class ResAttnDecodeMixin:
         if dec.max_seq_len:                                   # unknown length: the host entry plans by itself
             plan = _host.plan_qmul4_decode(
                 n, self.num_kv_heads, dec.max_seq_len, q.device, head_dim=self.head_size,
-                grouped_head_tile=_host._residue_padded_group_size(self.num_heads, self.num_kv_heads))
+                grouped_head_tile=_host._residue_padded_group_size(self.num_heads, self.num_kv_heads),
+                seq_lens=getattr(dec, "seq_lens_host", None))
             if plan[1] == "kernel":
                 ws = self._get_decode_reduction_workspace(_host, plan[0], n, q.device)
         _host.run_paged_fp4_decode_qmul4_tmem(
@@ -70,7 +72,8 @@ class ResAttnDecodeMixin:
         dec = md.decode
         q = _decode_slice(q_all, n)
         _host.check_shape_supported(self.num_heads, self.num_kv_heads, self.head_size)
-        plan = _host.plan_qmul4_decode_nvfp4(n, self.num_heads, self.num_kv_heads, dec.max_seq_len, q.device)
+        plan = _host.plan_qmul4_decode_nvfp4(n, self.num_heads, self.num_kv_heads, dec.max_seq_len, q.device,
+                                             seq_lens=getattr(dec, "seq_lens_host", None))
         ws = None
         if plan[1] in _PERSISTENT_REDUCERS:
             ws = self._get_decode_reduction_workspace(_host, plan[0], n, q.device, reduction=plan[1])

@@ -79,6 +79,15 @@ def test_decode_plan_selection_and_validation():
     assert select_decode_plan(8, 8, 32768, 148) == (8, "kernel")       # head_dim 128: two CTAs per SM
     assert select_decode_plan(64, 8, 32768, 148) == (3, "kernel")     # a few waves: thirds even out the tail
     assert select_decode_plan(1, 8, 64, 148) == (1, "none")          # too short to split
+    # lengths known on the host, small grid: the most splits whose working CTAs fit the device once
+    assert select_decode_plan(4, 8, 32768, 148, seq_lens=[32768] * 4) == (9, "kernel")        # 288 of 296 slots
+    assert select_decode_plan(8, 8, 32768, 148, seq_lens=[32768] * 8) == (4, "kernel")
+    assert select_decode_plan(8, 8, 32768, 148, head_dim=256, seq_lens=[32768] * 8) == (2, "kernel")
+    uneven = [2525, 19358, 12195, 15818, 10090, 9605, 25861, 5305]
+    assert select_decode_plan(8, 8, 25861, 148, seq_lens=uneven) == (8, "kernel")             # short sequences leave splits unused
+    assert select_decode_plan(2, 8, 8192, 148, seq_lens=[8192, 8192]) == (16, "kernel")        # 64 tiles: pieces of 4, no empty splits
+    assert select_decode_plan(64, 8, 32768, 148, seq_lens=[32768] * 64) == select_decode_plan(64, 8, 32768, 148)   # large grids: unchanged
+    assert select_decode_plan(8, 8, 32768, 148, seq_lens=[32768] * 7) == select_decode_plan(8, 8, 32768, 148)      # wrong count: ignored
     assert (1, "none") in static_compile_plans()
     validate_decode_plan((4, "kernel"))
     for bad in ((0, "kernel"), (2, "none"), (2, "magic"), (1024, "kernel")):

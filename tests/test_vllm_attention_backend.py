@@ -183,7 +183,14 @@ def test_builder_refuses_decode_context_parallel_and_lengthens_the_capture(monke
     b = Bld(None, [], cfg, "cpu")
     assert b.reorder_batch_threshold == 1 and b._cg_capture_seq_len == 4096
     md = b.build_for_cudagraph_capture(_metadata())                    # the fake stock build hands the metadata through
-    assert md.decode.max_seq_len == 4096
+    assert md.decode.max_seq_len == 4096 and md.decode.seq_lens_host is None
+    # host lengths, when vLLM has them, travel with the decode metadata for the split plan (never under capture)
+    common = _metadata(num_decodes=3, num_prefill_tokens=4)
+    common.seq_lens_cpu_upper_bound = torch.tensor([700, 9000, 33, 4])  # three decodes, then the prefill request
+    assert b.build(0, common).decode.seq_lens_host == [700, 9000, 33]
+    assert b.build_for_cudagraph_capture(common).decode.seq_lens_host is None
+    plain = _metadata(num_decodes=2)
+    assert b.build(0, plain).decode.seq_lens_host is None
     monkeypatch.setenv("RESIDUE_ATTN_CG_CAPTURE_LEN", "512")
     assert Bld(None, [], cfg, "cpu")._cg_capture_seq_len == 512
     with pytest.raises(NotImplementedError):
