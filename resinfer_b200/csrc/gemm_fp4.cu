@@ -79,6 +79,7 @@ struct GemmParams {
   int32_t* status;
   // shared memory carve-up
   int smem_act_off, smem_sfa_off, smem_sfb_off, stage_bytes;
+  int map3;                     // 512-element stages: the tensor maps are 3-D (128 B, rows, 256-element sub-tiles), one copy per stage
   long long* trace;             // development builds: [grid][8] nanosecond stamps
   // Fused all-reduce over peer memory (ri_fp4_gemm_allreduce).  Every rank owns an "inbox" with one area per
   // source rank.  The CTA that completes an output tile goes over the tile twice.  First pass: the BF16 tile is
@@ -398,7 +399,12 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
 // (no K split).  Cross-CTA signals: the scale warps of both CTAs arrive on the leader's scale barrier (an
 // arrival implies that CTA's stage has landed), the leader's commits arrive on the barriers of both CTAs,
 // both epilogues arrive on the leader's accumulator-free barrier.
-template <bool MX, bool PAIR, bool AR = false>
+// KS = K tiles of 256 FP4 that make up one pipeline stage (1 or 2).  What a stage costs is mostly the hand-shakes
+// around it -- a turn of the producers, the scale warps and the MMA warp takes 0.4 - 0.45 us whatever the stage
+// holds (traced; the kernel took the same time with the weight loads left out) -- so with few token columns, where
+// shared and tensor memory have the room, a stage carries 512 elements of K: two 128-byte-swizzled sub-tiles per
+// operand, eight scale chunks, eight MMAs, one round of barriers.
+template <bool MX, bool PAIR, bool AR = false, int KS = 1>
 __global__ void __launch_bounds__(kThreads, 1)
 fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap act_map,
                 const __grid_constant__ GemmParams p) {
@@ -427,7 +433,13 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
   const bool kcat = p.layout == RI_GEMM_CONCAT_K;
   const int halves = kcat ? 2 : 1;
   const int row_tiles = (p.n_tile + 127) / 128;             // scale row tiles per activation tile
-  const int act_tile_bytes = (PAIR ? p.n_tile / 2 : p.n_tile) * kTileKBytes;   // activation rows this CTA loads
+  static_assert(KS == 1 || !PAIR, "two-CTA tiles keep 256-element stages");
+  constexpr int kKTile = 256 * KS;                           // elements of K per stage
+  constexpr int kMmas = kMmaPerTile * KS;                    // K64 instructions per stage
+  constexpr int kWSub = kTileW * kTileKBytes;                // bytes of one 256-element weight sub-tile
+  constexpr int kSfaCols = 16 * KS;                          // tensor-memory columns of a stage's weight scales
+  const int act_sub_bytes = (PAIR ? p.n_tile / 2 : p.n_tile) * kTileKBytes;   // activation rows this CTA loads, one sub-tile
+  const int act_tile_bytes = act_sub_bytes * KS;             // ... per stage and half
   const int nbuf = p.n_tile <= 128 ? 2 : 1;                  // accumulator buffers in tensor memory
 
   // Set-up.  Warp 0 (the weight producer) initialises the barriers and only *arrives* at the set-up
@@ -510,9 +522,9 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
             if (first_row_tile + t < p.act_row_tiles) ++valid_row_tiles;
           w_sf_tile = p.w_sf + int64_t(w_tile) * p.w_sf_tile_stride;
         }
-        // the last K tile may hold fewer than four K64 steps: copy only the scale chunks that exist
-        const int rem = p.k - w.kt * 256;
-        const int n_mma = rem >= 256 ? kMmaPerTile : rem >> 6;
+        // the last K tile may hold fewer K64 steps: copy only the scale chunks that exist
+        const int rem = p.k - w.kt * kKTile;
+        const int n_mma = rem >= kKTile ? kMmas : rem >> 6;
         const uint32_t sf_bytes = uint32_t(MX ? (n_mma + 1) >> 1 : n_mma) * 512;
         if (w.it >= p.stages) {
           if (!wait_bar<PAIR>(smem_u32(&bar_empty[w.stage]), w.stage_par ^ 1, &abort_flag, w_role ? 1 : 2)) break;
@@ -521,17 +533,29 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
         const uint32_t full = smem_u32(&bar_full[w.stage]);
         trace_ev(p, w_role ? 0 : (act_tile_role ? 1 : 7), i);
         if (w_role) {
-          const uint32_t tx = kTileW * kTileKBytes + (w_sf_valid ? sf_bytes : 0u) +
+          const uint32_t tx = KS * kWSub + (w_sf_valid ? sf_bytes : 0u) +
                               halves * (act_tile_bytes + valid_row_tiles * sf_bytes);
           mbar_expect_tx(full, tx);
-          tma_load_2d(smem_u32(st), &w_map, w.kt * kTileKBytes, w_tile * kTileW, full);   // rows past N read as zero
+          if (KS == 2 && p.map3) {                            // both sub-tiles with one copy: issuing a copy is what costs
+            tma_load_3d(smem_u32(st), &w_map, 0, w_tile * kTileW, w.kt * KS, full);
+          } else {
+#pragma unroll
+            for (int sub = 0; sub < KS; ++sub)                // rows past N and columns past K read as zero
+              tma_load_2d(smem_u32(st + sub * kWSub), &w_map, (w.kt * KS + sub) * kTileKBytes, w_tile * kTileW, full);
+          }
           if (w_sf_valid) bulk_load_1d(smem_u32(st + p.smem_sfa_off), w_sf_tile + w.kt * sf_stride, sf_bytes, full);
         } else {
           for (int h = 0; h < halves; ++h) {
             if (act_tile_role) {
-              tma_load_2d(smem_u32(st + p.smem_act_off + h * act_tile_bytes), &act_map,
-                          w.kt * kTileKBytes + h * p.act_res_col0,
-                          tok_tile * p.n_tile + (PAIR ? rank * (p.n_tile / 2) : 0), full);
+              if (KS == 2 && p.map3) {                        // (one half only with 512-element stages)
+                tma_load_3d(smem_u32(st + p.smem_act_off), &act_map, 0, tok_tile * p.n_tile, w.kt * KS, full);
+                continue;
+              }
+#pragma unroll
+              for (int sub = 0; sub < KS; ++sub)
+                tma_load_2d(smem_u32(st + p.smem_act_off + h * act_tile_bytes + sub * act_sub_bytes), &act_map,
+                            (w.kt * KS + sub) * kTileKBytes + h * p.act_res_col0,
+                            tok_tile * p.n_tile + (PAIR ? rank * (p.n_tile / 2) : 0), full);
               continue;
             }
             for (int t = 0; t < row_tiles; ++t) {
@@ -552,6 +576,9 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
                                   (MX ? (1u << 23) : 0u) | (uint32_t((PAIR ? 2 * kTileW : kTileW) >> 4) << 24);
       bool ok = true;
       const int n_units = int(u_end - u_begin);
+      const uint32_t smem_addr0 = smem_u32(smem);
+      const int act_sub_units = act_sub_bytes >> 4;           // an activation sub-tile in descriptor units
+      const bool sets_per_stage = p.sf_sets == p.stages;
       Walk w;
       w.init(p, u_begin);
       int seg = 0, i = 0;
@@ -565,26 +592,32 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
         const uint32_t d_tmem = tmem_base + buf * p.n_tile;
         uint32_t accumulate = 0;
         for (;;) {                                  // K tiles of this segment (same output tile)
-          bool got = wait_bar<PAIR>(smem_u32(&bar_full[w.stage]), w.stage_par, &abort_flag, 4);
-          // the scale warps have put this K tile's block scales into scale set `set` of tensor memory
-          // (pair: by the scale warps of both CTAs, which also tells that the other CTA's stage has landed)
+          // The scale warps have put this K tile's block scales into scale set `set` of tensor memory (pair: the
+          // scale warps of both CTAs).  They waited for the stage's data before they read its scales, so their
+          // arrival also tells that the stage has landed -- here and in the other CTA of a pair.  Only when scale
+          // sets are recycled faster than stages (sets < stages) is the stage's own barrier looked at as well.
+          bool got = sets_per_stage || wait_bar<PAIR>(smem_u32(&bar_full[w.stage]), w.stage_par, &abort_flag, 4);
           got = got && wait_bar<PAIR>(smem_u32(&bar_sf_full[w.set]), w.set_par, &abort_flag, 5);
           if (!__all_sync(0xffffffffu, got)) { ok = false; break; }       // warp-uniform decision
           tc_fence_after();
           if (w.it == 0 && lane == 0) stamp(p, 3);
           if (lane == 0) trace_ev(p, 2, i);
           const bool leader = elect_one();
-          uint8_t* st = smem + w.stage * p.stage_bytes;
-          const int rem = p.k - w.kt * 256;
-          const int n_mma = rem >= 256 ? kMmaPerTile : rem >> 6;
+          const uint32_t st_addr = smem_addr0 + uint32_t(w.stage * p.stage_bytes);
+          const int rem = p.k - w.kt * kKTile;
+          const int n_mma = rem >= kKTile ? kMmas : rem >> 6;
           const uint32_t sfa_col = tmem_base + kSfCol + w.set * p.sf_set_cols;
-          const uint32_t sfb_col = sfa_col + 16;
-          const uint64_t a_desc = desc_sw128(smem_u32(st));
+          const uint32_t sfb_col = sfa_col + kSfaCols;
+          // descriptors: the start address field counts 16-byte units, so the K64 steps of a sub-tile (32 bytes
+          // apart) and the sub-tiles of a stage are constant offsets from the stage's first descriptor
+          const uint64_t a_desc0 = desc_sw128(st_addr);
           for (int h = 0; h < halves; ++h) {
-            const uint64_t b_desc = desc_sw128(smem_u32(st + p.smem_act_off + h * act_tile_bytes));
+            const uint64_t b_desc0 = desc_sw128(st_addr + uint32_t(p.smem_act_off + h * act_tile_bytes));
 #pragma unroll
-            for (int j = 0; j < kMmaPerTile; ++j) {
+            for (int j = 0; j < kMmas; ++j) {
               if (j >= n_mma) break;
+              const uint64_t a_desc = a_desc0 + uint64_t((j >> 2) * (kWSub >> 4) + (j & 3) * 2);
+              const uint64_t b_desc = b_desc0 + uint64_t((j >> 2) * act_sub_units + (j & 3) * 2);
               // NVFP4: one chunk per instruction; MXFP4: one chunk per two instructions, the second
               // uses scale bytes 2-3 of each column (scale-factor id 2)
               const int c = MX ? (j >> 1) : j;
@@ -592,10 +625,10 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
               const uint32_t idesc = idesc_base | (sf_id << 4) | (sf_id << 29);
               if (leader) {
                 if constexpr (PAIR)
-                  mma_fp4_pair<MX>(d_tmem, a_desc + uint64_t(j * 2), b_desc + uint64_t(j * 2), idesc,
+                  mma_fp4_pair<MX>(d_tmem, a_desc, b_desc, idesc,
                                    sfa_col + 4 * c, sfb_col + ((h * p.chunks + c) * row_tiles) * 4, accumulate);
                 else
-                  mma_fp4<MX>(d_tmem, a_desc + uint64_t(j * 2), b_desc + uint64_t(j * 2), idesc,
+                  mma_fp4<MX>(d_tmem, a_desc, b_desc, idesc,
                               sfa_col + 4 * c, sfb_col + ((h * p.chunks + c) * row_tiles) * 4, accumulate);
               }
               accumulate = 1;
@@ -646,8 +679,8 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
       {
         for (; i < n_units; ++i, w.next(p)) {
           if (!scale_alive) continue;
-          const int rem = p.k - w.kt * 256;
-          const int n_mma = rem >= 256 ? kMmaPerTile : rem >> 6;
+          const int rem = p.k - w.kt * kKTile;
+          const int n_mma = rem >= kKTile ? kMmas : rem >> 6;
           const int n_chunks = MX ? (n_mma + 1) >> 1 : n_mma;
           bool got = wait_bar<PAIR>(smem_u32(&bar_full[w.stage]), w.stage_par, &abort_flag, 6);
           if (got && p.sf_sets < p.stages && w.it >= p.sf_sets) {
@@ -665,7 +698,26 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
           const uint32_t col0 = tmem_base + q_lane + kSfCol + w.set * p.sf_set_cols;
           const uint8_t* sfa_src = st + p.smem_sfa_off + lane * 16;
           const uint8_t* sfb_src = st + p.smem_sfb_off + lane * 16;
-          if (n_chunks == p.chunks) {
+          if (KS == 2 && n_chunks == p.chunks) {
+            // 512-element stages (one scale row tile, no two-CTA tiles): groups of four chunks = 16 columns
+            constexpr int kGroups = MX ? 1 : 2;
+#pragma unroll
+            for (int g = 0; g < kGroups; ++g) {
+              uint4 a[4];
+#pragma unroll
+              for (int c = 0; c < 4; ++c) a[c] = *reinterpret_cast<const uint4*>(sfa_src + (g * 4 + c) * 512);
+              tmem_st16(col0 + g * 16, a);
+            }
+            for (int h = 0; h < halves; ++h) {
+#pragma unroll
+              for (int g = 0; g < kGroups; ++g) {
+                uint4 b[4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) b[c] = *reinterpret_cast<const uint4*>(sfb_src + h * sf_stride + (g * 4 + c) * 512);
+                tmem_st16(col0 + kSfaCols + (h * p.chunks + g * 4) * 4, b);
+              }
+            }
+          } else if (n_chunks == p.chunks) {
             // full K tile: 16-byte chunk slices are fetched first, then written with wide stores
             // (4 chunks = 16 columns per instruction; MXFP4 has 2 chunks = 8 columns)
             if constexpr (MX) {
@@ -713,7 +765,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
               tmem_st4(col0 + 4 * c, *reinterpret_cast<const uint4*>(sfa_src + c * 512));
               for (int h = 0; h < halves; ++h)
                 for (int t = 0; t < row_tiles; ++t)
-                  tmem_st4(col0 + 16 + ((h * p.chunks + c) * row_tiles + t) * 4,
+                  tmem_st4(col0 + kSfaCols + ((h * p.chunks + c) * row_tiles + t) * 4,
                            *reinterpret_cast<const uint4*>(sfb_src + (h * row_tiles + t) * sf_stride + c * 512));
             }
           }
@@ -1035,16 +1087,41 @@ int make_map(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t ro
   return RI_OK;
 }
 
+// The same bytes as a 3-D tensor [row_bytes / 128 sub-tiles, rows, 128 B] with a [2, box_rows, 128 B] box: one copy
+// brings two consecutive 128-byte-swizzled K sub-tiles of the same rows, laid out one after the other in shared
+// memory exactly as two copies of the 2-D box would.  row_bytes must be a multiple of 128 (every sub-tile whole).
+// Returns RI_ERR_UNSUPPORTED, without touching the error text, if the driver does not take the map.
+int make_map_subtiles(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t rows, uint64_t stride,
+                      uint32_t box_rows) {
+  EncodeTiledFn fn;
+  int s = get_encode_fn(&fn);
+  if (s) return s;
+  cuuint64_t dims[3] = {kTileKBytes, rows, row_bytes / kTileKBytes};
+  cuuint64_t strides[2] = {stride, kTileKBytes};
+  cuuint32_t box[3] = {kTileKBytes, box_rows, 2};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? RI_OK : RI_ERR_UNSUPPORTED;
+}
+
 // Pairs (clusters of two CTAs with the kernel's shared-memory footprint) that can be resident at once,
 // per device; 0 = not asked yet (then SMs / 2 is assumed).  Filled by ri_fp4_gemm before it plans.
 int g_pair_slots[64] = {};
 int g_plan_device = 0;
+#ifdef RI_GEMM_FORCE_KS           // development builds: 1 / 2 forces the stage size where the shape allows it
+constexpr int g_force_ks = RI_GEMM_FORCE_KS;
+#else
+constexpr int g_force_ks = 0;
+#endif
 
 struct Plan {
   int n_tile, tok_per_tile, tok_tiles, w_tiles, k_tiles, tiles, stages;
   long long units;
   int grid, tile_granular;      // persistent CTAs (pair plans: pairs) and how their unit ranges are cut
   int pair;                     // two-CTA tiles of 256 weight rows (cta_group::2), whole tiles only
+  int ks;                       // 256-element K tiles per pipeline stage (1 or 2)
   int chunks, stage_bytes, smem_act_off, smem_sfa_off, smem_sfb_off, smem_total;
 };
 
@@ -1076,9 +1153,14 @@ int make_plan(int m, int n, int k, int fmt, int layout, int splits, int sm_count
   const int act_rows = layout == RI_GEMM_ROW_PAIR ? 2 * m : m;
   const int halves_c = layout == RI_GEMM_CONCAT_K ? 2 : 1;
   pl->w_tiles = (n + kTileW - 1) / kTileW;
-  pl->k_tiles = (k + 255) / 256;
+  // Stages of 512 elements of K while the activation tile has at most 64 columns and one half: four scale sets
+  // of 64 columns then fit tensor memory and four 48-56 KB stages fit shared memory.  (Per-stage hand-shake costs
+  // dominate these launches, see the kernel.)
+  pl->ks = (g_force_ks == 1 || halves_c != 1 || (act_rows + 15) / 16 * 16 > 64 || k < 1024) ? 1 : 2;
+  if (g_force_ks == 2 && halves_c == 1 && (act_rows + 15) / 16 * 16 <= 128) pl->ks = 2;
+  pl->k_tiles = (k + 256 * pl->ks - 1) / (256 * pl->ks);
   pl->pair = 0;
-  pl->chunks = fmt == RI_FMT_NVFP4 ? 4 : 2;
+  pl->chunks = (fmt == RI_FMT_NVFP4 ? 4 : 2) * pl->ks;
   // accumulator columns per CTA: one tile for up to `cap` activation rows, tiles of `cap` rows above.
   // Plans that split K use cap 128 (smaller FP32 partials, double-buffered accumulators), others 256.
   auto geometry = [&](int cap) {
@@ -1097,8 +1179,8 @@ int make_plan(int m, int n, int k, int fmt, int layout, int splits, int sm_count
   //     for ragged ranges (more contributors per tile, two partials per CTA);
   //   * the output pass costs about 0.75 us per 32 accumulator columns.
   // Candidates: whole tiles per CTA; even K splits s = 2 .. SMs / tiles; ragged ranges on every SM.
-  const double w_unit_kb = (kTileW * kTileKBytes + pl->chunks * 512) / 1024.0;
-  auto act_unit_kb = [&](int n_tile) { return halves_c * (n_tile * kTileKBytes + pl->chunks * 512 * ((n_tile + 127) / 128)) / 1024.0; };
+  const double w_unit_kb = (pl->ks * kTileW * kTileKBytes + pl->chunks * 512) / 1024.0;
+  auto act_unit_kb = [&](int n_tile) { return halves_c * (pl->ks * n_tile * kTileKBytes + pl->chunks * 512 * ((n_tile + 127) / 128)) / 1024.0; };
   auto stream_us = [&](double units_per_cta, int ctas, int n_tile) {
     const double rate = ctas <= 96 ? 42.0 : 35.0;
     return units_per_cta * (w_unit_kb / rate + act_unit_kb(n_tile) / 120.0);     // KB / (GB/s) = us
@@ -1187,8 +1269,8 @@ int make_plan(int m, int n, int k, int fmt, int layout, int splits, int sm_count
   const int halves = layout == RI_GEMM_CONCAT_K ? 2 : 1;
   const int row_tiles = (pl->n_tile + 127) / 128;
   const int sf_bytes = pl->chunks * 512;
-  pl->smem_act_off = kTileW * kTileKBytes;
-  pl->smem_sfa_off = pl->smem_act_off + halves * (pl->pair ? pl->n_tile / 2 : pl->n_tile) * kTileKBytes;
+  pl->smem_act_off = pl->ks * kTileW * kTileKBytes;
+  pl->smem_sfa_off = pl->smem_act_off + halves * pl->ks * (pl->pair ? pl->n_tile / 2 : pl->n_tile) * kTileKBytes;
   pl->smem_sfb_off = pl->smem_sfa_off + sf_bytes;
   int stage = pl->smem_sfb_off + halves * row_tiles * sf_bytes;
   pl->stage_bytes = (stage + 1023) / 1024 * 1024;
@@ -1355,11 +1437,19 @@ int gemm_launch(const uint8_t* act, int64_t act_row_bytes, const uint8_t* act_sf
   }
 
   CUtensorMap w_map, act_map;
-  s = make_map(&w_map, w, uint64_t(k / 2), uint64_t(n), uint64_t(w_row_bytes), kTileW);
-  if (s) return s;
-  s = make_map(&act_map, act, uint64_t(act_cols), uint64_t(act_rows), uint64_t(act_row_bytes),
-               uint32_t(pl.pair ? pl.n_tile / 2 : pl.n_tile));
-  if (s) return s;
+  int map3 = 0;
+  if (pl.ks == 2 && k % 256 == 0 && act_cols == k / 2) {      // every 128-byte sub-tile whole: one copy per stage and operand
+    map3 = make_map_subtiles(&w_map, w, uint64_t(k / 2), uint64_t(n), uint64_t(w_row_bytes), kTileW) == RI_OK &&
+           make_map_subtiles(&act_map, act, uint64_t(act_cols), uint64_t(act_rows), uint64_t(act_row_bytes),
+                             uint32_t(pl.n_tile)) == RI_OK;
+  }
+  if (!map3) {
+    s = make_map(&w_map, w, uint64_t(k / 2), uint64_t(n), uint64_t(w_row_bytes), kTileW);
+    if (s) return s;
+    s = make_map(&act_map, act, uint64_t(act_cols), uint64_t(act_rows), uint64_t(act_row_bytes),
+                 uint32_t(pl.pair ? pl.n_tile / 2 : pl.n_tile));
+    if (s) return s;
+  }
 
   GemmParams p{};
   p.m = m; p.n = n; p.k = k; p.fmt = fmt; p.layout = layout;
@@ -1370,7 +1460,7 @@ int gemm_launch(const uint8_t* act, int64_t act_row_bytes, const uint8_t* act_sf
   {
     const int halves_h = layout == RI_GEMM_CONCAT_K ? 2 : 1;
     const int row_tiles_h = (pl.n_tile + 127) / 128;
-    p.sf_set_cols = 16 + pl.chunks * halves_h * row_tiles_h * 4;
+    p.sf_set_cols = 16 * pl.ks + pl.chunks * halves_h * row_tiles_h * 4;
     // one scale set per pipeline stage if tensor memory has room for at least two (the scale warps then
     // need no second wait per K tile); the stage count is trimmed to the sets that fit
     const int sets_max = (kTmemCols - kSfCol) / p.sf_set_cols;
@@ -1392,6 +1482,7 @@ int gemm_launch(const uint8_t* act, int64_t act_row_bytes, const uint8_t* act_sf
   p.ws_partial = ws_partial; p.ws_counter = ws_counter; p.status = status;
   p.smem_act_off = pl.smem_act_off; p.smem_sfa_off = pl.smem_sfa_off; p.smem_sfb_off = pl.smem_sfb_off;
   p.stage_bytes = pl.stage_bytes;
+  p.map3 = map3;
 #ifdef RI_GEMM_TRACE
   p.trace = g_trace;
 #endif
@@ -1424,10 +1515,14 @@ int gemm_launch(const uint8_t* act, int64_t act_row_bytes, const uint8_t* act_sf
   if (ar)                                           // the variant whose epilogue sums over the ranks
     kernel = pl.pair ? (mxk ? fp4_gemm_kernel<true, true, true> : fp4_gemm_kernel<false, true, true>)
                      : (mxk ? fp4_gemm_kernel<true, false, true> : fp4_gemm_kernel<false, false, true>);
-  static bool attr_set[64][2][2][2] = {};           // function attributes are per device
-  if (!attr_set[di.ordinal][fmt][pl.pair][ar ? 1 : 0]) {
+  if (pl.ks == 2) {                                 // 512-element stages (never with two-CTA tiles)
+    kernel = mxk ? fp4_gemm_kernel<true, false, false, 2> : fp4_gemm_kernel<false, false, false, 2>;
+    if (ar) kernel = mxk ? fp4_gemm_kernel<true, false, true, 2> : fp4_gemm_kernel<false, false, true, 2>;
+  }
+  static bool attr_set[64][2][2][2][2] = {};        // function attributes are per device
+  if (!attr_set[di.ordinal][fmt][pl.pair][ar ? 1 : 0][pl.ks - 1]) {
     RI_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem));
-    attr_set[di.ordinal][fmt][pl.pair][ar ? 1 : 0] = true;
+    attr_set[di.ordinal][fmt][pl.pair][ar ? 1 : 0][pl.ks - 1] = true;
   }
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(pl.pair ? 2 * pl.grid : pl.grid);
