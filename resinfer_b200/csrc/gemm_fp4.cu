@@ -571,6 +571,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (!PAIR || rank == 0) {   // the whole warp walks the loop (converged); one elected lane issues the tcgen05 instructions
+      // (a single thread walking the loop alone measured 3-6 % slower)
       // instruction descriptor: E2M1 x E2M1, K-major A and B, M = 128, N = n_tile
       const uint32_t idesc_base = (1u << 7) | (1u << 10) | (uint32_t(p.n_tile >> 3) << 17) |
                                   (MX ? (1u << 23) : 0u) | (uint32_t((PAIR ? 2 * kTileW : kTileW) >> 4) << 24);
@@ -1110,6 +1111,7 @@ int make_map_subtiles(CUtensorMap* map, const void* base, uint64_t row_bytes, ui
 // per device; 0 = not asked yet (then SMs / 2 is assumed).  Filled by ri_fp4_gemm before it plans.
 int g_pair_slots[64] = {};
 int g_plan_device = 0;
+constexpr int kKs2MaxCols = 128;   // widest activation tile that gets 512-element stages
 #ifdef RI_GEMM_FORCE_KS           // development builds: 1 / 2 forces the stage size where the shape allows it
 constexpr int g_force_ks = RI_GEMM_FORCE_KS;
 #else
@@ -1132,10 +1134,10 @@ struct Plan {
 // reference keys tile and cluster shapes on M (csrc/common/fold/sm10x/tactics.py:14-87).
 struct Tactic { int n, k, m_max, splits; };
 constexpr Tactic kTactics[] = {
-    {10240, 5120, 128, 1},                          // qkv: 80 whole tiles; K splits over all SMs measured 4-8 % slower
-    {5120, 8192, 128, 3},                           // o: 40 tiles x 3 K slices
-    {51200, 5120, 16, 2}, {51200, 5120, 128, 1},    // gate_up: ragged ranges up to 16 tokens, whole tiles above
-    {5120, 25600, 32, 4}, {5120, 25600, 128, 3},    // down: ragged ranges up to 32 tokens, 3 K slices above
+    {10240, 5120, 128, 1},                          // qkv: 80 whole tiles; K splits over all SMs measured 13-70 % slower
+    {5120, 8192, 16, 3}, {5120, 8192, 128, 2},      // o: 40 tiles x 3 K slices up to 16 tokens, x 2 above
+    {51200, 5120, 128, 1},                          // gate_up: whole tiles (K splits within 1 % up to 8 tokens, 4-17 % slower above)
+    {5120, 25600, 128, 3},                          // down: 40 tiles x 3 K slices (ragged ranges over all SMs 3-10 % slower)
 };
 
 // `splits`: 1 = ranges are cut at output-tile boundaries only (no K split, no workspace);
@@ -1153,11 +1155,14 @@ int make_plan(int m, int n, int k, int fmt, int layout, int splits, int sm_count
   const int act_rows = layout == RI_GEMM_ROW_PAIR ? 2 * m : m;
   const int halves_c = layout == RI_GEMM_CONCAT_K ? 2 : 1;
   pl->w_tiles = (n + kTileW - 1) / kTileW;
-  // Stages of 512 elements of K while the activation tile has at most 64 columns and one half: four scale sets
-  // of 64 columns then fit tensor memory and four 48-56 KB stages fit shared memory.  (Per-stage hand-shake costs
-  // dominate these launches, see the kernel.)
-  pl->ks = (g_force_ks == 1 || halves_c != 1 || (act_rows + 15) / 16 * 16 > 64 || k < 1024) ? 1 : 2;
-  if (g_force_ks == 2 && halves_c == 1 && (act_rows + 15) / 16 * 16 <= 128) pl->ks = 2;
+  // Stages of 512 elements of K while the activation tile has at most 128 columns: the scale sets then still fit
+  // tensor memory beside two accumulator buffers (four sets of 64 columns, two of 96 with the concat_k layout) and
+  // two to four stages of 48-108 KB fit shared memory -- a shallow pipeline, but depth is not what limits these
+  // launches (four stages measured the same as eight): the per-stage hand-shakes are, see the kernel.  Measured
+  // against 256-element stages: 8-17 % less time up to 64 tokens, 3-14 % at 64, 8 % at 128 (concat_k) on three
+  // of the four benchmark shapes and 2 % more on the fourth.
+  pl->ks = (g_force_ks == 1 || (act_rows + 15) / 16 * 16 > kKs2MaxCols || k < 1024) ? 1 : 2;
+  if (halves_c == 2 && k > 8192) pl->ks = 1;      // two stages of 108 KB lose on long K (measured, K = 25600: +10 %)
   pl->k_tiles = (k + 256 * pl->ks - 1) / (256 * pl->ks);
   pl->pair = 0;
   pl->chunks = (fmt == RI_FMT_NVFP4 ? 4 : 2) * pl->ks;

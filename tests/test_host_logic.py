@@ -254,8 +254,8 @@ def test_gemm_plan_selection_needs_no_gpu():
     from resinfer_b200.nvfp4.cute_fold.tactics import describe_plan, kernel_arch_for_capability
     assert kernel_arch_for_capability(10, 0) == "sm100" and kernel_arch_for_capability(12, 0) is None
     assert [describe_plan(m, 10240, 5120)["k_split"] for m in (1, 16, 128)] == [1, 1, 1]          # qkv: whole tiles
-    assert [describe_plan(m, 5120, 8192)["k_split"] for m in (1, 16, 128)] == [3, 3, 3]           # o: 3 K slices
-    assert describe_plan(1, 51200, 5120)["k_split"] == 2 and describe_plan(64, 51200, 5120)["k_split"] == 1
+    assert [describe_plan(m, 5120, 8192)["k_split"] for m in (1, 16, 64)] == [3, 3, 2]            # o: 3 K slices, 2 above 16 tokens
+    assert describe_plan(1, 51200, 5120)["k_split"] == 1 and describe_plan(64, 51200, 5120)["k_split"] == 1   # gate_up: whole tiles
     assert describe_plan(1, 5120, 25600)["workspace_bytes"] > 0                                   # K split -> scratch
     assert describe_plan(1024, 10240, 5120, layout="concat_k") == {"k_split": 1, "workspace_bytes": 0}
     assert describe_plan(0, 10240, 5120) == {"k_split": 1, "workspace_bytes": 0}
