@@ -536,7 +536,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
           const uint32_t tx = KS * kWSub + (w_sf_valid ? sf_bytes : 0u) +
                               halves * (act_tile_bytes + valid_row_tiles * sf_bytes);
           mbar_expect_tx(full, tx);
-          if (KS == 2 && p.map3) {                            // both sub-tiles with one copy: issuing a copy is what costs
+          if (KS > 1 && p.map3) {                             // all sub-tiles with one copy: issuing a copy is what costs
             tma_load_3d(smem_u32(st), &w_map, 0, w_tile * kTileW, w.kt * KS, full);
           } else {
 #pragma unroll
@@ -547,7 +547,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
         } else {
           for (int h = 0; h < halves; ++h) {
             if (act_tile_role) {
-              if (KS == 2 && p.map3) {                        // (one half only with 512-element stages)
+              if (KS > 1 && p.map3) {                         // (one half only with a 3-D map)
                 tma_load_3d(smem_u32(st + p.smem_act_off), &act_map, 0, tok_tile * p.n_tile, w.kt * KS, full);
                 continue;
               }
@@ -699,9 +699,9 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
           const uint32_t col0 = tmem_base + q_lane + kSfCol + w.set * p.sf_set_cols;
           const uint8_t* sfa_src = st + p.smem_sfa_off + lane * 16;
           const uint8_t* sfb_src = st + p.smem_sfb_off + lane * 16;
-          if (KS == 2 && n_chunks == p.chunks) {
-            // 512-element stages (one scale row tile, no two-CTA tiles): groups of four chunks = 16 columns
-            constexpr int kGroups = MX ? 1 : 2;
+          if (KS > 1 && n_chunks == p.chunks) {
+            // 512- / 1024-element stages (one scale row tile, no two-CTA tiles): groups of four chunks = 16 columns
+            constexpr int kGroups = (MX ? 2 : 4) * KS / 4;
 #pragma unroll
             for (int g = 0; g < kGroups; ++g) {
               uint4 a[4];
@@ -1093,13 +1093,13 @@ int make_map(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t ro
 // memory exactly as two copies of the 2-D box would.  row_bytes must be a multiple of 128 (every sub-tile whole).
 // Returns RI_ERR_UNSUPPORTED, without touching the error text, if the driver does not take the map.
 int make_map_subtiles(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t rows, uint64_t stride,
-                      uint32_t box_rows) {
+                      uint32_t box_rows, uint32_t sub_tiles) {
   EncodeTiledFn fn;
   int s = get_encode_fn(&fn);
   if (s) return s;
   cuuint64_t dims[3] = {kTileKBytes, rows, row_bytes / kTileKBytes};
   cuuint64_t strides[2] = {stride, kTileKBytes};
-  cuuint32_t box[3] = {kTileKBytes, box_rows, 2};
+  cuuint32_t box[3] = {kTileKBytes, box_rows, sub_tiles};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -1163,6 +1163,7 @@ int make_plan(int m, int n, int k, int fmt, int layout, int splits, int sm_count
   // of the four benchmark shapes and 2 % more on the fourth.
   pl->ks = (g_force_ks == 1 || (act_rows + 15) / 16 * 16 > kKs2MaxCols || k < 1024) ? 1 : 2;
   if (halves_c == 2 && k > 8192) pl->ks = 1;      // two stages of 108 KB lose on long K (measured, K = 25600: +10 %)
+  // (1024-element stages were built and measured too: two stages fit, and the launch is 5 % slower)
   pl->k_tiles = (k + 256 * pl->ks - 1) / (256 * pl->ks);
   pl->pair = 0;
   pl->chunks = (fmt == RI_FMT_NVFP4 ? 4 : 2) * pl->ks;
@@ -1443,10 +1444,10 @@ int gemm_launch(const uint8_t* act, int64_t act_row_bytes, const uint8_t* act_sf
 
   CUtensorMap w_map, act_map;
   int map3 = 0;
-  if (pl.ks == 2 && k % 256 == 0 && act_cols == k / 2) {      // every 128-byte sub-tile whole: one copy per stage and operand
-    map3 = make_map_subtiles(&w_map, w, uint64_t(k / 2), uint64_t(n), uint64_t(w_row_bytes), kTileW) == RI_OK &&
+  if (pl.ks > 1 && k % 256 == 0 && act_cols == k / 2) {       // every 128-byte sub-tile whole: one copy per stage and operand
+    map3 = make_map_subtiles(&w_map, w, uint64_t(k / 2), uint64_t(n), uint64_t(w_row_bytes), kTileW, pl.ks) == RI_OK &&
            make_map_subtiles(&act_map, act, uint64_t(act_cols), uint64_t(act_rows), uint64_t(act_row_bytes),
-                             uint32_t(pl.n_tile)) == RI_OK;
+                             uint32_t(pl.n_tile), pl.ks) == RI_OK;
   }
   if (!map3) {
     s = make_map(&w_map, w, uint64_t(k / 2), uint64_t(n), uint64_t(w_row_bytes), kTileW);
@@ -1524,10 +1525,10 @@ int gemm_launch(const uint8_t* act, int64_t act_row_bytes, const uint8_t* act_sf
     kernel = mxk ? fp4_gemm_kernel<true, false, false, 2> : fp4_gemm_kernel<false, false, false, 2>;
     if (ar) kernel = mxk ? fp4_gemm_kernel<true, false, true, 2> : fp4_gemm_kernel<false, false, true, 2>;
   }
-  static bool attr_set[64][2][2][2][2] = {};        // function attributes are per device
-  if (!attr_set[di.ordinal][fmt][pl.pair][ar ? 1 : 0][pl.ks - 1]) {
+  static bool attr_set[64][2][2][2][5] = {};        // function attributes are per device
+  if (!attr_set[di.ordinal][fmt][pl.pair][ar ? 1 : 0][pl.ks]) {
     RI_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem));
-    attr_set[di.ordinal][fmt][pl.pair][ar ? 1 : 0][pl.ks - 1] = true;
+    attr_set[di.ordinal][fmt][pl.pair][ar ? 1 : 0][pl.ks] = true;
   }
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(pl.pair ? 2 * pl.grid : pl.grid);
