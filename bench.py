@@ -47,7 +47,7 @@ L2_BYTES = 126 * 1024 * 1024
 SWEEPS_PER_STEP = 40                 # replays of the 32-case sweep graph per step
 CPU_MS = (1, 16, 128)                # token counts the CPU arm runs (4 shapes each)
 # DRAM traffic of the GEMM kernel / its algorithmic bytes, from one ncu capture per shape (see roofline.traffic_source)
-NCU_TRAFFIC_RATIO = 286.68 / 277.36
+NCU_TRAFFIC_RATIO = 281.31 / 277.36
 
 
 def load_peaks():
