@@ -36,7 +36,9 @@ def _nvfp4_case(m, n, k, dev, seed=1):
 
 @pytest.mark.parametrize("m,n,k,splits", [(1, 128, 256, 1), (16, 256, 512, 1), (16, 256, 1024, 2), (128, 384, 1024, 1),
                                          (100, 200, 2048, 4), (300, 256, 512, 1), (5, 1000, 4096, 0),
-                                         (64, 5120, 8192, 0)])
+                                         (64, 5120, 8192, 0),
+                                         # an odd number of 256-element K tiles: the last 512-element stage is half empty
+                                         (16, 256, 1280, 1), (8, 384, 2304, 0), (48, 640, 3328, 2)])
 def test_nvfp4_fold_layouts(cuda_device, m, n, k, splits):
     from resinfer_b200 import nvfp4, ops
     x_np, w_np, x, gi, alpha, wc, wsf = _nvfp4_case(m, n, k, cuda_device)
@@ -80,7 +82,8 @@ def test_nvfp4_kext_plain_layout_with_partial_k_tile(cuda_device, m, n, k, per8)
     assert rel_fro(y.cpu().numpy(), ref) < TOL_F32
 
 
-@pytest.mark.parametrize("m,n,k,splits", [(1, 128, 256, 1), (16, 256, 1024, 2), (100, 224, 2048, 4), (130, 256, 640, 1)])
+@pytest.mark.parametrize("m,n,k,splits", [(1, 128, 256, 1), (16, 256, 1024, 2), (100, 224, 2048, 4), (130, 256, 640, 1),
+                                         (16, 256, 1408, 1)])          # 5.5 K tiles of 256: half a 512-element stage at the end
 def test_mxfp4_gemms(cuda_device, m, n, k, splits):
     from resinfer_b200 import ops
     from resinfer_b200.nvfp4 import mxfp4 as mx
