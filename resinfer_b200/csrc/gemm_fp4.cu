@@ -1178,17 +1178,20 @@ int make_plan(int m, int n, int k, int fmt, int layout, int splits, int sm_count
     pl->units = (long long)pl->tiles * pl->k_tiles;
   };
   // Plan choice for splits == 0: a cost model fitted to measurements on B200 (microseconds).
-  //   * an SM pulls weight bytes (HBM) at about 42 GB/s while up to ~96 CTAs stream and 35 GB/s when
+  //   * an SM pulls weight bytes (HBM) at about 58 GB/s while up to ~96 CTAs stream and 44 GB/s when
   //     all SMs do (the HBM ceiling is shared), and activation tiles (L2) at about 120 GB/s;
-  //   * a plan that splits K pays for the exchange of FP32 partials: about 2 us + 0.02 us per
-  //     accumulator column when every CTA owns one even slice of one tile, 3 us + 0.05 us per column
+  //   * a plan that splits K pays for the exchange of FP32 partials: about 3 us + 0.04 us per
+  //     accumulator column when every CTA owns one even slice of one tile, 4 us + 0.06 us per column
   //     for ragged ranges (more contributors per tile, two partials per CTA);
+  //   (constants re-fitted with 512-element stages on the tensor-parallel shards of the benchmark shapes at
+  //   M = 1, 16, 64: the plan chosen is within 6 % of the best of splits 1..4 on all 36 cases, 0.4 % on average;
+  //   the constants of the 256-element kernel, 42 / 35 GB/s and 2 + 0.02 / 3 + 0.05 us, lost 7 % on average there)
   //   * the output pass costs about 0.75 us per 32 accumulator columns.
   // Candidates: whole tiles per CTA; even K splits s = 2 .. SMs / tiles; ragged ranges on every SM.
   const double w_unit_kb = (pl->ks * kTileW * kTileKBytes + pl->chunks * 512) / 1024.0;
   auto act_unit_kb = [&](int n_tile) { return halves_c * (pl->ks * n_tile * kTileKBytes + pl->chunks * 512 * ((n_tile + 127) / 128)) / 1024.0; };
   auto stream_us = [&](double units_per_cta, int ctas, int n_tile) {
-    const double rate = ctas <= 96 ? 42.0 : 35.0;
+    const double rate = ctas <= 96 ? 58.0 : 44.0;
     return units_per_cta * (w_unit_kb / rate + act_unit_kb(n_tile) / 120.0);     // KB / (GB/s) = us
   };
   auto epi_us = [&](int n_tile) { return 0.75 * ((n_tile + 31) / 32); };
@@ -1224,13 +1227,13 @@ int make_plan(int m, int n, int k, int fmt, int layout, int splits, int sm_count
     if (pl->units >= 2) {
       for (int s = 2; s * pl->tiles <= sm_count && s <= pl->k_tiles; ++s) {
         const double upc = double((pl->k_tiles + s - 1) / s);
-        const double c = stream_us(upc, s * pl->tiles, pl->n_tile) + epi_us(pl->n_tile) + 2.0 + 0.02 * pl->n_tile;
+        const double c = stream_us(upc, s * pl->tiles, pl->n_tile) + epi_us(pl->n_tile) + 3.0 + 0.04 * pl->n_tile;
         if (c < best) { best = c; best_split = s; }
       }
       long long g = sm_count;
       if (pl->units / 2 < g) g = pl->units / 2;                 // at least two K tiles per CTA
       if (g > 0 && pl->tiles % g != 0) {
-        const double c = stream_us(double(pl->units) / g, int(g), pl->n_tile) + epi_us(pl->n_tile) + 3.0 + 0.05 * pl->n_tile;
+        const double c = stream_us(double(pl->units) / g, int(g), pl->n_tile) + epi_us(pl->n_tile) + 4.0 + 0.06 * pl->n_tile;
         if (c < best) { best = c; best_split = -1; }
       }
     }
@@ -1242,7 +1245,7 @@ int make_plan(int m, int n, int k, int fmt, int layout, int splits, int sm_count
       const int grid_p = pair_tiles < slots ? pair_tiles : slots;
       const double waves_p = double((pair_tiles + grid_p - 1) / grid_p);
       const double act_kb = halves_c * (128 * kTileKBytes + pl->chunks * 512 * 2) / 1024.0;
-      const double rate = 2 * grid_p <= 96 ? 42.0 : 35.0;
+      const double rate = 2 * grid_p <= 96 ? 58.0 : 44.0;
       const double c = waves_p * pl->k_tiles * (w_unit_kb / rate + act_kb / 120.0) + waves_p * epi_us(256) + 1.0;
       if (c < best) { best = c; best_split = -2; }
     }

@@ -259,4 +259,5 @@ def test_gemm_plan_selection_needs_no_gpu():
     assert describe_plan(1, 5120, 25600)["workspace_bytes"] > 0                                   # K split -> scratch
     assert describe_plan(1024, 10240, 5120, layout="concat_k") == {"k_split": 1, "workspace_bytes": 0}
     assert describe_plan(0, 10240, 5120) == {"k_split": 1, "workspace_bytes": 0}
-    assert describe_plan(16, 4096, 4096)["k_split"] > 1                                           # 32 tiles: split K
+    assert describe_plan(16, 1280, 5120)["k_split"] > 1                                           # 10 tiles: split K
+    assert describe_plan(16, 5120, 2048)["k_split"] == 1                                          # 40 tiles, short K: whole tiles
